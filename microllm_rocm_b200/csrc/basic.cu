@@ -1,0 +1,166 @@
+// Row-wise and element-wise kernels of the decoder: token embedding gather, RMSNorm
+// (alone, with the residual add fused in front, and on selected rows), SiLU(gate)*up.
+// All arithmetic in fp32; storage types are template parameters.
+//
+// Formulas follow the reference's CPU loops:
+//   embedding        src/ops/ops.cpp:581-618      out[t,:] = table[id[t],:], bad id -> NaN
+//                    (src/ops/hip/basic_kernels.hip:339-352)
+//   rms_norm         src/ops/ops.cpp:684-699      y = x * (1/sqrt(sum(x^2)/W + eps)) * w
+//   add_rms_norm     src/ops/ops.cpp:702-740      s = l + r (stored), then rms_norm(s)
+//   swiglu           src/ops/ops.cpp:72-76,760-785  g*sigmoid(g)*u, two-branch sigmoid
+#include "common.cuh"
+
+using namespace mlb;
+
+MLB_DEFINE_LAST_ERROR()
+
+// ------------------------------------------------------------------ embedding gather
+template <typename TableT>
+__global__ void embed_gather_kernel(const TableT* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ out, int tokens, int width, int vocab) {
+    const int t = blockIdx.x;
+    if (t >= tokens) return;
+    const int id = ids[t];
+    float* dst = out + (size_t)t * width;
+    if (id < 0 || id >= vocab) {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = nanf("");
+        return;
+    }
+    const TableT* src = table + (size_t)id * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = to_f32(src[c]);
+}
+
+MLB_EXPORT int mlb_embed_gather(const void* table, int table_dtype, const int* ids, float* out,
+                                int tokens, int width, int vocab, cudaStream_t stream) {
+    if (tokens < 0 || width <= 0 || vocab <= 0) return fail(MLB_INVALID_ARGUMENT, "embed_gather: bad sizes");
+    if (tokens == 0) return MLB_OK;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (table_dtype == MLB_F32)
+        embed_gather_kernel<float><<<tokens, threads, 0, stream>>>((const float*)table, ids, out, tokens, width, vocab);
+    else if (table_dtype == MLB_BF16)
+        embed_gather_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, tokens, width, vocab);
+    else
+        return fail(MLB_INVALID_ARGUMENT, "embed_gather: unknown table dtype %d", table_dtype);
+    return check_launch("embed_gather");
+}
+
+// ------------------------------------------------------------------ RMSNorm family
+// One block per output row.  `rows` (may be null) selects input rows: out[r] = norm(x[rows[r]]).
+// With ADD, `delta` is first added into `x` in place (x is the fp32 residual stream) and the
+// sum is what gets normalised.  The reduction order depends only on `width` and the block
+// size, never on the number of rows.
+template <typename OutT, bool ADD>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
+                               const float* __restrict__ weight, OutT* __restrict__ out,
+                               const int* __restrict__ rows, int width, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const size_t src_row = rows ? (size_t)rows[r] : (size_t)r;
+    float* xr = x + src_row * width;
+    OutT* yr = out + (size_t)r * width;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = xr[c];
+        if (ADD) {
+            v += delta[src_row * width + c];
+            xr[c] = v;
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        yr[c] = from_f32<OutT>(xr[c] * inv * weight[c]);
+    }
+}
+
+template <bool ADD>
+static int launch_rmsnorm(float* x, const float* delta, const float* w, void* out, int out_dtype,
+                          const int* rows, int n_rows, int width, float eps, cudaStream_t stream) {
+    if (n_rows < 0 || width <= 0 || !(eps > 0.0f)) return fail(MLB_INVALID_ARGUMENT, "rmsnorm: bad sizes or eps");
+    if (n_rows == 0) return MLB_OK;
+    int threads = 128;
+    if (width >= 2048) threads = 512; else if (width >= 512) threads = 256;
+    if (out_dtype == MLB_F32)
+        rmsnorm_kernel<float, ADD><<<n_rows, threads, 0, stream>>>(x, delta, w, (float*)out, rows, width, eps);
+    else if (out_dtype == MLB_BF16)
+        rmsnorm_kernel<__nv_bfloat16, ADD><<<n_rows, threads, 0, stream>>>(x, delta, w, (__nv_bfloat16*)out, rows, width, eps);
+    else
+        return fail(MLB_INVALID_ARGUMENT, "rmsnorm: unknown output dtype %d", out_dtype);
+    return check_launch("rmsnorm");
+}
+
+MLB_EXPORT int mlb_rmsnorm(const float* x, const float* weight, void* out, int out_dtype, const int* rows,
+                           int n_rows, int width, float eps, cudaStream_t stream) {
+    return launch_rmsnorm<false>(const_cast<float*>(x), nullptr, weight, out, out_dtype, rows, n_rows, width, eps, stream);
+}
+
+MLB_EXPORT int mlb_add_rmsnorm(float* residual, const float* delta, const float* weight, void* out,
+                               int out_dtype, int n_rows, int width, float eps, cudaStream_t stream) {
+    if (!delta) return fail(MLB_INVALID_ARGUMENT, "add_rmsnorm: delta is null");
+    return launch_rmsnorm<true>(residual, delta, weight, out, out_dtype, nullptr, n_rows, width, eps, stream);
+}
+
+// ------------------------------------------------------------------ residual add
+__global__ void add_inplace_kernel(float* __restrict__ x, const float* __restrict__ delta, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += delta[i];
+}
+
+MLB_EXPORT int mlb_add_inplace(float* x, const float* delta, long long n, cudaStream_t stream) {
+    if (n < 0) return fail(MLB_INVALID_ARGUMENT, "add_inplace: negative size");
+    if (n == 0) return MLB_OK;
+    add_inplace_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, delta, (size_t)n);
+    return check_launch("add_inplace");
+}
+
+// ------------------------------------------------------------------ SiLU(gate) * up
+__device__ __forceinline__ float stable_sigmoid(float v) {
+    // the reference's overflow-safe two-branch form (ops.cpp:72-76)
+    if (v >= 0.0f) return 1.0f / (1.0f + expf(-v));
+    const float e = expf(v);
+    return e / (1.0f + e);
+}
+
+template <typename InT, typename OutT>
+__global__ void silu_mul_kernel(const InT* __restrict__ gate, const InT* __restrict__ up, long long in_stride,
+                                OutT* __restrict__ out, int rows, int width) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * width) return;
+    const int r = (int)(i / width), c = (int)(i % width);
+    const float g = to_f32(gate[r * in_stride + c]);
+    const float u = to_f32(up[r * in_stride + c]);
+    out[i] = from_f32<OutT>(g * stable_sigmoid(g) * u);
+}
+
+// gate and up are two column blocks of one [rows, in_stride] matrix (the fused gate/up
+// projection) or two separate matrices; `in_stride` is their row pitch in elements.
+MLB_EXPORT int mlb_silu_mul(const void* gate, const void* up, long long in_stride, int in_dtype, void* out,
+                            int out_dtype, int rows, int width, cudaStream_t stream) {
+    if (rows < 0 || width <= 0 || in_stride < width) return fail(MLB_INVALID_ARGUMENT, "silu_mul: bad sizes");
+    if (rows == 0) return MLB_OK;
+    const long long n = (long long)rows * width;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (in_dtype == MLB_F32 && out_dtype == MLB_F32)
+        silu_mul_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)gate, (const float*)up, in_stride, (float*)out, rows, width);
+    else if (in_dtype == MLB_BF16 && out_dtype == MLB_BF16)
+        silu_mul_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, in_stride, (__nv_bfloat16*)out, rows, width);
+    else if (in_dtype == MLB_F32 && out_dtype == MLB_BF16)
+        silu_mul_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)gate, (const float*)up, in_stride, (__nv_bfloat16*)out, rows, width);
+    else
+        return fail(MLB_INVALID_ARGUMENT, "silu_mul: unsupported dtype pair %d -> %d", in_dtype, out_dtype);
+    return check_launch("silu_mul");
+}
+
+// ------------------------------------------------------------------ fp32 -> bf16 cast
+__global__ void cast_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2bfloat16_rn(in[i]);
+}
+
+MLB_EXPORT int mlb_cast_f32_bf16(const float* in, void* out, long long n, cudaStream_t stream) {
+    if (n < 0) return fail(MLB_INVALID_ARGUMENT, "cast: negative size");
+    if (n == 0) return MLB_OK;
+    cast_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(in, (__nv_bfloat16*)out, (size_t)n);
+    return check_launch("cast_f32_bf16");
+}

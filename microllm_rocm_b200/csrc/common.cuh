@@ -1,0 +1,90 @@
+// Shared declarations of the kernel library: exported-symbol macro, status codes, the
+// last-error string, element load/store helpers and warp/block reductions.
+//
+// Every launcher is `extern "C"`, takes raw device pointers plus a CUDA stream, validates
+// its sizes on the host and returns a status (0 = ok).  A refused size never launches a
+// kernel: the caller reads the reason with mlb_last_error().  This is the C-ABI manner of
+// the reference's bindings (bindings/capi/microllm_c.cpp:43-62: status code plus a
+// thread-local message), applied to kernels instead of tensors.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstdarg>
+#include <cmath>
+
+#define MLB_EXPORT extern "C" __attribute__((visibility("default")))
+
+enum MlbStatus : int {
+    MLB_OK = 0,
+    MLB_INVALID_ARGUMENT = 1,
+    MLB_UNSUPPORTED_SIZE = 2,
+    MLB_CUDA_ERROR = 3,
+};
+
+// dtype tags shared with the Python side
+enum MlbDType : int { MLB_F32 = 0, MLB_BF16 = 1 };
+
+namespace mlb {
+
+inline char* error_buffer() {
+    static thread_local char buffer[512] = {0};
+    return buffer;
+}
+
+inline int fail(int status, const char* format, ...) {
+    va_list args;
+    va_start(args, format);
+    vsnprintf(error_buffer(), 512, format, args);
+    va_end(args);
+    return status;
+}
+
+inline int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "%s: %s", what, cudaGetErrorString(e));
+    return MLB_OK;
+}
+
+// ---- element access: all arithmetic happens in fp32 ------------------------------------
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);   // round to nearest even, as the reference's
+}                                    // float_to_bfloat16_bits (base/low_precision.h:69-74)
+
+// ---- reductions with a fixed order (the result never depends on the batch) ------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `scratch` must
+// hold 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();                       // scratch may still be read from a previous call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = lane < warps ? scratch[lane] : 0.0f;
+    return warp_sum(total);
+}
+
+}  // namespace mlb
+
+// Every shared object of the library exports these two.
+#define MLB_DEFINE_LAST_ERROR()                                                     \
+    MLB_EXPORT const char* mlb_last_error() { return mlb::error_buffer(); }

@@ -1,0 +1,134 @@
+// Bias + rotary position encoding + key/value store, in one pass over the fused QKV
+// projection output.
+//
+//   q' = rotate(q + bq, pos)            -> q_out[T, NH*D]            (fp32 or bf16)
+//   k' = rotate(k + bk, pos), v + bv    -> pages[page, 0|1, kvh, slot, :] through the block table
+//
+// Rotation as the reference computes it (src/ops/ops.cpp:861-879, with bias :913-940, per
+// row positions :1086-1115): for pair i, angle = float(pos) * base^(-2 i / D) in fp32,
+// (a, b) -> (a cos - b sin, a sin + b cos); split-half pairs element i with i + D/2.  The
+// inverse frequencies come in as a table (computed once with the same fp32 expression), so
+// another rotary variant (partial width, interleaved pairs, scaled frequencies) is a
+// different table and flag, not a different kernel.  Values and rotation stay fp32; only
+// the store converts.  The reference keeps separate kernels for rotation, bias and cache
+// store (basic_kernels.hip:456-592, 927-983) and copies K/V into a capacity-strided cache
+// (src/model/model.cpp:129-164); here the cache is paged.
+#include "common.cuh"
+
+using namespace mlb;
+
+MLB_DEFINE_LAST_ERROR()
+
+namespace {
+
+struct RopeKvParams {
+    const float* qkv;        // [T, ld]  columns: NH*D of q, NKV*D of k, NKV*D of v
+    long long ld;
+    const float* bias;       // [(NH+2NKV)*D] or null
+    const int* positions;    // [T] absolute position of each token
+    const int* token_seq;    // [T] index of the token's sequence in this batch
+    const int* block_table;  // [A, max_blocks] physical page of each logical block, -1 if none
+    int max_blocks;
+    const float* inv_freq;   // [rot_dim/2]
+    int rot_dim;
+    int interleaved;         // 0: pairs (i, i+rot/2); 1: pairs (2i, 2i+1)
+    void* q_out;             // [T, NH*D]
+    void* pages;             // [num_pages, 2, NKV, page_size, D] or null (read-only run)
+    int num_pages, page_size;
+    int tokens, num_heads, num_kv_heads, head_dim;
+    int* error_flag;         // set to 1 when a token maps to no valid page
+};
+
+template <typename QT, typename KVT>
+__global__ void rope_kv_kernel(RopeKvParams p) {
+    const int half = p.head_dim / 2;
+    const int heads_all = p.num_heads + 2 * p.num_kv_heads;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = (long long)p.tokens * heads_all * half;
+    if (idx >= total) return;
+    const int i = (int)(idx % half);
+    const int head = (int)((idx / half) % heads_all);
+    const int t = (int)(idx / ((long long)half * heads_all));
+
+    const bool is_q = head < p.num_heads;
+    const bool is_k = !is_q && head < p.num_heads + p.num_kv_heads;
+    const bool is_v = !is_q && !is_k;
+    if (!is_q && p.pages == nullptr) return;
+
+    // which two elements of the head this thread owns
+    int e0, e1;
+    bool rotate = false;
+    const int rot_half = p.rot_dim / 2;
+    if (!is_v && i < rot_half) {
+        rotate = true;
+        if (p.interleaved) { e0 = 2 * i; e1 = 2 * i + 1; }
+        else               { e0 = i;     e1 = i + rot_half; }
+    } else if (!is_v) {
+        e0 = p.rot_dim + 2 * (i - rot_half); e1 = e0 + 1;
+    } else {
+        e0 = 2 * i; e1 = e0 + 1;
+    }
+    const size_t col = (size_t)head * p.head_dim;
+    const float* src = p.qkv + (size_t)t * p.ld + col;
+    float a = src[e0], b = src[e1];
+    if (p.bias) { a += p.bias[col + e0]; b += p.bias[col + e1]; }
+    const int pos = p.positions[t];
+    if (rotate) {
+        const float angle = (float)pos * p.inv_freq[i];
+        float s, c;
+        sincosf(angle, &s, &c);
+        const float ra = a * c - b * s;
+        const float rb = a * s + b * c;
+        a = ra; b = rb;
+    }
+    if (is_q) {
+        QT* dst = (QT*)p.q_out + (size_t)t * p.num_heads * p.head_dim + col;
+        dst[e0] = from_f32<QT>(a);
+        dst[e1] = from_f32<QT>(b);
+        return;
+    }
+    const int kvh = is_k ? head - p.num_heads : head - p.num_heads - p.num_kv_heads;
+    const int block = pos / p.page_size, slot = pos % p.page_size;
+    int page = -1;
+    if (pos >= 0 && block < p.max_blocks) page = p.block_table[(size_t)p.token_seq[t] * p.max_blocks + block];
+    if (page < 0 || page >= p.num_pages) {
+        if (p.error_flag) atomicExch(p.error_flag, 1);
+        return;                                   // never write outside the pool
+    }
+    KVT* dst = (KVT*)p.pages +
+               ((((size_t)page * 2 + (is_v ? 1 : 0)) * p.num_kv_heads + kvh) * p.page_size + slot) * p.head_dim;
+    dst[e0] = from_f32<KVT>(a);
+    dst[e1] = from_f32<KVT>(b);
+}
+
+}  // namespace
+
+MLB_EXPORT int mlb_rope_kv_write(const float* qkv, long long ld, const float* bias, const int* positions,
+                                 const int* token_seq, const int* block_table, int max_blocks,
+                                 const float* inv_freq, int rot_dim, int interleaved, void* q_out, int q_dtype,
+                                 void* pages, int kv_dtype, int num_pages, int page_size, int tokens,
+                                 int num_heads, int num_kv_heads, int head_dim, int* error_flag,
+                                 cudaStream_t stream) {
+    if (tokens < 0 || num_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || head_dim % 2 != 0)
+        return fail(MLB_INVALID_ARGUMENT, "rope_kv_write: bad head sizes");
+    if (rot_dim < 0 || rot_dim > head_dim || rot_dim % 2 != 0)
+        return fail(MLB_INVALID_ARGUMENT, "rope_kv_write: rot_dim %d must be even and <= head_dim %d", rot_dim, head_dim);
+    if (ld < (long long)(num_heads + 2 * num_kv_heads) * head_dim)
+        return fail(MLB_INVALID_ARGUMENT, "rope_kv_write: row pitch smaller than the fused width");
+    if (pages && (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !block_table || !token_seq))
+        return fail(MLB_INVALID_ARGUMENT, "rope_kv_write: cache geometry missing");
+    if (tokens == 0) return MLB_OK;
+    RopeKvParams p{qkv, ld, bias, positions, token_seq, block_table, max_blocks, inv_freq, rot_dim, interleaved,
+                   q_out, pages, num_pages, page_size, tokens, num_heads, num_kv_heads, head_dim, error_flag};
+    const long long total = (long long)tokens * (num_heads + 2 * num_kv_heads) * (head_dim / 2);
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    const int key = q_dtype * 2 + kv_dtype;
+    switch (key) {
+        case MLB_F32 * 2 + MLB_F32: rope_kv_kernel<float, float><<<blocks, 256, 0, stream>>>(p); break;
+        case MLB_BF16 * 2 + MLB_BF16: rope_kv_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>(p); break;
+        case MLB_F32 * 2 + MLB_BF16: rope_kv_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>(p); break;
+        case MLB_BF16 * 2 + MLB_F32: rope_kv_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>(p); break;
+        default: return fail(MLB_INVALID_ARGUMENT, "rope_kv_write: unknown dtypes %d/%d", q_dtype, kv_dtype);
+    }
+    return check_launch("rope_kv_write");
+}

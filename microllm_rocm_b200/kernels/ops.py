@@ -1,0 +1,267 @@
+"""Python faces of the CUDA kernels: each function checks what it is given, then launches
+on torch's current stream through the library's C ABI.  Tensors are torch CUDA tensors
+used as typed device memory; no torch operator computes anything here.
+
+There is no CPU path and no silent fallback: a missing compiler or extension raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+from .build import KernelError
+
+F32, BF16 = 0, 1
+_DTYPE_TAG = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def dtype_tag(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_TAG[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported tensor dtype {t.dtype}") from None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name} must have {dims} dimensions, got {tuple(t.shape)}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+_SIGNATURES = {
+    "basic.cu": {
+        "mlb_embed_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mlb_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
+        "mlb_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+        "mlb_add_inplace": [c_void_p, c_void_p, c_longlong, c_void_p],
+        "mlb_silu_mul": [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mlb_cast_f32_bf16": [c_void_p, c_void_p, c_longlong, c_void_p],
+    },
+    "gemm_f32.cu": {
+        "mlb_gemm_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                         c_longlong, c_longlong, c_longlong, c_int, c_void_p],
+    },
+    "rope_kv.cu": {
+        "mlb_rope_kv_write": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                              c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                              c_int, c_int, c_int, c_void_p, c_void_p],
+    },
+    "attention_plain.cu": {
+        "mlb_paged_attention_plain": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                      c_float, c_void_p, c_void_p],
+    },
+    "sampling.cu": {
+        "mlb_argmax_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
+        "mlb_sample_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_void_p],
+    },
+}
+
+_libs = {}
+
+
+def lib(source: str, defines=None) -> ctypes.CDLL:
+    key = (source, tuple(sorted((defines or {}).items())))
+    got = _libs.get(key)
+    if got is None:
+        got = build.load(source, defines)
+        for name, argtypes in _SIGNATURES.get(source, {}).items():
+            fn = getattr(got, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        _libs[key] = got
+    return got
+
+
+def register_signatures(source: str, signatures) -> None:
+    _SIGNATURES.setdefault(source, {}).update(signatures)
+
+
+def base_sources():
+    """(source, defines) of every kernel that any model needs."""
+    return [("basic.cu", {}), ("gemm_f32.cu", {}), ("rope_kv.cu", {}), ("attention_plain.cu", {}),
+            ("sampling.cu", {})]
+
+
+# ------------------------------------------------------------------------------ basic
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    _need(table, "table", dims=2); _need(ids, "ids", torch.int32, 1); _need(out, "out", torch.float32, 2)
+    vocab, width = table.shape
+    if out.shape != (ids.shape[0], width):
+        raise KernelError(f"embed_gather: out {tuple(out.shape)} does not match ({ids.shape[0]}, {width})")
+    L = lib("basic.cu")
+    build.check(L, L.mlb_embed_gather(table.data_ptr(), dtype_tag(table), ids.data_ptr(), out.data_ptr(),
+                                      ids.shape[0], width, vocab, _stream()))
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = rmsnorm(x[rows[r]] if rows is given else x[r])."""
+    _need(x, "x", torch.float32, 2); _need(weight, "weight", torch.float32, 1); _need(out, "out", dims=2)
+    width = x.shape[1]
+    n = rows.shape[0] if rows is not None else x.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+    if weight.shape[0] != width or out.shape != (n, width):
+        raise KernelError("rmsnorm: shapes do not agree")
+    L = lib("basic.cu")
+    build.check(L, L.mlb_rmsnorm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), dtype_tag(out), _ptr(rows),
+                                 n, width, float(eps), _stream()))
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float,
+                out: torch.Tensor) -> None:
+    """residual += delta (in place, fp32), then out = rmsnorm(residual)."""
+    _need(residual, "residual", torch.float32, 2); _need(delta, "delta", torch.float32, 2)
+    _need(weight, "weight", torch.float32, 1); _need(out, "out", dims=2)
+    if delta.shape != residual.shape or out.shape != residual.shape or weight.shape[0] != residual.shape[1]:
+        raise KernelError("add_rmsnorm: shapes do not agree")
+    L = lib("basic.cu")
+    build.check(L, L.mlb_add_rmsnorm(residual.data_ptr(), delta.data_ptr(), weight.data_ptr(), out.data_ptr(),
+                                     dtype_tag(out), residual.shape[0], residual.shape[1], float(eps), _stream()))
+
+
+def add_inplace(x: torch.Tensor, delta: torch.Tensor) -> None:
+    _need(x, "x", torch.float32); _need(delta, "delta", torch.float32)
+    if x.shape != delta.shape:
+        raise KernelError("add_inplace: shapes do not agree")
+    L = lib("basic.cu")
+    build.check(L, L.mlb_add_inplace(x.data_ptr(), delta.data_ptr(), x.numel(), _stream()))
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r, c] = silu(gate_up[r, c]) * gate_up[r, width + c] for a fused [rows, 2*width] input."""
+    _need(gate_up, "gate_up", dims=2); _need(out, "out", dims=2)
+    rows, width = out.shape
+    if gate_up.shape != (rows, 2 * width):
+        raise KernelError("silu_mul: input must be [rows, 2*width]")
+    L = lib("basic.cu")
+    esz = gate_up.element_size()
+    build.check(L, L.mlb_silu_mul(gate_up.data_ptr(), gate_up.data_ptr() + width * esz, 2 * width,
+                                  dtype_tag(gate_up), out.data_ptr(), dtype_tag(out), rows, width, _stream()))
+
+
+def cast_f32_bf16(x: torch.Tensor, out: torch.Tensor) -> None:
+    _need(x, "x", torch.float32); _need(out, "out", torch.bfloat16)
+    if x.numel() != out.numel():
+        raise KernelError("cast: sizes differ")
+    L = lib("basic.cu")
+    build.check(L, L.mlb_cast_f32_bf16(x.data_ptr(), out.data_ptr(), x.numel(), _stream()))
+
+
+# ------------------------------------------------------------------------------ fp32 GEMM
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+             accumulate: bool = False) -> None:
+    """out[M,N] (+)= a[M,K] @ w[N,K]^T (+ bias[N]); plain fp32 FMA on CUDA cores."""
+    _need(a, "a", torch.float32, 2); _need(w, "w", torch.float32, 2); _need(out, "out", torch.float32, 2)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm_f32: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} do not agree")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != N:
+            raise KernelError("gemm_f32: bias length differs from N")
+    L = lib("gemm_f32.cu")
+    build.check(L, L.mlb_gemm_f32(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K, K, K, N,
+                                  1 if accumulate else 0, _stream()))
+
+
+# ------------------------------------------------------------------------------ rope + kv store
+def rope_kv_write(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
+                  token_seq: torch.Tensor, block_table: Optional[torch.Tensor], inv_freq: torch.Tensor,
+                  rot_dim: int, interleaved: bool, q_out: torch.Tensor, pages: Optional[torch.Tensor],
+                  num_heads: int, num_kv_heads: int, head_dim: int, error_flag: Optional[torch.Tensor]) -> None:
+    """Bias, rotation and the K/V store for a fused [T, (NH+2NKV)*D] fp32 projection output.
+    `pages` is [num_pages, 2, NKV, page_size, D]; None makes the call query-only."""
+    _need(qkv, "qkv", torch.float32, 2); _need(positions, "positions", torch.int32, 1)
+    _need(token_seq, "token_seq", torch.int32, 1); _need(inv_freq, "inv_freq", torch.float32, 1)
+    _need(q_out, "q_out", dims=2)
+    T = qkv.shape[0]
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    if qkv.shape[1] != width or q_out.shape != (T, num_heads * head_dim) or positions.shape[0] != T:
+        raise KernelError("rope_kv_write: shapes do not agree")
+    if inv_freq.shape[0] * 2 != rot_dim:
+        raise KernelError("rope_kv_write: inv_freq must have rot_dim/2 entries")
+    num_pages = page_size = max_blocks = 0
+    if pages is not None:
+        _need(pages, "pages", dims=5); _need(block_table, "block_table", torch.int32, 2)
+        num_pages, two, nkv, page_size, d = pages.shape
+        if two != 2 or nkv != num_kv_heads or d != head_dim:
+            raise KernelError(f"rope_kv_write: pages {tuple(pages.shape)} do not match the head geometry")
+        max_blocks = block_table.shape[1]
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != width:
+            raise KernelError("rope_kv_write: bias length differs from the fused width")
+    L = lib("rope_kv.cu")
+    build.check(L, L.mlb_rope_kv_write(
+        qkv.data_ptr(), width, _ptr(bias), positions.data_ptr(), token_seq.data_ptr(), _ptr(block_table), max_blocks,
+        inv_freq.data_ptr(), rot_dim, 1 if interleaved else 0, q_out.data_ptr(), dtype_tag(q_out),
+        _ptr(pages), dtype_tag(pages) if pages is not None else F32, num_pages, page_size, T,
+        num_heads, num_kv_heads, head_dim, _ptr(error_flag), _stream()))
+
+
+# ------------------------------------------------------------------------------ attention
+def paged_attention_plain(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
+                          token_seq: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int,
+                          head_dim: int, scale: float, window: Optional[int],
+                          error_flag: Optional[torch.Tensor]) -> None:
+    _need(q, "q", dims=2); _need(pages, "pages", dims=5); _need(out, "out", dims=2)
+    _need(positions, "positions", torch.int32, 1); _need(token_seq, "token_seq", torch.int32, 1)
+    _need(block_table, "block_table", torch.int32, 2)
+    T = q.shape[0]
+    num_pages, two, nkv, page_size, d = pages.shape
+    if two != 2 or nkv != num_kv_heads or d != head_dim:
+        raise KernelError(f"paged_attention: pages {tuple(pages.shape)} do not match the head geometry")
+    if q.shape[1] != num_heads * head_dim or out.shape != q.shape or positions.shape[0] != T:
+        raise KernelError("paged_attention: shapes do not agree")
+    L = lib("attention_plain.cu")
+    build.check(L, L.mlb_paged_attention_plain(
+        q.data_ptr(), dtype_tag(q), pages.data_ptr(), dtype_tag(pages), out.data_ptr(), dtype_tag(out),
+        positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], num_pages,
+        page_size, T, num_heads, num_kv_heads, head_dim, int(window or 0), float(scale), _ptr(error_flag),
+        _stream()))
+
+
+# ------------------------------------------------------------------------------ sampling
+def argmax_rows(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _need(logits, "logits", torch.float32, 2); _need(out, "out", torch.int32, 1)
+    if out.shape[0] != logits.shape[0]:
+        raise KernelError("argmax_rows: out length differs from the number of rows")
+    L = lib("sampling.cu")
+    build.check(L, L.mlb_argmax_rows(logits.data_ptr(), logits.shape[1], logits.shape[0], logits.shape[1],
+                                     out.data_ptr(), _stream()))
+
+
+def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, seed: torch.Tensor,
+                draw: torch.Tensor, out: torch.Tensor) -> None:
+    """Per row: greedy when temperature == 0 or top_k == 1, else the seeded draw.  `seed` and
+    `draw` are int64 tensors read as unsigned 64-bit."""
+    _need(logits, "logits", torch.float32, 2); _need(out, "out", torch.int32, 1)
+    _need(temperature, "temperature", torch.float32, 1); _need(top_k, "top_k", torch.int32, 1)
+    _need(seed, "seed", torch.int64, 1); _need(draw, "draw", torch.int64, 1)
+    R = logits.shape[0]
+    if not (out.shape[0] == temperature.shape[0] == top_k.shape[0] == seed.shape[0] == draw.shape[0] == R):
+        raise KernelError("sample_rows: per-row arrays must have one entry per logits row")
+    L = lib("sampling.cu")
+    build.check(L, L.mlb_sample_rows(logits.data_ptr(), logits.shape[1], R, logits.shape[1], temperature.data_ptr(),
+                                     top_k.data_ptr(), seed.data_ptr(), draw.data_ptr(), out.data_ptr(), _stream()))

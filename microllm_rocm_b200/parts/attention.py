@@ -1,0 +1,81 @@
+"""Grouped-query attention over the paged cache.
+
+  q, k, v = x Wq^T + bq, x Wk^T + bk, x Wv^T + bv      one fused product (the reference runs
+                                                       three: src/model/model.cpp:457-476)
+  q, k rotated by the position encoding's table; k, v stored into this run's pages
+  head h attends with kv head h // (NH/NKV) over keys lo..pos, scale 1/sqrt(D) after the dot
+  out = concat_heads(o) Wo^T
+
+All sizes are parameters; `window` (keys visible, itself included) is per layer and may be
+None.  The part never learns which layer or model it belongs to.  Formulas:
+src/model/model.cpp:447-523 (prefill), :525-603 (decode); scale at :513-514.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from ..kernels import attention as attention_kernels
+from ..kernels import ops
+from ..kernels.linear import linear
+from .base import Mixer, PagedKVNeed, PagedKVView, PositionEncoding, Runtime, StepContext, WeightSpec, register_mixer
+
+
+@register_mixer("attention")
+class Attention(Mixer):
+    def __init__(self, params: dict, rt: Runtime, position: Optional[PositionEncoding] = None):
+        self.prefix = params.get("prefix", "")
+        self.hidden = int(params["hidden_size"])
+        self.nh = int(params["num_heads"])
+        self.nkv = int(params["num_kv_heads"])
+        self.d = int(params["head_dim"])
+        self.qkv_bias = bool(params.get("qkv_bias", False))
+        self.out_bias = bool(params.get("out_bias", False))
+        self.window = params.get("window")
+        self.scale = float(params.get("scale", 1.0 / math.sqrt(float(self.d))))
+        if self.nh % self.nkv:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        attention_kernels.check_head_dim(self.d)
+        self.rt = rt
+        self.rotary = position.rotary_table(self.d) if position is not None else None
+        if self.rotary is None:        # no rotation: an empty table makes the kernel pass q/k through
+            self._no_rot = torch.zeros(0, dtype=torch.float32, device=rt.device)
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+
+    # --- declarations -----------------------------------------------------------------
+    def cache_need(self):
+        return PagedKVNeed(self.nkv, self.d, self.window)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        q, kv = self.nh * self.d, self.nkv * self.d
+        specs = {"q_proj.weight": WeightSpec((q, self.hidden)), "k_proj.weight": WeightSpec((kv, self.hidden)),
+                 "v_proj.weight": WeightSpec((kv, self.hidden)), "o_proj.weight": WeightSpec((self.hidden, q))}
+        if self.qkv_bias:
+            specs.update({"q_proj.bias": WeightSpec((q,), role="vector"), "k_proj.bias": WeightSpec((kv,), role="vector"),
+                          "v_proj.bias": WeightSpec((kv,), role="vector")})
+        if self.out_bias:
+            specs["o_proj.bias"] = WeightSpec((self.hidden,), role="vector")
+        return specs
+
+    def bind(self, tensors):
+        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]], 0).contiguous()
+        if self.qkv_bias:
+            self.b_qkv = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]], 0).contiguous()
+        self.w_o = tensors["o_proj.weight"]
+        self.b_o = tensors.get("o_proj.bias")
+
+    # --- compute ------------------------------------------------------------------------
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVView) -> torch.Tensor:
+        T = x.shape[0]
+        qkv = linear(x, self.w_qkv, None, torch.float32)                       # [T, (NH+2NKV)*D] f32
+        q = torch.empty((T, self.nh * self.d), dtype=self.rt.dtype, device=x.device)
+        inv_freq, rot, inter = ((self.rotary.inv_freq, self.rotary.rotary_dim, self.rotary.interleaved)
+                                if self.rotary is not None else (self._no_rot, 0, False))
+        ops.rope_kv_write(qkv, self.b_qkv, ctx.positions, ctx.token_seq, cache.block_table, inv_freq, rot, inter,
+                          q, cache.pages if cache.writable else None, self.nh, self.nkv, self.d, ctx.error_flag)
+        o = torch.empty_like(q)
+        attention_kernels.paged_attention(q, cache.pages, o, ctx, cache.block_table, self.nh, self.nkv, self.d,
+                                          self.scale, self.window)
+        return linear(o, self.w_o, self.b_o, torch.float32)                    # [T, H] f32

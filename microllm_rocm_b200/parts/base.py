@@ -1,0 +1,217 @@
+"""Interfaces of the parts a decoder is put together from, and their registries.
+
+A part is built from a `PartSpec`'s params and a `Runtime` (device + compute dtype).  It
+declares the tensors it wants by LOCAL name (`weight_specs`), receives them already on the
+device and in the engine's dtype policy (`bind`), and then computes.  No part knows which
+model it sits in, which layer it is, or what runs before and after it.
+
+Kinds (each has a registry; `register_*` adds to it, tests may add their own):
+
+  Norm             forward(x[T,H] f32, out)            and add_forward(residual, delta, out)
+  PositionEncoding rotary_table() for mixers that rotate q/k, on_embedding() for additive ones
+  Mixer            cache_need(); forward(x[T,H], ctx, cache_view) -> delta[T,H] f32
+  FeedForward      forward(x[T,H], ctx) -> delta[T,H] f32
+  Block            the arrangement of norm/mixer/feed-forward around the residual stream
+
+`StepContext` is everything a part may know about the batch it is running: flat tokens with
+their absolute positions and the index of their sequence, per-sequence extents, and the
+per-group block tables and state slots of the cache manager.
+
+The reference welds these together in one file: Linear/Norm/Attention/FeedForward/Block
+are private classes of the one model (src/model/model.cpp:280-908).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+
+
+# ----------------------------------------------------------------------------- runtime
+@dataclass(frozen=True)
+class Runtime:
+    device: torch.device
+    dtype: torch.dtype                      # torch.float32 (true 32-bit path) or torch.bfloat16
+
+    @property
+    def is_fp32(self) -> bool:
+        return self.dtype == torch.float32
+
+
+# ----------------------------------------------------------------------------- weights
+@dataclass(frozen=True)
+class WeightSpec:
+    """What a part expects of one tensor.
+
+    role   'matrix' / 'table': kept in the compute dtype (bf16 or f32)
+           'vector': norm weights, biases; always f32 on the device (their math is f32)
+           'int_table': integer tables, int32 on the device
+    init   how the random-weights mode draws it: ('normal', std) or ('one_plus_normal', std)
+    """
+    shape: Tuple[int, ...]
+    role: str = "matrix"
+    init: Tuple[str, float] = ("normal", 0.02)
+
+
+# ----------------------------------------------------------------------------- cache needs
+@dataclass(frozen=True)
+class PagedKVNeed:
+    """Keys and values that grow with the tokens.  `window`: only the last `window` keys are
+    ever read (pages behind it may be given back while the request lives); None: all keys."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class FixedStateNeed:
+    """Per-request state of a fixed size, whatever the number of tokens."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class PagedKVView:
+    pages: torch.Tensor            # [num_pages, 2, NKV, page_size, D]
+    block_table: torch.Tensor      # [A, max_blocks] int32, this step's sequences, this group
+    page_size: int
+    writable: bool                 # False: the run reads a cache another run wrote
+
+
+@dataclass
+class StateView:
+    storage: torch.Tensor          # [num_slots, *shape]
+    slots: torch.Tensor            # [A] int32 slot of each sequence of the step
+    slots_host: List[int]
+    writable: bool
+
+
+# ----------------------------------------------------------------------------- step context
+@dataclass
+class StepContext:
+    """One step's batch as the parts see it.  Device tensors are int32."""
+    num_tokens: int
+    num_seqs: int
+    token_ids: torch.Tensor        # [T]
+    positions: torch.Tensor        # [T] absolute position of each token in its sequence
+    token_seq: torch.Tensor        # [T] which sequence (0..A-1) the token belongs to
+    seq_starts: torch.Tensor       # [A+1] first flat index of each sequence's tokens
+    seq_pos0: torch.Tensor         # [A] tokens the sequence held before this step
+    seq_lens: torch.Tensor         # [A] tokens it holds after this step
+    block_tables: Dict[str, torch.Tensor]   # cache group -> [A, max_blocks]
+    state_slots: torch.Tensor      # [A]
+    logit_rows: torch.Tensor       # [R] flat token indices whose logits are wanted
+    error_flag: torch.Tensor       # [1] int32, kernels raise it on a bad page or slot
+    # host mirrors, for parts that plan launches on the host
+    seq_starts_host: List[int] = field(default_factory=list)
+    seq_pos0_host: List[int] = field(default_factory=list)
+    state_slots_host: List[int] = field(default_factory=list)
+    max_new_tokens: int = 0        # longest run of new tokens of one sequence
+    max_seq_len: int = 0           # longest sequence after the step
+    extras: Dict[str, Any] = field(default_factory=dict)   # per-step scratch shared by parts
+
+    @property
+    def decode_only(self) -> bool:
+        return self.max_new_tokens == 1
+
+
+# ----------------------------------------------------------------------------- part kinds
+class Part:
+    """Common surface: declare tensors, receive them."""
+    prefix: str = ""
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        pass
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+        raise NotImplementedError
+
+    def add_forward(self, residual: torch.Tensor, delta: torch.Tensor, out: torch.Tensor) -> None:
+        """residual += delta in place, then out = norm(residual)."""
+        raise NotImplementedError
+
+
+@dataclass(frozen=True)
+class RotaryTable:
+    inv_freq: torch.Tensor         # [rotary_dim/2] f32 on the device
+    rotary_dim: int
+    interleaved: bool
+
+
+class PositionEncoding(Part):
+    def rotary_table(self, head_dim: int) -> Optional[RotaryTable]:
+        """Inverse frequencies for mixers that rotate q and k; None if this encoding does
+        nothing there."""
+        return None
+
+    def on_embedding(self, x: torch.Tensor, ctx: StepContext) -> None:
+        """Hook for encodings that add to the embedded tokens (in place); default none."""
+        return None
+
+
+class Mixer(Part):
+    def cache_need(self):
+        """PagedKVNeed, FixedStateNeed or None."""
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block:
+    """Arrangement of two norms, a mixer and a feed-forward around the residual stream.
+    `forward` gets the residual and a delta not yet added to it (or None) and returns the
+    same pair, so the add can be fused into whichever norm comes next."""
+
+    def __init__(self, params, rt, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, feed_forward: FeedForward):
+        raise NotImplementedError
+
+    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext, cache):
+        raise NotImplementedError
+
+
+# ----------------------------------------------------------------------------- registries
+NORMS: Dict[str, Callable] = {}
+POSITION_ENCODINGS: Dict[str, Callable] = {}
+MIXERS: Dict[str, Callable] = {}
+FEED_FORWARDS: Dict[str, Callable] = {}
+BLOCKS: Dict[str, Callable] = {}
+EMBEDDINGS: Dict[str, Callable] = {}
+HEADS: Dict[str, Callable] = {}
+
+
+def _register(table: Dict[str, Callable], what: str):
+    def deco_factory(kind: str, *, replace: bool = False):
+        def deco(cls):
+            if kind in table and not replace:
+                raise KeyError(f"{what} {kind!r} is already registered")
+            table[kind] = cls
+            return cls
+        return deco
+    return deco_factory
+
+
+register_norm = _register(NORMS, "norm")
+register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
+register_mixer = _register(MIXERS, "mixer")
+register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
+register_block = _register(BLOCKS, "block")
+register_embedding = _register(EMBEDDINGS, "embedding")
+register_head = _register(HEADS, "head")
+
+
+def make(table: Dict[str, Callable], what: str, spec, *args, **kwargs):
+    if spec.kind not in table:
+        raise KeyError(f"unknown {what} kind {spec.kind!r}; registered: {', '.join(sorted(table))}")
+    return table[spec.kind](spec.params, *args, **kwargs)

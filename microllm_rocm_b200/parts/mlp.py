@@ -1,0 +1,40 @@
+"""SwiGLU feed-forward: down( silu(gate(x)) * up(x) ), no biases
+(reference: src/model/model.cpp:757-794; activation src/ops/ops.cpp:760-785).
+Gate and up are one fused product (gate rows first, then up rows)."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..kernels import ops
+from ..kernels.linear import linear
+from .base import FeedForward, Runtime, StepContext, WeightSpec, register_feed_forward
+
+
+@register_feed_forward("swiglu")
+class SwiGLU(FeedForward):
+    def __init__(self, params: dict, rt: Runtime):
+        self.prefix = params.get("prefix", "")
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.rt = rt
+        self.w_gate_up = self.w_down = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {"gate_proj.weight": WeightSpec((self.inter, self.hidden)),
+                "up_proj.weight": WeightSpec((self.inter, self.hidden)),
+                "down_proj.weight": WeightSpec((self.hidden, self.inter))}
+
+    def bind(self, tensors):
+        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], 0).contiguous()
+        self.w_down = tensors["down_proj.weight"]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        # fp32 path: everything f32.  bf16 path: gate/up leave the product as bf16, the
+        # activation is evaluated in fp32 and stored bf16, down returns fp32 at the residual
+        # boundary -- the reference's policy for its bf16 feed-forward (src/ops/optimized.cpp:676-683).
+        gate_up = linear(x, self.w_gate_up, None, self.rt.dtype)
+        act = torch.empty((x.shape[0], self.inter), dtype=self.rt.dtype, device=x.device)
+        ops.silu_mul(gate_up, act)
+        return linear(act, self.w_down, None, torch.float32)
