@@ -101,6 +101,12 @@ def base_sources():
             ("sampling.cu", {})]
 
 
+def all_sources():
+    """Every object the package can ask for with its default head sizes: what the build
+    check compiles."""
+    return base_sources()
+
+
 # ------------------------------------------------------------------------------ basic
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
     _need(table, "table", dims=2); _need(ids, "ids", torch.int32, 1); _need(out, "out", torch.float32, 2)

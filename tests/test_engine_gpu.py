@@ -1,0 +1,116 @@
+"""The engine against the plain implementation, in fp32 and in bf16, cut in every way:
+whole; most in one step and the tail token by token; portions of changing size; and mixed
+batches over a pool so small that pages are used again."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers
+from tests.helpers import (collect, compare_with_plain, make_folder, random_tokens, steps_mixed, steps_portions,
+                           steps_prefill_then_decode, steps_whole, tiny_config)
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"a": [5, 11, 17, 70, 133], "b": [1, 9, 40, 70, 150]}
+PRECISION = {"float32": "float32", "bfloat16": "bfloat16"}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {key: make_folder(tmp_path_factory, key, "float32") for key in ("a", "b")}
+
+
+def requests_for(key):
+    vocab = tiny_config(key).vocab_size
+    return {f"r{i}": random_tokens(n, vocab, 100 * i + n) for i, n in enumerate(LENGTHS[key])}
+
+
+def engine_for(folder, dtype, max_tokens=1024, page_size=16):
+    from microllm_rocm_b200.engine.loading import load_engine
+    return load_engine(folder, dtype=dtype, page_size=page_size, max_tokens=max_tokens, max_requests=8)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["a", "b"])
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions"])
+def test_one_request_at_a_time(folders, key, dtype, cut):
+    reqs = requests_for(key)
+    steps = {"whole": steps_whole, "tail": steps_prefill_then_decode, "portions": steps_portions}[cut](reqs)
+    got = collect(engine_for(folders[key], dtype), steps)
+    compare_with_plain(got, folders[key], reqs, PRECISION[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["a", "b"])
+def test_mixed_batches_with_reused_pages(folders, key, dtype):
+    vocab = tiny_config(key).vocab_size
+    lengths = [60, 33, 150, 90, 47, 128, 75, 20, 101, 64]
+    reqs = {f"m{i}": random_tokens(n, vocab, 7 * i + n) for i, n in enumerate(lengths)}
+    steps, peak = steps_mixed(reqs, max_live=4, seed=3)
+    engine = engine_for(folders[key], dtype, max_tokens=peak)
+    got = collect(engine, steps)
+    compare_with_plain(got, folders[key], reqs, PRECISION[dtype])
+    stats = engine.cache.stats()
+    for group in engine.cache.groups:
+        assert stats[group]["allocations"] > stats[group]["pages"], "the pool was not tight enough to reuse pages"
+    if key == "b":
+        assert stats["pages_released_by_window"] > 0
+
+
+@pytest.mark.parametrize("key", ["a", "b"])
+def test_fp32_is_bit_stable_across_cuts(folders, key):
+    """In the fp32 path every summation order is fixed by the token's own position, so the
+    four ways of cutting give identical bits, not merely close ones."""
+    reqs = requests_for(key)
+    base = collect(engine_for(folders[key], "float32"), steps_whole(reqs))
+    for other in (steps_prefill_then_decode(reqs), steps_portions(reqs)):
+        got = collect(engine_for(folders[key], "float32"), other)
+        for k, row in base.items():
+            assert torch.equal(row, got[k]), k
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decode_and_first_tokens(folders, dtype):
+    """A two-token prompt, then 200 tokens one by one: the first positions of a sequence
+    and a long decode across many pages and, for the windowed layers, far past the window."""
+    key = "b"
+    toks = random_tokens(202, tiny_config(key).vocab_size, 5)
+    steps = [{"step": 0, "entries": [{"id": "d", "tokens": toks[:2], "want": [0, 1]}], "end": []}]
+    for i in range(2, len(toks)):
+        steps.append({"step": i - 1, "entries": [{"id": "d", "tokens": [toks[i]], "want": [0]}],
+                      "end": ["d"] if i == len(toks) - 1 else []})
+    got = collect(engine_for(folders[key], dtype), steps)
+    compare_with_plain(got, folders[key], {"d": toks}, PRECISION[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(folders, tmp_path, dtype):
+    """bin/trace_run as a user runs it: a process, JSON lines in, files and `done` lines out."""
+    key = "a"
+    reqs = {f"t{i}": random_tokens(n, tiny_config(key).vocab_size, n) for i, n in enumerate([70, 45, 100])}
+    steps, peak = steps_mixed(reqs, max_live=3, seed=1)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    proc = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", folders[key], "--dtype", dtype,
+                           "--out", str(out), "--max-tokens", str(peak)],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split("\n")[:-1] == [f"done {s['step']}" for s in steps]
+    fed, got = {}, {}
+    vocab = tiny_config(key).vocab_size
+    for s in steps:
+        keys = []
+        for e in s["entries"]:
+            base = fed.get(e["id"], 0)
+            keys += [(e["id"], base + w) for w in e["want"]]
+            fed[e["id"]] = base + len(e["tokens"])
+        data = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(len(keys), vocab)
+        for k, row in zip(keys, data):
+            got[k] = torch.from_numpy(row.copy())
+    compare_with_plain(got, folders[key], reqs, PRECISION[dtype])
