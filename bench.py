@@ -1,0 +1,259 @@
+"""Decode throughput of the engine on one B200, with prefill and roofline figures.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+The model has the layer sizes of the Qwen2.5-1.5B shape (BASELINE.json configs[2]) with
+random bf16 weights; the default run decodes a batch of 8 requests that hold 2,048-token
+prompts (context budget 4,096).  One "step" is one decode step: every live request gets one
+new token from one pass through the model.  It prints ONE JSON line:
+
+  value        decoded tokens per second, K steps timed on the device with CUDA events
+  e2e          the same through the Python entry point (LLM.submit/step): token ids start
+               on the host, every step copies its inputs host->device from pinned memory and
+               its selected tokens device->host
+  prefill      one 2,048-token prompt: tokens/s, ms, fraction of the bf16 tensor peak
+  roofline     bytes the decode step must read (every weight once + the live cache) / time
+  points       decode tokens/s at batch 1 and 64
+  clocks       SM clock and throttle reasons sampled with nvidia-smi during the timed region
+
+Each decode step reads ~3 GB of weights, far more than the 126 MB L2, so no L2 flush is
+needed between timed iterations.  The reference (walkinglabs/microLLM-rocm) is HIP/ROCm
+code without a CUDA path, so `--impl reference` reports that it is unavailable.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+BASELINE_DECODE_B8 = 435.0      # reference, DeepSeek-R1-Distill-Qwen-1.5B, T2048 B8, MI300X
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            raw = json.load(open(path))
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw.get("bf16_tflops_sustained", raw["bf16_tflops"])),
+                    "bf16_tflops_burst": float(raw["bf16_tflops"]), "source": "measured"}
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc = [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        mhz = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[3 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": float(self.samples[0][1]),
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def decode_bytes(cfg, layers, batch, context, dtype_bytes=2):
+    """Bytes one decode step has to read: every weight it uses once (the embedding rows it
+    gathers are negligible; a tied table is read once, as the head) plus the K and V of the
+    live requests."""
+    h, d = cfg.hidden_size, cfg.head_size
+    q, kv = cfg.num_attention_heads * d, cfg.num_key_value_heads * d
+    per_layer = (h * (q + 2 * kv) + q * h + 3 * h * cfg.intermediate_size) * dtype_bytes + ((q + 2 * kv) + 2 * h) * 4
+    weights = layers * per_layer + cfg.vocab_size * h * dtype_bytes + h * 4
+    cache = layers * batch * context * 2 * kv * dtype_bytes
+    return weights + cache
+
+
+def prefill_flops(cfg, layers, tokens):
+    h, d = cfg.hidden_size, cfg.head_size
+    q, kv = cfg.num_attention_heads * d, cfg.num_key_value_heads * d
+    linear = 2 * tokens * layers * (h * (q + 2 * kv) + q * h + 3 * h * cfg.intermediate_size)
+    attention = layers * 2 * 2 * cfg.num_attention_heads * d * tokens * (tokens + 1) // 2
+    head = 2 * h * cfg.vocab_size
+    return linear + attention + head
+
+
+def run_ours(args):
+    import torch
+
+    from microllm_rocm_b200.config import preset
+    from microllm_rocm_b200.engine.decode_bench import DecodeSession, count_launches
+    from microllm_rocm_b200.engine.llm import LLM
+    from microllm_rocm_b200.engine.loading import random_engine
+    from microllm_rocm_b200.engine.step import StepEntry
+    from microllm_rocm_b200.sampling import GenerationConfig
+
+    pk = peaks()
+    full = preset("qwen2.5-1.5b")
+    layers = args.layers or full.num_hidden_layers
+    cfg = preset("qwen2.5-1.5b", num_hidden_layers=layers)
+    prompt_len, context, page = args.prompt, args.context, 64
+    max_batch = max(args.batch, 64 if not args.skip_points else args.batch)
+    tokens_needed = max_batch * (context + page)
+    engine = random_engine(cfg, seed=0, dtype="bfloat16", page_size=page, max_tokens=tokens_needed,
+                           max_requests=max_batch, draw_on_device=True)
+    gen = torch.Generator().manual_seed(0)
+
+    def prompts(n):
+        return [torch.randint(0, cfg.vocab_size, (prompt_len,), generator=gen).tolist() for _ in range(n)]
+
+    # ---- prefill of 2,048 tokens ------------------------------------------------------------
+    def prefill_once():
+        engine.cache.add("pf")
+        toks = prompts(1)[0][:args.prefill_tokens]
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        engine.step([StepEntry("pf", toks, [len(toks) - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        engine.cache.release("pf")
+        return start.elapsed_time(end)
+
+    for _ in range(max(3, args.warmup)):
+        prefill_once()
+    prefill_ms = statistics.median([prefill_once() for _ in range(5)])
+    pf_flops = prefill_flops(cfg, layers, args.prefill_tokens)
+    prefill = {"value": args.prefill_tokens / (prefill_ms / 1e3), "tokens": args.prefill_tokens, "ms": prefill_ms,
+               "frac": pf_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+
+    # ---- decode, device-timed ------------------------------------------------------------------
+    def decode_device(batch, steps, warmup, sampler=None):
+        session = DecodeSession(engine, prompts(batch), steps + warmup + 1)
+        for _ in range(warmup):
+            session.step()
+        torch.cuda.synchronize()
+        launches = count_launches(session)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if sampler:
+            sampler.__enter__()
+        start.record()
+        for _ in range(steps):
+            session.step()
+        end.record()
+        torch.cuda.synchronize()
+        if sampler:
+            sampler.__exit__()
+        ms = start.elapsed_time(end) / steps
+        ctx = session.context_length()
+        session.close()
+        return ms, launches * steps, ctx
+
+    sampler = ClockSampler()
+    ms_per_step, launches, ctx_len = decode_device(args.batch, args.steps, args.warmup, sampler)
+    value = args.batch / (ms_per_step / 1e3)
+    bytes_step = decode_bytes(cfg, layers, args.batch, ctx_len)
+    achieved = bytes_step / (ms_per_step / 1e3) / 1e9
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            ms_b, _, _ = decode_device(b, max(8, args.steps // 2), args.warmup)
+            points[f"decode_b{b}"] = b / (ms_b / 1e3)
+
+    # ---- decode, end to end through the Python entry point -----------------------------------
+    llm = LLM(engine, max_tokens_per_step=max(2048, args.batch), max_seqs=max_batch)
+    host_prompts = prompts(args.batch)
+    ids = [llm.submit(p, GenerationConfig(max_new_tokens=args.steps + args.warmup + 1, temperature=0.0)) for p in host_prompts]
+    while any(llm.poll(i).computed < prompt_len for i in ids):          # prompts in, first token out
+        llm.step()
+    for _ in range(args.warmup):
+        llm.step()
+    h2d0, d2h0 = llm.h2d_bytes, llm.d2h_bytes
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        llm.step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    for i in ids:
+        llm.cancel(i)
+    e2e = {"value": args.batch * args.steps / e2e_s, "unit": "tokens/s",
+           "h2d_bytes_per_step": (llm.h2d_bytes - h2d0) // args.steps, "d2h_bytes_per_step": (llm.d2h_bytes - d2h0) // args.steps}
+
+    out = {
+        "metric": "decode tokens/s (Qwen2.5-1.5B shape, bf16, batch 8, 2048-token prompts)", "value": value,
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": value / BASELINE_DECODE_B8, "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02) seed 0, uniform random token ids", "impl": "ours",
+        "config": {"model": "qwen2.5-1.5b-shape", "layers": layers, "layers_of_model": full.num_hidden_layers,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_size, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "tied": cfg.tie_word_embeddings, "global_batch": args.batch, "seq_len": prompt_len,
+                   "context": context, "decode_context": ctx_len, "page_size": page, "parallelism": "single-gpu",
+                   "l2": "step reads >3 GB, larger than L2", "peaks": pk["source"]},
+        "e2e": e2e, "gpu_launches": launches, "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "bytes_per_step": bytes_step},
+        "points": points, "clocks": sampler.summary(),
+    }
+    print(json.dumps(out))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt", type=int, default=2048)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "walkinglabs/microLLM-rocm is a CMake C++/HIP project "
+                          "for ROCm (gfx942) with no CUDA path and no pip-installable package: it cannot run on a B200"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

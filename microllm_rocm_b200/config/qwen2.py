@@ -146,7 +146,7 @@ class Qwen2Config:
             del d["sliding_window"]
         for k in ("bos_token_id", "eos_token_id"):
             if d[k] is None:
-                d[k] = 0
+                del d[k]
         return d
 
     def save(self, folder: str) -> None:

@@ -1,0 +1,100 @@
+"""The Python entry point: a model folder in, tokens out.
+
+`LLM.generate(prompts, config)` is the call a user makes; `submit` / `step` / `poll` /
+`cancel` expose the scheduler for callers that feed requests over time.  Option names and
+meanings are the reference's (`GenerationConfig`, include/microllm/inference/generator.h:11-23;
+`submit`/`step`/`cancel` of its continuous scheduler, include/microllm/inference/scheduler.h:191-290).
+Token ids travel host -> device once per step inside the step's metadata buffer; one small
+device -> host copy per step brings the selected tokens (and the kernels' error flag) back.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..sampling.config import GenerationConfig
+from ..sampling.sampler import Sampler
+from .loading import DEFAULT_PAGE_SIZE, load_engine
+from .scheduler import Request, Scheduler, StepPlan
+from .step import Engine, StepEntry, StepError
+
+
+class LLM:
+    def __init__(self, model: Union[str, Engine], dtype="bfloat16", page_size: int = DEFAULT_PAGE_SIZE,
+                 num_pages: Optional[int] = None, max_tokens: Optional[int] = None, max_tokens_per_step: int = 2048,
+                 max_seqs: int = 64, device: Optional[str] = None):
+        if isinstance(model, Engine):
+            self.engine = model
+        else:
+            self.engine = load_engine(model, dtype=dtype, page_size=page_size, num_pages=num_pages,
+                                      max_tokens=max_tokens, max_requests=max_seqs, device=device)
+        spec = self.engine.model.spec
+        self.scheduler = Scheduler(self.engine.cache, spec.vocab_size, spec.max_position,
+                                   max_tokens_per_step=max_tokens_per_step,
+                                   max_seqs=min(max_seqs, self.engine.cache.max_requests))
+        self.sampler = Sampler(self.engine.device)
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    # ------------------------------------------------------------------ request interface
+    def submit(self, prompt: Sequence[int], config: Optional[GenerationConfig] = None) -> int:
+        return self.scheduler.submit(prompt, config)
+
+    def cancel(self, request_id: int) -> bool:
+        return self.scheduler.cancel(request_id)
+
+    def poll(self, request_id: int) -> Request:
+        return self.scheduler.requests[request_id]
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def step(self) -> List[Request]:
+        """One scheduler decision, one model step, one token selection.  Returns the requests
+        that finished in it."""
+        plan = self.scheduler.schedule()
+        if not plan.entries:
+            if self.scheduler.has_work() and not plan.preempted:
+                raise StepError("the scheduler has work but could plan nothing: the page pool is too small")
+            return []
+        entries = [StepEntry(e.request.id, e.request.tokens(e.begin, e.begin + e.count),
+                             [e.count - 1] if e.wants_logits else []) for e in plan.entries]
+        logits = self.engine.step(entries)
+        wanting = [e.request for e in plan.entries if e.wants_logits]
+        R = len(wanting)
+        packed = torch.empty(R + 1, dtype=torch.int32, device=self.engine.device)
+        if R:
+            self.sampler.sample_into(logits, [r.config for r in wanting], [len(r.generated) for r in wanting], packed[:R])
+        packed[R:].copy_(self.engine.error_flag)
+        host = packed.tolist()                                   # the step's one device -> host copy
+        self.h2d_bytes += 4 * plan.num_tokens
+        self.d2h_bytes += 4 * (R + 1)
+        if host[R]:
+            self.engine.error_flag.zero_()
+            raise StepError(f"a kernel met a token without a valid page (code {host[R]})")
+        return self.scheduler.update(plan, host[:R])
+
+    # ------------------------------------------------------------------ whole generations
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 config: Union[GenerationConfig, Sequence[GenerationConfig], None] = None) -> List[List[int]]:
+        """Generate for every prompt (token ids); returns the new tokens of each, in order."""
+        if prompts and isinstance(prompts[0], int):
+            raise TypeError("generate takes a list of prompts, each a list of token ids")
+        configs = list(config) if isinstance(config, (list, tuple)) else [config or GenerationConfig()] * len(prompts)
+        if len(configs) != len(prompts):
+            raise ValueError("one GenerationConfig per prompt, or one for all")
+        ids = [self.submit(p, c) for p, c in zip(prompts, configs)]
+        while self.scheduler.has_work():
+            self.step()
+        out = [list(self.scheduler.requests[i].generated) for i in ids]
+        for i in ids:
+            del self.scheduler.requests[i]
+        return out
+
+    generate_batch = generate
+
+    def metrics(self) -> Dict[str, object]:
+        m = dict(vars(self.scheduler.metrics))
+        m["cache"] = self.engine.cache.stats()
+        return m

@@ -59,18 +59,18 @@ def pages_for_tokens(max_tokens: int, page_size: int) -> int:
 
 def load_engine(folder: str, dtype="bfloat16", page_size: int = DEFAULT_PAGE_SIZE, num_pages: Optional[int] = None,
                 max_tokens: Optional[int] = None, max_requests: int = 64, device: Optional[str] = None,
-                strict: bool = True) -> Engine:
+                strict: bool = True, config_path: Optional[str] = None, weights_path: Optional[str] = None) -> Engine:
     """Read config.json, choose the architecture by its name, load model.safetensors, and set
     up a cache of `num_pages` pages per layer group (or enough for `max_tokens` tokens)."""
     dev = require_gpu(device)
-    with open(os.path.join(folder, "config.json"), "r", encoding="utf-8") as f:
+    with open(config_path or os.path.join(folder, "config.json"), "r", encoding="utf-8") as f:
         raw = json.load(f)
     arch = architecture_of(raw)
     config = arch.config_class.from_dict(raw)
     rt = Runtime(dev, resolve_dtype(dtype))
     model = build_model(arch.build_spec(config), rt)
     prepare_kernels(model)
-    load_weights(model, folder, strict=strict)
+    load_weights(model, weights_path or folder, strict=strict)
     if num_pages is None:
         num_pages = pages_for_tokens(max_tokens if max_tokens is not None else config.max_position_embeddings, page_size)
     engine = make_engine(model, page_size, num_pages, max_requests)

@@ -180,7 +180,14 @@ def load(source: str, defines: Optional[Dict[str, object]] = None) -> ctypes.CDL
     return lib
 
 
+class LaunchCounter:
+    """How many kernels of this library were launched (one per successful launcher call)."""
+    own = 0
+    library = 0          # library matrix products issued on the same path
+
+
 def check(lib: ctypes.CDLL, status: int) -> None:
+    LaunchCounter.own += 1
     if status != 0:
         message = lib.mlb_last_error()
         raise KernelError(message.decode("utf-8", "replace") if message else f"kernel launcher returned {status}")

@@ -8,6 +8,8 @@ import torch
 
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
                 out: Optional[torch.Tensor]) -> torch.Tensor:
+    from .build import LaunchCounter
+    LaunchCounter.library += 1
     # Library product: cuBLASLt, bf16 operands, fp32 accumulate, output written in out_dtype.
     if out_dtype == torch.bfloat16:
         y = torch.mm(x, weight.t()) if out is None else torch.mm(x, weight.t(), out=out)

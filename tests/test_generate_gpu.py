@@ -1,0 +1,141 @@
+"""Generation through the Python entry point and the command line: greedy and seeded
+temperature sampling against the plain implementation, many requests at once, and a pool so
+small that requests are preempted and recomputed."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from tests.helpers import make_folder, plain_logits, random_tokens, tiny_config
+from tests.plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {key: make_folder(tmp_path_factory, key, "float32") for key in ("a", "b")}
+
+
+def plain_generate(folder, prompt, n, **kw):
+    weights = plain.read_safetensors(os.path.join(folder, "model.safetensors"))
+    cfg = plain.read_config(os.path.join(folder, "config.json"))
+    return plain.generate(weights, cfg, prompt, n, **kw)
+
+
+def llm_for(folder, dtype, **kw):
+    from microllm_rocm_b200 import LLM
+    return LLM(folder, dtype=dtype, page_size=16, **kw)
+
+
+@pytest.mark.parametrize("key,lengths,new", [("a", [5, 11, 17], 8), ("b", [1, 9, 40, 70], 12)])
+def test_greedy_generation_fp32_equals_plain(folders, key, lengths, new):
+    from microllm_rocm_b200 import GenerationConfig
+    vocab = tiny_config(key).vocab_size
+    prompts = [random_tokens(n, vocab, n) for n in lengths]
+    llm = llm_for(folders[key], "float32", max_tokens=1024)
+    got = llm.generate(prompts, GenerationConfig(max_new_tokens=new, temperature=0.0))
+    for p, g in zip(prompts, got):
+        assert g == plain_generate(folders[key], p, new)
+    # one by one gives the same tokens as all together
+    llm2 = llm_for(folders[key], "float32", max_tokens=1024)
+    assert [llm2.generate([p], GenerationConfig(max_new_tokens=new, temperature=0.0))[0] for p in prompts] == got
+
+
+def test_seeded_temperature_sampling_fp32_equals_plain(folders):
+    from microllm_rocm_b200 import GenerationConfig
+    key = "b"
+    prompts = [random_tokens(n, tiny_config(key).vocab_size, n) for n in [1, 9, 40, 70]]
+    cfg = GenerationConfig(max_new_tokens=12, temperature=0.8, seed=7)
+    got = llm_for(folders[key], "float32", max_tokens=1024).generate(prompts, cfg)
+    for p, g in zip(prompts, got):
+        assert g == plain_generate(folders[key], p, 12, temperature=0.8, seed=7)
+    again = llm_for(folders[key], "float32", max_tokens=1024).generate(prompts, cfg)
+    assert again == got
+    other = llm_for(folders[key], "float32", max_tokens=1024).generate(
+        prompts, GenerationConfig(max_new_tokens=12, temperature=0.8, seed=8))
+    assert other != got
+    topk = llm_for(folders[key], "float32", max_tokens=1024).generate(
+        prompts[:2], GenerationConfig(max_new_tokens=6, temperature=1.3, top_k=4, seed=3))
+    for p, g in zip(prompts, topk):
+        assert g == plain_generate(folders[key], p, 6, temperature=1.3, top_k=4, seed=3)
+
+
+@pytest.mark.parametrize("key", ["a", "b"])
+def test_greedy_generation_bf16_follows_the_plain_logits(folders, key):
+    """bf16 tokens may leave the fp32 ones at a near tie; what must hold is that every chosen
+    token is (within bf16 error) a maximum of the plain bf16 logits for the same prefix."""
+    from microllm_rocm_b200 import GenerationConfig
+    prompts = [random_tokens(n, tiny_config(key).vocab_size, 3 * n) for n in [3, 20, 45]]
+    got = llm_for(folders[key], "bfloat16", max_tokens=1024).generate(prompts, GenerationConfig(max_new_tokens=10, temperature=0.0))
+    for p, g in zip(prompts, got):
+        assert len(g) == 10
+        ref = plain_logits(folders[key], p + g[:-1], "bfloat16")[len(p) - 1:]
+        for i, t in enumerate(g):
+            assert float(ref[i].max() - ref[i, t]) <= 0.03 * float(ref[i].abs().max()), (i, t)
+
+
+def test_tight_pool_preempts_and_still_generates_the_same_tokens(folders):
+    from microllm_rocm_b200 import GenerationConfig
+    key = "b"
+    prompts = [random_tokens(n, tiny_config(key).vocab_size, 11 * n) for n in [30, 28, 33, 25]]
+    cfg = GenerationConfig(max_new_tokens=40, temperature=0.0)
+    want = llm_for(folders[key], "float32", max_tokens=2048).generate(prompts, cfg)
+    tight = llm_for(folders[key], "float32", num_pages=10, max_tokens_per_step=24)      # 160 tokens for 4 x ~70
+    got = tight.generate(prompts, cfg)
+    assert got == want
+    m = tight.metrics()
+    assert m["preemptions"] > 0 and m["cache"]["full"]["used"] == 0
+    tight.engine.cache.check()
+
+
+def test_stop_tokens_and_requests_over_time(folders):
+    from microllm_rocm_b200 import GenerationConfig
+    key = "a"
+    llm = llm_for(folders[key], "float32", max_tokens=512)
+    p = random_tokens(12, tiny_config(key).vocab_size, 1)
+    full = plain_generate(folders[key], p, 10)
+    stop = full[4]
+    a = llm.submit(p, GenerationConfig(max_new_tokens=10, temperature=0.0, stop_tokens=(stop,)))
+    llm.step(); llm.step()
+    b = llm.submit(p, GenerationConfig(max_new_tokens=3, temperature=0.0))       # arrives while a decodes
+    while llm.has_work():
+        llm.step()
+    assert llm.poll(a).generated == full[:full.index(stop) + 1]
+    assert llm.poll(b).generated == full[:3]
+    assert llm.poll(b).first_token_step == 2
+
+
+def test_command_line(folders, tmp_path):
+    key = "a"
+    prompt = random_tokens(9, tiny_config(key).vocab_size, 2)
+    logits_file, cached_file = tmp_path / "l.f32", tmp_path / "c.f32"
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "microllm_hf_infer"), "--config", os.path.join(folders[key], "config.json"),
+           "--weights", os.path.join(folders[key], "model.safetensors"), "--tokens", ",".join(map(str, prompt)),
+           "--device", "cuda", "--workload", "both", "--new-tokens", "4", "--logits-output", str(logits_file),
+           "--cache-logits-output", str(cached_file), "--top-k", "3"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    info = json.loads(proc.stdout.strip().splitlines()[-1])
+    want = plain_generate(folders[key], prompt, 4)
+    assert info["status"] == "pass" and info["generated_tokens"] == want and info["compute_dtype"] == "float32"
+    import numpy as np
+    last = torch.from_numpy(np.fromfile(logits_file, dtype="<f4"))
+    assert torch.allclose(last, plain_logits(folders[key], prompt)[-1], atol=2e-5)
+    assert [t["token"] for t in info["top_logits"]] == torch.topk(last, 3).indices.tolist()
+    cached = torch.from_numpy(np.fromfile(cached_file, dtype="<f4"))
+    assert torch.allclose(cached, plain_logits(folders[key], prompt + want[:-1])[-1], atol=2e-5)
+    # continuous workload: delayed arrivals over two slots
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "microllm_hf_infer"), "--model", folders[key], "--workload", "continuous",
+           "--tokens", ",".join(map(str, prompt)), "--continuous-slots", "2", "--continuous-prompt-lengths", "4,9,6",
+           "--continuous-new-token-lengths", "3,2,4", "--continuous-arrival-steps", "0,1,1"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    info = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert info["generated_tokens"] == [plain_generate(folders[key], prompt[:n], k) for n, k in ((4, 3), (9, 2), (6, 4))]
+    assert info["admissions"] == 3

@@ -1,0 +1,361 @@
+"""Each kernel alone against a plain fp32 reference of the same operation, at sizes other
+than the engine's tests use: widths and vocabularies that are no power of two, head sizes
+from 16 to 256, odd group sizes.  Where random inputs would hide a fault the inputs are made
+so that it shows (one far key that must dominate, the exact edge of a window, keys that sit
+in the last slot of a page)."""
+import math
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from tests.plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def ops():
+    from microllm_rocm_b200.kernels import ops as o
+    return o
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+# ------------------------------------------------------------------------------ rows
+@pytest.mark.parametrize("width", [16, 100, 1536, 5000])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_and_fused_add(width, out_dtype):
+    torch.manual_seed(width)
+    x = torch.randn(37, width) * 3
+    w = 1 + 0.1 * torch.randn(width)
+    d = torch.randn(37, width)
+    eps = 1e-5
+    want = plain.rms_norm(x, w, eps)
+    out = torch.empty(37, width, dtype=out_dtype, device=DEV)
+    ops().rmsnorm(x.to(DEV), w.to(DEV), eps, out)
+    assert torch.allclose(out.float().cpu(), want, **tol(out_dtype))
+    # selected rows only
+    rows = torch.tensor([5, 0, 36, 5], dtype=torch.int32)
+    out2 = torch.empty(4, width, dtype=out_dtype, device=DEV)
+    ops().rmsnorm(x.to(DEV), w.to(DEV), eps, out2, rows=rows.to(DEV))
+    assert torch.allclose(out2.float().cpu(), want[rows.long()], **tol(out_dtype))
+    # residual += delta, then norm
+    res = x.to(DEV).clone()
+    ops().add_rmsnorm(res, d.to(DEV), w.to(DEV), eps, out)
+    assert torch.equal(res.cpu(), x + d)
+    assert torch.allclose(out.float().cpu(), plain.rms_norm(x + d, w, eps), **tol(out_dtype))
+
+
+def test_rmsnorm_row_result_does_not_depend_on_the_batch():
+    torch.manual_seed(0)
+    x = torch.randn(64, 777, device=DEV)
+    w = torch.randn(777, device=DEV)
+    a = torch.empty_like(x)
+    ops().rmsnorm(x, w, 1e-6, a)
+    b = torch.empty(1, 777, device=DEV)
+    ops().rmsnorm(x[13:14].contiguous(), w, 1e-6, b)
+    assert torch.equal(a[13], b[0])
+
+
+@pytest.mark.parametrize("table_dtype", [torch.float32, torch.bfloat16])
+def test_embedding_gather_and_bad_id(table_dtype):
+    torch.manual_seed(1)
+    table = torch.randn(301, 70).to(table_dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32)
+    out = torch.empty(5, 70, device=DEV)
+    ops().embed_gather(table.to(DEV), ids.to(DEV), out)
+    assert torch.equal(out.cpu(), plain.embedding(table.float(), ids.tolist()))
+    bad = torch.tensor([3, 301, -1], dtype=torch.int32, device=DEV)
+    out = torch.empty(3, 70, device=DEV)
+    ops().embed_gather(table.to(DEV), bad, out)
+    assert torch.isfinite(out[0]).all() and torch.isnan(out[1]).all() and torch.isnan(out[2]).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(dtype):
+    torch.manual_seed(2)
+    gu = (torch.randn(9, 2 * 173) * 4).to(dtype)
+    gu[0, 0], gu[0, 1] = 90.0, -90.0                    # both branches of the stable sigmoid
+    out = torch.empty(9, 173, dtype=dtype, device=DEV)
+    ops().silu_mul(gu.to(DEV), out)
+    want = plain.swiglu(gu[:, :173].float(), gu[:, 173:].float())
+    assert torch.allclose(out.float().cpu(), want, **tol(dtype))
+
+
+# ------------------------------------------------------------------------------ fp32 product
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (3, 70, 33), (65, 129, 200), (130, 64, 17), (7, 1000, 1536)])
+def test_gemm_f32_is_a_true_fp32_product(M, N, K):
+    torch.manual_seed(M * N + K)
+    a, w, bias = torch.randn(M, K), torch.randn(N, K), torch.randn(N)
+    want = (a.double() @ w.double().t() + bias.double())
+    out = torch.empty(M, N, device=DEV)
+    ops().gemm_f32(a.to(DEV), w.to(DEV), out, bias=bias.to(DEV))
+    err = (out.cpu().double() - want).abs().max()
+    # fp32 accumulation over K terms: far below what a reduced-precision matrix mode gives
+    assert err <= 2e-6 * math.sqrt(K) * 4, err
+    base = torch.randn(M, N)
+    acc = base.to(DEV).clone()
+    ops().gemm_f32(a.to(DEV), w.to(DEV), acc, accumulate=True)
+    assert torch.allclose(acc.cpu().double(), base.double() + a.double() @ w.double().t(), atol=2e-5 * math.sqrt(K))
+
+
+def test_gemm_f32_row_does_not_depend_on_the_batch():
+    torch.manual_seed(3)
+    a, w = torch.randn(77, 300, device=DEV), torch.randn(91, 300, device=DEV)
+    full = torch.empty(77, 91, device=DEV)
+    ops().gemm_f32(a, w, full)
+    one = torch.empty(1, 91, device=DEV)
+    ops().gemm_f32(a[40:41].contiguous(), w, one)
+    assert torch.equal(full[40], one[0])
+
+
+# ------------------------------------------------------------------------------ paged cache helpers
+def paged_from_dense(k, v, page_size, num_pages, dtype, seed=0):
+    """k, v: lists (one per sequence) of [n, NKV, D].  Returns pages and a block table with
+    the physical pages shuffled, so that logical order never equals physical order."""
+    rng = random.Random(seed)
+    nkv, d = k[0].shape[1], k[0].shape[2]
+    pages = torch.full((num_pages, 2, nkv, page_size, d), float("nan"), dtype=torch.float32)
+    free = list(range(num_pages))
+    rng.shuffle(free)
+    width = max(-(-x.shape[0] // page_size) for x in k)
+    table = torch.full((len(k), width), -1, dtype=torch.int32)
+    for s, (ks, vs) in enumerate(zip(k, v)):
+        for b in range(-(-ks.shape[0] // page_size)):
+            p = free.pop()
+            table[s, b] = p
+            n = min(page_size, ks.shape[0] - b * page_size)
+            pages[p, 0, :, :n] = ks[b * page_size:b * page_size + n].transpose(0, 1)
+            pages[p, 1, :, :n] = vs[b * page_size:b * page_size + n].transpose(0, 1)
+    return pages.to(dtype), table
+
+
+def run_attention(q_list, k_list, v_list, pos0_list, nh, nkv, d, window, dtype, page_size=16):
+    """Queries q_list[s] ([n_s, NH, D]) sit at positions pos0_list[s].. of sequence s whose
+    keys are k_list[s]."""
+    pages, table = paged_from_dense(k_list, v_list, page_size, 64, dtype)
+    q = torch.cat([x.reshape(x.shape[0], nh * d) for x in q_list]).to(dtype)
+    positions = torch.cat([torch.arange(p, p + x.shape[0], dtype=torch.int32) for p, x in zip(pos0_list, q_list)])
+    token_seq = torch.cat([torch.full((x.shape[0],), s, dtype=torch.int32) for s, x in enumerate(q_list)])
+    out = torch.empty(q.shape, dtype=dtype, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    from microllm_rocm_b200.kernels import attention
+    from microllm_rocm_b200.parts.base import StepContext
+    ctx = StepContext(num_tokens=q.shape[0], num_seqs=len(q_list), token_ids=positions.to(DEV), positions=positions.to(DEV),
+                      token_seq=token_seq.to(DEV),
+                      seq_starts=torch.tensor(np.cumsum([0] + [x.shape[0] for x in q_list]), dtype=torch.int32).to(DEV),
+                      seq_pos0=torch.tensor(list(pos0_list), dtype=torch.int32).to(DEV),
+                      seq_lens=torch.tensor([p + x.shape[0] for p, x in zip(pos0_list, q_list)], dtype=torch.int32).to(DEV),
+                      block_tables={},
+                      state_slots=None, logit_rows=None, error_flag=flag,
+                      seq_starts_host=[int(v) for v in np.cumsum([0] + [x.shape[0] for x in q_list])],
+                      seq_pos0_host=list(pos0_list), max_new_tokens=max(x.shape[0] for x in q_list),
+                      max_seq_len=max(p + x.shape[0] for p, x in zip(pos0_list, q_list)))
+    attention.paged_attention(q.to(DEV), pages.to(DEV), out, ctx, table.to(DEV), nh, nkv, d, 1.0 / math.sqrt(d), window)
+    assert int(flag.item()) == 0
+    return out.float().cpu()
+
+
+def plain_attention_rows(q, k, v, pos0, window):
+    """Reference for queries at positions pos0.. over keys k (which include those positions)."""
+    n = q.shape[0]
+    full_q = torch.zeros(pos0 + n, q.shape[1], q.shape[2])
+    full_q[pos0:] = q
+    return plain.causal_gqa_attention(full_q, k[:pos0 + n], v[:pos0 + n], window)[pos0:]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,d,window", [(4, 1, 16, None), (6, 2, 32, 32), (7, 7, 48, None), (12, 2, 128, 40),
+                                             (5, 5, 80, 17), (3, 1, 256, None), (14, 2, 64, 33)])
+def test_paged_attention_prompts_and_decodes_in_one_batch(dtype, nh, nkv, d, window):
+    torch.manual_seed(nh * d)
+    lens = [70, 33, 1, 129]          # cached tokens after the step
+    news = [70, 1, 1, 20]            # whole prompt, decode token, first token, later portion
+    ks = [torch.randn(n, nkv, d) for n in lens]
+    vs = [torch.randn(n, nkv, d) for n in lens]
+    qs = [torch.randn(n, nh, d) for n in news]
+    if dtype == torch.bfloat16:
+        ks, vs, qs = ([x.to(dtype).float() for x in y] for y in (ks, vs, qs))
+    got = run_attention(qs, ks, vs, [l - n for l, n in zip(lens, news)], nh, nkv, d, window, dtype)
+    want = torch.cat([plain_attention_rows(q, k, v, l - n, window).reshape(n, nh * d)
+                      for q, k, v, l, n in zip(qs, ks, vs, lens, news)])
+    assert torch.allclose(got, want, **tol(dtype)), float((got - want).abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_one_far_key_among_hundreds_dominates(dtype):
+    """Query and one key far back are scaled so that their score stands out: the output must
+    be (nearly) that key's value, which a kernel that drops or misplaces far keys cannot give."""
+    torch.manual_seed(5)
+    nh, nkv, d, n = 4, 2, 64, 700
+    k, v = torch.randn(n, nkv, d) * 0.1, torch.randn(n, nkv, d)
+    q = torch.randn(1, nh, d) * 0.1
+    far = 3                                             # sits in the first page
+    direction = torch.randn(d)
+    direction /= direction.norm()
+    q[0, :] = direction * 30
+    k[far, :] = direction * 30
+    if dtype == torch.bfloat16:
+        k, v, q = (x.to(dtype).float() for x in (k, v, q))
+    got = run_attention([q], [k], [v], [n - 1], nh, nkv, d, None, dtype).reshape(nh, d)
+    for h in range(nh):
+        assert torch.allclose(got[h], v[far, h // 2], atol=3e-2 if dtype == torch.bfloat16 else 1e-4)
+    # with a window that ends one key short of it, the far key must be invisible
+    got_w = run_attention([q], [k], [v], [n - 1], nh, nkv, d, n - 1 - far, dtype).reshape(nh, d)
+    want_w = plain_attention_rows(q, k, v, n - 1, n - 1 - far).reshape(nh, d)
+    assert torch.allclose(got_w, want_w, **tol(dtype))
+    assert not torch.allclose(got_w[0], v[far, 0], atol=0.2)
+    # and with a window that just reaches it, visible again
+    got_in = run_attention([q], [k], [v], [n - 1], nh, nkv, d, n - far, dtype).reshape(nh, d)
+    assert torch.allclose(got_in[0], v[far, 0], atol=3e-2 if dtype == torch.bfloat16 else 1e-4)
+
+
+@pytest.mark.parametrize("page_size", [4, 16, 64])
+def test_window_and_page_edges(page_size):
+    """Every query position around page edges and the window's edge, one token at a time."""
+    torch.manual_seed(6)
+    nh, nkv, d, W, n = 2, 1, 32, 2 * page_size, 3 * page_size + 3
+    k, v, q = torch.randn(n, nkv, d), torch.randn(n, nkv, d), torch.randn(n, nh, d)
+    want = plain.causal_gqa_attention(q, k, v, W)
+    for pos in list(range(0, 3)) + list(range(page_size - 2, page_size + 2)) + list(range(W - 2, W + 3)) + [n - 1]:
+        got = run_attention([q[pos:pos + 1]], [k[:pos + 1]], [v[:pos + 1]], [pos], nh, nkv, d, W, torch.float32,
+                            page_size=page_size)
+        assert torch.allclose(got.reshape(nh, d), want[pos], atol=2e-5), pos
+
+
+# ------------------------------------------------------------------------------ rope + kv store
+@pytest.mark.parametrize("kv_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,d,rot,inter", [(4, 1, 16, 16, False), (6, 2, 32, 32, False), (3, 3, 128, 64, False),
+                                                (2, 1, 48, 48, True), (5, 1, 256, 256, False)])
+def test_rope_bias_and_paged_store(kv_dtype, nh, nkv, d, rot, inter):
+    from microllm_rocm_b200.parts.rotary import inverse_frequencies
+    torch.manual_seed(d + nh)
+    T, page, theta = 23, 8, 1e6
+    width = (nh + 2 * nkv) * d
+    qkv, bias = torch.randn(T, width), torch.randn(width) * 0.3
+    positions = torch.tensor([0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 100, 101, 40, 41, 42, 43, 44, 45, 46, 47, 48, 63, 64],
+                             dtype=torch.int32)
+    token_seq = torch.tensor([0] * 10 + [1] * 2 + [2] * 9 + [3] * 2, dtype=torch.int32)
+    num_pages, maxb = 40, 16
+    table = torch.full((4, maxb), -1, dtype=torch.int32)
+    perm = list(range(num_pages))
+    random.Random(1).shuffle(perm)
+    for s_, p_ in sorted({(s_, int(p_) // page) for s_, p_ in zip(token_seq.tolist(), positions.tolist())}):
+        table[s_, p_] = perm.pop()
+    pages = torch.zeros(num_pages, 2, nkv, page, d, dtype=kv_dtype, device=DEV)
+    q_out = torch.empty(T, nh * d, dtype=kv_dtype, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    inv = torch.from_numpy(inverse_frequencies(theta, rot)).to(DEV)
+    ops().rope_kv_write(qkv.to(DEV), bias.to(DEV), positions.to(DEV), token_seq.to(DEV), table.to(DEV), inv, rot, inter,
+                        q_out, pages, nh, nkv, d, flag)
+    assert int(flag.item()) == 0
+    x = (qkv + bias).view(T, nh + 2 * nkv, d)
+
+    def rotate(heads):                  # plain rotation of the first `rot` elements
+        part = heads[..., :rot]
+        if inter:
+            part = torch.cat([part[..., 0::2], part[..., 1::2]], -1)
+        # frequencies of a rotary width `rot`
+        half = rot // 2
+        i = np.arange(half, dtype=np.float32)
+        invf = np.power(np.float32(theta), (np.float32(-2.0) * i) / np.float32(rot), dtype=np.float32)
+        out = part.clone()
+        for t in range(T):
+            ang = np.float32(positions[t].item()) * invf
+            c, s = torch.from_numpy(np.cos(ang)), torch.from_numpy(np.sin(ang))
+            a, b = part[t, :, :half], part[t, :, half:]
+            out[t, :, :half], out[t, :, half:] = a * c - b * s, a * s + b * c
+        if inter:
+            re = torch.empty_like(out)
+            re[..., 0::2], re[..., 1::2] = out[..., :half], out[..., half:]
+            out = re
+        return torch.cat([out, heads[..., rot:]], -1)
+
+    if rot == d and not inter:          # the model's own case: also against the plain implementation
+        assert torch.allclose(rotate(x[:, :nh]), plain.rope_split_half(x[:, :nh], positions.tolist(), theta), atol=1e-6)
+    want_q, want_k, want_v = rotate(x[:, :nh]), rotate(x[:, nh:nh + nkv]), x[:, nh + nkv:]
+    t_ = tol(kv_dtype)
+    assert torch.allclose(q_out.float().cpu().view(T, nh, d), want_q, **t_)
+    pc = pages.float().cpu()
+    for t in range(T):
+        p = table[token_seq[t], positions[t] // page]
+        slot = positions[t] % page
+        assert torch.allclose(pc[p, 0, :, slot], want_k[t], **t_)
+        assert torch.allclose(pc[p, 1, :, slot], want_v[t], **t_)
+    # nothing else was touched
+    written = torch.zeros(num_pages, page, dtype=torch.bool)
+    for t in range(T):
+        written[table[token_seq[t], positions[t] // page], positions[t] % page] = True
+    assert (pc[:, :, :, :, :].abs().sum(dim=(1, 2, 4))[~written] == 0).all()
+
+
+def test_rope_kv_write_refuses_to_write_without_a_page():
+    from microllm_rocm_b200.parts.rotary import inverse_frequencies
+    nh, nkv, d = 2, 1, 16
+    qkv = torch.randn(2, (nh + 2 * nkv) * d, device=DEV)
+    table = torch.tensor([[0, -1]], dtype=torch.int32, device=DEV)           # block 1 has no page
+    pages = torch.zeros(2, 2, nkv, 4, d, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q = torch.empty(2, nh * d, device=DEV)
+    ops().rope_kv_write(qkv, None, torch.tensor([3, 4], dtype=torch.int32, device=DEV),
+                        torch.zeros(2, dtype=torch.int32, device=DEV), table,
+                        torch.from_numpy(inverse_frequencies(1e4, d)).to(DEV), d, False, q, pages, nh, nkv, d, flag)
+    assert int(flag.item()) == 1
+    assert pages[1].abs().sum() == 0, "page 1 belongs to someone else and must stay untouched"
+
+
+# ------------------------------------------------------------------------------ selection
+def test_argmax_ties_and_non_finite():
+    x = torch.randn(5, 1003)
+    x[0, 7] = x[0, 500] = 50.0                         # tie: the smaller index wins
+    x[1, 1002] = 60.0                                  # last element
+    x[2, 10] = float("nan")
+    x[3, 0] = float("inf")
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops().argmax_rows(x.to(DEV), out)
+    assert out.tolist() == [7, 1002, -1, -1, int(x[4].argmax())]
+
+
+@pytest.mark.parametrize("vocab", [97, 1003, 40000])
+def test_sampling_kernel_matches_the_plain_sampler(vocab):
+    torch.manual_seed(vocab)
+    rows = 24
+    x = torch.randn(rows, vocab) * 2
+    x[3, 5] = x[3, 9] = x[3].max() + 1                 # ties at the top-k edge
+    temps = [0.0, 0.8, 1.0, 0.8, 0.3, 2.0] * 4
+    topk = [0, 0, 1, 2, 5, min(50, vocab)] * 4
+    seeds = [7, 7, 7, 11, 12345678901234, 3] * 4
+    draws = list(range(rows))
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops().sample_rows(x.to(DEV), torch.tensor(temps).to(DEV), torch.tensor(topk, dtype=torch.int32).to(DEV),
+                      torch.tensor(seeds, dtype=torch.int64).to(DEV), torch.tensor(draws, dtype=torch.int64).to(DEV), out)
+    want = [plain.sample_token(x[r].numpy(), temps[r], topk[r], seeds[r], draws[r]) for r in range(rows)]
+    assert out.tolist() == want
+
+
+def test_sampling_kernel_follows_the_distribution():
+    logits = torch.tensor([[0.0, 1.0, 2.0, 0.5, -1.0]]).repeat(4000, 1)
+    out = torch.empty(4000, dtype=torch.int32, device=DEV)
+    ops().sample_rows(logits.to(DEV), torch.full((4000,), 0.8).to(DEV), torch.zeros(4000, dtype=torch.int32).to(DEV),
+                      torch.full((4000,), 7, dtype=torch.int64).to(DEV), torch.arange(4000, dtype=torch.int64).to(DEV), out)
+    p = torch.softmax(logits[0] / 0.8, 0)
+    freq = torch.bincount(out.cpu().long(), minlength=5) / 4000.0
+    assert (freq - p).abs().max() < 0.03
+
+
+def test_kernels_refuse_bad_sizes_with_a_clear_error():
+    from microllm_rocm_b200.kernels.build import KernelError
+    with pytest.raises(KernelError, match="no CPU path"):
+        ops().rmsnorm(torch.randn(2, 4), torch.randn(4), 1e-5, torch.empty(2, 4))
+    with pytest.raises(KernelError, match="shapes"):
+        ops().gemm_f32(torch.randn(2, 4, device=DEV), torch.randn(3, 5, device=DEV), torch.empty(2, 3, device=DEV))
+    from microllm_rocm_b200.kernels import attention
+    with pytest.raises(KernelError, match="head_dim"):
+        attention.check_head_dim(264)
+    with pytest.raises(KernelError, match="head_dim"):
+        attention.check_head_dim(17)

@@ -1,0 +1,169 @@
+"""Weights: the safetensors container, binding by name, the one error that lists every
+problem, dtype policy, random-weights mode."""
+import json
+import os
+import struct
+
+import pytest
+import torch
+
+from microllm_rocm_b200.config import Qwen2Config, get_architecture
+from microllm_rocm_b200.parts import Runtime, build_model
+from microllm_rocm_b200.weights import (SafetensorsError, SafetensorsFile, WeightLoadError, load_weights, save_file,
+                                        write_random_model)
+from microllm_rocm_b200.weights.safetensors import inspect_file, open_model_files
+from tests.helpers import tiny_config
+from tests.plain import qwen2_plain as plain
+
+ARCH = get_architecture("Qwen2ForCausalLM")
+
+
+def cpu_model(key, dtype=torch.float32):
+    return build_model(ARCH.build_spec(tiny_config(key)), Runtime(torch.device("cpu"), dtype))
+
+
+def rewrite(folder, edit):
+    path = os.path.join(folder, "model.safetensors")
+    f = SafetensorsFile(path)
+    tensors = {n: f.tensor(n).clone() for n in f.names()}
+    edit(tensors)
+    save_file(tensors, path)
+
+
+def test_round_trip_all_float_dtypes(tmp_path):
+    t = {"a": torch.randn(3, 5), "b": torch.randn(7).to(torch.bfloat16), "c": torch.randn(2, 2).to(torch.float16),
+         "i": torch.arange(6, dtype=torch.int32).reshape(2, 3), "empty": torch.zeros(0, 4)}
+    p = str(tmp_path / "x.safetensors")
+    save_file(t, p, metadata={"k": "v"})
+    f = SafetensorsFile(p)
+    assert set(f.names()) == set(t)
+    for n, v in t.items():
+        assert f.tensor(n).dtype == v.dtype and torch.equal(f.tensor(n), v)
+    # and the independent reader of the plain implementation agrees on the float tensors
+    p2 = str(tmp_path / "y.safetensors")
+    save_file({k: t[k] for k in "abc"}, p2)
+    again = plain.read_safetensors(p2)
+    for k in "abc":
+        assert torch.equal(again[k], t[k].to(torch.float32))
+
+
+def test_container_corruption_is_refused(tmp_path):
+    p = str(tmp_path / "x.safetensors")
+    save_file({"a": torch.randn(4, 4), "b": torch.randn(3)}, p)
+    raw = open(p, "rb").read()
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + hlen])
+
+    def write(h, payload=raw[8 + hlen:]):
+        blob = json.dumps(h).encode()
+        open(p, "wb").write(struct.pack("<Q", len(blob)) + blob + payload)
+
+    open(p, "wb").write(raw[:-5])
+    with pytest.raises(SafetensorsError):
+        inspect_file(p)
+    h = json.loads(json.dumps(header)); h["a"]["data_offsets"] = [0, 60]
+    write(h)
+    with pytest.raises(SafetensorsError, match="do not match shape"):
+        inspect_file(p)
+    h = json.loads(json.dumps(header)); h["b"]["data_offsets"] = [60, 72]; h["b"]["shape"] = [3]
+    write(h)
+    with pytest.raises(SafetensorsError, match="overlap|hole|cover"):
+        inspect_file(p)
+    h = json.loads(json.dumps(header)); h["a"]["dtype"] = "F8_E4M3"
+    write(h)
+    with pytest.raises(SafetensorsError, match="unsupported dtype"):
+        inspect_file(p)
+    open(p, "wb").write(struct.pack("<Q", 1 << 40) + b"{}")
+    with pytest.raises(SafetensorsError, match="header length"):
+        inspect_file(p)
+    blob = b'{"a":{"dtype":"F32","shape":[1],"data_offsets":[0,4]},"a":{"dtype":"F32","shape":[1],"data_offsets":[0,4]}}'
+    open(p, "wb").write(struct.pack("<Q", len(blob)) + blob + b"\0\0\0\0")
+    with pytest.raises(SafetensorsError, match="duplicate"):
+        inspect_file(p)
+
+
+def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
+    folder = write_random_model(ARCH, tiny_config("b"), 1, str(tmp_path / "m"), "float32")
+
+    def edit(t):
+        del t["model.layers.1.self_attn.k_proj.bias"]
+        del t["lm_head.weight"]
+        t["model.layers.0.mlp.gate_proj.weight"] = torch.zeros(512, 100)
+        t["model.layers.9.extra.weight"] = torch.zeros(2)
+        t["model.norm.weight"] = torch.zeros(192, dtype=torch.int32)
+    rewrite(folder, edit)
+    model = cpu_model("b")
+    with pytest.raises(WeightLoadError) as e:
+        load_weights(model, folder)
+    msg = str(e.value)
+    for piece in ("model.layers.1.self_attn.k_proj.bias", "lm_head.weight", "model.layers.9.extra.weight",
+                  "model.layers.0.mlp.gate_proj.weight expected [512, 192] got [512, 100]", "model.norm.weight is"):
+        assert piece in msg, piece
+    r = e.value.report
+    assert len(r.missing) == 2 and len(r.unexpected) == 1 and len(r.wrong_shape) == 1 and len(r.wrong_dtype) == 1
+    assert not model.bound, "a failed load must bind nothing"
+
+
+def test_tied_head_tolerates_a_redundant_lm_head_and_non_strict_tolerates_extras(tmp_path):
+    folder = write_random_model(ARCH, tiny_config("a"), 0, str(tmp_path / "m"), "float32")
+    rewrite(folder, lambda t: t.update({"lm_head.weight": t["model.embed_tokens.weight"].clone()}))
+    model = cpu_model("a")
+    report = load_weights(model, folder)
+    assert report.ignored == ["lm_head.weight"] and model.bound
+    assert model.head.weight is model.embedding.table
+    rewrite(folder, lambda t: t.update({"something.else": torch.zeros(1)}))
+    with pytest.raises(WeightLoadError, match="something.else"):
+        load_weights(cpu_model("a"), folder)
+    assert "something.else" in load_weights(cpu_model("a"), folder, strict=False).ignored
+
+
+@pytest.mark.parametrize("storage", ["float32", "bfloat16"])
+@pytest.mark.parametrize("compute", [torch.float32, torch.bfloat16])
+def test_dtype_policy(tmp_path, storage, compute):
+    folder = write_random_model(ARCH, tiny_config("b"), 1, str(tmp_path / "m"), storage)
+    model = cpu_model("b", compute)
+    load_weights(model, folder)
+    attn = model.blocks[0].mixer
+    assert attn.w_qkv.dtype == compute and attn.w_o.dtype == compute and model.embedding.table.dtype == compute
+    assert attn.b_qkv.dtype == torch.float32 and model.final_norm.weight.dtype == torch.float32
+    assert attn.w_qkv.shape == ((6 + 2 * 2) * 32, 192) and model.blocks[0].feed_forward.w_gate_up.shape == (1024, 192)
+    # values are the stored ones, rounded at most once
+    stored = SafetensorsFile(os.path.join(folder, "model.safetensors")).tensor("model.layers.0.self_attn.o_proj.weight")
+    assert torch.equal(attn.w_o, stored.to(compute))
+
+
+def test_random_mode_is_seeded_and_has_the_stated_distributions(tmp_path):
+    a = write_random_model(ARCH, tiny_config("b"), 5, str(tmp_path / "a"), "float32")
+    b = write_random_model(ARCH, tiny_config("b"), 5, str(tmp_path / "b"), "float32")
+    c = write_random_model(ARCH, tiny_config("b"), 6, str(tmp_path / "c"), "float32")
+    fa, fb, fc = (SafetensorsFile(os.path.join(x, "model.safetensors")) for x in (a, b, c))
+    assert all(torch.equal(fa.tensor(n), fb.tensor(n)) for n in fa.names())
+    assert not torch.equal(fa.tensor("model.embed_tokens.weight"), fc.tensor("model.embed_tokens.weight"))
+    w = fa.tensor("model.layers.0.mlp.up_proj.weight")
+    assert abs(float(w.mean())) < 2e-3 and abs(float(w.std()) - 0.02) < 2e-3
+    n = torch.cat([fa.tensor(k) for k in fa.names() if k.endswith("norm.weight")])
+    assert abs(float(n.mean()) - 1.0) < 0.03 and abs(float(n.std()) - 0.1) < 0.03
+    bias = fa.tensor("model.layers.2.self_attn.q_proj.bias")
+    assert 0.01 < float(bias.std()) < 0.03
+    cfg = json.load(open(os.path.join(a, "config.json")))
+    assert cfg["architectures"] == ["Qwen2ForCausalLM"] and Qwen2Config.from_dict(cfg) == Qwen2Config.from_dict(
+        dict(tiny_config("b").to_dict()))
+    # 39 tensors: 12 per layer, embedding, final norm, head
+    assert len(fa.names()) == 3 * 12 + 3
+
+
+def test_sharded_folder_through_index(tmp_path):
+    folder = write_random_model(ARCH, tiny_config("a"), 0, str(tmp_path / "m"), "float32")
+    f = SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    names = f.names()
+    half = len(names) // 2
+    save_file({n: f.tensor(n).clone() for n in names[:half]}, os.path.join(folder, "s1.safetensors"))
+    save_file({n: f.tensor(n).clone() for n in names[half:]}, os.path.join(folder, "s2.safetensors"))
+    os.remove(os.path.join(folder, "model.safetensors"))
+    index = {"weight_map": {n: ("s1.safetensors" if i < half else "s2.safetensors") for i, n in enumerate(names)}}
+    json.dump(index, open(os.path.join(folder, "model.safetensors.index.json"), "w"))
+    assert load_weights(cpu_model("a"), folder).ok
+    index["weight_map"][names[0]] = "../s1.safetensors"
+    json.dump(index, open(os.path.join(folder, "model.safetensors.index.json"), "w"))
+    with pytest.raises(SafetensorsError, match="leaves the model folder"):
+        open_model_files(folder)
