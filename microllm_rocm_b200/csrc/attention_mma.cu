@@ -1,0 +1,432 @@
+// Tensor-core attention over the paged bf16 cache, for prompt portions and decoded tokens
+// alike.  Compiled per head size (-DHEAD_DIM=...).
+//
+// The unit of work is a ROW TILE: 16 rows of one (sequence, kv head), a row being one
+// (new token, query head of the group).  A decoded token contributes G = NH/NKV rows, a
+// prompt portion n*G; every row carries its own position, so one causal/window rule covers
+// both.  A warp walks the keys lo..hi of its tile 16 at a time:
+//     S = Q K^T   (mma.sync m16n8k16, bf16 in, fp32 out; Q from shared memory, K straight
+//                  from the page into registers with 16-byte loads)
+//     online softmax in fp32 (running max and sum per row, base-2 exponentials)
+//     O += P V    (P rounded to bf16 as the tensor-core operand; V straight from the page)
+// K/V are read once per row tile and shared by all query heads of the group; the reference
+// re-reads them per query head and keeps every score in shared memory
+// (src/ops/hip/basic_kernels.hip:1035-1083, limit 4096 keys at src/ops/ops.cpp:1592).
+//
+// Two launch shapes of the same warp routine:
+//   prefill  one CTA = 4 warps = 4 consecutive row tiles; no key split
+//   decode   one CTA = one row tile, its 4 warps take every 4th key tile and are merged in
+//            shared memory; the keys are further split over gridDim.z CTAs whose partial
+//            results (normalised output + log-sum-exp, in scratch memory) a second kernel merges.
+//
+// Operand layout trick: mma.sync only needs A and B to agree on which contraction index a
+// register holds.  Thread t of a quad therefore loads 8 CONSECUTIVE head elements of a key
+// (one 16-byte load) and uses them as the fragments of two k-steps; Q is read from shared
+// memory with the same permutation.  For V the output columns are permuted instead.
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=<multiple of 32, at most 256>"
+#endif
+
+using namespace mlb;
+
+MLB_DEFINE_LAST_ERROR()
+
+namespace {
+
+constexpr int D = HEAD_DIM;
+static_assert(D % 32 == 0 && D >= 32 && D <= 256, "HEAD_DIM must be a multiple of 32 in 32..256");
+constexpr int KCHUNKS = D / 32;             // 32 head elements per chunk of the QK^T contraction
+constexpr int VBLOCKS = (D + 63) / 64;      // 64 output elements per block of PV
+constexpr int NB_O = VBLOCKS * 8;           // 8-wide output column blocks
+constexpr int WARPS = 4;
+constexpr int Q_STRIDE = D + 32;            // bf16 elements; +64 bytes keeps 16-byte row loads conflict free
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct FaParams {
+    const __nv_bfloat16* q;         // [T, NH*D]
+    const __nv_bfloat16* pages;     // [num_pages, 2, NKV, page_size, D]
+    __nv_bfloat16* out;             // [T, NH*D]
+    float* part_o;                  // [T*NH, splits, D]   scratch, decode with splits > 1
+    float* part_lse;                // [T*NH, splits]
+    const int* seq_starts;          // [A+1] first flat token of each sequence
+    const int* seq_pos0;            // [A]   tokens cached before this step
+    const int* block_table;         // [A, max_blocks]
+    const int* work;                // [num_work, 2] (sequence, first row tile)
+    int max_blocks, num_pages, page_size;
+    int num_heads, num_kv_heads, group;
+    int window;
+    float scale_log2;               // softmax scale * log2(e)
+    int splits;
+    int* error_flag;
+};
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+__device__ __forceinline__ uint4 load16(const __nv_bfloat16* p) {
+    return __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+struct RowState {
+    float m[2];            // running maximum (base-2 scaled) of rows g and g+8
+    float l[2];            // this thread's share of the running sum
+    float o[NB_O][4];      // output accumulators; column permutation: see store_rows()
+};
+
+// Rows of a tile: row r (0..15) is flat row row0 + r of the (sequence, kv head) row space,
+// token = row / group, head-in-group = row % group.
+struct TileGeometry {
+    int seq, kvh, row0, n_new, pos0, token0;   // token0: flat index of the sequence's first new token
+    __device__ __forceinline__ int token_of(int r, int group) const { return (row0 + r) / group; }
+};
+
+// Keys [tile_begin, tile_end) in units of 16, visiting every `stride`-th starting at
+// tile_begin + first; hi_tile is the last position any row of the tile may see.  q_s: this tile's queries, [16][Q_STRIDE] bf16 in shared memory.
+__device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& geo, const __nv_bfloat16* q_s,
+                                       int tile_begin, int tile_end, int first, int stride, int hi_tile,
+                                       RowState& st) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    int pos_row[2], lo_row[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int tok = geo.token_of(g + 8 * i, p.group);
+        if (tok < geo.n_new) {
+            pos_row[i] = geo.pos0 + tok;
+            lo_row[i] = (p.window > 0 && pos_row[i] - p.window + 1 > 0) ? pos_row[i] - p.window + 1 : 0;
+        } else {
+            pos_row[i] = -1;            // padding row: sees nothing
+            lo_row[i] = 0;
+        }
+    }
+    const int* table = p.block_table + (size_t)geo.seq * p.max_blocks;
+    const size_t page_stride = (size_t)2 * p.num_kv_heads * p.page_size * D;
+    const size_t v_off = (size_t)p.num_kv_heads * p.page_size * D;
+
+    for (int kt = tile_begin + first; kt < tile_end; kt += stride) {
+        const int base = kt * 16;
+        const int block = base / p.page_size;
+        const int page = block < p.max_blocks ? table[block] : -1;
+        if (page < 0 || page >= p.num_pages) {
+            if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 3);
+            continue;
+        }
+        const __nv_bfloat16* kbase = p.pages + (size_t)page * page_stride +
+                                     ((size_t)geo.kvh * p.page_size + (base % p.page_size)) * D;
+        const __nv_bfloat16* vbase = kbase + v_off;
+
+        // ---- S = Q K^T for 16 keys -----------------------------------------------------------
+        float s[2][4];
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[nb][e] = 0.0f;
+        uint4 kreg[2][KCHUNKS];
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+            for (int c = 0; c < KCHUNKS; ++c) kreg[nb][c] = load16(kbase + (size_t)(nb * 8 + g) * D + c * 32 + t * 8);
+#pragma unroll
+        for (int c = 0; c < KCHUNKS; ++c) {
+            const uint4 qa = *reinterpret_cast<const uint4*>(q_s + g * Q_STRIDE + c * 32 + t * 8);
+            const uint4 qb = *reinterpret_cast<const uint4*>(q_s + (g + 8) * Q_STRIDE + c * 32 + t * 8);
+#pragma unroll
+            for (int nb = 0; nb < 2; ++nb) {
+                mma_bf16(s[nb], qa.x, qb.x, qa.y, qb.y, kreg[nb][c].x, kreg[nb][c].y);
+                mma_bf16(s[nb], qa.z, qb.z, qa.w, qb.w, kreg[nb][c].z, kreg[nb][c].w);
+            }
+        }
+
+        // ---- masks and the running softmax -----------------------------------------------------
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = e >> 1;
+                const int key = base + nb * 8 + 2 * t + (e & 1);
+                const bool ok = key >= lo_row[i] && key <= pos_row[i];
+                s[nb][e] = ok ? s[nb][e] * p.scale_log2 : -INFINITY;
+                mx[i] = fmaxf(mx[i], s[nb][e]);
+            }
+        float corr[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float m_new = fmaxf(st.m[i], mx[i]);
+            corr[i] = (m_new == -INFINITY) ? 1.0f : exp2f(st.m[i] - m_new);
+            st.m[i] = m_new;
+        }
+        float rowsum[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = e >> 1;
+                const float pv = (s[nb][e] == -INFINITY) ? 0.0f : exp2f(s[nb][e] - st.m[i]);
+                s[nb][e] = pv;
+                rowsum[i] += pv;
+            }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) st.l[i] = st.l[i] * corr[i] + rowsum[i];
+#pragma unroll
+        for (int nbo = 0; nbo < NB_O; ++nbo) {
+            st.o[nbo][0] *= corr[0]; st.o[nbo][1] *= corr[0];
+            st.o[nbo][2] *= corr[1]; st.o[nbo][3] *= corr[1];
+        }
+        const unsigned pa0 = pack_bf16(s[0][0], s[0][1]);     // row g,   keys 2t, 2t+1
+        const unsigned pa1 = pack_bf16(s[0][2], s[0][3]);     // row g+8
+        const unsigned pa2 = pack_bf16(s[1][0], s[1][1]);     // row g,   keys 8+2t, 9+2t
+        const unsigned pa3 = pack_bf16(s[1][2], s[1][3]);     // row g+8
+
+        // ---- O += P V: this thread reads keys 2t, 2t+1, 2t+8, 2t+9, eight elements each ------------
+#pragma unroll
+        for (int vb = 0; vb < VBLOCKS; ++vb) {
+            const int col = vb * 64 + g * 8;
+            uint4 v[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+            if (col < D) {
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const int key = 2 * t + (r & 1) + 8 * (r >> 1);
+                    // slots past the tile's last position were never written by this sequence: their
+                    // probability is zero, and zero times stale memory must stay zero
+                    if (base + key <= hi_tile) v[r] = load16(vbase + (size_t)key * D + col);
+                }
+            }
+            const unsigned* v0 = reinterpret_cast<const unsigned*>(&v[0]);
+            const unsigned* v1 = reinterpret_cast<const unsigned*>(&v[1]);
+            const unsigned* v2 = reinterpret_cast<const unsigned*>(&v[2]);
+            const unsigned* v3 = reinterpret_cast<const unsigned*>(&v[3]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const unsigned sel = (j & 1) ? 0x7632u : 0x5410u;       // high or low bf16 of both words
+                const unsigned b0 = __byte_perm(v0[j >> 1], v1[j >> 1], sel);
+                const unsigned b1 = __byte_perm(v2[j >> 1], v3[j >> 1], sel);
+                mma_bf16(st.o[vb * 8 + j], pa0, pa1, pa2, pa3, b0, b1);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void init_state(RowState& st) {
+    st.m[0] = st.m[1] = -INFINITY;
+    st.l[0] = st.l[1] = 0.0f;
+#pragma unroll
+    for (int nbo = 0; nbo < NB_O; ++nbo)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) st.o[nbo][e] = 0.0f;
+}
+
+// Accumulator o[vb*8 + j][e] of thread (g, t) is output row g (e < 2) or g+8, element
+// vb*64 + (2t + (e & 1)) * 8 + j: the thread that fed column n of B read elements n*8 + j.
+__device__ __forceinline__ int out_dim(int nbo, int e, int t) {
+    return (nbo >> 3) * 64 + (2 * t + (e & 1)) * 8 + (nbo & 7);
+}
+
+__device__ __forceinline__ void load_q_tile(const FaParams& p, const TileGeometry& geo, __nv_bfloat16* q_s, int lane) {
+    // 16 rows x D elements, 16 bytes per load
+    constexpr int VEC_PER_ROW = D / 8;
+    for (int i = lane; i < 16 * VEC_PER_ROW; i += 32) {
+        const int r = i / VEC_PER_ROW, c = (i % VEC_PER_ROW) * 8;
+        const int tok = geo.token_of(r, p.group);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (tok < geo.n_new) {
+            const int head = geo.kvh * p.group + (geo.row0 + r) % p.group;
+            v = load16(p.q + ((size_t)(geo.token0 + tok) * p.num_heads + head) * D + c);
+        }
+        *reinterpret_cast<uint4*>(q_s + r * Q_STRIDE + c) = v;
+    }
+}
+
+__device__ __forceinline__ bool geometry(const FaParams& p, int work_index, int tile_offset, int kvh, TileGeometry& geo) {
+    geo.seq = p.work[2 * work_index];
+    const int tile = p.work[2 * work_index + 1] + tile_offset;
+    geo.kvh = kvh;
+    geo.token0 = p.seq_starts[geo.seq];
+    geo.n_new = p.seq_starts[geo.seq + 1] - geo.token0;
+    geo.pos0 = p.seq_pos0[geo.seq];
+    geo.row0 = tile * 16;
+    return geo.row0 < geo.n_new * p.group;
+}
+
+// ---------------------------------------------------------------------------------- prefill
+__global__ void __launch_bounds__(WARPS * 32) fa_prefill_kernel(FaParams p) {
+    __shared__ __align__(16) __nv_bfloat16 q_s[WARPS][16 * Q_STRIDE];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    TileGeometry geo;
+    if (!geometry(p, blockIdx.x, warp, blockIdx.y, geo)) return;
+    load_q_tile(p, geo, q_s[warp], lane);
+    __syncwarp();
+    const int first_tok = geo.token_of(0, p.group);
+    const int last_tok = min(geo.token_of(15, p.group), geo.n_new - 1);
+    const int first_pos = geo.pos0 + first_tok, last_pos = geo.pos0 + last_tok;
+    const int lo = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
+    RowState st;
+    init_state(st);
+    attend(p, geo, q_s[warp], lo / 16, last_pos / 16 + 1, 0, 1, last_pos, st);
+    // normalise and write through shared memory so that rows leave as whole 16-byte pieces
+    float inv[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float l = st.l[i];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        inv[i] = l > 0.0f ? 1.0f / l : 0.0f;
+    }
+    __syncwarp();
+    __nv_bfloat16* o_s = q_s[warp];
+#pragma unroll
+    for (int nbo = 0; nbo < NB_O; ++nbo)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int dim = out_dim(nbo, e, t);
+            if (dim < D) o_s[(g + 8 * (e >> 1)) * Q_STRIDE + dim] = __float2bfloat16_rn(st.o[nbo][e] * inv[e >> 1]);
+        }
+    __syncwarp();
+    constexpr int VEC_PER_ROW = D / 8;
+    for (int i = lane; i < 16 * VEC_PER_ROW; i += 32) {
+        const int r = i / VEC_PER_ROW, c = (i % VEC_PER_ROW) * 8;
+        const int tok = geo.token_of(r, p.group);
+        if (tok >= geo.n_new) continue;
+        const int head = geo.kvh * p.group + (geo.row0 + r) % p.group;
+        *reinterpret_cast<uint4*>(p.out + ((size_t)(geo.token0 + tok) * p.num_heads + head) * D + c) =
+            *reinterpret_cast<const uint4*>(o_s + r * Q_STRIDE + c);
+    }
+}
+
+// ---------------------------------------------------------------------------------- decode
+__global__ void __launch_bounds__(WARPS * 32) fa_decode_kernel(FaParams p) {
+    __shared__ __align__(16) __nv_bfloat16 q_s[16 * Q_STRIDE];
+    __shared__ float merge_o[16][D];
+    __shared__ float merge_m[16], merge_l[16];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    TileGeometry geo;
+    if (!geometry(p, blockIdx.x, 0, blockIdx.y, geo)) return;          // uniform over the CTA
+    if (warp == 0) load_q_tile(p, geo, q_s, lane);
+    __syncthreads();
+    const int first_tok = geo.token_of(0, p.group);
+    const int last_tok = min(geo.token_of(15, p.group), geo.n_new - 1);
+    const int first_pos = geo.pos0 + first_tok, last_pos = geo.pos0 + last_tok;
+    const int lo = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
+    int tile_begin = lo / 16, tile_end = last_pos / 16 + 1;
+    if (p.splits > 1) {                       // this CTA's even share of the sequence's key tiles
+        const int per_split = (tile_end - tile_begin + p.splits - 1) / p.splits;
+        tile_begin += (int)blockIdx.z * per_split;
+        tile_end = min(tile_end, tile_begin + per_split);
+    }
+    RowState st;
+    init_state(st);
+    attend(p, geo, q_s, tile_begin, tile_end, warp, WARPS, last_pos, st);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 1);
+        st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 2);
+    }
+    // merge the four warps one after the other into shared memory
+    for (int w = 0; w < WARPS; ++w) {
+        if (warp == w) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = g + 8 * i;
+                const float m_old = w == 0 ? -INFINITY : merge_m[r];
+                const float l_old = w == 0 ? 0.0f : merge_l[r];
+                const float m_new = fmaxf(m_old, st.m[i]);
+                const float c_old = (m_new == -INFINITY || m_old == -INFINITY) ? 0.0f : exp2f(m_old - m_new);
+                const float c_me = (m_new == -INFINITY || st.m[i] == -INFINITY) ? 0.0f : exp2f(st.m[i] - m_new);
+#pragma unroll
+                for (int nbo = 0; nbo < NB_O; ++nbo)
+#pragma unroll
+                    for (int e2 = 0; e2 < 2; ++e2) {
+                        const int dim = out_dim(nbo, 2 * i + e2, t);
+                        if (dim < D) {
+                            const float prev = w == 0 ? 0.0f : merge_o[r][dim];
+                            merge_o[r][dim] = prev * c_old + st.o[nbo][2 * i + e2] * c_me;
+                        }
+                    }
+                __syncwarp();
+                if (t == 0) { merge_m[r] = m_new; merge_l[r] = l_old * c_old + st.l[i] * c_me; }
+            }
+        }
+        __syncthreads();
+    }
+    // rows out: final values, or this split's normalised share and its log-sum-exp
+    for (int i = threadIdx.x; i < 16 * D; i += WARPS * 32) {
+        const int r = i / D, dim = i % D;
+        const int tok = geo.token_of(r, p.group);
+        if (tok >= geo.n_new) continue;
+        const int head = geo.kvh * p.group + (geo.row0 + r) % p.group;
+        const size_t row = (size_t)(geo.token0 + tok) * p.num_heads + head;
+        const float l = merge_l[r];
+        const float val = l > 0.0f ? merge_o[r][dim] / l : 0.0f;
+        if (p.splits > 1) {
+            p.part_o[(row * p.splits + blockIdx.z) * D + dim] = val;
+            if (dim == 0) p.part_lse[row * p.splits + blockIdx.z] = l > 0.0f ? merge_m[r] + log2f(l) : -INFINITY;
+        } else {
+            p.out[row * D + dim] = __float2bfloat16_rn(val);
+        }
+    }
+}
+
+// out[row] = sum_s w_s O_s / sum_s w_s,  w_s = 2^(lse_s - max lse)
+__global__ void fa_merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                       __nv_bfloat16* __restrict__ out, int splits) {
+    const size_t row = blockIdx.x;
+    float mx = -INFINITY;
+    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_lse[row * splits + s]);
+    for (int dim = threadIdx.x; dim < D; dim += blockDim.x) {
+        float acc = 0.0f, wsum = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float lse = part_lse[row * splits + s];
+            if (lse == -INFINITY) continue;
+            const float w = exp2f(lse - mx);
+            wsum += w;
+            acc += w * part_o[(row * splits + s) * D + dim];
+        }
+        out[row * D + dim] = __float2bfloat16_rn(wsum > 0.0f ? acc / wsum : 0.0f);
+    }
+}
+
+}  // namespace
+
+MLB_EXPORT int mlb_fa_head_dim() { return D; }
+
+// mode 0: prefill shape (work items name the first of 4 row tiles); mode 1: decode shape
+// (one row tile per work item, keys split `splits` ways; scratch needed when splits > 1).
+MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* out, float* part_o, float* part_lse,
+                                       const int* seq_starts, const int* seq_pos0, const int* block_table,
+                                       const int* work, int num_work, int max_blocks, int num_pages, int page_size,
+                                       int num_heads, int num_kv_heads, int window, float scale, int mode, int splits,
+                                       int total_rows, int* error_flag, cudaStream_t stream) {
+    if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
+        return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: bad head counts %d/%d", num_heads, num_kv_heads);
+    if (page_size <= 0 || page_size % 16 != 0)
+        return fail(MLB_UNSUPPORTED_SIZE, "paged_attention_mma: page_size %d must be a multiple of 16", page_size);
+    if (num_pages <= 0 || max_blocks <= 0 || window < 0 || num_work < 0)
+        return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: bad cache geometry");
+    if (mode == 1 && (splits < 1 || splits > 65535 || (splits > 1 && (!part_o || !part_lse))))
+        return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: bad split arguments");
+    if (num_work == 0) return MLB_OK;
+    FaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, part_o, part_lse, seq_starts,
+               seq_pos0, block_table, work, max_blocks, num_pages, page_size, num_heads, num_kv_heads,
+               num_heads / num_kv_heads, window, scale * LOG2E, mode == 1 ? splits : 1, error_flag};
+    if (mode == 0) {
+        fa_prefill_kernel<<<dim3(num_work, num_kv_heads, 1), WARPS * 32, 0, stream>>>(p);
+        return check_launch("fa_prefill");
+    }
+    fa_decode_kernel<<<dim3(num_work, num_kv_heads, splits), WARPS * 32, 0, stream>>>(p);
+    int status = check_launch("fa_decode");
+    if (status != MLB_OK || splits == 1) return status;
+    fa_merge_splits_kernel<<<total_rows, D >= 128 ? 128 : 64, 0, stream>>>(part_o, part_lse, (__nv_bfloat16*)out, splits);
+    return check_launch("fa_merge_splits");
+}

@@ -164,3 +164,26 @@ MLB_EXPORT int mlb_cast_f32_bf16(const float* in, void* out, long long n, cudaSt
     cast_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(in, (__nv_bfloat16*)out, (size_t)n);
     return check_launch("cast_f32_bf16");
 }
+
+// ------------------------------------------------------------------ decode bookkeeping
+// After a captured decode step: every sequence holds one token more.  The selected tokens
+// already sit in the token buffer (the sampler wrote them there); this advances the
+// positions, the per-sequence extents and the per-request draw counters on the device, so
+// that the same captured step can run again without the host touching its inputs.
+__global__ void decode_advance_kernel(int* __restrict__ positions, int* __restrict__ seq_pos0,
+                                      int* __restrict__ seq_lens, long long* __restrict__ draw, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    positions[i] += 1;
+    seq_pos0[i] += 1;
+    seq_lens[i] += 1;
+    draw[i] += 1;
+}
+
+MLB_EXPORT int mlb_decode_advance(int* positions, int* seq_pos0, int* seq_lens, long long* draw, int n,
+                                  cudaStream_t stream) {
+    if (n < 0) return fail(MLB_INVALID_ARGUMENT, "decode_advance: negative size");
+    if (n == 0) return MLB_OK;
+    decode_advance_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, seq_pos0, seq_lens, draw, n);
+    return check_launch("decode_advance");
+}

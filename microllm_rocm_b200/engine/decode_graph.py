@@ -1,0 +1,217 @@
+"""Steady decoding as one captured CUDA graph whose inputs live on the device.
+
+When every request of a step brings exactly one token (its last selected one), the step's
+launches are always the same ~10 per layer; issuing them one by one from Python costs more
+than the kernels take.  A `DecodeGraph` holds the step's metadata in fixed device buffers,
+captures model forward + token selection + bookkeeping once, and replays it: the selected
+token is written where the next replay's embedding reads it, positions and lengths advance
+on the device, and the host only (a) makes sure each request has a page for its next token
+and refreshes the device block table when one was added, and (b) reads the selected tokens.
+
+The reference keeps tokens on the device for greedy decoding in the same spirit
+(src/inference/generator.cpp:108-126: argmax writes into a device history that is the next
+step's input) but launches every kernel of every step from the host.
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from ..parts.base import StepContext
+from ..sampling.config import GenerationConfig
+from .step import Engine, OutOfPages, StepError
+
+
+def graph_capable(engine: Engine) -> bool:
+    return all(getattr(b.mixer, "graph_safe", False) for b in engine.model.blocks)
+
+
+def _round_up_pow2(n: int) -> int:
+    return 1 << max(0, (int(n) - 1).bit_length())
+
+
+class DecodeGraph:
+    def __init__(self, engine: Engine, batch: int, table_widths: Dict[str, int]):
+        self.engine, self.batch = engine, batch
+        self.widths = dict(table_widths)
+        dev = engine.device
+        A = batch
+        cursor = 0
+
+        def take(n, align=1):
+            nonlocal cursor
+            cursor = -(-cursor // align) * align
+            view = (cursor, cursor + n)
+            cursor += n
+            return view
+
+        self._s = {name: take(A) for name in ("tokens", "positions", "token_seq", "seq_pos0", "seq_lens", "slots",
+                                              "logit_rows", "temperature", "top_k")}
+        self._s["seq_starts"] = take(A + 1)
+        self._s["seed"] = take(2 * A, align=2)
+        self._s["draw"] = take(2 * A, align=2)
+        self._dynamic_end = cursor
+        self._tables = {g: take(A * w) for g, w in self.widths.items()}
+        self.total = cursor
+        self.host = torch.zeros(self.total, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.zeros(self.total, dtype=torch.int32, device=dev)
+        self.out_host = torch.zeros(A + 1, dtype=torch.int32, pin_memory=True)     # tokens, then the error flag
+        self._upload_done: Optional[torch.cuda.Event] = None
+        d = lambda name: self.dev[self._s[name][0]:self._s[name][1]]
+        self.temperature = d("temperature").view(torch.float32)
+        self.top_k = d("top_k")
+        self.seed = d("seed").view(torch.int64)
+        self.draw = d("draw").view(torch.int64)
+        self.ctx = StepContext(
+            num_tokens=A, num_seqs=A, token_ids=d("tokens"), positions=d("positions"), token_seq=d("token_seq"),
+            seq_starts=d("seq_starts"), seq_pos0=d("seq_pos0"), seq_lens=d("seq_lens"),
+            block_tables={g: self.dev[v[0]:v[1]].view(A, self.widths[g]) for g, v in self._tables.items()},
+            state_slots=d("slots"), logit_rows=d("logit_rows"), error_flag=engine.error_flag,
+            seq_starts_host=list(range(A + 1)), seq_pos0_host=[], state_slots_host=[], max_new_tokens=1, max_seq_len=1)
+        self.views = engine.cache_views(self.ctx)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.requests: List[Hashable] = []
+        self._table_state: Dict[str, List[tuple]] = {}
+        self.replays = 0
+
+    # ------------------------------------------------------------------ host -> device state
+    def _h(self, name):
+        a, b = self._s[name]
+        return self.host.numpy()[a:b]
+
+    def load(self, requests: Sequence[Hashable], tokens: Sequence[int], lengths: Sequence[int],
+             configs: Sequence[GenerationConfig], draws: Sequence[int]) -> None:
+        """Set the device state: request i feeds `tokens[i]` at position `lengths[i]`."""
+        A = self.batch
+        if len(requests) != A:
+            raise StepError("a decode graph serves exactly the batch size it was built for")
+        self._wait_upload()
+        cache = self.engine.cache
+        self.requests = list(requests)
+        self._h("tokens")[:] = tokens
+        self._h("positions")[:] = lengths
+        self._h("token_seq")[:] = np.arange(A)
+        self._h("seq_pos0")[:] = lengths
+        self._h("seq_lens")[:] = np.asarray(lengths) + 1
+        self._h("slots")[:] = [cache.slot(q) for q in requests]
+        self._h("logit_rows")[:] = np.arange(A)
+        self._h("seq_starts")[:] = np.arange(A + 1)
+        self._h("temperature").view(np.float32)[:] = [0.0 if c.greedy else c.temperature for c in configs]
+        self._h("top_k")[:] = [c.top_k for c in configs]
+        self._h("seed").view(np.int64)[:] = [c.seed for c in configs]
+        self._h("draw").view(np.int64)[:] = list(draws)
+        self._fill_tables()
+        self.dev.copy_(self.host, non_blocking=True)
+        self._mark_upload()
+        self.ctx.max_seq_len = max(lengths) + 1
+
+    def _mark_upload(self) -> None:
+        if self._upload_done is None:
+            self._upload_done = torch.cuda.Event()
+        self._upload_done.record()
+
+    def _wait_upload(self) -> None:
+        """The staging buffer may be rewritten only once the last copy out of it has run."""
+        if self._upload_done is not None:
+            self._upload_done.synchronize()
+
+    def _fill_tables(self) -> bool:
+        """Write the requests' block tables into the staging buffer; True if they changed."""
+        cache = self.engine.cache
+        arr = self.host.numpy()
+        changed = False
+        for g, (a, b) in self._tables.items():
+            state = [tuple(cache.requests[q].tables[g]) for q in self.requests]
+            if self._table_state.get(g) == state:
+                continue
+            changed = True
+            self._table_state[g] = state
+            rows = cache.block_table(g, self.requests, self.widths[g])
+            arr[a:b] = np.asarray(rows, dtype=np.int32).reshape(-1)
+        return changed
+
+    def refresh_tables(self) -> None:
+        """After the host reserved pages (or a window released some): bring the device tables up
+        to date.  Only the table region travels."""
+        cache = self.engine.cache
+        if all(self._table_state.get(g) == [tuple(cache.requests[q].tables[g]) for q in self.requests]
+               for g in self._tables):
+            return
+        self._wait_upload()
+        if self._fill_tables():
+            a = min(v[0] for v in self._tables.values())
+            self.dev[a:self.total].copy_(self.host[a:self.total], non_blocking=True)
+            self._mark_upload()
+
+    def fits(self, requests: Sequence[Hashable]) -> bool:
+        cache = self.engine.cache
+        return all(len(cache.requests[q].tables[g]) <= w for g, w in self.widths.items() for q in requests)
+
+    # ------------------------------------------------------------------ capture and replay
+    def _body(self) -> None:
+        logits = self.engine.model.forward(self.ctx, self.views)
+        ops.sample_rows(logits, self.temperature, self.top_k, self.seed, self.draw, self.ctx.token_ids)
+        ops.decode_advance(self.ctx.positions, self.ctx.seq_pos0, self.ctx.seq_lens, self.draw)
+
+    def capture(self) -> None:
+        """Run the step once eagerly (plans launches, warms libraries), then record it.  The
+        eager run really executes: callers `load()` the true state again afterwards."""
+        side = torch.cuda.Stream(device=self.engine.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._body()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        from ..kernels.build import LaunchCounter
+        before = LaunchCounter.own
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._body()
+        self.launches_per_replay = LaunchCounter.own - before      # kernels of this library in the graph
+
+    def replay(self) -> None:
+        self.graph.replay()
+        self.replays += 1
+
+    def read_tokens(self) -> List[int]:
+        """The tokens the last replay selected (one device -> host copy, synchronising)."""
+        A = self.batch
+        self.out_host[:A].copy_(self.ctx.token_ids, non_blocking=True)
+        self.out_host[A:].copy_(self.engine.error_flag, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        host = self.out_host.tolist()
+        if host[A]:
+            self.engine.error_flag.zero_()
+            raise StepError(f"a kernel met a token without a valid page (code {host[A]})")
+        return host[:A]
+
+
+class DecodeGraphPool:
+    """Captured decode steps by batch size and table width; built on first use."""
+
+    def __init__(self, engine: Engine):
+        self.engine = engine
+        self.graphs: Dict[tuple, DecodeGraph] = {}
+        self.captures = 0
+
+    def get(self, requests: Sequence[Hashable], headroom_tokens: int = 0) -> DecodeGraph:
+        cache = self.engine.cache
+        widths = {}
+        for g in cache.groups:
+            need = max(cache.blocks_for(cache.length(q) + 1 + headroom_tokens) for q in requests)
+            need = max(need, max(len(cache.requests[q].tables[g]) for q in requests))
+            widths[g] = max(8, _round_up_pow2(need))
+        key = (len(requests), tuple(sorted(widths.items())))
+        graph = self.graphs.get(key)
+        if graph is None:
+            graph = DecodeGraph(self.engine, len(requests), widths)
+            self.graphs[key] = graph
+        return graph
+
+    def ensure_captured(self, graph: DecodeGraph) -> None:
+        if graph.graph is None:
+            graph.capture()
+            self.captures += 1

@@ -15,6 +15,7 @@ import torch
 
 from ..sampling.config import GenerationConfig
 from ..sampling.sampler import Sampler
+from .decode_graph import DecodeGraph, DecodeGraphPool, graph_capable
 from .loading import DEFAULT_PAGE_SIZE, load_engine
 from .scheduler import Request, Scheduler, StepPlan
 from .step import Engine, StepEntry, StepError
@@ -23,7 +24,7 @@ from .step import Engine, StepEntry, StepError
 class LLM:
     def __init__(self, model: Union[str, Engine], dtype="bfloat16", page_size: int = DEFAULT_PAGE_SIZE,
                  num_pages: Optional[int] = None, max_tokens: Optional[int] = None, max_tokens_per_step: int = 2048,
-                 max_seqs: int = 64, device: Optional[str] = None):
+                 max_seqs: int = 64, device: Optional[str] = None, cuda_graphs: bool = True):
         if isinstance(model, Engine):
             self.engine = model
         else:
@@ -34,6 +35,9 @@ class LLM:
                                    max_tokens_per_step=max_tokens_per_step,
                                    max_seqs=min(max_seqs, self.engine.cache.max_requests))
         self.sampler = Sampler(self.engine.device)
+        self.graphs = DecodeGraphPool(self.engine) if cuda_graphs and graph_capable(self.engine) else None
+        self._graph: Optional[DecodeGraph] = None       # the captured step whose device state is current
+        self.graph_steps = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -58,6 +62,10 @@ class LLM:
             if self.scheduler.has_work() and not plan.preempted:
                 raise StepError("the scheduler has work but could plan nothing: the page pool is too small")
             return []
+        if self.graphs is not None and not plan.preempted and all(
+                e.count == 1 and e.wants_logits and e.begin >= len(e.request.prompt) for e in plan.entries):
+            return self._graph_step(plan)
+        self._graph = None
         entries = [StepEntry(e.request.id, e.request.tokens(e.begin, e.begin + e.count),
                              [e.count - 1] if e.wants_logits else []) for e in plan.entries]
         logits = self.engine.step(entries)
@@ -74,6 +82,37 @@ class LLM:
             self.engine.error_flag.zero_()
             raise StepError(f"a kernel met a token without a valid page (code {host[R]})")
         return self.scheduler.update(plan, host[:R])
+
+    def _graph_step(self, plan: StepPlan) -> List[Request]:
+        """A step in which every request brings its one last-selected token: replay the captured
+        decode step instead of launching it kernel by kernel."""
+        ids = [e.request.id for e in plan.entries]
+        graph = self._graph
+        if graph is None or graph.requests != ids or not graph.fits(ids):
+            remaining = max(e.request.config.max_new_tokens - len(e.request.generated) for e in plan.entries)
+            graph = self.graphs.get(ids, headroom_tokens=remaining)
+            state = ([e.request.token(e.begin) for e in plan.entries], [e.begin for e in plan.entries],
+                     [e.request.config for e in plan.entries], [len(e.request.generated) for e in plan.entries])
+            graph.load(ids, *state)
+            if graph.graph is None:
+                self.graphs.ensure_captured(graph)
+                graph.load(ids, *state)                  # the eager run before capture moved the state
+            self._graph = graph
+            self.h2d_bytes += 4 * graph.total
+        else:
+            graph.refresh_tables()
+        graph.replay()
+        tokens = graph.read_tokens()
+        self.d2h_bytes += 4 * (len(ids) + 1)
+        self.graph_steps += 1
+        for e in plan.entries:
+            self.engine.cache.commit(e.request.id, e.begin + 1)
+        self.engine.steps_run += 1
+        self.engine.tokens_run += len(ids)
+        finished = self.scheduler.update(plan, tokens)
+        if finished:
+            self._graph = None
+        return finished
 
     # ------------------------------------------------------------------ whole generations
     def generate(self, prompts: Sequence[Sequence[int]],

@@ -44,7 +44,16 @@ def require_gpu(device: Optional[str] = None) -> torch.device:
 
 def prepare_kernels(model=None) -> None:
     """Compile, at once and in parallel, every kernel object this model will ask for."""
-    kernel_build.compile_many(ops.base_sources())
+    from ..kernels import attention
+    sources = ops.base_sources()
+    if model is not None and model.rt.dtype == torch.bfloat16:
+        for entry in model.cache_entries.values():
+            head_dim = getattr(entry.need, "head_dim", None)
+            if head_dim:
+                for item in attention.mma_sources(head_dim):
+                    if item not in sources:
+                        sources.append(item)
+    kernel_build.compile_many(sources)
 
 
 def make_engine(model, page_size: int, num_pages: int, max_requests: int) -> Engine:

@@ -53,6 +53,7 @@ _SIGNATURES = {
         "mlb_add_inplace": [c_void_p, c_void_p, c_longlong, c_void_p],
         "mlb_silu_mul": [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
         "mlb_cast_f32_bf16": [c_void_p, c_void_p, c_longlong, c_void_p],
+        "mlb_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     },
     "gemm_f32.cu": {
         "mlb_gemm_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -104,7 +105,11 @@ def base_sources():
 def all_sources():
     """Every object the package can ask for with its default head sizes: what the build
     check compiles."""
-    return base_sources()
+    from . import attention
+    out = base_sources()
+    for d in (32, 64, 128):
+        out += attention.mma_sources(d)
+    return out
 
 
 # ------------------------------------------------------------------------------ basic
@@ -171,6 +176,19 @@ def cast_f32_bf16(x: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError("cast: sizes differ")
     L = lib("basic.cu")
     build.check(L, L.mlb_cast_f32_bf16(x.data_ptr(), out.data_ptr(), x.numel(), _stream()))
+
+
+def decode_advance(positions: torch.Tensor, seq_pos0: torch.Tensor, seq_lens: torch.Tensor, draw: torch.Tensor) -> None:
+    """Every sequence of a captured decode step has grown by one token: advance its position,
+    extents and draw counter on the device."""
+    n = positions.shape[0]
+    _need(positions, "positions", torch.int32, 1); _need(seq_pos0, "seq_pos0", torch.int32, 1)
+    _need(seq_lens, "seq_lens", torch.int32, 1); _need(draw, "draw", torch.int64, 1)
+    if not (seq_pos0.shape[0] == seq_lens.shape[0] == draw.shape[0] == n):
+        raise KernelError("decode_advance: one entry per sequence in every array")
+    L = lib("basic.cu")
+    build.check(L, L.mlb_decode_advance(positions.data_ptr(), seq_pos0.data_ptr(), seq_lens.data_ptr(), draw.data_ptr(),
+                                        n, _stream()))
 
 
 # ------------------------------------------------------------------------------ fp32 GEMM

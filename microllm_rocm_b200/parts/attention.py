@@ -25,6 +25,8 @@ from .base import Mixer, PagedKVNeed, PagedKVView, PositionEncoding, Runtime, St
 
 @register_mixer("attention")
 class Attention(Mixer):
+    graph_safe = True
+
     def __init__(self, params: dict, rt: Runtime, position: Optional[PositionEncoding] = None):
         self.prefix = params.get("prefix", "")
         self.hidden = int(params["hidden_size"])

@@ -156,6 +156,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True when forward() only launches work on the current stream from device-resident
+    # inputs (no host mirrors of the context, no synchronisation): such a mixer may be
+    # captured into a CUDA graph for steady decoding.
+    graph_safe = False
+
     def cache_need(self):
         """PagedKVNeed, FixedStateNeed or None."""
         return None

@@ -102,15 +102,14 @@ def test_stop_tokens_and_requests_over_time(folders):
     full = plain_generate(folders[key], p, 10)
     stop = full[4]
     a = llm.submit(p, GenerationConfig(max_new_tokens=10, temperature=0.0, stop_tokens=(stop,)))
-    llm.step(); llm.step()
-    b = llm.submit(p, GenerationConfig(max_new_tokens=3, temperature=0.0))       # arrives while a decodes
+    llm.step()
+    b = llm.submit(p, GenerationConfig(max_new_tokens=3, temperature=0.0))       # arrives one step later
     while llm.has_work():
         llm.step()
     assert llm.poll(a).generated == full[:full.index(stop) + 1]
     assert llm.poll(b).generated == full[:3]
-    assert llm.poll(b).first_token_step == 2
-
-
+    assert llm.poll(a).first_token_step == 0 and llm.poll(b).arrival_step == 1 and llm.poll(b).first_token_step == 1
+    assert llm.poll(b).completion_step == 3
 def test_command_line(folders, tmp_path):
     key = "a"
     prompt = random_tokens(9, tiny_config(key).vocab_size, 2)
@@ -139,3 +138,22 @@ def test_command_line(folders, tmp_path):
     info = json.loads(proc.stdout.strip().splitlines()[-1])
     assert info["generated_tokens"] == [plain_generate(folders[key], prompt[:n], k) for n, k in ((4, 3), (9, 2), (6, 4))]
     assert info["admissions"] == 3
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_decode_steps_equal_launched_ones(folders, dtype):
+    """Steady decoding replays a captured step whose inputs live on the device; it must select
+    the tokens that kernel-by-kernel steps select, across page edges, past the window, with
+    greedy and sampled requests side by side, and when requests finish at different times."""
+    from microllm_rocm_b200 import GenerationConfig
+    key = "b"
+    prompts = [random_tokens(n, tiny_config(key).vocab_size, 5 * n) for n in [3, 30, 61]]
+    cfgs = [GenerationConfig(max_new_tokens=90, temperature=0.0), GenerationConfig(max_new_tokens=40, temperature=0.9, seed=5),
+            GenerationConfig(max_new_tokens=70, temperature=0.7, top_k=8, seed=9)]
+    plain_path = llm_for(folders[key], dtype, max_tokens=1024, cuda_graphs=False)
+    want = plain_path.generate(prompts, cfgs)
+    graphed = llm_for(folders[key], dtype, max_tokens=1024)
+    got = graphed.generate(prompts, cfgs)
+    assert graphed.graph_steps > 100 and plain_path.graph_steps == 0
+    assert got == want
+    graphed.engine.cache.check()
