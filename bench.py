@@ -128,7 +128,7 @@ def run_ours(args):
     layers = args.layers or full.num_hidden_layers
     cfg = preset("qwen2.5-1.5b", num_hidden_layers=layers)
     prompt_len, context, page = args.prompt, args.context, 64
-    max_batch = max(args.batch, 64 if not args.skip_points else args.batch)
+    max_batch = max(args.batch, 64 if not (args.skip_points or args.only) else args.batch)
     tokens_needed = max_batch * (context + page)
     engine = random_engine(cfg, seed=0, dtype="bfloat16", page_size=page, max_tokens=tokens_needed,
                            max_requests=max_batch, draw_on_device=True)
@@ -150,9 +150,15 @@ def run_ours(args):
         engine.cache.release("pf")
         return start.elapsed_time(end)
 
-    for _ in range(max(3, args.warmup)):
-        prefill_once()
-    prefill_ms = statistics.median([prefill_once() for _ in range(5)])
+    if args.only == "decode":
+        prefill_ms = float("nan")
+    else:
+        for _ in range(max(3, args.warmup)):
+            prefill_once()
+        prefill_ms = statistics.median([prefill_once() for _ in range(1 if args.only == "prefill" else 5)])
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "ms": prefill_ms, "tokens": args.prefill_tokens, "layers": layers}))
+        return 0
     pf_flops = prefill_flops(cfg, layers, args.prefill_tokens)
     prefill = {"value": args.prefill_tokens / (prefill_ms / 1e3), "tokens": args.prefill_tokens, "ms": prefill_ms,
                "frac": pf_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
@@ -185,15 +191,21 @@ def run_ours(args):
     bytes_step = decode_bytes(cfg, layers, args.batch, ctx_len)
     achieved = bytes_step / (ms_per_step / 1e3) / 1e9
     points = {}
-    if not args.skip_points:
+    if not args.skip_points and not args.only:
         for b in (1, 64):
             ms_b, _, _ = decode_device(b, max(8, args.steps // 2), args.warmup)
             points[f"decode_b{b}"] = b / (ms_b / 1e3)
 
+    if args.only == "decode":
+        print(json.dumps({"only": "decode", "ms_per_step": ms_per_step, "batch": args.batch, "layers": layers,
+                          "context": ctx_len, "launches_per_step": launches // args.steps,
+                          "hbm_frac": achieved / pk["hbm_gbs"]}))
+        return 0
+
     # ---- decode, end to end through the Python entry point -----------------------------------
     llm = LLM(engine, max_tokens_per_step=max(2048, args.batch), max_seqs=max_batch)
     host_prompts = prompts(args.batch)
-    ids = [llm.submit(p, GenerationConfig(max_new_tokens=args.steps + args.warmup + 1, temperature=0.0)) for p in host_prompts]
+    ids = [llm.submit(p, GenerationConfig(max_new_tokens=args.steps + args.warmup + args.batch + 8, temperature=0.0)) for p in host_prompts]
     while any(llm.poll(i).computed < prompt_len for i in ids):          # prompts in, first token out
         llm.step()
     for _ in range(args.warmup):
@@ -242,6 +254,8 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+                    help="run just one timed part and print a short line (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "walkinglabs/microLLM-rocm is a CMake C++/HIP project "

@@ -4,7 +4,8 @@ fp32: always the plain kernel (fixed summation order, bit-stable across ways of 
 bf16: the tensor-core kernel (`attention_mma.cu`, compiled for the model's head size) when
 the head size is a multiple of 32 and the page size a multiple of 16; the plain kernel
 otherwise.  A step whose sequences all bring one token runs the decode shape (keys split
-over CTAs, partial results merged from scratch memory); any other step runs the prefill shape.
+over CTAs, partial results in scratch memory, merged by the CTA that finishes last); any
+other step runs the prefill shape.
 """
 from __future__ import annotations
 
@@ -18,13 +19,14 @@ from .build import KernelError
 
 MAX_HEAD_DIM = 256
 SM_COUNT = 148
-TARGET_CTAS = SM_COUNT * 3          # resident CTAs of the decode kernel at its register use
+TARGET_CTAS = SM_COUNT * 3          # resident CTAs of the lean decode kernel
+MAX_SPLITS = 64
 MIN_KEY_TILES_PER_SPLIT = 4         # one 16-key tile per warp at least
 
 ops.register_signatures("attention_mma.cu", {
     "mlb_paged_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                                c_int, c_void_p, c_void_p],
+                                c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                c_int, c_int, c_void_p, c_void_p],
 })
 
 
@@ -60,8 +62,13 @@ def _plan(ctx, group: int, num_kv_heads: int):
         # each CTA takes an even share of its own sequence's keys, so the launch shape chosen
         # here stays balanced while the sequences of a captured step grow
         key_tiles = max(1, -(-ctx.max_seq_len // 16))
-        splits = max(1, min(TARGET_CTAS // max(1, len(work) * num_kv_heads), key_tiles // MIN_KEY_TILES_PER_SPLIT))
-    plan = (work_dev, len(work), 1 if decode else 0, splits)
+        splits = max(1, min(TARGET_CTAS // max(1, len(work) * num_kv_heads), key_tiles // MIN_KEY_TILES_PER_SPLIT,
+                            MAX_SPLITS))
+    # one ticket per (work item, kv head): which split finished last; the kernel leaves them zero
+    tickets = torch.zeros(len(work) * num_kv_heads, dtype=torch.int32, device=ctx.positions.device) if splits > 1 else None
+    # do warps walk more than two key tiles each?  (4 warps share a CTA's tiles)
+    long_loops = 1 if decode and -(-max(1, -(-ctx.max_seq_len // 16)) // splits) > 8 else 0
+    plan = (work_dev, len(work), 1 if decode else 0, splits, tickets, long_loops)
     ctx.extras[key] = plan
     return plan
 
@@ -76,14 +83,14 @@ def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx
     if pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("paged_attention: the tensor-core kernel wants bf16 queries, pages and output")
     T = q.shape[0]
-    work, num_work, mode, splits = _plan(ctx, num_heads // num_kv_heads, num_kv_heads)
+    work, num_work, mode, splits, tickets, long_loops = _plan(ctx, num_heads // num_kv_heads, num_kv_heads)
     part_o = part_lse = None
     if splits > 1:
         part_o = torch.empty((T * num_heads, splits, head_dim), dtype=torch.float32, device=q.device)
         part_lse = torch.empty((T * num_heads, splits), dtype=torch.float32, device=q.device)
     L = ops.lib("attention_mma.cu", {"HEAD_DIM": head_dim})
     build.check(L, L.mlb_paged_attention_mma(
-        q.data_ptr(), pages.data_ptr(), out.data_ptr(), ops._ptr(part_o), ops._ptr(part_lse),
+        q.data_ptr(), pages.data_ptr(), out.data_ptr(), ops._ptr(part_o), ops._ptr(part_lse), ops._ptr(tickets),
         ctx.seq_starts.data_ptr(), ctx.seq_pos0.data_ptr(), block_table.data_ptr(), work.data_ptr(), num_work,
         block_table.shape[1], pages.shape[0], page_size, num_heads, num_kv_heads, int(window or 0), float(scale),
-        mode, splits, T * num_heads, ops._ptr(ctx.error_flag), ops._stream()))
+        mode, splits, long_loops, ops._ptr(ctx.error_flag), ops._stream()))
