@@ -93,6 +93,31 @@ struct TileGeometry {
     __device__ __forceinline__ int token_of(int r, int group) const { return (row0 + r) / group; }
 };
 
+// The block-table entries a CTA will need, fetched once into shared memory: a lookup in the
+// key loop must not cost a trip to global memory, because the loads of a tile cannot issue
+// before its page is known.  Blocks outside the cached span fall back to global memory.
+constexpr int TABLE_SPAN = 1024;
+struct PageTable {
+    const int* global;       // this sequence's row of the block table
+    const int* cached;       // shared-memory copy of blocks [first, first + count)
+    int first, count, max_blocks;
+    __device__ __forceinline__ int page_of(int block) const {
+        if (block >= max_blocks) return -1;
+        const int i = block - first;
+        return (i >= 0 && i < count) ? cached[i] : __ldg(global + block);
+    }
+};
+
+__device__ __forceinline__ void fill_page_table(PageTable& pt, int* table_s, const int* row, int max_blocks,
+                                                int first_block, int last_block, int tid, int threads) {
+    pt.global = row;
+    pt.cached = table_s;
+    pt.max_blocks = max_blocks;
+    pt.first = first_block;
+    pt.count = max(0, min(min(last_block, max_blocks - 1) - first_block + 1, TABLE_SPAN));
+    for (int i = tid; i < pt.count; i += threads) table_s[i] = __ldg(row + first_block + i);
+}
+
 // The K and V of 16 keys as this thread holds them for the tensor cores.
 struct KeyTile {
     uint4 k[2][KCHUNKS];
@@ -103,11 +128,11 @@ struct KeyTile {
 // Issue every load of one 16-key tile (nothing waits here).  hi_tile: last position any row
 // of the row tile may see; slots behind it were never written by this sequence, so their V
 // stays zero (their probability is zero, and zero times stale memory must stay zero).
-__device__ __forceinline__ void load_keys(const FaParams& p, const TileGeometry& geo, int kt, int hi_tile, KeyTile& kv) {
+__device__ __forceinline__ void load_keys(const FaParams& p, const TileGeometry& geo, const PageTable& pt, int kt,
+                                          int hi_tile, KeyTile& kv) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int base = kt * 16;
-    const int block = base / p.page_size;
-    const int page = block < p.max_blocks ? __ldg(p.block_table + (size_t)geo.seq * p.max_blocks + block) : -1;
+    const int page = pt.page_of(base / p.page_size);
     if (page < 0 || page >= p.num_pages) {
         if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 3);
         kv.base = -1;
@@ -214,9 +239,9 @@ __device__ __forceinline__ void consume_keys(const FaParams& p, const __nv_bfloa
 // tile_begin + first.  q_s: this tile's queries, [16][Q_STRIDE] bf16 in shared memory.  With
 // PREFETCH the loads of the next key tile are in flight while the current one is consumed.
 template <bool PREFETCH>
-__device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& geo, const __nv_bfloat16* q_s,
-                                       int tile_begin, int tile_end, int first, int stride, int hi_tile,
-                                       RowState& st) {
+__device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& geo, const PageTable& pt,
+                                       const __nv_bfloat16* q_s, int tile_begin, int tile_end, int first, int stride,
+                                       int hi_tile, RowState& st) {
     const int lane = threadIdx.x & 31, g = lane >> 2;
     int pos_row[2], lo_row[2];
 #pragma unroll
@@ -234,15 +259,15 @@ __device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& ge
     if (kt >= tile_end) return;
     if (PREFETCH) {
         KeyTile a, b;
-        load_keys(p, geo, kt, hi_tile, a);
+        load_keys(p, geo, pt, kt, hi_tile, a);
         while (true) {
             const bool more_b = kt + stride < tile_end;
-            if (more_b) load_keys(p, geo, kt + stride, hi_tile, b);
+            if (more_b) load_keys(p, geo, pt, kt + stride, hi_tile, b);
             consume_keys(p, q_s, a, pos_row, lo_row, st);
             if (!more_b) break;
             kt += stride;
             const bool more_a = kt + stride < tile_end;
-            if (more_a) load_keys(p, geo, kt + stride, hi_tile, a);
+            if (more_a) load_keys(p, geo, pt, kt + stride, hi_tile, a);
             consume_keys(p, q_s, b, pos_row, lo_row, st);
             if (!more_a) break;
             kt += stride;
@@ -250,7 +275,7 @@ __device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& ge
     } else {
         KeyTile a;
         for (; kt < tile_end; kt += stride) {
-            load_keys(p, geo, kt, hi_tile, a);
+            load_keys(p, geo, pt, kt, hi_tile, a);
             consume_keys(p, q_s, a, pos_row, lo_row, st);
         }
     }
@@ -301,19 +326,31 @@ __device__ __forceinline__ bool geometry(const FaParams& p, int work_index, int 
 
 // ---------------------------------------------------------------------------------- prefill
 __global__ void __launch_bounds__(WARPS * 32) fa_prefill_kernel(FaParams p) {
+    pdl_prologue();
     __shared__ __align__(16) __nv_bfloat16 q_s[WARPS][16 * Q_STRIDE];
+    __shared__ int table_s[WARPS][TABLE_SPAN / WARPS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     TileGeometry geo;
     if (!geometry(p, blockIdx.x, warp, blockIdx.y, geo)) return;
-    load_q_tile(p, geo, q_s[warp], lane, 32);
-    __syncwarp();
     const int first_tok = geo.token_of(0, p.group);
     const int last_tok = min(geo.token_of(15, p.group), geo.n_new - 1);
     const int first_pos = geo.pos0 + first_tok, last_pos = geo.pos0 + last_tok;
     const int lo = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
+    // each warp keeps the LAST blocks of its key range at hand (it reaches them however long
+    // the range is); earlier blocks of a very long range are looked up in global memory
+    PageTable pt;
+    {
+        const int last_block = last_pos / p.page_size;
+        const int first_block = max(lo / p.page_size, last_block - TABLE_SPAN / WARPS + 1);
+        fill_page_table(pt, table_s[warp], p.block_table + (size_t)geo.seq * p.max_blocks, p.max_blocks, first_block,
+                        last_block, lane, 32);
+        pt.count = min(pt.count, TABLE_SPAN / WARPS);
+    }
+    load_q_tile(p, geo, q_s[warp], lane, 32);
+    __syncwarp();
     RowState st;
     init_state(st);
-    attend<USE_PREFETCH>(p, geo, q_s[warp], lo / 16, last_pos / 16 + 1, 0, 1, last_pos, st);
+    attend<USE_PREFETCH>(p, geo, pt, q_s[warp], lo / 16, last_pos / 16 + 1, 0, 1, last_pos, st);
     // normalise and write through shared memory so that rows leave as whole 16-byte pieces
     float inv[2];
 #pragma unroll
@@ -351,10 +388,12 @@ __global__ void __launch_bounds__(WARPS * 32) fa_prefill_kernel(FaParams p) {
 constexpr int FRAGS = NB_O * 4;
 constexpr int MAX_SPLITS = 64;
 constexpr size_t DECODE_SMEM = 16 * Q_STRIDE * sizeof(__nv_bfloat16) + (size_t)WARPS * FRAGS * 32 * sizeof(float) +
-                               2 * WARPS * 16 * sizeof(float) + 16 * MAX_SPLITS * sizeof(float) + 16;
+                               2 * WARPS * 16 * sizeof(float) + 16 * MAX_SPLITS * sizeof(float) + 16 +
+                               TABLE_SPAN * sizeof(int);
 
 template <bool PREFETCH>
 __global__ void __launch_bounds__(WARPS * 32, PREFETCH ? 2 : 3) fa_decode_kernel(FaParams p) {
+    pdl_prologue();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     float* frag = reinterpret_cast<float*>(smem_raw + 16 * Q_STRIDE * sizeof(__nv_bfloat16));   // [WARPS][FRAGS][32]
@@ -362,6 +401,7 @@ __global__ void __launch_bounds__(WARPS * 32, PREFETCH ? 2 : 3) fa_decode_kernel
     float* warp_l = warp_m + WARPS * 16;              // [WARPS][16]
     float* split_w = warp_l + WARPS * 16;             // [16][MAX_SPLITS] normalised weights of the final merge
     int* ticket_s = reinterpret_cast<int*>(split_w + 16 * MAX_SPLITS);
+    int* table_s = ticket_s + 4;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     TileGeometry geo;
     if (!geometry(p, blockIdx.x, 0, blockIdx.y, geo)) return;          // uniform over the CTA
@@ -391,6 +431,9 @@ __global__ void __launch_bounds__(WARPS * 32, PREFETCH ? 2 : 3) fa_decode_kernel
         tile_begin += (int)blockIdx.z * per_split;
         tile_end = min(tile_end, tile_begin + per_split);
     }
+    PageTable pt;
+    fill_page_table(pt, table_s, p.block_table + (size_t)geo.seq * p.max_blocks, p.max_blocks,
+                    tile_begin * 16 / p.page_size, max(tile_begin, tile_end - 1) * 16 / p.page_size, threadIdx.x, WARPS * 32);
     // where this thread's two rows (g and g+8) go
     size_t out_row[2];
     bool row_ok[2];
@@ -405,7 +448,7 @@ __global__ void __launch_bounds__(WARPS * 32, PREFETCH ? 2 : 3) fa_decode_kernel
     __syncthreads();
     RowState st;
     init_state(st);
-    attend<PREFETCH>(p, geo, q_s, tile_begin, tile_end, warp, WARPS, last_pos, st);
+    attend<PREFETCH>(p, geo, pt, q_s, tile_begin, tile_end, warp, WARPS, last_pos, st);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 1);
@@ -502,16 +545,14 @@ __global__ void __launch_bounds__(WARPS * 32, PREFETCH ? 2 : 3) fa_decode_kernel
         const size_t row = (size_t)(geo.token0 + tok) * p.num_heads + head;
         const float* src = p.part_o + row * p.splits * D + dim;
         float acc = 0.0f;
-        int s = 0;
-        for (; s + 4 <= p.splits; s += 4) {            // four loads in flight; the sum keeps split order
-            const float a0 = __ldcg(src + (size_t)(s + 0) * D), a1 = __ldcg(src + (size_t)(s + 1) * D);
-            const float a2 = __ldcg(src + (size_t)(s + 2) * D), a3 = __ldcg(src + (size_t)(s + 3) * D);
-            acc += split_w[r * MAX_SPLITS + s] * a0;
-            acc += split_w[r * MAX_SPLITS + s + 1] * a1;
-            acc += split_w[r * MAX_SPLITS + s + 2] * a2;
-            acc += split_w[r * MAX_SPLITS + s + 3] * a3;
+        for (int s0 = 0; s0 < p.splits; s0 += 16) {    // sixteen loads in flight; the sum keeps split order
+            float part[16];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) part[k] = s0 + k < p.splits ? __ldcg(src + (size_t)(s0 + k) * D) : 0.0f;
+#pragma unroll
+            for (int k = 0; k < 16; ++k)
+                if (s0 + k < p.splits) acc += split_w[r * MAX_SPLITS + s0 + k] * part[k];
         }
-        for (; s < p.splits; ++s) acc += split_w[r * MAX_SPLITS + s] * __ldcg(src + (size_t)s * D);
         p.out[row * D + dim] = __float2bfloat16_rn(acc);
     }
 }
@@ -545,7 +586,7 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
                seq_starts, seq_pos0, block_table, work, max_blocks, num_pages, page_size, num_heads, num_kv_heads,
                num_heads / num_kv_heads, window, scale * LOG2E, mode == 1 ? splits : 1, error_flag};
     if (mode == 0) {
-        fa_prefill_kernel<<<dim3(num_work, num_kv_heads, 1), WARPS * 32, 0, stream>>>(p);
+        launch_kernel(fa_prefill_kernel, dim3(num_work, num_kv_heads, 1), WARPS * 32, 0, stream, p);
         return check_launch("fa_prefill");
     }
     // long_loops: every warp walks several key tiles, so loads of the next tile are worth their
@@ -560,8 +601,8 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
         configured = true;
     }
     if (long_loops && USE_PREFETCH)
-        fa_decode_kernel<true><<<dim3(num_work, num_kv_heads, splits), WARPS * 32, DECODE_SMEM, stream>>>(p);
+        launch_kernel(fa_decode_kernel<true>, dim3(num_work, num_kv_heads, splits), WARPS * 32, DECODE_SMEM, stream, p);
     else
-        fa_decode_kernel<false><<<dim3(num_work, num_kv_heads, splits), WARPS * 32, DECODE_SMEM, stream>>>(p);
+        launch_kernel(fa_decode_kernel<false>, dim3(num_work, num_kv_heads, splits), WARPS * 32, DECODE_SMEM, stream, p);
     return check_launch("fa_decode");
 }

@@ -42,6 +42,7 @@ struct AttnParams {
 template <typename QT, typename KVT, typename OutT>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_attention_plain_kernel(AttnParams p) {
+    pdl_prologue();
     __shared__ float q_s[WARPS][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -136,13 +137,13 @@ MLB_EXPORT int mlb_paged_attention_plain(const void* q, int q_dtype, const void*
     const long long items = (long long)tokens * num_heads;
     const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
     if (q_dtype == MLB_F32 && kv_dtype == MLB_F32 && out_dtype == MLB_F32)
-        paged_attention_plain_kernel<float, float, float><<<blocks, WARPS * 32, 0, stream>>>(p);
+        launch_kernel(paged_attention_plain_kernel<float, float, float>, blocks, WARPS * 32, 0, stream, p);
     else if (q_dtype == MLB_BF16 && kv_dtype == MLB_BF16 && out_dtype == MLB_BF16)
-        paged_attention_plain_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(p);
+        launch_kernel(paged_attention_plain_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, blocks, WARPS * 32, 0, stream, p);
     else if (q_dtype == MLB_F32 && kv_dtype == MLB_BF16 && out_dtype == MLB_F32)
-        paged_attention_plain_kernel<float, __nv_bfloat16, float><<<blocks, WARPS * 32, 0, stream>>>(p);
+        launch_kernel(paged_attention_plain_kernel<float, __nv_bfloat16, float>, blocks, WARPS * 32, 0, stream, p);
     else if (q_dtype == MLB_BF16 && kv_dtype == MLB_BF16 && out_dtype == MLB_F32)
-        paged_attention_plain_kernel<__nv_bfloat16, __nv_bfloat16, float><<<blocks, WARPS * 32, 0, stream>>>(p);
+        launch_kernel(paged_attention_plain_kernel<__nv_bfloat16, __nv_bfloat16, float>, blocks, WARPS * 32, 0, stream, p);
     else
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_plain: unsupported dtypes %d/%d/%d", q_dtype, kv_dtype, out_dtype);
     return check_launch("paged_attention_plain");

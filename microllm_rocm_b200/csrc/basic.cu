@@ -18,6 +18,7 @@ MLB_DEFINE_LAST_ERROR()
 template <typename TableT>
 __global__ void embed_gather_kernel(const TableT* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int tokens, int width, int vocab) {
+    pdl_prologue();
     const int t = blockIdx.x;
     if (t >= tokens) return;
     const int id = ids[t];
@@ -36,9 +37,9 @@ MLB_EXPORT int mlb_embed_gather(const void* table, int table_dtype, const int* i
     if (tokens == 0) return MLB_OK;
     const int threads = width >= 1024 ? 256 : 128;
     if (table_dtype == MLB_F32)
-        embed_gather_kernel<float><<<tokens, threads, 0, stream>>>((const float*)table, ids, out, tokens, width, vocab);
+        launch_kernel(embed_gather_kernel<float>, tokens, threads, 0, stream, (const float*)table, ids, out, tokens, width, vocab);
     else if (table_dtype == MLB_BF16)
-        embed_gather_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, tokens, width, vocab);
+        launch_kernel(embed_gather_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, tokens, width, vocab);
     else
         return fail(MLB_INVALID_ARGUMENT, "embed_gather: unknown table dtype %d", table_dtype);
     return check_launch("embed_gather");
@@ -47,22 +48,77 @@ MLB_EXPORT int mlb_embed_gather(const void* table, int table_dtype, const int* i
 // ------------------------------------------------------------------ RMSNorm family
 // One block per output row.  `rows` (may be null) selects input rows: out[r] = norm(x[rows[r]]).
 // With ADD, `delta` is first added into `x` in place (x is the fp32 residual stream) and the
-// sum is what gets normalised.  The reduction order depends only on `width` and the block
+// sum is what gets normalised.  `delta` may be `n_delta` partial results laid `delta_stride`
+// elements apart (a product whose K range was split over CTAs): they are added in order,
+// which is the split's reduction.  The reduction order depends only on `width` and the block
 // size, never on the number of rows.
+constexpr int NORM_THREADS = 512;
+constexpr int NORM_VECS = 4;            // float4 per thread kept in registers: widths up to 8192
+
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+
+// sum of the partial deltas at one float4, eight loads in flight, added in split order
+__device__ __forceinline__ float4 delta_sum4(const float* delta, int n_delta, long long stride) {
+    float4 d = ld4(delta);
+    for (int k0 = 1; k0 < n_delta; k0 += 8) {
+        float4 part[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            part[k] = k0 + k < n_delta ? ld4(delta + (size_t)(k0 + k) * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { d.x += part[k].x; d.y += part[k].y; d.z += part[k].z; d.w += part[k].w; }
+    }
+    return d;
+}
+
 template <typename OutT, bool ADD>
-__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
-                               const float* __restrict__ weight, OutT* __restrict__ out,
-                               const int* __restrict__ rows, int width, float eps) {
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_delta, long long delta_stride,
+               const float* __restrict__ weight, OutT* __restrict__ out, const int* __restrict__ rows, int width,
+               float eps, int vectorised) {
+    pdl_prologue();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const size_t src_row = rows ? (size_t)rows[r] : (size_t)r;
     float* xr = x + src_row * width;
     OutT* yr = out + (size_t)r * width;
     float ss = 0.0f;
+    if (vectorised) {                       // width % 4 == 0, 16-byte aligned rows, width <= NORM_VECS * 4 * threads
+        const int nvec = width / 4;
+        float4 v[NORM_VECS];
+#pragma unroll
+        for (int i = 0; i < NORM_VECS; ++i) {
+            const int c = (threadIdx.x + i * NORM_THREADS) * 4;
+            if (c >= width) break;
+            v[i] = ld4(xr + c);
+            if (ADD) {
+                const float4 d = delta_sum4(delta + src_row * width + c, n_delta, delta_stride);
+                v[i].x += d.x; v[i].y += d.y; v[i].z += d.z; v[i].w += d.w;
+                *reinterpret_cast<float4*>(xr + c) = v[i];
+            }
+            ss += v[i].x * v[i].x; ss += v[i].y * v[i].y; ss += v[i].z * v[i].z; ss += v[i].w * v[i].w;
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+#pragma unroll
+        for (int i = 0; i < NORM_VECS; ++i) {
+            const int c = (threadIdx.x + i * NORM_THREADS) * 4;
+            if (c >= width) break;
+            const float4 w = ld4(weight + c);
+            yr[c + 0] = from_f32<OutT>(v[i].x * inv * w.x);
+            yr[c + 1] = from_f32<OutT>(v[i].y * inv * w.y);
+            yr[c + 2] = from_f32<OutT>(v[i].z * inv * w.z);
+            yr[c + 3] = from_f32<OutT>(v[i].w * inv * w.w);
+        }
+        (void)nvec;
+        return;
+    }
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float v = xr[c];
         if (ADD) {
-            v += delta[src_row * width + c];
+            float d = delta[src_row * width + c];
+            for (int k = 1; k < n_delta; ++k) d += delta[(size_t)k * delta_stride + src_row * width + c];
+            v += d;
             xr[c] = v;
         }
         ss += v * v;
@@ -75,16 +131,23 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
 }
 
 template <bool ADD>
-static int launch_rmsnorm(float* x, const float* delta, const float* w, void* out, int out_dtype,
-                          const int* rows, int n_rows, int width, float eps, cudaStream_t stream) {
+static int launch_rmsnorm(float* x, const float* delta, int n_delta, long long delta_stride, const float* w, void* out,
+                          int out_dtype, const int* rows, int n_rows, int width, float eps, cudaStream_t stream) {
     if (n_rows < 0 || width <= 0 || !(eps > 0.0f)) return fail(MLB_INVALID_ARGUMENT, "rmsnorm: bad sizes or eps");
     if (n_rows == 0) return MLB_OK;
-    int threads = 128;
-    if (width >= 2048) threads = 512; else if (width >= 512) threads = 256;
+    const bool aligned = ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && (!delta || (uintptr_t)delta % 16 == 0) &&
+                         (delta_stride % 4 == 0);
+    const int vectorised = (width % 4 == 0 && aligned && width <= NORM_VECS * 4 * NORM_THREADS) ? 1 : 0;
+    int threads = NORM_THREADS;
+    if (!vectorised) threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    else if (width <= 4 * 128) threads = 128;
+    else if (width <= 4 * 256) threads = 256;
+    // (the vectorised path strides by NORM_THREADS: smaller blocks simply leave the upper slots unused)
+    if (vectorised) threads = NORM_THREADS;
     if (out_dtype == MLB_F32)
-        rmsnorm_kernel<float, ADD><<<n_rows, threads, 0, stream>>>(x, delta, w, (float*)out, rows, width, eps);
+        launch_kernel(rmsnorm_kernel<float, ADD>, n_rows, threads, 0, stream, x, delta, n_delta, delta_stride, w, (float*)out, rows, width, eps, vectorised);
     else if (out_dtype == MLB_BF16)
-        rmsnorm_kernel<__nv_bfloat16, ADD><<<n_rows, threads, 0, stream>>>(x, delta, w, (__nv_bfloat16*)out, rows, width, eps);
+        launch_kernel(rmsnorm_kernel<__nv_bfloat16, ADD>, n_rows, threads, 0, stream, x, delta, n_delta, delta_stride, w, (__nv_bfloat16*)out, rows, width, eps, vectorised);
     else
         return fail(MLB_INVALID_ARGUMENT, "rmsnorm: unknown output dtype %d", out_dtype);
     return check_launch("rmsnorm");
@@ -92,25 +155,32 @@ static int launch_rmsnorm(float* x, const float* delta, const float* w, void* ou
 
 MLB_EXPORT int mlb_rmsnorm(const float* x, const float* weight, void* out, int out_dtype, const int* rows,
                            int n_rows, int width, float eps, cudaStream_t stream) {
-    return launch_rmsnorm<false>(const_cast<float*>(x), nullptr, weight, out, out_dtype, rows, n_rows, width, eps, stream);
+    return launch_rmsnorm<false>(const_cast<float*>(x), nullptr, 0, 0, weight, out, out_dtype, rows, n_rows, width, eps, stream);
 }
 
-MLB_EXPORT int mlb_add_rmsnorm(float* residual, const float* delta, const float* weight, void* out,
-                               int out_dtype, int n_rows, int width, float eps, cudaStream_t stream) {
-    if (!delta) return fail(MLB_INVALID_ARGUMENT, "add_rmsnorm: delta is null");
-    return launch_rmsnorm<true>(residual, delta, weight, out, out_dtype, nullptr, n_rows, width, eps, stream);
+MLB_EXPORT int mlb_add_rmsnorm(float* residual, const float* delta, int n_delta, long long delta_stride,
+                               const float* weight, void* out, int out_dtype, int n_rows, int width, float eps,
+                               cudaStream_t stream) {
+    if (!delta || n_delta < 1) return fail(MLB_INVALID_ARGUMENT, "add_rmsnorm: delta is missing");
+    return launch_rmsnorm<true>(residual, delta, n_delta, delta_stride, weight, out, out_dtype, nullptr, n_rows, width, eps, stream);
 }
 
 // ------------------------------------------------------------------ residual add
-__global__ void add_inplace_kernel(float* __restrict__ x, const float* __restrict__ delta, size_t n) {
+__global__ void add_inplace_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_delta,
+                                   long long delta_stride, size_t n) {
+    pdl_prologue();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) x[i] += delta[i];
+    if (i >= n) return;
+    float d = delta[i];
+    for (int k = 1; k < n_delta; ++k) d += delta[(size_t)k * delta_stride + i];
+    x[i] += d;
 }
 
-MLB_EXPORT int mlb_add_inplace(float* x, const float* delta, long long n, cudaStream_t stream) {
-    if (n < 0) return fail(MLB_INVALID_ARGUMENT, "add_inplace: negative size");
+MLB_EXPORT int mlb_add_inplace(float* x, const float* delta, int n_delta, long long delta_stride, long long n,
+                               cudaStream_t stream) {
+    if (n < 0 || n_delta < 1) return fail(MLB_INVALID_ARGUMENT, "add_inplace: bad sizes");
     if (n == 0) return MLB_OK;
-    add_inplace_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, delta, (size_t)n);
+    launch_kernel(add_inplace_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, x, delta, n_delta, delta_stride, (size_t)n);
     return check_launch("add_inplace");
 }
 
@@ -124,29 +194,36 @@ __device__ __forceinline__ float stable_sigmoid(float v) {
 
 template <typename InT, typename OutT>
 __global__ void silu_mul_kernel(const InT* __restrict__ gate, const InT* __restrict__ up, long long in_stride,
-                                OutT* __restrict__ out, int rows, int width) {
+                                int n_partials, long long partial_stride, OutT* __restrict__ out, int rows, int width) {
+    pdl_prologue();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)rows * width) return;
     const int r = (int)(i / width), c = (int)(i % width);
-    const float g = to_f32(gate[r * in_stride + c]);
-    const float u = to_f32(up[r * in_stride + c]);
+    float g = to_f32(gate[r * in_stride + c]);
+    float u = to_f32(up[r * in_stride + c]);
+    for (int k = 1; k < n_partials; ++k) {           // partial results of a split product, added in order
+        g += to_f32(gate[(size_t)k * partial_stride + r * in_stride + c]);
+        u += to_f32(up[(size_t)k * partial_stride + r * in_stride + c]);
+    }
     out[i] = from_f32<OutT>(g * stable_sigmoid(g) * u);
 }
 
 // gate and up are two column blocks of one [rows, in_stride] matrix (the fused gate/up
-// projection) or two separate matrices; `in_stride` is their row pitch in elements.
-MLB_EXPORT int mlb_silu_mul(const void* gate, const void* up, long long in_stride, int in_dtype, void* out,
-                            int out_dtype, int rows, int width, cudaStream_t stream) {
-    if (rows < 0 || width <= 0 || in_stride < width) return fail(MLB_INVALID_ARGUMENT, "silu_mul: bad sizes");
+// projection) or two separate matrices; `in_stride` is their row pitch in elements.  The input
+// may be `n_partials` partial results `partial_stride` elements apart.
+MLB_EXPORT int mlb_silu_mul(const void* gate, const void* up, long long in_stride, int in_dtype, int n_partials,
+                            long long partial_stride, void* out, int out_dtype, int rows, int width,
+                            cudaStream_t stream) {
+    if (rows < 0 || width <= 0 || in_stride < width || n_partials < 1) return fail(MLB_INVALID_ARGUMENT, "silu_mul: bad sizes");
     if (rows == 0) return MLB_OK;
     const long long n = (long long)rows * width;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (in_dtype == MLB_F32 && out_dtype == MLB_F32)
-        silu_mul_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)gate, (const float*)up, in_stride, (float*)out, rows, width);
+        launch_kernel(silu_mul_kernel<float, float>, blocks, 256, 0, stream, (const float*)gate, (const float*)up, in_stride, n_partials, partial_stride, (float*)out, rows, width);
     else if (in_dtype == MLB_BF16 && out_dtype == MLB_BF16)
-        silu_mul_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, in_stride, (__nv_bfloat16*)out, rows, width);
+        launch_kernel(silu_mul_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, in_stride, n_partials, partial_stride, (__nv_bfloat16*)out, rows, width);
     else if (in_dtype == MLB_F32 && out_dtype == MLB_BF16)
-        silu_mul_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)gate, (const float*)up, in_stride, (__nv_bfloat16*)out, rows, width);
+        launch_kernel(silu_mul_kernel<float, __nv_bfloat16>, blocks, 256, 0, stream, (const float*)gate, (const float*)up, in_stride, n_partials, partial_stride, (__nv_bfloat16*)out, rows, width);
     else
         return fail(MLB_INVALID_ARGUMENT, "silu_mul: unsupported dtype pair %d -> %d", in_dtype, out_dtype);
     return check_launch("silu_mul");
@@ -154,6 +231,7 @@ MLB_EXPORT int mlb_silu_mul(const void* gate, const void* up, long long in_strid
 
 // ------------------------------------------------------------------ fp32 -> bf16 cast
 __global__ void cast_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, size_t n) {
+    pdl_prologue();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __float2bfloat16_rn(in[i]);
 }
@@ -161,7 +239,7 @@ __global__ void cast_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __
 MLB_EXPORT int mlb_cast_f32_bf16(const float* in, void* out, long long n, cudaStream_t stream) {
     if (n < 0) return fail(MLB_INVALID_ARGUMENT, "cast: negative size");
     if (n == 0) return MLB_OK;
-    cast_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(in, (__nv_bfloat16*)out, (size_t)n);
+    launch_kernel(cast_bf16_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, in, (__nv_bfloat16*)out, (size_t)n);
     return check_launch("cast_f32_bf16");
 }
 
@@ -172,6 +250,7 @@ MLB_EXPORT int mlb_cast_f32_bf16(const float* in, void* out, long long n, cudaSt
 // that the same captured step can run again without the host touching its inputs.
 __global__ void decode_advance_kernel(int* __restrict__ positions, int* __restrict__ seq_pos0,
                                       int* __restrict__ seq_lens, long long* __restrict__ draw, int n) {
+    pdl_prologue();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     positions[i] += 1;
@@ -184,6 +263,6 @@ MLB_EXPORT int mlb_decode_advance(int* positions, int* seq_pos0, int* seq_lens, 
                                   cudaStream_t stream) {
     if (n < 0) return fail(MLB_INVALID_ARGUMENT, "decode_advance: negative size");
     if (n == 0) return MLB_OK;
-    decode_advance_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, seq_pos0, seq_lens, draw, n);
+    launch_kernel(decode_advance_kernel, (n + 127) / 128, 128, 0, stream, positions, seq_pos0, seq_lens, draw, n);
     return check_launch("decode_advance");
 }

@@ -14,6 +14,7 @@
 #include <cstdio>
 #include <cstdarg>
 #include <cmath>
+#include <cstdlib>
 
 #define MLB_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -81,6 +82,43 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     __syncthreads();
     float total = lane < warps ? scratch[lane] : 0.0f;
     return warp_sum(total);
+}
+
+// ---- programmatic dependent launch ---------------------------------------------------------
+// A decode step is a chain of ~200 short kernels, each waiting for the one before.  Launched
+// the plain way, every link pays the full launch latency after its predecessor has drained.
+// With programmatic stream serialisation a kernel's CTAs may become resident while the
+// predecessor still runs; they block in pdl_wait() until the predecessor has finished and its
+// writes are visible, so only the launch latency overlaps, never the data dependence.
+// Every kernel of this library calls pdl_prologue() before it touches memory that another
+// kernel may have written.  MLB_PDL=0 in the environment turns the attribute off.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_prologue() { pdl_launch_dependents(); pdl_wait(); }
+
+inline bool pdl_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* e = getenv("MLB_PDL");
+        enabled = (e && e[0] == '0') ? 0 : 1;
+    }
+    return enabled == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);      // errors surface in check_launch()
 }
 
 }  // namespace mlb

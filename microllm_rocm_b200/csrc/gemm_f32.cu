@@ -21,6 +21,7 @@ template <bool ACCUMULATE>
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
                 float* __restrict__ C, int M, int N, int K, long long lda, long long ldw, long long ldc) {
+    pdl_prologue();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -85,8 +86,8 @@ MLB_EXPORT int mlb_gemm_f32(const float* A, const float* W, const float* bias, f
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return fail(MLB_UNSUPPORTED_SIZE, "gemm_f32: M=%d exceeds %d rows per call", M, 65535 * BM);
     if (accumulate)
-        gemm_f32_kernel<true><<<grid, 256, 0, stream>>>(A, W, bias, C, M, N, K, lda, ldw, ldc);
+        launch_kernel(gemm_f32_kernel<true>, grid, 256, 0, stream, A, W, bias, C, M, N, K, lda, ldw, ldc);
     else
-        gemm_f32_kernel<false><<<grid, 256, 0, stream>>>(A, W, bias, C, M, N, K, lda, ldw, ldc);
+        launch_kernel(gemm_f32_kernel<false>, grid, 256, 0, stream, A, W, bias, C, M, N, K, lda, ldw, ldc);
     return check_launch("gemm_f32");
 }

@@ -24,6 +24,8 @@ namespace {
 struct RopeKvParams {
     const float* qkv;        // [T, ld]  columns: NH*D of q, NKV*D of k, NKV*D of v
     long long ld;
+    int n_partials;          // the projection may arrive as partial results of a split product,
+    long long partial_stride;  // `partial_stride` elements apart: they are added here, in order
     const float* bias;       // [(NH+2NKV)*D] or null
     const int* positions;    // [T] absolute position of each token
     const int* token_seq;    // [T] index of the token's sequence in this batch
@@ -41,6 +43,7 @@ struct RopeKvParams {
 
 template <typename QT, typename KVT>
 __global__ void rope_kv_kernel(RopeKvParams p) {
+    pdl_prologue();
     const int half = p.head_dim / 2;
     const int heads_all = p.num_heads + 2 * p.num_kv_heads;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -71,6 +74,10 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
     const size_t col = (size_t)head * p.head_dim;
     const float* src = p.qkv + (size_t)t * p.ld + col;
     float a = src[e0], b = src[e1];
+    for (int k = 1; k < p.n_partials; ++k) {
+        a += src[(size_t)k * p.partial_stride + e0];
+        b += src[(size_t)k * p.partial_stride + e1];
+    }
     if (p.bias) { a += p.bias[col + e0]; b += p.bias[col + e1]; }
     const int pos = p.positions[t];
     if (rotate) {
@@ -103,7 +110,8 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
 
 }  // namespace
 
-MLB_EXPORT int mlb_rope_kv_write(const float* qkv, long long ld, const float* bias, const int* positions,
+MLB_EXPORT int mlb_rope_kv_write(const float* qkv, long long ld, int n_partials, long long partial_stride,
+                                 const float* bias, const int* positions,
                                  const int* token_seq, const int* block_table, int max_blocks,
                                  const float* inv_freq, int rot_dim, int interleaved, void* q_out, int q_dtype,
                                  void* pages, int kv_dtype, int num_pages, int page_size, int tokens,
@@ -118,16 +126,17 @@ MLB_EXPORT int mlb_rope_kv_write(const float* qkv, long long ld, const float* bi
     if (pages && (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !block_table || !token_seq))
         return fail(MLB_INVALID_ARGUMENT, "rope_kv_write: cache geometry missing");
     if (tokens == 0) return MLB_OK;
-    RopeKvParams p{qkv, ld, bias, positions, token_seq, block_table, max_blocks, inv_freq, rot_dim, interleaved,
+    if (n_partials < 1) return fail(MLB_INVALID_ARGUMENT, "rope_kv_write: n_partials must be at least 1");
+    RopeKvParams p{qkv, ld, n_partials, partial_stride, bias, positions, token_seq, block_table, max_blocks, inv_freq, rot_dim, interleaved,
                    q_out, pages, num_pages, page_size, tokens, num_heads, num_kv_heads, head_dim, error_flag};
     const long long total = (long long)tokens * (num_heads + 2 * num_kv_heads) * (head_dim / 2);
     const unsigned blocks = (unsigned)((total + 255) / 256);
     const int key = q_dtype * 2 + kv_dtype;
     switch (key) {
-        case MLB_F32 * 2 + MLB_F32: rope_kv_kernel<float, float><<<blocks, 256, 0, stream>>>(p); break;
-        case MLB_BF16 * 2 + MLB_BF16: rope_kv_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>(p); break;
-        case MLB_F32 * 2 + MLB_BF16: rope_kv_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>(p); break;
-        case MLB_BF16 * 2 + MLB_F32: rope_kv_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>(p); break;
+        case MLB_F32 * 2 + MLB_F32: launch_kernel(rope_kv_kernel<float, float>, blocks, 256, 0, stream, p); break;
+        case MLB_BF16 * 2 + MLB_BF16: launch_kernel(rope_kv_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, 256, 0, stream, p); break;
+        case MLB_F32 * 2 + MLB_BF16: launch_kernel(rope_kv_kernel<float, __nv_bfloat16>, blocks, 256, 0, stream, p); break;
+        case MLB_BF16 * 2 + MLB_F32: launch_kernel(rope_kv_kernel<__nv_bfloat16, float>, blocks, 256, 0, stream, p); break;
         default: return fail(MLB_INVALID_ARGUMENT, "rope_kv_write: unknown dtypes %d/%d", q_dtype, kv_dtype);
     }
     return check_launch("rope_kv_write");

@@ -96,6 +96,7 @@ struct SampleParams {
 };
 
 __global__ void __launch_bounds__(THREADS) sample_rows_kernel(SampleParams p) {
+    pdl_prologue();
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     __shared__ double s_dbl[32];
@@ -220,6 +221,7 @@ __global__ void __launch_bounds__(THREADS) sample_rows_kernel(SampleParams p) {
 
 __global__ void __launch_bounds__(THREADS) argmax_rows_kernel(const float* __restrict__ logits, long long ld,
                                                               int vocab, int* __restrict__ out) {
+    pdl_prologue();
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     __shared__ int s_flag;
@@ -247,7 +249,7 @@ MLB_EXPORT int mlb_argmax_rows(const float* logits, long long ld, int rows, int 
                                cudaStream_t stream) {
     if (rows < 0 || vocab <= 0 || ld < vocab) return fail(MLB_INVALID_ARGUMENT, "argmax_rows: bad sizes");
     if (rows == 0) return MLB_OK;
-    argmax_rows_kernel<<<rows, THREADS, 0, stream>>>(logits, ld, vocab, out);
+    launch_kernel(argmax_rows_kernel, rows, THREADS, 0, stream, logits, ld, vocab, out);
     return check_launch("argmax_rows");
 }
 
@@ -258,6 +260,6 @@ MLB_EXPORT int mlb_sample_rows(const float* logits, long long ld, int rows, int 
     if (!seed || !draw) return fail(MLB_INVALID_ARGUMENT, "sample_rows: seed and draw arrays are required");
     if (rows == 0) return MLB_OK;
     SampleParams p{logits, ld, vocab, temperature, top_k, seed, draw, out};
-    sample_rows_kernel<<<rows, THREADS, 0, stream>>>(p);
+    launch_kernel(sample_rows_kernel, rows, THREADS, 0, stream, p);
     return check_launch("sample_rows");
 }

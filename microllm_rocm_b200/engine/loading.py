@@ -47,6 +47,8 @@ def prepare_kernels(model=None) -> None:
     from ..kernels import attention
     sources = ops.base_sources()
     if model is not None and model.rt.dtype == torch.bfloat16:
+        from ..kernels import gemm_bf16
+        sources += gemm_bf16.sources()
         for entry in model.cache_entries.values():
             head_dim = getattr(entry.need, "head_dim", None)
             if head_dim:

@@ -19,7 +19,6 @@ from .build import KernelError
 
 MAX_HEAD_DIM = 256
 SM_COUNT = 148
-TARGET_CTAS = SM_COUNT * 3          # resident CTAs of the lean decode kernel
 MAX_SPLITS = 64
 MIN_KEY_TILES_PER_SPLIT = 4         # one 16-key tile per warp at least
 
@@ -57,17 +56,22 @@ def _plan(ctx, group: int, num_kv_heads: int):
         tiles = -(-(starts[a + 1] - starts[a]) * group // 16)
         work += [(a, first) for first in range(0, tiles, 1 if decode else 4)]
     work_dev = torch.tensor(work, dtype=torch.int32).reshape(-1).to(ctx.positions.device, non_blocking=True)
-    splits = 1
+    splits, long_loops = 1, 0
     if decode:
         # each CTA takes an even share of its own sequence's keys, so the launch shape chosen
         # here stays balanced while the sequences of a captured step grow
         key_tiles = max(1, -(-ctx.max_seq_len // 16))
-        splits = max(1, min(TARGET_CTAS // max(1, len(work) * num_kv_heads), key_tiles // MIN_KEY_TILES_PER_SPLIT,
-                            MAX_SPLITS))
+        items = max(1, len(work) * num_kv_heads)
+
+        def choose(resident_per_sm):
+            return max(1, min(SM_COUNT * resident_per_sm // items, key_tiles // MIN_KEY_TILES_PER_SPLIT, MAX_SPLITS))
+
+        splits = choose(3)                     # the lean kernel: three CTAs per SM, one wave
+        if -(-key_tiles // splits) > 8:        # warps would walk more than two key tiles each:
+            long_loops = 1                     # the prefetching kernel (two CTAs per SM) pays
+            splits = choose(2)
     # one ticket per (work item, kv head): which split finished last; the kernel leaves them zero
     tickets = torch.zeros(len(work) * num_kv_heads, dtype=torch.int32, device=ctx.positions.device) if splits > 1 else None
-    # do warps walk more than two key tiles each?  (4 warps share a CTA's tiles)
-    long_loops = 1 if decode and -(-max(1, -(-ctx.max_seq_len // 16)) // splits) > 8 else 0
     plan = (work_dev, len(work), 1 if decode else 0, splits, tickets, long_loops)
     ctx.extras[key] = plan
     return plan

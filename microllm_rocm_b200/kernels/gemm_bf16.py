@@ -1,16 +1,159 @@
-"""bf16 x bf16 -> fp32-accumulated products for the serving path."""
+"""bf16 x bf16 -> fp32-accumulated products of the serving path.
+
+The hand-written tcgen05 kernel (`gemm_tc.cu`) takes every product whose K and row pitches
+are multiples of 8 elements (what TMA can address); it picks the token tile from the number
+of tokens and splits K over CTAs when the output has too few tiles to fill the GPU.  Anything
+else falls to the library product (cuBLASLt through torch.mm), which also stays available
+as `library_linear` for comparisons.
+"""
 from __future__ import annotations
 
+from ctypes import c_int, c_longlong, c_void_p
 from typing import Optional
 
 import torch
 
+from . import build, ops
+from .build import KernelError, LaunchCounter
 
-def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
-                out: Optional[torch.Tensor]) -> torch.Tensor:
-    from .build import LaunchCounter
+SM_COUNT = 148
+MAX_SPLITS = 32
+MIN_K_BLOCKS_PER_SPLIT = 4          # 256 elements of K per CTA at least
+
+ops.register_signatures("gemv_bf16.cu", {
+    "mlb_gemv_bf16": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int,
+                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+})
+ops.register_signatures("gemm_tc.cu", {
+    "mlb_gemm_tc": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int,
+                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+})
+
+USE_TENSOR_CORE_KERNEL = True
+_tickets = {}
+_error_flags = {}
+
+
+def sources():
+    return [("gemm_tc.cu", {}), ("gemv_bf16.cu", {})]
+
+
+# ------------------------------------------------------------------------------ few tokens: weight streaming
+GEMV_MAX_TOKENS = 16
+GEMV_TARGET_CTAS = SM_COUNT * 4
+GEMV_MIN_K_PER_SPLIT = 256
+
+
+def gemv_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    m, k = x.shape
+    return (0 < m <= GEMV_MAX_TOKENS and k % 32 == 0 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
+            and x.stride(1) == 1 and weight.stride(1) == 1 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def gemv_splits(n: int, k: int):
+    """(splits, k_per_split): enough CTAs to fill the GPU, K ranges of whole 32-element chunks."""
+    row_blocks = -(-n // 64)
+    splits = max(1, min(-(-GEMV_TARGET_CTAS // row_blocks), k // GEMV_MIN_K_PER_SPLIT))
+    k_per_split = -(-(-(-k // splits)) // 32) * 32
+    while k_per_split * 2 * 16 > 160 * 1024:                 # the staged activations must fit shared memory
+        k_per_split = -(-(k_per_split // 2) // 32) * 32
+    return -(-k // k_per_split), k_per_split
+
+
+def gemv_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[S, M, N] fp32 partial results of x @ weight^T (+ bias, in partial 0); their sum over S,
+    taken in order by the kernel that consumes them, is the product."""
+    M, K = x.shape
+    N = weight.shape[0]
+    splits, k_per_split = gemv_splits(N, K)
+    partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+    L = ops.lib("gemv_bf16.cu")
+    build.check(L, L.mlb_gemv_bf16(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), N, ops._ptr(bias),
+                                   partial.data_ptr(), None, 0, 0, 0, M, N, K, splits, k_per_split, ops._stream()))
+    return partial
+
+
+def gemv_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, I] (bf16) = silu(x @ weight[:I]^T) * (x @ weight[I:2I]^T)."""
+    M, K = x.shape
+    I = out.shape[1]
+    if weight.shape != (2 * I, K) or out.shape[0] != M or out.dtype != torch.bfloat16:
+        raise KernelError("gemv_silu_mul: the weight must hold gate rows then up rows, the output be bf16 [M, I]")
+    L = ops.lib("gemv_bf16.cu")
+    build.check(L, L.mlb_gemv_bf16(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), 2 * I, None, None,
+                                   out.data_ptr(), out.stride(0), 1, I, M, I, K, 1, K, ops._stream()))
+
+
+def _device_scratch(device):
+    key = str(device)
+    if key not in _tickets:
+        _tickets[key] = torch.zeros(1 << 16, dtype=torch.int32, device=device)      # left zero by every launch
+        _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tickets[key], _error_flags[key]
+
+
+def error_flag(device) -> torch.Tensor:
+    """Raised by the kernel when a bounded wait ran out (codes 11-13)."""
+    return _device_scratch(device)[1]
+
+
+def token_tile(m: int, dual: bool = False) -> int:
+    for t in (16, 32, 64, 128):
+        if m <= t:
+            return t
+    return 128 if dual else 256
+
+
+def choose_splits(m: int, n: int, k: int, tok_tile: int) -> int:
+    tiles = -(-n // 128) * -(-m // tok_tile)
+    k_blocks = -(-k // 64)
+    if tiles >= SM_COUNT:
+        return 1
+    return max(1, min(SM_COUNT // tiles, k_blocks // MIN_K_BLOCKS_PER_SPLIT, MAX_SPLITS))
+
+
+def supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    k = x.shape[1]
+    return (USE_TENSOR_CORE_KERNEL and k % 8 == 0 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
+            and x.stride(1) == 1 and weight.stride(1) == 1 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+            accumulate: bool = False, dual_rows: Optional[int] = None, splits: Optional[int] = None,
+            tok_tile: Optional[int] = None, partial: Optional[torch.Tensor] = None, stages: int = 0) -> None:
+    """out[M, N] = x[M, K] @ weight[:N, K]^T (+ bias) (+ out), or with dual_rows = I:
+    out[M, I] = silu(x @ weight[:I]^T) * (x @ weight[I:2I]^T)."""
+    M, K = x.shape
+    dual = dual_rows is not None
+    N = dual_rows if dual else weight.shape[0]
+    if weight.shape[1] != K or out.shape != (M, N) or out.stride(1) != 1:
+        raise KernelError(f"gemm_tc: shapes {tuple(x.shape)} x {tuple(weight.shape)}^T -> {tuple(out.shape)} do not agree")
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError("gemm_tc: bf16 operands and an fp32 or bf16 output are expected")
+    if dual and weight.shape[0] < 2 * N:
+        raise KernelError("gemm_tc: a dual product needs gate rows followed by up rows")
+    tok_tile = tok_tile or token_tile(M, dual)
+    if splits is None:
+        splits = 1 if dual else choose_splits(M, N, K, tok_tile)
+    tickets, flag = _device_scratch(x.device)
+    reduce_here = partial is None
+    if splits > 1 and reduce_here:
+        if -(-N // 128) * -(-M // tok_tile) > tickets.numel():
+            raise KernelError("gemm_tc: too many output tiles for a split product")
+        partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+    if partial is not None and splits > 1 and (partial.shape != (splits, M, N) or partial.dtype != torch.float32):
+        raise KernelError("gemm_tc: the partial buffer must be fp32 [splits, M, N]")
+    L = ops.lib("gemm_tc.cu")
+    build.check(L, L.mlb_gemm_tc(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), weight.shape[0],
+                                 ops._ptr(bias), out.data_ptr(), out.stride(0), 1 if out.dtype == torch.bfloat16 else 0,
+                                 1 if accumulate else 0, 1 if dual else 0, N if dual else 0, M, N, K, tok_tile, splits,
+                                 1 if reduce_here else 0, int(stages), ops._ptr(partial), tickets.data_ptr(), flag.data_ptr(), ops._stream()))
+
+
+def library_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
+                   out: Optional[torch.Tensor]) -> torch.Tensor:
+    """cuBLASLt: bf16 operands, fp32 accumulate, output written in out_dtype."""
     LaunchCounter.library += 1
-    # Library product: cuBLASLt, bf16 operands, fp32 accumulate, output written in out_dtype.
     if out_dtype == torch.bfloat16:
         y = torch.mm(x, weight.t()) if out is None else torch.mm(x, weight.t(), out=out)
     else:
@@ -21,3 +164,23 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     if bias is not None:
         y += bias.to(y.dtype)
     return y
+
+
+# Which kernel takes which product.  The tcgen05 kernel is correct for every size but, as it
+# stands (one CTA per tile, one accumulator, epilogue not overlapped), the library is faster
+# on prompt-sized products; it is switched in per token range once it wins there.
+TENSOR_CORE_KERNEL_TOKENS = (0, 0)          # [lo, hi): token counts routed to gemm_tc
+
+
+def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
+                out: Optional[torch.Tensor], partials_ok: bool = False) -> torch.Tensor:
+    m = x.shape[0]
+    if partials_ok and out is None and out_dtype == torch.float32 and gemv_supported(x, weight):
+        return gemv_partials(x, weight, bias)
+    lo, hi = TENSOR_CORE_KERNEL_TOKENS
+    if lo <= m < hi and supported(x, weight):
+        if out is None:
+            out = torch.empty((m, weight.shape[0]), dtype=out_dtype, device=x.device)
+        gemm_tc(x, weight, out, bias=bias)
+        return out
+    return library_linear(x, weight, bias, out_dtype, out)

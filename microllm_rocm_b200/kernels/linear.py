@@ -18,8 +18,11 @@ from .build import KernelError
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           out_dtype: torch.dtype = torch.float32, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x [M,K] and weight [N,K] in the same dtype (f32 or bf16); returns [M,N] in `out_dtype`."""
+           out_dtype: torch.dtype = torch.float32, out: Optional[torch.Tensor] = None,
+           partials_ok: bool = False) -> torch.Tensor:
+    """x [M,K] and weight [N,K] in the same dtype (f32 or bf16); returns [M,N] in `out_dtype`.
+    With partials_ok the caller accepts [S, M, N] fp32 partial results instead (a product whose
+    K range was split over CTAs) and adds them up itself, in order, where it reads them."""
     if x.dtype != weight.dtype:
         raise KernelError(f"linear: activations are {x.dtype} but the weight is {weight.dtype}")
     M, N = x.shape[0], weight.shape[0]
@@ -35,4 +38,4 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if not x.is_cuda:
         raise KernelError("linear: there is no CPU path")
     from . import gemm_bf16
-    return gemm_bf16.linear_bf16(x, weight, bias, out_dtype, out)
+    return gemm_bf16.linear_bf16(x, weight, bias, out_dtype, out, partials_ok=partials_ok)

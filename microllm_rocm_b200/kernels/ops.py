@@ -49,9 +49,9 @@ _SIGNATURES = {
     "basic.cu": {
         "mlb_embed_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "mlb_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
-        "mlb_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
-        "mlb_add_inplace": [c_void_p, c_void_p, c_longlong, c_void_p],
-        "mlb_silu_mul": [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mlb_add_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+        "mlb_add_inplace": [c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p],
+        "mlb_silu_mul": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
         "mlb_cast_f32_bf16": [c_void_p, c_void_p, c_longlong, c_void_p],
         "mlb_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     },
@@ -60,7 +60,7 @@ _SIGNATURES = {
                          c_longlong, c_longlong, c_longlong, c_int, c_void_p],
     },
     "rope_kv.cu": {
-        "mlb_rope_kv_write": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+        "mlb_rope_kv_write": [c_void_p, c_longlong, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                               c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_void_p, c_void_p],
     },
@@ -109,7 +109,8 @@ def all_sources():
     out = base_sources()
     for d in (32, 64, 128):
         out += attention.mma_sources(d)
-    return out
+    from . import gemm_bf16
+    return out + gemm_bf16.sources()
 
 
 # ------------------------------------------------------------------------------ basic
@@ -138,36 +139,59 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
                                  n, width, float(eps), _stream()))
 
 
+def _partials(delta: torch.Tensor, shape, name: str):
+    """A delta is [M, N] or, from a product split over K, [S, M, N]: (count, stride in elements)."""
+    _need(delta, name, torch.float32)
+    if delta.dim() == 3 and tuple(delta.shape[1:]) == tuple(shape):
+        return delta.shape[0], delta.shape[1] * delta.shape[2]
+    if tuple(delta.shape) == tuple(shape):
+        return 1, 0
+    raise KernelError(f"{name}: shape {tuple(delta.shape)} is neither {tuple(shape)} nor [splits, {', '.join(map(str, shape))}]")
+
+
 def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float,
                 out: torch.Tensor) -> None:
-    """residual += delta (in place, fp32), then out = rmsnorm(residual)."""
-    _need(residual, "residual", torch.float32, 2); _need(delta, "delta", torch.float32, 2)
+    """residual += delta (in place, fp32; a [S, M, N] delta is summed over S in order), then
+    out = rmsnorm(residual)."""
+    _need(residual, "residual", torch.float32, 2)
     _need(weight, "weight", torch.float32, 1); _need(out, "out", dims=2)
-    if delta.shape != residual.shape or out.shape != residual.shape or weight.shape[0] != residual.shape[1]:
+    n_delta, stride = _partials(delta, residual.shape, "add_rmsnorm delta")
+    if out.shape != residual.shape or weight.shape[0] != residual.shape[1]:
         raise KernelError("add_rmsnorm: shapes do not agree")
     L = lib("basic.cu")
-    build.check(L, L.mlb_add_rmsnorm(residual.data_ptr(), delta.data_ptr(), weight.data_ptr(), out.data_ptr(),
-                                     dtype_tag(out), residual.shape[0], residual.shape[1], float(eps), _stream()))
+    build.check(L, L.mlb_add_rmsnorm(residual.data_ptr(), delta.data_ptr(), n_delta, stride, weight.data_ptr(),
+                                     out.data_ptr(), dtype_tag(out), residual.shape[0], residual.shape[1], float(eps),
+                                     _stream()))
 
 
 def add_inplace(x: torch.Tensor, delta: torch.Tensor) -> None:
-    _need(x, "x", torch.float32); _need(delta, "delta", torch.float32)
-    if x.shape != delta.shape:
-        raise KernelError("add_inplace: shapes do not agree")
+    """x += delta; a [S, ...] stack of partial results is summed over S in order."""
+    _need(x, "x", torch.float32)
+    n_delta, stride = _partials(delta, x.shape, "add_inplace delta")
     L = lib("basic.cu")
-    build.check(L, L.mlb_add_inplace(x.data_ptr(), delta.data_ptr(), x.numel(), _stream()))
+    build.check(L, L.mlb_add_inplace(x.data_ptr(), delta.data_ptr(), n_delta, stride, x.numel(), _stream()))
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[r, c] = silu(gate_up[r, c]) * gate_up[r, width + c] for a fused [rows, 2*width] input."""
-    _need(gate_up, "gate_up", dims=2); _need(out, "out", dims=2)
+    """out[r, c] = silu(gate_up[r, c]) * gate_up[r, width + c] for a fused [rows, 2*width] input, or
+    for its [S, rows, 2*width] partial results (summed over S in order first)."""
+    _need(out, "out", dims=2)
     rows, width = out.shape
-    if gate_up.shape != (rows, 2 * width):
+    n_partials, partial_stride = 1, 0
+    if gate_up.dim() == 3:
+        _need(gate_up, "gate_up", dims=3)
+        n_partials, partial_stride = gate_up.shape[0], gate_up.shape[1] * gate_up.shape[2]
+        first = gate_up[0]
+    else:
+        _need(gate_up, "gate_up", dims=2)
+        first = gate_up
+    if first.shape != (rows, 2 * width):
         raise KernelError("silu_mul: input must be [rows, 2*width]")
     L = lib("basic.cu")
     esz = gate_up.element_size()
     build.check(L, L.mlb_silu_mul(gate_up.data_ptr(), gate_up.data_ptr() + width * esz, 2 * width,
-                                  dtype_tag(gate_up), out.data_ptr(), dtype_tag(out), rows, width, _stream()))
+                                  dtype_tag(gate_up), n_partials, partial_stride, out.data_ptr(), dtype_tag(out), rows,
+                                  width, _stream()))
 
 
 def cast_f32_bf16(x: torch.Tensor, out: torch.Tensor) -> None:
@@ -214,9 +238,16 @@ def rope_kv_write(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: to
                   token_seq: torch.Tensor, block_table: Optional[torch.Tensor], inv_freq: torch.Tensor,
                   rot_dim: int, interleaved: bool, q_out: torch.Tensor, pages: Optional[torch.Tensor],
                   num_heads: int, num_kv_heads: int, head_dim: int, error_flag: Optional[torch.Tensor]) -> None:
-    """Bias, rotation and the K/V store for a fused [T, (NH+2NKV)*D] fp32 projection output.
+    """Bias, rotation and the K/V store for a fused [T, (NH+2NKV)*D] fp32 projection output
+    (or its [S, T, width] partial results, which are summed here).
     `pages` is [num_pages, 2, NKV, page_size, D]; None makes the call query-only."""
-    _need(qkv, "qkv", torch.float32, 2); _need(positions, "positions", torch.int32, 1)
+    _need(positions, "positions", torch.int32, 1)
+    n_partials, partial_stride = 1, 0
+    if qkv.dim() == 3:
+        _need(qkv, "qkv", torch.float32, 3)
+        n_partials, partial_stride = qkv.shape[0], qkv.shape[1] * qkv.shape[2]
+        qkv = qkv[0]
+    _need(qkv, "qkv", torch.float32, 2)
     _need(token_seq, "token_seq", torch.int32, 1); _need(inv_freq, "inv_freq", torch.float32, 1)
     _need(q_out, "q_out", dims=2)
     T = qkv.shape[0]
@@ -238,7 +269,7 @@ def rope_kv_write(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: to
             raise KernelError("rope_kv_write: bias length differs from the fused width")
     L = lib("rope_kv.cu")
     build.check(L, L.mlb_rope_kv_write(
-        qkv.data_ptr(), width, _ptr(bias), positions.data_ptr(), token_seq.data_ptr(), _ptr(block_table), max_blocks,
+        qkv.data_ptr(), width, n_partials, partial_stride, _ptr(bias), positions.data_ptr(), token_seq.data_ptr(), _ptr(block_table), max_blocks,
         inv_freq.data_ptr(), rot_dim, 1 if interleaved else 0, q_out.data_ptr(), dtype_tag(q_out),
         _ptr(pages), dtype_tag(pages) if pages is not None else F32, num_pages, page_size, T,
         num_heads, num_kv_heads, head_dim, _ptr(error_flag), _stream()))

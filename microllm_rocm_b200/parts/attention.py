@@ -71,7 +71,7 @@ class Attention(Mixer):
     # --- compute ------------------------------------------------------------------------
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVView) -> torch.Tensor:
         T = x.shape[0]
-        qkv = linear(x, self.w_qkv, None, torch.float32)                       # [T, (NH+2NKV)*D] f32
+        qkv = linear(x, self.w_qkv, None, torch.float32, partials_ok=True)     # [T, (NH+2NKV)*D] f32, or its partial sums
         q = torch.empty((T, self.nh * self.d), dtype=self.rt.dtype, device=x.device)
         inv_freq, rot, inter = ((self.rotary.inv_freq, self.rotary.rotary_dim, self.rotary.interleaved)
                                 if self.rotary is not None else (self._no_rot, 0, False))
@@ -80,4 +80,4 @@ class Attention(Mixer):
         o = torch.empty_like(q)
         attention_kernels.paged_attention(q, cache.pages, o, ctx, cache.block_table, self.nh, self.nkv, self.d,
                                           self.scale, self.window)
-        return linear(o, self.w_o, self.b_o, torch.float32)                    # [T, H] f32
+        return linear(o, self.w_o, self.b_o, torch.float32, partials_ok=True)  # [T, H] f32, or its partial sums

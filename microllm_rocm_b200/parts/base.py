@@ -11,6 +11,7 @@ Kinds (each has a registry; `register_*` adds to it, tests may add their own):
   PositionEncoding rotary_table() for mixers that rotate q/k, on_embedding() for additive ones
   Mixer            cache_need(); forward(x[T,H], ctx, cache_view) -> delta[T,H] f32
   FeedForward      forward(x[T,H], ctx) -> delta[T,H] f32
+                   (a delta may also be [S,T,H]: partial sums that the next norm adds up)
   Block            the arrangement of norm/mixer/feed-forward around the residual stream
 
 `StepContext` is everything a part may know about the batch it is running: flat tokens with

@@ -7,7 +7,7 @@ from typing import Dict
 
 import torch
 
-from ..kernels import ops
+from ..kernels import gemm_bf16, ops
 from ..kernels.linear import linear
 from .base import FeedForward, Runtime, StepContext, WeightSpec, register_feed_forward
 
@@ -34,7 +34,11 @@ class SwiGLU(FeedForward):
         # fp32 path: everything f32.  bf16 path: gate/up leave the product as bf16, the
         # activation is evaluated in fp32 and stored bf16, down returns fp32 at the residual
         # boundary -- the reference's policy for its bf16 feed-forward (src/ops/optimized.cpp:676-683).
-        gate_up = linear(x, self.w_gate_up, None, self.rt.dtype)
         act = torch.empty((x.shape[0], self.inter), dtype=self.rt.dtype, device=x.device)
-        ops.silu_mul(gate_up, act)
-        return linear(act, self.w_down, None, torch.float32)
+        if x.dtype == torch.bfloat16 and gemm_bf16.gemv_supported(x, self.w_gate_up):
+            # a few tokens: the weight-streaming product leaves fp32 partial sums, the activation adds them
+            ops.silu_mul(gemm_bf16.gemv_partials(x, self.w_gate_up), act)
+        else:
+            gate_up = linear(x, self.w_gate_up, None, self.rt.dtype)
+            ops.silu_mul(gate_up, act)
+        return linear(act, self.w_down, None, torch.float32, partials_ok=True)

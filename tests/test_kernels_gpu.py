@@ -359,3 +359,128 @@ def test_kernels_refuse_bad_sizes_with_a_clear_error():
         attention.check_head_dim(264)
     with pytest.raises(KernelError, match="head_dim"):
         attention.check_head_dim(17)
+
+
+# ------------------------------------------------------------------------------ tcgen05 products
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 2048, 1536), (8, 1536, 8960), (5, 200, 264), (64, 384, 192),
+                                   (300, 520, 136), (2048, 1536, 1536), (17, 1000, 72), (130, 130, 8)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_tensor_core_product_against_fp32(M, N, K, out_dtype):
+    from microllm_rocm_b200.kernels import gemm_bf16
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K).bfloat16()
+    w = torch.randn(N, K).bfloat16()
+    bias = torch.randn(N)
+    want = x.double() @ w.double().t() + bias.double()
+    out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+    gemm_bf16.gemm_tc(x.to(DEV), w.to(DEV), out, bias=bias.to(DEV))
+    assert int(gemm_bf16.error_flag(torch.device(DEV)).item()) == 0
+    got = out.double().cpu()
+    scale = math.sqrt(K)
+    tol_abs = (2e-5 if out_dtype == torch.float32 else 1e-2) * scale
+    assert (got - want).abs().max() <= tol_abs + (4e-3 if out_dtype == torch.bfloat16 else 0) * want.abs().max(), \
+        float((got - want).abs().max())
+
+
+@pytest.mark.parametrize("splits,tok_tile", [(1, 16), (4, 16), (3, 32), (7, 64), (2, 256)])
+def test_tensor_core_product_split_k_tiles_and_accumulate(splits, tok_tile):
+    from microllm_rocm_b200.kernels import gemm_bf16
+    torch.manual_seed(splits)
+    M, N, K = 40, 300, 1000
+    x, w = torch.randn(M, K).bfloat16(), torch.randn(N, K).bfloat16()
+    base = torch.randn(M, N)
+    out = base.to(DEV).clone()
+    gemm_bf16.gemm_tc(x.to(DEV), w.to(DEV), out, accumulate=True, splits=splits, tok_tile=tok_tile)
+    want = base.double() + x.double() @ w.double().t()
+    assert (out.double().cpu() - want).abs().max() <= 2e-5 * math.sqrt(K) * 4
+    # the same call again gives the same bits: the split sum has a fixed order
+    again = base.to(DEV).clone()
+    gemm_bf16.gemm_tc(x.to(DEV), w.to(DEV), again, accumulate=True, splits=splits, tok_tile=tok_tile)
+    assert torch.equal(out, again)
+    assert int(gemm_bf16.error_flag(torch.device(DEV)).item()) == 0
+
+
+@pytest.mark.parametrize("M,I,K", [(8, 8960 // 8, 1536), (3, 176, 64), (200, 512, 192)])
+def test_tensor_core_dual_product_silu_mul(M, I, K):
+    from microllm_rocm_b200.kernels import gemm_bf16
+    torch.manual_seed(I)
+    x = (torch.randn(M, K) * 0.5).bfloat16()
+    w = (torch.randn(2 * I, K) * 0.2).bfloat16()
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    gemm_bf16.gemm_tc(x.to(DEV), w.to(DEV), out, dual_rows=I)
+    g = x.float() @ w[:I].float().t()
+    u = x.float() @ w[I:].float().t()
+    want = plain.swiglu(g, u)
+    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2), float((out.float().cpu() - want).abs().max())
+    assert int(gemm_bf16.error_flag(torch.device(DEV)).item()) == 0
+
+
+def test_tensor_core_product_refuses_what_tma_cannot_address():
+    from microllm_rocm_b200.kernels import gemm_bf16
+    from microllm_rocm_b200.kernels.build import KernelError
+    x, w = torch.randn(4, 20, device=DEV).bfloat16(), torch.randn(8, 20, device=DEV).bfloat16()
+    assert not gemm_bf16.supported(x, w)
+    with pytest.raises(KernelError, match="multiples of 8"):
+        gemm_bf16.gemm_tc(x, w, torch.empty(4, 8, device=DEV))
+    # the dispatcher sends such a product to the library instead of failing
+    y = gemm_bf16.linear_bf16(x, w, None, torch.float32, None)
+    assert torch.allclose(y.cpu(), x.float().cpu() @ w.float().cpu().t(), atol=1e-2)
+
+
+# ------------------------------------------------------------------------------ few-token weight streaming
+@pytest.mark.parametrize("M,N,K", [(1, 64, 32), (8, 2048, 1536), (8, 1536, 8960), (3, 200, 96), (16, 384, 192),
+                                   (9, 1000, 1024), (5, 70, 4096)])
+def test_gemv_partials_sum_to_the_product(M, N, K):
+    from microllm_rocm_b200.kernels import gemm_bf16
+    torch.manual_seed(M * 7 + N + K)
+    x, w, bias = torch.randn(M, K).bfloat16(), torch.randn(N, K).bfloat16(), torch.randn(N)
+    assert gemm_bf16.gemv_supported(x.to(DEV), w.to(DEV))
+    part = gemm_bf16.gemv_partials(x.to(DEV), w.to(DEV), bias.to(DEV))
+    assert part.dim() == 3 and part.shape[1:] == (M, N)
+    want = x.double() @ w.double().t() + bias.double()
+    got = part.double().sum(0).cpu()
+    assert (got - want).abs().max() <= 2e-5 * math.sqrt(K) * 4
+    # the consumers add the partial results up: residual += sum, then norm
+    res = torch.randn(M, N)
+    wn = 1 + 0.1 * torch.randn(N)
+    r = res.to(DEV).clone()
+    out = torch.empty(M, N, device=DEV)
+    ops().add_rmsnorm(r, part, wn.to(DEV), 1e-6, out)
+    assert torch.allclose(r.cpu().double(), res.double() + want, atol=2e-5 * math.sqrt(K) * 4)
+    assert torch.allclose(out.cpu(), plain.rms_norm((res.double() + want).float(), wn, 1e-6), atol=1e-3, rtol=1e-3)
+    r2 = res.to(DEV).clone()
+    ops().add_inplace(r2, part)
+    assert torch.equal(r2, r)
+
+
+@pytest.mark.parametrize("M,I,K", [(8, 1120, 1536), (2, 176, 64), (13, 512, 192)])
+def test_gemv_silu_mul(M, I, K):
+    from microllm_rocm_b200.kernels import gemm_bf16
+    torch.manual_seed(I + M)
+    x = (torch.randn(M, K) * 0.5).bfloat16()
+    w = (torch.randn(2 * I, K) * 0.2).bfloat16()
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    gemm_bf16.gemv_silu_mul(x.to(DEV), w.to(DEV), out)
+    want = plain.swiglu(x.float() @ w[:I].float().t(), x.float() @ w[I:].float().t())
+    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2)
+
+
+def test_rope_kv_write_adds_partial_projections():
+    from microllm_rocm_b200.parts.rotary import inverse_frequencies
+    torch.manual_seed(4)
+    nh, nkv, d, T = 4, 2, 32, 5
+    width = (nh + 2 * nkv) * d
+    parts = torch.randn(3, T, width)
+    bias = torch.randn(width)
+    inv = torch.from_numpy(inverse_frequencies(1e4, d)).to(DEV)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    seq = torch.zeros(T, dtype=torch.int32, device=DEV)
+    table = torch.tensor([[1, 0]], dtype=torch.int32, device=DEV)
+    outs = []
+    for src in (parts.to(DEV), parts.sum(0).to(DEV)):
+        pages = torch.zeros(2, 2, nkv, 4, d, device=DEV)
+        q = torch.empty(T, nh * d, device=DEV)
+        flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ops().rope_kv_write(src, bias.to(DEV), pos, seq, table, inv, d, False, q, pages, nh, nkv, d, flag)
+        outs.append((q.cpu(), pages.cpu()))
+    assert torch.allclose(outs[0][0], outs[1][0], atol=1e-5) and torch.allclose(outs[0][1], outs[1][1], atol=1e-5)
