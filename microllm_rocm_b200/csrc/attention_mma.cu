@@ -16,15 +16,16 @@
 // Two launch shapes of the same warp routine:
 //   prefill  one CTA = 4 warps = 4 consecutive row tiles; no key split
 //   decode   one CTA = one row tile, its 4 warps take every 4th key tile and are merged in
-//            shared memory; the keys are further split over gridDim.z CTAs that leave partial
-//            results (normalised output + log-sum-exp) in scratch memory, and the CTA that
-//            finishes last merges them, always in split order.
+//            shared memory; the keys are further split over a thread-block cluster whose CTAs
+//            combine their results through distributed shared memory, in rank order.
 //
 // Operand layout trick: mma.sync only needs A and B to agree on which contraction index a
 // register holds.  Thread t of a quad therefore loads 8 CONSECUTIVE head elements of a key
 // (one 16-byte load) and uses them as the fragments of two k-steps; Q is read from shared
 // memory with the same permutation.  For V the output columns are permuted instead.
 #include "common.cuh"
+
+#include <cooperative_groups.h>
 
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=<multiple of 32, at most 256>"
@@ -49,9 +50,6 @@ struct FaParams {
     const __nv_bfloat16* q;         // [T, NH*D]
     const __nv_bfloat16* pages;     // [num_pages, 2, NKV, page_size, D]
     __nv_bfloat16* out;             // [T, NH*D]
-    float* part_o;                  // [T*NH, splits, D]   scratch, decode with splits > 1
-    float* part_lse;                // [T*NH, splits]
-    int* tickets;                   // [num_work * NKV] zero between launches: which split finished last
     const int* seq_starts;          // [A+1] first flat token of each sequence
     const int* seq_pos0;            // [A]   tokens cached before this step
     const int* block_table;         // [A, max_blocks]
@@ -60,7 +58,6 @@ struct FaParams {
     int num_heads, num_kv_heads, group;
     int window;
     float scale_log2;               // softmax scale * log2(e)
-    int splits;
     int* error_flag;
 };
 
@@ -382,73 +379,76 @@ __global__ void __launch_bounds__(WARPS * 32) fa_prefill_kernel(FaParams p) {
 }
 
 // ---------------------------------------------------------------------------------- decode
-// Shared memory of the decode kernel (dynamic): the query tile, then per warp its output
-// fragments in thread order (conflict free), its row maxima and sums, and the weights of the
-// final merge.
+// Every sequence brings ONE token.  A thread-block CLUSTER of `splits` CTAs (1, 2, 4 or 8)
+// shares the keys of one (sequence, kv head, row tile): each CTA walks an even share of the
+// key tiles, its four warps are merged in its own shared memory, and after one cluster barrier
+// every CTA combines a slice of the head dimension by reading the other CTAs' results through
+// distributed shared memory.  Nothing is staged in global memory and no second launch or
+// atomic is needed; the sum over CTAs always runs in rank order.
 constexpr int FRAGS = NB_O * 4;
-constexpr int MAX_SPLITS = 64;
+constexpr int MAX_SPLITS = 8;
+// shared memory (dynamic): queries | per-warp fragments [WARPS][FRAGS][32] | warp max/sum |
+// this CTA's merged rows [16][D] with their max and sum | block table
 constexpr size_t DECODE_SMEM = 16 * Q_STRIDE * sizeof(__nv_bfloat16) + (size_t)WARPS * FRAGS * 32 * sizeof(float) +
-                               2 * WARPS * 16 * sizeof(float) + 16 * MAX_SPLITS * sizeof(float) + 16 +
+                               2 * WARPS * 16 * sizeof(float) + (size_t)16 * D * sizeof(float) + 32 * sizeof(float) +
                                TABLE_SPAN * sizeof(int);
 
-template <bool PREFETCH>
-__global__ void __launch_bounds__(WARPS * 32, PREFETCH ? 2 : 3) fa_decode_kernel(FaParams p) {
+__global__ void __launch_bounds__(WARPS * 32, 2) fa_decode_kernel(FaParams p) {
     pdl_prologue();
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     float* frag = reinterpret_cast<float*>(smem_raw + 16 * Q_STRIDE * sizeof(__nv_bfloat16));   // [WARPS][FRAGS][32]
     float* warp_m = frag + WARPS * FRAGS * 32;        // [WARPS][16]
     float* warp_l = warp_m + WARPS * 16;              // [WARPS][16]
-    float* split_w = warp_l + WARPS * 16;             // [16][MAX_SPLITS] normalised weights of the final merge
-    int* ticket_s = reinterpret_cast<int*>(split_w + 16 * MAX_SPLITS);
-    int* table_s = ticket_s + 4;
+    float* cta_o = warp_l + WARPS * 16;               // [16][D]  this CTA's rows, scaled to cta_m
+    float* cta_m = cta_o + 16 * D;                    // [16]
+    float* cta_l = cta_m + 16;                        // [16]
+    int* table_s = reinterpret_cast<int*>(cta_l + 16);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+
+    // one token per sequence: the work item is (sequence, row tile) = blockIdx.x, no lookup
+    const int tiles_per_seq = (p.group + 15) / 16;
     TileGeometry geo;
-    if (!geometry(p, blockIdx.x, 0, blockIdx.y, geo)) return;          // uniform over the CTA
-    const int rows_valid = min(16, geo.n_new * p.group - geo.row0);
-    const bool upper = rows_valid > 8;                                // rows 8..15 hold anything at all
-    // queries: only rows that exist are read, the rest of the tile is zero
+    geo.seq = blockIdx.x / tiles_per_seq;
+    geo.kvh = blockIdx.y;
+    geo.token0 = geo.seq;
+    geo.n_new = 1;
+    geo.row0 = (blockIdx.x % tiles_per_seq) * 16;
+    const int rows_valid = min(16, p.group - geo.row0);
+    const bool upper = rows_valid > 8;
+    // first trip to memory, all at once: the sequence's length, its queries, its block table
+    const int pos0_load = __ldg(p.seq_pos0 + geo.seq);
     {
         constexpr int VEC_PER_ROW = D / 8;
         for (int i = threadIdx.x; i < 16 * VEC_PER_ROW; i += WARPS * 32) {
             const int r = i / VEC_PER_ROW, c = (i % VEC_PER_ROW) * 8;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (r < rows_valid) {
-                const int tok = geo.token_of(r, p.group);
-                const int head = geo.kvh * p.group + (geo.row0 + r) % p.group;
-                v = load16(p.q + ((size_t)(geo.token0 + tok) * p.num_heads + head) * D + c);
+                const int head = geo.kvh * p.group + geo.row0 + r;
+                v = load16(p.q + ((size_t)geo.token0 * p.num_heads + head) * D + c);
             }
             *reinterpret_cast<uint4*>(q_s + r * Q_STRIDE + c) = v;
         }
     }
-    const int first_tok = geo.token_of(0, p.group);
-    const int last_tok = min(geo.token_of(15, p.group), geo.n_new - 1);
-    const int first_pos = geo.pos0 + first_tok, last_pos = geo.pos0 + last_tok;
-    const int lo = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
-    int tile_begin = lo / 16, tile_end = last_pos / 16 + 1;
-    if (p.splits > 1) {                       // this CTA's even share of the sequence's key tiles
-        const int per_split = (tile_end - tile_begin + p.splits - 1) / p.splits;
-        tile_begin += (int)blockIdx.z * per_split;
-        tile_end = min(tile_end, tile_begin + per_split);
-    }
     PageTable pt;
-    fill_page_table(pt, table_s, p.block_table + (size_t)geo.seq * p.max_blocks, p.max_blocks,
-                    tile_begin * 16 / p.page_size, max(tile_begin, tile_end - 1) * 16 / p.page_size, threadIdx.x, WARPS * 32);
-    // where this thread's two rows (g and g+8) go
-    size_t out_row[2];
-    bool row_ok[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int r = g + 8 * i;
-        row_ok[i] = r < rows_valid;
-        const int tok = row_ok[i] ? geo.token_of(r, p.group) : 0;
-        const int head = geo.kvh * p.group + (geo.row0 + r) % p.group;
-        out_row[i] = (size_t)(geo.token0 + tok) * p.num_heads + head;
+    fill_page_table(pt, table_s, p.block_table + (size_t)geo.seq * p.max_blocks, p.max_blocks, 0, p.max_blocks - 1,
+                    threadIdx.x, WARPS * 32);
+    geo.pos0 = pos0_load;
+    const int last_pos = geo.pos0;
+    const int lo = (p.window > 0 && last_pos - p.window + 1 > 0) ? last_pos - p.window + 1 : 0;
+    int tile_begin = lo / 16, tile_end = last_pos / 16 + 1;
+    const int splits = (int)gridDim.z, rank = (int)blockIdx.z;
+    if (splits > 1) {                        // this CTA's even share of the sequence's key tiles
+        const int per_split = (tile_end - tile_begin + splits - 1) / splits;
+        tile_begin += rank * per_split;
+        tile_end = min(tile_end, tile_begin + per_split);
     }
     __syncthreads();
     RowState st;
     init_state(st);
-    attend<PREFETCH>(p, geo, pt, q_s, tile_begin, tile_end, warp, WARPS, last_pos, st);
+    attend<USE_PREFETCH>(p, geo, pt, q_s, tile_begin, tile_end, warp, WARPS, last_pos, st);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 1);
@@ -469,92 +469,59 @@ __global__ void __launch_bounds__(WARPS * 32, PREFETCH ? 2 : 3) fa_decode_kernel
         warp_l[warp * 16 + g] = st.l[0]; warp_l[warp * 16 + g + 8] = st.l[1];
     }
     __syncthreads();
-    float m_all[2], inv_l[2], scale_w[2][WARPS];
+    float scale_w[2][WARPS];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r = g + 8 * i;
-        m_all[i] = -INFINITY;
+        float m_all = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) m_all[i] = fmaxf(m_all[i], warp_m[w * 16 + r]);
+        for (int w = 0; w < WARPS; ++w) m_all = fmaxf(m_all, warp_m[w * 16 + r]);
         float l_all = 0.0f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
             const float mw = warp_m[w * 16 + r];
-            scale_w[i][w] = (mw == -INFINITY) ? 0.0f : exp2f(mw - m_all[i]);
+            scale_w[i][w] = (mw == -INFINITY) ? 0.0f : exp2f(mw - m_all);
             l_all += warp_l[w * 16 + r] * scale_w[i][w];
         }
-        inv_l[i] = l_all > 0.0f ? 1.0f / l_all : 0.0f;
-        if (p.splits > 1 && warp == 0 && t == 0 && row_ok[i])
-            p.part_lse[out_row[i] * p.splits + blockIdx.z] = l_all > 0.0f ? m_all[i] + log2f(l_all) : -INFINITY;
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) scale_w[i][w] *= inv_l[i];
+        if (warp == 0 && t == 0) { cta_m[r] = m_all; cta_l[r] = l_all; }
     }
 #pragma unroll
     for (int k = 0; k < FRAGS / WARPS; ++k) {
         const int idx = warp + k * WARPS;              // this thread merges fragment idx of all warps
-        const int nbo = idx >> 2, e = idx & 3, i = e >> 1;
+        const int nbo = idx >> 2, e = idx & 3, i = e >> 1, r = g + 8 * i;
         const int dim = out_dim(nbo, e, t);
-        if (dim >= D || !row_ok[i]) continue;
+        if (dim >= D || r >= rows_valid) continue;
         float val = 0.0f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) val += frag[(w * FRAGS + idx) * 32 + lane] * scale_w[i][w];
-        if (p.splits > 1) p.part_o[(out_row[i] * p.splits + blockIdx.z) * D + dim] = val;
-        else p.out[out_row[i] * D + dim] = __float2bfloat16_rn(val);
+        cta_o[r * D + dim] = val;
     }
-    if (p.splits == 1) return;
-    // the CTA that finishes last for this (row tile, kv head) merges the splits: no second launch
-    const int work_slot = blockIdx.x * p.num_kv_heads + blockIdx.y;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) *ticket_s = atomicAdd(p.tickets + work_slot, 1);
-    __syncthreads();
-    if (*ticket_s != p.splits - 1) return;
-    __threadfence();
-    if (threadIdx.x == 0) p.tickets[work_slot] = 0;        // ready for the next launch
-    // weights 2^(lse_s - max) / sum of every row at once: one warp per row, one lane per split
-    for (int r = warp; r < rows_valid; r += WARPS) {
-        const int tok = geo.token_of(r, p.group);
-        const int head = geo.kvh * p.group + (geo.row0 + r) % p.group;
-        const size_t row = (size_t)(geo.token0 + tok) * p.num_heads + head;
-        float lse[MAX_SPLITS / 32];
-        float mx = -INFINITY;
+    // across the cluster: CTA `rank` finishes the slice [rank, rank + 1) * D / splits of every row
+    cluster.sync();
+    const int slice = D / splits;
+    for (int i = threadIdx.x; i < rows_valid * slice; i += WARPS * 32) {
+        const int r = i / slice, dim = rank * slice + i % slice;
+        float m_all = -INFINITY;
+        float ms[MAX_SPLITS];
 #pragma unroll
-        for (int k = 0; k < MAX_SPLITS / 32; ++k) {
-            const int s = lane + 32 * k;
-            lse[k] = s < p.splits ? __ldcg(p.part_lse + row * p.splits + s) : -INFINITY;
-            mx = fmaxf(mx, lse[k]);
+        for (int s2 = 0; s2 < MAX_SPLITS; ++s2) {
+            ms[s2] = -INFINITY;
+            if (s2 < splits) ms[s2] = *cluster.map_shared_rank(cta_m + r, s2);
+            m_all = fmaxf(m_all, ms[s2]);
         }
-        mx = warp_max(mx);
-        float w[MAX_SPLITS / 32], sum = 0.0f;
+        float acc = 0.0f, l_all = 0.0f;
 #pragma unroll
-        for (int k = 0; k < MAX_SPLITS / 32; ++k) {
-            w[k] = (lse[k] == -INFINITY) ? 0.0f : exp2f(lse[k] - mx);
-            sum += w[k];
+        for (int s2 = 0; s2 < MAX_SPLITS; ++s2) {
+            if (s2 < splits && ms[s2] != -INFINITY) {
+                const float w = exp2f(ms[s2] - m_all);
+                acc += w * *cluster.map_shared_rank(cta_o + r * D + dim, s2);
+                l_all += w * *cluster.map_shared_rank(cta_l + r, s2);
+            }
         }
-        sum = warp_sum(sum);
-        const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
-#pragma unroll
-        for (int k = 0; k < MAX_SPLITS / 32; ++k)
-            if (lane + 32 * k < p.splits) split_w[r * MAX_SPLITS + lane + 32 * k] = w[k] * inv;
+        const int head = geo.kvh * p.group + geo.row0 + r;
+        p.out[((size_t)geo.token0 * p.num_heads + head) * D + dim] = __float2bfloat16_rn(l_all > 0.0f ? acc / l_all : 0.0f);
     }
-    __syncthreads();
-    for (int i = threadIdx.x; i < rows_valid * D; i += WARPS * 32) {
-        const int r = i / D, dim = i % D;
-        const int tok = geo.token_of(r, p.group);
-        const int head = geo.kvh * p.group + (geo.row0 + r) % p.group;
-        const size_t row = (size_t)(geo.token0 + tok) * p.num_heads + head;
-        const float* src = p.part_o + row * p.splits * D + dim;
-        float acc = 0.0f;
-        for (int s0 = 0; s0 < p.splits; s0 += 16) {    // sixteen loads in flight; the sum keeps split order
-            float part[16];
-#pragma unroll
-            for (int k = 0; k < 16; ++k) part[k] = s0 + k < p.splits ? __ldcg(src + (size_t)(s0 + k) * D) : 0.0f;
-#pragma unroll
-            for (int k = 0; k < 16; ++k)
-                if (s0 + k < p.splits) acc += split_w[r * MAX_SPLITS + s0 + k] * part[k];
-        }
-        p.out[row * D + dim] = __float2bfloat16_rn(acc);
-    }
+    cluster.sync();                          // nobody leaves while its shared memory may still be read
 }
 
 }  // namespace
@@ -562,16 +529,13 @@ __global__ void __launch_bounds__(WARPS * 32, PREFETCH ? 2 : 3) fa_decode_kernel
 MLB_EXPORT int mlb_fa_head_dim() { return D; }
 MLB_EXPORT int mlb_fa_max_splits() { return MAX_SPLITS; }
 
-// mode 0: prefill shape (work items name the first of 4 row tiles).
-// mode 1: decode shape (one row tile per work item, keys split `splits` ways).  With
-// splits > 1 it needs scratch: part_o [rows, splits, D] and part_lse [rows, splits] fp32, and
-// `tickets`, one int per (work item, kv head) that is ZERO before the first launch (the
-// kernel leaves it zero again).
-MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* out, float* part_o, float* part_lse,
-                                       int* tickets, const int* seq_starts, const int* seq_pos0,
-                                       const int* block_table, const int* work, int num_work, int max_blocks,
-                                       int num_pages, int page_size, int num_heads, int num_kv_heads, int window,
-                                       float scale, int mode, int splits, int long_loops, int* error_flag,
+// mode 0: prefill shape (work items name the first of 4 row tiles of a sequence).
+// mode 1: decode shape: every sequence brings one token (num_work = sequences * ceil(group / 16));
+// the keys are cut `splits` ways (1, 2, 4 or 8; D / splits must be whole) over a thread-block cluster.
+MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* out, const int* seq_starts,
+                                       const int* seq_pos0, const int* block_table, const int* work, int num_work,
+                                       int max_blocks, int num_pages, int page_size, int num_heads, int num_kv_heads,
+                                       int window, float scale, int mode, int splits, int* error_flag,
                                        cudaStream_t stream) {
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: bad head counts %d/%d", num_heads, num_kv_heads);
@@ -579,30 +543,37 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
         return fail(MLB_UNSUPPORTED_SIZE, "paged_attention_mma: page_size %d must be a multiple of 16", page_size);
     if (num_pages <= 0 || max_blocks <= 0 || window < 0 || num_work < 0)
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: bad cache geometry");
-    if (mode == 1 && (splits < 1 || splits > MAX_SPLITS || (splits > 1 && (!part_o || !part_lse || !tickets))))
-        return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: bad split arguments (1..%d splits, scratch required)", MAX_SPLITS);
+    if (mode == 1 && !(splits == 1 || splits == 2 || splits == 4 || splits == 8))
+        return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: %d splits, expected 1, 2, 4 or 8", splits);
     if (num_work == 0) return MLB_OK;
-    FaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, part_o, part_lse, tickets,
-               seq_starts, seq_pos0, block_table, work, max_blocks, num_pages, page_size, num_heads, num_kv_heads,
-               num_heads / num_kv_heads, window, scale * LOG2E, mode == 1 ? splits : 1, error_flag};
+    FaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, seq_starts, seq_pos0,
+               block_table, work, max_blocks, num_pages, page_size, num_heads, num_kv_heads,
+               num_heads / num_kv_heads, window, scale * LOG2E, error_flag};
     if (mode == 0) {
         launch_kernel(fa_prefill_kernel, dim3(num_work, num_kv_heads, 1), WARPS * 32, 0, stream, p);
         return check_launch("fa_prefill");
     }
-    // long_loops: every warp walks several key tiles, so loads of the next tile are worth their
-    // registers; otherwise the leaner instance fits more warps on an SM
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(fa_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
         if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "fa_decode: cannot reserve %d bytes of shared memory: %s",
                                           (int)DECODE_SMEM, cudaGetErrorString(e));
         configured = true;
     }
-    if (long_loops && USE_PREFETCH)
-        launch_kernel(fa_decode_kernel<true>, dim3(num_work, num_kv_heads, splits), WARPS * 32, DECODE_SMEM, stream, p);
-    else
-        launch_kernel(fa_decode_kernel<false>, dim3(num_work, num_kv_heads, splits), WARPS * 32, DECODE_SMEM, stream, p);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(num_work, num_kv_heads, splits);
+    config.blockDim = dim3(WARPS * 32);
+    config.dynamicSmemBytes = DECODE_SMEM;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = 1;
+    attributes[0].val.clusterDim.y = 1;
+    attributes[0].val.clusterDim.z = splits;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attributes;
+    config.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&config, fa_decode_kernel, p);
     return check_launch("fa_decode");
 }

@@ -4,8 +4,8 @@ fp32: always the plain kernel (fixed summation order, bit-stable across ways of 
 bf16: the tensor-core kernel (`attention_mma.cu`, compiled for the model's head size) when
 the head size is a multiple of 32 and the page size a multiple of 16; the plain kernel
 otherwise.  A step whose sequences all bring one token runs the decode shape (keys split
-over CTAs, partial results in scratch memory, merged by the CTA that finishes last); any
-other step runs the prefill shape.
+over a thread-block cluster that merges through distributed shared memory); any other step
+runs the prefill shape.
 """
 from __future__ import annotations
 
@@ -19,13 +19,11 @@ from .build import KernelError
 
 MAX_HEAD_DIM = 256
 SM_COUNT = 148
-MAX_SPLITS = 64
 MIN_KEY_TILES_PER_SPLIT = 4         # one 16-key tile per warp at least
 
 ops.register_signatures("attention_mma.cu", {
-    "mlb_paged_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                                c_int, c_int, c_void_p, c_void_p],
+    "mlb_paged_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
 })
 
 
@@ -56,23 +54,17 @@ def _plan(ctx, group: int, num_kv_heads: int):
         tiles = -(-(starts[a + 1] - starts[a]) * group // 16)
         work += [(a, first) for first in range(0, tiles, 1 if decode else 4)]
     work_dev = torch.tensor(work, dtype=torch.int32).reshape(-1).to(ctx.positions.device, non_blocking=True)
-    splits, long_loops = 1, 0
+    splits = 1
     if decode:
-        # each CTA takes an even share of its own sequence's keys, so the launch shape chosen
-        # here stays balanced while the sequences of a captured step grow
+        # a cluster of 1, 2, 4 or 8 CTAs shares the keys of one (sequence, kv head): as many as
+        # still fit the GPU in one wave (two CTAs per SM) and leave every warp a key tile
         key_tiles = max(1, -(-ctx.max_seq_len // 16))
         items = max(1, len(work) * num_kv_heads)
-
-        def choose(resident_per_sm):
-            return max(1, min(SM_COUNT * resident_per_sm // items, key_tiles // MIN_KEY_TILES_PER_SPLIT, MAX_SPLITS))
-
-        splits = choose(3)                     # the lean kernel: three CTAs per SM, one wave
-        if -(-key_tiles // splits) > 8:        # warps would walk more than two key tiles each:
-            long_loops = 1                     # the prefetching kernel (two CTAs per SM) pays
-            splits = choose(2)
-    # one ticket per (work item, kv head): which split finished last; the kernel leaves them zero
-    tickets = torch.zeros(len(work) * num_kv_heads, dtype=torch.int32, device=ctx.positions.device) if splits > 1 else None
-    plan = (work_dev, len(work), 1 if decode else 0, splits, tickets, long_loops)
+        for cand in (8, 4, 2):
+            if items * cand <= SM_COUNT * 2 and key_tiles >= cand * MIN_KEY_TILES_PER_SPLIT:
+                splits = cand
+                break
+    plan = (work_dev, len(work), 1 if decode else 0, splits)
     ctx.extras[key] = plan
     return plan
 
@@ -87,14 +79,9 @@ def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx
     if pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("paged_attention: the tensor-core kernel wants bf16 queries, pages and output")
     T = q.shape[0]
-    work, num_work, mode, splits, tickets, long_loops = _plan(ctx, num_heads // num_kv_heads, num_kv_heads)
-    part_o = part_lse = None
-    if splits > 1:
-        part_o = torch.empty((T * num_heads, splits, head_dim), dtype=torch.float32, device=q.device)
-        part_lse = torch.empty((T * num_heads, splits), dtype=torch.float32, device=q.device)
+    work, num_work, mode, splits = _plan(ctx, num_heads // num_kv_heads, num_kv_heads)
     L = ops.lib("attention_mma.cu", {"HEAD_DIM": head_dim})
     build.check(L, L.mlb_paged_attention_mma(
-        q.data_ptr(), pages.data_ptr(), out.data_ptr(), ops._ptr(part_o), ops._ptr(part_lse), ops._ptr(tickets),
-        ctx.seq_starts.data_ptr(), ctx.seq_pos0.data_ptr(), block_table.data_ptr(), work.data_ptr(), num_work,
+        q.data_ptr(), pages.data_ptr(), out.data_ptr(), ctx.seq_starts.data_ptr(), ctx.seq_pos0.data_ptr(), block_table.data_ptr(), work.data_ptr(), num_work,
         block_table.shape[1], pages.shape[0], page_size, num_heads, num_kv_heads, int(window or 0), float(scale),
-        mode, splits, long_loops, ops._ptr(ctx.error_flag), ops._stream()))
+        mode, splits, ops._ptr(ctx.error_flag), ops._stream()))
