@@ -208,6 +208,28 @@ __global__ void silu_mul_kernel(const InT* __restrict__ gate, const InT* __restr
     out[i] = from_f32<OutT>(g * stable_sigmoid(g) * u);
 }
 
+// bf16 in, bf16 out, eight elements per thread (16-byte loads and stores)
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
+                                       long long in_stride, __nv_bfloat16* __restrict__ out, int rows, int width) {
+    pdl_prologue();
+    const int vec_per_row = width / 8;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * vec_per_row) return;
+    const int r = (int)(i / vec_per_row), c = (int)(i % vec_per_row) * 8;
+    const uint4 gv = *reinterpret_cast<const uint4*>(gate + (size_t)r * in_stride + c);
+    const uint4 uv = *reinterpret_cast<const uint4*>(up + (size_t)r * in_stride + c);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    uint4 ov;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+        o2[k] = __floats2bfloat162_rn(g.x * stable_sigmoid(g.x) * u.x, g.y * stable_sigmoid(g.y) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)r * width + c) = ov;
+}
+
 // gate and up are two column blocks of one [rows, in_stride] matrix (the fused gate/up
 // projection) or two separate matrices; `in_stride` is their row pitch in elements.  The input
 // may be `n_partials` partial results `partial_stride` elements apart.
@@ -220,6 +242,10 @@ MLB_EXPORT int mlb_silu_mul(const void* gate, const void* up, long long in_strid
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (in_dtype == MLB_F32 && out_dtype == MLB_F32)
         launch_kernel(silu_mul_kernel<float, float>, blocks, 256, 0, stream, (const float*)gate, (const float*)up, in_stride, n_partials, partial_stride, (float*)out, rows, width);
+    else if (in_dtype == MLB_BF16 && out_dtype == MLB_BF16 && n_partials == 1 && width % 8 == 0 && in_stride % 8 == 0 &&
+             (uintptr_t)gate % 16 == 0 && (uintptr_t)up % 16 == 0 && (uintptr_t)out % 16 == 0)
+        launch_kernel(silu_mul_bf16x8_kernel, (unsigned)((n / 8 + 255) / 256), 256, 0, stream, (const __nv_bfloat16*)gate,
+                      (const __nv_bfloat16*)up, in_stride, (__nv_bfloat16*)out, rows, width);
     else if (in_dtype == MLB_BF16 && out_dtype == MLB_BF16)
         launch_kernel(silu_mul_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, in_stride, n_partials, partial_stride, (__nv_bfloat16*)out, rows, width);
     else if (in_dtype == MLB_F32 && out_dtype == MLB_BF16)

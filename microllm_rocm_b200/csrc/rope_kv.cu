@@ -108,6 +108,79 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
     dst[e1] = from_f32<KVT>(b);
 }
 
+__device__ __forceinline__ void store4(float* dst, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, const float (&v)[4]) {
+    uint2 packed;
+    *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+// Split-half rotation over the whole head (the model's own case), four pairs per thread:
+// elements i..i+3 and i+D/2..i+D/2+3 travel as 16-byte pieces.  V heads copy eight elements.
+template <typename QT, typename KVT>
+__global__ void rope_kv_split_half_x4_kernel(RopeKvParams p) {
+    pdl_prologue();
+    const int half = p.head_dim / 2, quads = half / 4;
+    const int heads_all = p.num_heads + 2 * p.num_kv_heads;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)p.tokens * heads_all * quads) return;
+    const int i = (int)(idx % quads) * 4;
+    const int head = (int)((idx / quads) % heads_all);
+    const int t = (int)(idx / ((long long)quads * heads_all));
+    const bool is_q = head < p.num_heads;
+    const bool is_v = head >= p.num_heads + p.num_kv_heads;
+    if (!is_q && p.pages == nullptr) return;
+    const size_t col = (size_t)head * p.head_dim;
+    const float* src = p.qkv + (size_t)t * p.ld + col;
+    // V has nothing to rotate: its two pieces are simply elements i.. and i+half..
+    float4 a = *reinterpret_cast<const float4*>(src + i), b = *reinterpret_cast<const float4*>(src + i + half);
+    for (int k = 1; k < p.n_partials; ++k) {
+        const float4 a2 = *reinterpret_cast<const float4*>(src + (size_t)k * p.partial_stride + i);
+        const float4 b2 = *reinterpret_cast<const float4*>(src + (size_t)k * p.partial_stride + i + half);
+        a.x += a2.x; a.y += a2.y; a.z += a2.z; a.w += a2.w;
+        b.x += b2.x; b.y += b2.y; b.z += b2.z; b.w += b2.w;
+    }
+    if (p.bias) {
+        const float4 ba = *reinterpret_cast<const float4*>(p.bias + col + i), bb = *reinterpret_cast<const float4*>(p.bias + col + i + half);
+        a.x += ba.x; a.y += ba.y; a.z += ba.z; a.w += ba.w;
+        b.x += bb.x; b.y += bb.y; b.z += bb.z; b.w += bb.w;
+    }
+    const int pos = p.positions[t];
+    float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+    if (!is_v) {
+        const float4 f = *reinterpret_cast<const float4*>(p.inv_freq + i);
+        const float fr[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float s, c;
+            sincosf((float)pos * fr[k], &s, &c);
+            const float ra = av[k] * c - bv[k] * s, rb = av[k] * s + bv[k] * c;
+            av[k] = ra; bv[k] = rb;
+        }
+    }
+    if (is_q) {
+        QT* dst = (QT*)p.q_out + (size_t)t * p.num_heads * p.head_dim + col;
+        store4(dst + i, av);
+        store4(dst + i + half, bv);
+        return;
+    }
+    const int kvh = is_v ? head - p.num_heads - p.num_kv_heads : head - p.num_heads;
+    const int block = pos / p.page_size, slot = pos % p.page_size;
+    int page = -1;
+    if (pos >= 0 && block < p.max_blocks) page = p.block_table[(size_t)p.token_seq[t] * p.max_blocks + block];
+    if (page < 0 || page >= p.num_pages) {
+        if (p.error_flag) atomicExch(p.error_flag, 1);
+        return;
+    }
+    KVT* dst = (KVT*)p.pages +
+               ((((size_t)page * 2 + (is_v ? 1 : 0)) * p.num_kv_heads + kvh) * p.page_size + slot) * p.head_dim;
+    store4(dst + i, av);
+    store4(dst + i + half, bv);
+}
+
 }  // namespace
 
 MLB_EXPORT int mlb_rope_kv_write(const float* qkv, long long ld, int n_partials, long long partial_stride,
@@ -129,9 +202,24 @@ MLB_EXPORT int mlb_rope_kv_write(const float* qkv, long long ld, int n_partials,
     if (n_partials < 1) return fail(MLB_INVALID_ARGUMENT, "rope_kv_write: n_partials must be at least 1");
     RopeKvParams p{qkv, ld, n_partials, partial_stride, bias, positions, token_seq, block_table, max_blocks, inv_freq, rot_dim, interleaved,
                    q_out, pages, num_pages, page_size, tokens, num_heads, num_kv_heads, head_dim, error_flag};
+    const int key = q_dtype * 2 + kv_dtype;
+    // the model's own case in 16-byte pieces: split-half over the whole head, eight-element alignment
+    const bool wide = rot_dim == head_dim && !interleaved && head_dim % 8 == 0 && ld % 4 == 0 && partial_stride % 4 == 0 &&
+                      (uintptr_t)q_out % 16 == 0 && (!pages || (uintptr_t)pages % 16 == 0) && (uintptr_t)qkv % 16 == 0 && (!bias || (uintptr_t)bias % 16 == 0) && (uintptr_t)inv_freq % 16 == 0;
+    if (wide) {
+        const long long total4 = (long long)tokens * (num_heads + 2 * num_kv_heads) * (head_dim / 8);
+        const unsigned blocks4 = (unsigned)((total4 + 255) / 256);
+        switch (key) {
+            case MLB_F32 * 2 + MLB_F32: launch_kernel(rope_kv_split_half_x4_kernel<float, float>, blocks4, 256, 0, stream, p); break;
+            case MLB_BF16 * 2 + MLB_BF16: launch_kernel(rope_kv_split_half_x4_kernel<__nv_bfloat16, __nv_bfloat16>, blocks4, 256, 0, stream, p); break;
+            case MLB_F32 * 2 + MLB_BF16: launch_kernel(rope_kv_split_half_x4_kernel<float, __nv_bfloat16>, blocks4, 256, 0, stream, p); break;
+            case MLB_BF16 * 2 + MLB_F32: launch_kernel(rope_kv_split_half_x4_kernel<__nv_bfloat16, float>, blocks4, 256, 0, stream, p); break;
+            default: return fail(MLB_INVALID_ARGUMENT, "rope_kv_write: unknown dtypes %d/%d", q_dtype, kv_dtype);
+        }
+        return check_launch("rope_kv_write");
+    }
     const long long total = (long long)tokens * (num_heads + 2 * num_kv_heads) * (head_dim / 2);
     const unsigned blocks = (unsigned)((total + 255) / 256);
-    const int key = q_dtype * 2 + kv_dtype;
     switch (key) {
         case MLB_F32 * 2 + MLB_F32: launch_kernel(rope_kv_kernel<float, float>, blocks, 256, 0, stream, p); break;
         case MLB_BF16 * 2 + MLB_BF16: launch_kernel(rope_kv_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, 256, 0, stream, p); break;
