@@ -110,7 +110,7 @@ def all_sources():
     for d in (32, 64, 128):
         out += attention.mma_sources(d)
     from . import gemm_bf16
-    return out + gemm_bf16.sources()
+    return out + gemm_bf16.sources() + [("gemv_noalloc.cu", {})]
 
 
 # ------------------------------------------------------------------------------ basic
