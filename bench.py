@@ -51,7 +51,7 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons every 20 ms while the timed region runs."""
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -61,7 +61,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -173,6 +173,7 @@ def run_ours(args):
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         if sampler:
             sampler.__enter__()
+            time.sleep(0.3)                 # let the first samples arrive before the timed steps
         start.record()
         for _ in range(steps):
             session.step()

@@ -13,8 +13,9 @@
 // re-reads them per query head and keeps every score in shared memory
 // (src/ops/hip/basic_kernels.hip:1035-1083, limit 4096 keys at src/ops/ops.cpp:1592).
 //
-// Two launch shapes of the same warp routine:
-//   prefill  one CTA = 4 warps = 4 consecutive row tiles; no key split
+// Two launch shapes:
+//   prefill  one CTA = 4 warps = 4 consecutive row tiles; K/V tiles of 64 keys staged once per
+//            CTA in shared memory (cp.async, two stages), fragments by ldmatrix; no key split
 //   decode   one CTA = one row tile, its 4 warps take every 4th key tile and are merged in
 //            shared memory; the keys are further split over a thread-block cluster whose CTAs
 //            combine their results through distributed shared memory, in rank order.
@@ -295,86 +296,280 @@ __device__ __forceinline__ int out_dim(int nbo, int e, int t) {
     return (nbo >> 3) * 64 + (2 * t + (e & 1)) * 8 + (nbo & 7);
 }
 
-__device__ __forceinline__ void load_q_tile(const FaParams& p, const TileGeometry& geo, __nv_bfloat16* q_s, int lane,
-                                            int lanes) {
-    constexpr int VEC_PER_ROW = D / 8;        // 16 rows x D elements, 16 bytes per load
-    for (int i = lane; i < 16 * VEC_PER_ROW; i += lanes) {
-        const int r = i / VEC_PER_ROW, c = (i % VEC_PER_ROW) * 8;
-        const int tok = geo.token_of(r, p.group);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (tok < geo.n_new) {
-            const int head = geo.kvh * p.group + (geo.row0 + r) % p.group;
-            v = load16(p.q + ((size_t)(geo.token0 + tok) * p.num_heads + head) * D + c);
-        }
-        *reinterpret_cast<uint4*>(q_s + r * Q_STRIDE + c) = v;
+// ---------------------------------------------------------------------------------- prefill
+// One CTA = 4 warps = 4 consecutive row tiles (64 rows) of one (sequence, kv head).  The keys
+// are walked 64 at a time; each K/V tile is copied ONCE per CTA from the pages into shared
+// memory with cp.async (two stages, the next tile lands while this one is used) and every
+// warp takes its tensor-core fragments from there with ldmatrix (transposed for V).  16-byte
+// chunks are XOR-swizzled by the key's low bits so that ldmatrix reads are conflict free.
+constexpr int KEY_TILE = 64;
+constexpr int CHUNKS = D / 8;                       // 16-byte chunks per key row
+constexpr int KV_STAGE_ELEMS = 2 * KEY_TILE * D;    // K then V
+constexpr int QO_STRIDE = D + 8;                    // bf16; rows shift by one chunk: ldmatrix conflict free
+constexpr size_t PREFILL_SMEM = (size_t)(2 * KV_STAGE_ELEMS + WARPS * 16 * QO_STRIDE) * sizeof(__nv_bfloat16) +
+                                TABLE_SPAN * sizeof(int);
+
+__device__ __forceinline__ void cp_async16(__nv_bfloat16* dst, const __nv_bfloat16* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;               // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const __nv_bfloat16* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const __nv_bfloat16* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+// element offset of 16-byte chunk `chunk` of key row `key` inside a swizzled [KEY_TILE][D] tile
+constexpr int SWZ_MASK = CHUNKS >= 8 ? 7 : CHUNKS - 1;
+__device__ __forceinline__ int swz(int key, int chunk) { return key * D + ((chunk ^ (key & SWZ_MASK)) << 3); }
+
+// Copy keys [base, base + 64) of (sequence, kv head) into one stage.  Keys outside [lo, hi] --
+// behind every row's window (their pages may have been given back) or never written by this
+// sequence -- become zeros; a key inside the range without a page raises the error flag.
+// Thread `tid` always moves chunk tid % CHUNKS of keys tid / CHUNKS + j * KEYS_PER_PASS.
+constexpr int KEYS_PER_PASS = WARPS * 32 / CHUNKS;
+constexpr int PASSES = KEY_TILE / KEYS_PER_PASS;
+static_assert((WARPS * 32) % CHUNKS == 0 && KEY_TILE % KEYS_PER_PASS == 0, "head size does not tile the copy");
+
+__device__ __forceinline__ void load_kv_stage(const FaParams& p, const PageTable& pt, int kvh, int base, int lo, int hi,
+                                              __nv_bfloat16* stage) {
+    const size_t page_stride = (size_t)2 * p.num_kv_heads * p.page_size * D;
+    const size_t v_off = (size_t)p.num_kv_heads * p.page_size * D;
+    const int chunk = threadIdx.x % CHUNKS, key0 = threadIdx.x / CHUNKS;
+    const size_t head_off = (size_t)kvh * p.page_size * D + chunk * 8;
+#pragma unroll
+    for (int j = 0; j < PASSES; ++j) {
+        const int key = key0 + j * KEYS_PER_PASS;
+        const int pos = base + key;
+        const bool wanted = pos >= lo && pos <= hi;
+        const int page = wanted ? pt.page_of(pos / p.page_size) : -1;
+        const bool ok = page >= 0 && page < p.num_pages;
+        if (!ok && wanted && p.error_flag) atomicExch(p.error_flag, 3);
+        const __nv_bfloat16* src = p.pages;
+        if (ok) src += (size_t)page * page_stride + head_off + (size_t)(pos % p.page_size) * D;
+        __nv_bfloat16* dst = stage + swz(key, chunk);
+        cp_async16(dst, src, ok);
+        cp_async16(dst + KEY_TILE * D, ok ? src + v_off : src, ok);
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
-__device__ __forceinline__ bool geometry(const FaParams& p, int work_index, int tile_offset, int kvh, TileGeometry& geo) {
-    geo.seq = p.work[2 * work_index];
-    const int tile = p.work[2 * work_index + 1] + tile_offset;
-    geo.kvh = kvh;
+__global__ void __launch_bounds__(WARPS * 32, 2) fa_prefill_kernel(FaParams p) {
+    pdl_prologue();
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);                  // [2][K | V][64][D]
+    __nv_bfloat16* qo_s = kv_s + 2 * KV_STAGE_ELEMS;                                   // [WARPS][16][QO_STRIDE]
+    int* table_s = reinterpret_cast<int*>(qo_s + WARPS * 16 * QO_STRIDE);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+
+    // the CTA's rows: 4 tiles of 16 starting at work item's first tile; warps past the end idle along
+    TileGeometry geo;
+    geo.seq = p.work[2 * blockIdx.x];
+    geo.kvh = blockIdx.y;
     geo.token0 = p.seq_starts[geo.seq];
     geo.n_new = p.seq_starts[geo.seq + 1] - geo.token0;
     geo.pos0 = p.seq_pos0[geo.seq];
-    geo.row0 = tile * 16;
-    return geo.row0 < geo.n_new * p.group;
-}
+    const int first_tile = p.work[2 * blockIdx.x + 1];
+    const int total_rows = geo.n_new * p.group;
+    geo.row0 = (first_tile + warp) * 16;
+    const bool active = geo.row0 < total_rows;
+    // key range of the whole CTA (first row's window start .. last row's position)
+    const int cta_row_first = first_tile * 16, cta_row_last = min(total_rows, cta_row_first + WARPS * 16) - 1;
+    const int cta_first_pos = geo.pos0 + cta_row_first / p.group, cta_last_pos = geo.pos0 + cta_row_last / p.group;
+    const int cta_lo = (p.window > 0 && cta_first_pos - p.window + 1 > 0) ? cta_first_pos - p.window + 1 : 0;
+    const int tile_first = cta_lo / KEY_TILE, tile_last = cta_last_pos / KEY_TILE;
 
-// ---------------------------------------------------------------------------------- prefill
-__global__ void __launch_bounds__(WARPS * 32) fa_prefill_kernel(FaParams p) {
-    pdl_prologue();
-    __shared__ __align__(16) __nv_bfloat16 q_s[WARPS][16 * Q_STRIDE];
-    __shared__ int table_s[WARPS][TABLE_SPAN / WARPS];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    TileGeometry geo;
-    if (!geometry(p, blockIdx.x, warp, blockIdx.y, geo)) return;
-    const int first_tok = geo.token_of(0, p.group);
-    const int last_tok = min(geo.token_of(15, p.group), geo.n_new - 1);
-    const int first_pos = geo.pos0 + first_tok, last_pos = geo.pos0 + last_tok;
-    const int lo = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
-    // each warp keeps the LAST blocks of its key range at hand (it reaches them however long
-    // the range is); earlier blocks of a very long range are looked up in global memory
     PageTable pt;
     {
-        const int last_block = last_pos / p.page_size;
-        const int first_block = max(lo / p.page_size, last_block - TABLE_SPAN / WARPS + 1);
-        fill_page_table(pt, table_s[warp], p.block_table + (size_t)geo.seq * p.max_blocks, p.max_blocks, first_block,
-                        last_block, lane, 32);
-        pt.count = min(pt.count, TABLE_SPAN / WARPS);
+        const int last_block = cta_last_pos / p.page_size;
+        const int first_block = max(cta_lo / p.page_size, last_block - TABLE_SPAN + 1);
+        fill_page_table(pt, table_s, p.block_table + (size_t)geo.seq * p.max_blocks, p.max_blocks, first_block, last_block,
+                        threadIdx.x, WARPS * 32);
     }
-    load_q_tile(p, geo, q_s[warp], lane, 32);
-    __syncwarp();
-    RowState st;
-    init_state(st);
-    attend<USE_PREFETCH>(p, geo, pt, q_s[warp], lo / 16, last_pos / 16 + 1, 0, 1, last_pos, st);
+    // queries of this warp's tile -> shared memory (zeros for rows that do not exist)
+    __nv_bfloat16* my_q = qo_s + warp * 16 * QO_STRIDE;
+    for (int i = lane; i < 16 * CHUNKS; i += 32) {
+        const int r = i / CHUNKS, c = (i % CHUNKS) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (active) {
+            const int tok = geo.token_of(r, p.group);
+            if (tok < geo.n_new) {
+                const int head = geo.kvh * p.group + (geo.row0 + r) % p.group;
+                v = load16(p.q + ((size_t)(geo.token0 + tok) * p.num_heads + head) * D + c);
+            }
+        }
+        *reinterpret_cast<uint4*>(my_q + r * QO_STRIDE + c) = v;
+    }
+    __syncthreads();                                   // table and queries are in place
+    load_kv_stage(p, pt, geo.kvh, tile_first * KEY_TILE, cta_lo, cta_last_pos, kv_s);
+
+    // this thread's two rows
+    int pos_row[2], lo_row[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int tok = geo.token_of(g + 8 * i, p.group);
+        if (active && tok < geo.n_new) {
+            pos_row[i] = geo.pos0 + tok;
+            lo_row[i] = (p.window > 0 && pos_row[i] - p.window + 1 > 0) ? pos_row[i] - p.window + 1 : 0;
+        } else {
+            pos_row[i] = -1;
+            lo_row[i] = 0;
+        }
+    }
+    // the warp's own key range: tiles outside it are skipped (it still keeps step with the CTA)
+    const int warp_first_pos = geo.pos0 + geo.token_of(0, p.group);
+    const int warp_last_pos = geo.pos0 + min(geo.token_of(15, p.group), geo.n_new - 1);
+    const int warp_lo = (p.window > 0 && warp_first_pos - p.window + 1 > 0) ? warp_first_pos - p.window + 1 : 0;
+    const int warp_lo_last = (p.window > 0 && warp_last_pos - p.window + 1 > 0) ? warp_last_pos - p.window + 1 : 0;
+    const bool warp_rows_full = geo.row0 + 16 <= total_rows;
+
+    // lane-constant parts of the swizzled ldmatrix addresses (row & 7 is the lane's low bits)
+    const int lane7 = lane & 7;
+    const int k_lane = lane7 * D;                                  // K: key nb*8 + lane7, chunk 2ks + (lane >> 3)
+    const int v_lane = (lane7 + ((lane >> 3) & 1) * 8) * D;        // V: key 16kk + lane7 + 8*bit3, chunk nb + (lane >> 4)
+    // query fragments stay in registers
+    unsigned qf[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+        ldmatrix_x4(qf[ks], my_q + (lane & 15) * QO_STRIDE + ks * 16 + (lane >> 4) * 8);
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int nb = 0; nb < D / 8; ++nb)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[nb][e] = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+
+    for (int kt = tile_first; kt <= tile_last; ++kt) {
+        const int stage = (kt - tile_first) & 1;
+        if (kt < tile_last) {
+            load_kv_stage(p, pt, geo.kvh, (kt + 1) * KEY_TILE, cta_lo, cta_last_pos, kv_s + (stage ^ 1) * KV_STAGE_ELEMS);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const int base = kt * KEY_TILE;
+        if (active && base <= warp_last_pos && base + KEY_TILE - 1 >= warp_lo) {
+            const __nv_bfloat16* k_s = kv_s + stage * KV_STAGE_ELEMS;
+            const __nv_bfloat16* v_s = k_s + KEY_TILE * D;
+            // ---- S = Q K^T : 8 key blocks of 8 --------------------------------------------------
+            float s[8][4];
+#pragma unroll
+            for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[nb][e] = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ks += 2) {
+#pragma unroll
+                for (int nb = 0; nb < 8; ++nb) {
+                    // four 8x8 matrices: this key block at head chunks 2ks, 2ks+1, 2ks+2, 2ks+3
+                    unsigned kf[4];
+                    ldmatrix_x4(kf, k_s + nb * 8 * D + k_lane + ((((ks * 2) + (lane >> 3)) ^ (lane7 & SWZ_MASK)) << 3));
+                    mma_bf16(s[nb], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], kf[0], kf[1]);
+                    mma_bf16(s[nb], qf[ks + 1][0], qf[ks + 1][1], qf[ks + 1][2], qf[ks + 1][3], kf[2], kf[3]);
+                }
+            }
+            // ---- masks and the running softmax ----------------------------------------------------
+            float mx[2] = {-INFINITY, -INFINITY};
+            // a tile that lies inside every row's range (all 16 rows exist) needs no mask
+            const bool interior = base + KEY_TILE - 1 <= warp_first_pos && base >= warp_lo_last && warp_rows_full;
+            if (interior) {
+#pragma unroll
+                for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        s[nb][e] *= p.scale_log2;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
+                    }
+            } else {
+#pragma unroll
+                for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = e >> 1;
+                        const int key = base + nb * 8 + 2 * t + (e & 1);
+                        const bool ok = key >= lo_row[i] && key <= pos_row[i];
+                        s[nb][e] = ok ? s[nb][e] * p.scale_log2 : -INFINITY;
+                        mx[i] = fmaxf(mx[i], s[nb][e]);
+                    }
+            }
+            float corr[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                const float m_new = fmaxf(m_run[i], mx[i]);
+                corr[i] = (m_new == -INFINITY) ? 1.0f : exp2f(m_run[i] - m_new);
+                m_run[i] = m_new;
+            }
+            float rowsum[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = e >> 1;
+                    const float pv = (s[nb][e] == -INFINITY) ? 0.0f : exp2f(s[nb][e] - m_run[i]);
+                    s[nb][e] = pv;
+                    rowsum[i] += pv;
+                }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * corr[i] + rowsum[i];
+#pragma unroll
+            for (int nb = 0; nb < D / 8; ++nb) {
+                o[nb][0] *= corr[0]; o[nb][1] *= corr[0];
+                o[nb][2] *= corr[1]; o[nb][3] *= corr[1];
+            }
+            // ---- O += P V : 4 key steps of 16, D/8 output blocks --------------------------------
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                const unsigned pa0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                const unsigned pa1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                const unsigned pa2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                const unsigned pa3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int nb = 0; nb < D / 8; nb += 2) {
+                    // four 8x8 matrices, transposed on the way: keys 16kk..+7 / +8..15 at output chunks nb, nb+1
+                    unsigned vf[4];
+                    ldmatrix_x4_trans(vf, v_s + kk * 16 * D + v_lane + (((nb + (lane >> 4)) ^ (lane7 & SWZ_MASK)) << 3));
+                    mma_bf16(o[nb], pa0, pa1, pa2, pa3, vf[0], vf[1]);
+                    mma_bf16(o[nb + 1], pa0, pa1, pa2, pa3, vf[2], vf[3]);
+                }
+            }
+        }
+        __syncthreads();                               // the stage may be overwritten next round
+    }
+    if (!active) return;
     // normalise and write through shared memory so that rows leave as whole 16-byte pieces
     float inv[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        float l = st.l[i];
+        float l = l_run[i];
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         inv[i] = l > 0.0f ? 1.0f / l : 0.0f;
     }
     __syncwarp();
-    __nv_bfloat16* o_s = q_s[warp];
 #pragma unroll
-    for (int nbo = 0; nbo < NB_O; ++nbo)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int dim = out_dim(nbo, e, t);
-            if (dim < D) o_s[(g + 8 * (e >> 1)) * Q_STRIDE + dim] = __float2bfloat16_rn(st.o[nbo][e] * inv[e >> 1]);
-        }
+    for (int nb = 0; nb < D / 8; ++nb) {
+        *reinterpret_cast<__nv_bfloat162*>(my_q + g * QO_STRIDE + nb * 8 + 2 * t) =
+            __floats2bfloat162_rn(o[nb][0] * inv[0], o[nb][1] * inv[0]);
+        *reinterpret_cast<__nv_bfloat162*>(my_q + (g + 8) * QO_STRIDE + nb * 8 + 2 * t) =
+            __floats2bfloat162_rn(o[nb][2] * inv[1], o[nb][3] * inv[1]);
+    }
     __syncwarp();
-    constexpr int VEC_PER_ROW = D / 8;
-    for (int i = lane; i < 16 * VEC_PER_ROW; i += 32) {
-        const int r = i / VEC_PER_ROW, c = (i % VEC_PER_ROW) * 8;
+    for (int i = lane; i < 16 * CHUNKS; i += 32) {
+        const int r = i / CHUNKS, c = (i % CHUNKS) * 8;
         const int tok = geo.token_of(r, p.group);
         if (tok >= geo.n_new) continue;
         const int head = geo.kvh * p.group + (geo.row0 + r) % p.group;
         *reinterpret_cast<uint4*>(p.out + ((size_t)(geo.token0 + tok) * p.num_heads + head) * D + c) =
-            *reinterpret_cast<const uint4*>(o_s + r * Q_STRIDE + c);
+            *reinterpret_cast<const uint4*>(my_q + r * QO_STRIDE + c);
     }
 }
 
@@ -397,7 +592,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) fa_decode_kernel(FaParams p) {
     pdl_prologue();
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     float* frag = reinterpret_cast<float*>(smem_raw + 16 * Q_STRIDE * sizeof(__nv_bfloat16));   // [WARPS][FRAGS][32]
     float* warp_m = frag + WARPS * FRAGS * 32;        // [WARPS][16]
@@ -550,7 +745,14 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
                block_table, work, max_blocks, num_pages, page_size, num_heads, num_kv_heads,
                num_heads / num_kv_heads, window, scale * LOG2E, error_flag};
     if (mode == 0) {
-        launch_kernel(fa_prefill_kernel, dim3(num_work, num_kv_heads, 1), WARPS * 32, 0, stream, p);
+        static bool prefill_configured = false;
+        if (!prefill_configured) {
+            cudaError_t e = cudaFuncSetAttribute(fa_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM);
+            if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "fa_prefill: cannot reserve %d bytes of shared memory: %s",
+                                              (int)PREFILL_SMEM, cudaGetErrorString(e));
+            prefill_configured = true;
+        }
+        launch_kernel(fa_prefill_kernel, dim3(num_work, num_kv_heads, 1), WARPS * 32, PREFILL_SMEM, stream, p);
         return check_launch("fa_prefill");
     }
     static bool configured = false;

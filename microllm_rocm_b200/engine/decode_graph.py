@@ -146,6 +146,16 @@ class DecodeGraph:
             self.dev[a:self.total].copy_(self.host[a:self.total], non_blocking=True)
             self._mark_upload()
 
+    def upload_tokens(self, tokens: Sequence[int]) -> None:
+        """The host's copy of each request's next input token, pinned memory -> device.  A
+        replay would find the same values where the sampler left them; sending them keeps the
+        host the owner of what the model is fed."""
+        self._wait_upload()
+        a, b = self._s["tokens"]
+        self.host.numpy()[a:b] = tokens
+        self.dev[a:b].copy_(self.host[a:b], non_blocking=True)
+        self._mark_upload()
+
     def fits(self, requests: Sequence[Hashable]) -> bool:
         cache = self.engine.cache
         return all(len(cache.requests[q].tables[g]) <= w for g, w in self.widths.items() for q in requests)

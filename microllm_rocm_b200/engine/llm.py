@@ -101,6 +101,8 @@ class LLM:
             self.h2d_bytes += 4 * graph.total
         else:
             graph.refresh_tables()
+            graph.upload_tokens([e.request.token(e.begin) for e in plan.entries])
+            self.h2d_bytes += 4 * len(ids)
         graph.replay()
         tokens = graph.read_tokens()
         self.d2h_bytes += 4 * (len(ids) + 1)

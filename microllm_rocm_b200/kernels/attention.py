@@ -53,6 +53,9 @@ def _plan(ctx, group: int, num_kv_heads: int):
     for a in range(A):
         tiles = -(-(starts[a + 1] - starts[a]) * group // 16)
         work += [(a, first) for first in range(0, tiles, 1 if decode else 4)]
+    if not decode:
+        # causal work grows with the row tile: start the long ones first so that the tail is short
+        work.sort(key=lambda item: -item[1])
     work_dev = torch.tensor(work, dtype=torch.int32).reshape(-1).to(ctx.positions.device, non_blocking=True)
     splits = 1
     if decode:
