@@ -122,6 +122,18 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 accumulator columns of this thread's lane, no wait: several may be in flight before tmem_wait()
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t addr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ float silu(float g) {
     // two-branch sigmoid, as the reference's activation (src/ops/ops.cpp:72-76)
     if (g >= 0.0f) return g / (1.0f + expf(-g));
@@ -300,6 +312,152 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
 }
 
+// --------------------------------------------------------------------------------- persistent variant
+// For products with many output tiles (prompt portions): each CTA stays on its SM and walks
+// tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulator is DOUBLE-BUFFERED in tensor
+// memory, so while the four epilogue warps drain tile i (tcgen05.ld, activation, stores) the
+// MMA warp already runs tile i+1, and the TMA warp runs ahead of both across tile borders.
+// Consecutive tiles share a weight tile and differ in the token tile, so the weights of a
+// wave come from L2.  No split over K here (there are tiles enough).
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                          GemmParams p, int n_tiles, int m_tiles) {
+    pdl_launch_dependents();
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) unsigned long long full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = n_tiles * m_tiles;
+    const uint32_t ring = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    const uint32_t b_bytes = (uint32_t)p.tok_tile * BLOCK_K * 2;
+    const uint32_t a_bytes = p.dual ? 2u * A_TILE_BYTES : (uint32_t)A_TILE_BYTES;
+    const uint32_t stage_bytes = a_bytes + b_bytes;
+    const uint32_t acc_cols = (uint32_t)(p.dual ? 2 * p.tok_tile : p.tok_tile);     // columns of one accumulator buffer
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full[b]), 1);
+            mbar_init(smem_u32(&acc_empty[b]), 4);          // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_s)), "r"((uint32_t)p.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+    pdl_wait();
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer
+        if (lane == 0) {
+            uint32_t it = 0;                                  // k-blocks issued so far, over all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int n0 = (tile / m_tiles) * BLOCK_W, tok0 = (tile % m_tiles) * p.tok_tile;
+                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    const int s = it % p.stages;
+                    const uint32_t round = it / p.stages;
+                    if (round > 0 && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, p.error_flag, 21)) { ok = false; break; }
+                    const uint32_t dst = ring + (uint32_t)s * stage_bytes;
+                    const uint32_t bar = smem_u32(&full_bar[s]);
+                    mbar_expect_tx(bar, stage_bytes);
+                    const int k = kb * BLOCK_K;
+                    tma_load_2d(dst, &map_w, k, n0, bar);
+                    if (p.dual) tma_load_2d(dst + A_TILE_BYTES, &map_w, k, p.up_offset + n0, bar);
+                    tma_load_2d(dst + a_bytes, &map_x, k, tok0, bar);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issue
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(p.tok_tile);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+                const uint32_t buf = local & 1, use = local >> 1;
+                // the epilogue must have drained this buffer (first use of each buffer passes at once)
+                if (!mbar_wait(smem_u32(&acc_empty[buf]), (use & 1) ^ 1, p.error_flag, 22)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc = tmem_base + buf * acc_cols;
+                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    const int s = it % p.stages;
+                    if (!mbar_wait(smem_u32(&full_bar[s]), (it / p.stages) & 1, p.error_flag, 23)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = ring + (uint32_t)s * stage_bytes;
+                    const uint32_t b_addr = a_addr + a_bytes;
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                        const uint64_t bdesc = umma_desc(b_addr + k * UMMA_K * 2);
+                        umma(acc, umma_desc(a_addr + k * UMMA_K * 2), bdesc, idesc, accumulate);
+                        if (p.dual)
+                            umma(acc + (uint32_t)p.tok_tile, umma_desc(a_addr + A_TILE_BYTES + k * UMMA_K * 2), bdesc, idesc, accumulate);
+                    }
+                    umma_commit(smem_u32(&empty_bar[s]));
+                }
+                if (ok) umma_commit(smem_u32(&acc_full[buf]));
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const int quarter = warp & 3;
+        uint32_t local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            const uint32_t buf = local & 1, use = local >> 1;
+            const int n0 = (tile / m_tiles) * BLOCK_W, tok0 = (tile % m_tiles) * p.tok_tile;
+            const int f = n0 + quarter * 32 + lane;
+            ok = mbar_wait(smem_u32(&acc_full[buf]), use & 1, p.error_flag, 24);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t lane_addr = tmem_base + buf * acc_cols + ((uint32_t)(quarter * 32) << 16);
+            const float bias = (p.bias && f < p.N) ? p.bias[f] : 0.0f;
+            for (int c = 0; c < p.tok_tile; c += 32) {
+                if (tok0 + c >= p.M) break;
+                uint32_t raw[32], raw_u[32];
+                tmem_ld32_nowait(lane_addr + (uint32_t)c, raw);
+                if (p.dual) tmem_ld32_nowait(lane_addr + (uint32_t)(p.tok_tile + c), raw_u);
+                tmem_wait();
+                if (f >= p.N) continue;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int tok = tok0 + c + j;
+                    if (tok >= p.M || c + j >= p.tok_tile) break;
+                    float r = __uint_as_float(raw[j]);
+                    if (p.dual) r = silu(r) * __uint_as_float(raw_u[j]);
+                    r += bias;
+                    if (p.out_bf16) ((__nv_bfloat16*)p.out)[(size_t)tok * p.ldo + f] = __float2bfloat16_rn(r);
+                    else {
+                        float* o = (float*)p.out + (size_t)tok * p.ldo + f;
+                        *o = p.accumulate ? *o + r : r;
+                    }
+                }
+            }
+            // this warp is done reading the buffer: hand it back to the MMA warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
+    }
+}
+
 // --------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -404,8 +562,27 @@ MLB_EXPORT int mlb_gemm_tc(const void* x, long long ldx, const void* w, long lon
         if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "gemm_tc: cannot reserve shared memory: %s", cudaGetErrorString(e));
         configured = 220 * 1024;
     }
-    dim3 grid((N + BLOCK_W - 1) / BLOCK_W, (M + tok_tile - 1) / tok_tile, splits);
-    if (grid.y > 65535) return fail(MLB_UNSUPPORTED_SIZE, "gemm_tc: too many token tiles (%u)", grid.y);
+    const int n_tiles = (N + BLOCK_W - 1) / BLOCK_W, m_tiles = (M + tok_tile - 1) / tok_tile;
+    if (m_tiles > 65535) return fail(MLB_UNSUPPORTED_SIZE, "gemm_tc: too many token tiles (%d)", m_tiles);
+    if (splits == 1 && (long long)n_tiles * m_tiles > 148 && tok_tile % 32 == 0) {
+        // many tiles: persistent CTAs with a double-buffered accumulator
+        int acc_cols = 2 * cols;
+        p.tmem_cols = 32;
+        while (p.tmem_cols < acc_cols) p.tmem_cols *= 2;
+        p.stages = stages > 0 ? stages : (int)((200 * 1024) / stage_bytes);
+        if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
+        if (p.stages < 2) p.stages = 2;
+        const size_t smem_p = (size_t)p.stages * stage_bytes + 1024;
+        static bool configured_p = false;
+        if (!configured_p) {
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(220 * 1024));
+            if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "gemm_tc: cannot reserve shared memory: %s", cudaGetErrorString(e));
+            configured_p = true;
+        }
+        launch_kernel(gemm_tc_persistent_kernel, dim3(148), dim3(THREADS), smem_p, stream, map_w, map_x, p, n_tiles, m_tiles);
+        return check_launch("gemm_tc_persistent");
+    }
+    dim3 grid(n_tiles, m_tiles, splits);
     launch_kernel(gemm_tc_kernel, grid, THREADS, smem, stream, map_w, map_x, p);
     return check_launch("gemm_tc");
 }

@@ -363,7 +363,8 @@ def test_kernels_refuse_bad_sizes_with_a_clear_error():
 
 # ------------------------------------------------------------------------------ tcgen05 products
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 2048, 1536), (8, 1536, 8960), (5, 200, 264), (64, 384, 192),
-                                   (300, 520, 136), (2048, 1536, 1536), (17, 1000, 72), (130, 130, 8)])
+                                   (300, 520, 136), (2048, 1536, 1536), (17, 1000, 72), (130, 130, 8),
+                                   (2048, 4096, 256), (700, 9000, 200), (2100, 2500, 1536)])   # > 148 tiles: persistent CTAs
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_tensor_core_product_against_fp32(M, N, K, out_dtype):
     from microllm_rocm_b200.kernels import gemm_bf16
@@ -400,7 +401,7 @@ def test_tensor_core_product_split_k_tiles_and_accumulate(splits, tok_tile):
     assert int(gemm_bf16.error_flag(torch.device(DEV)).item()) == 0
 
 
-@pytest.mark.parametrize("M,I,K", [(8, 8960 // 8, 1536), (3, 176, 64), (200, 512, 192)])
+@pytest.mark.parametrize("M,I,K", [(8, 8960 // 8, 1536), (3, 176, 64), (200, 512, 192), (1200, 2100, 192)])
 def test_tensor_core_dual_product_silu_mul(M, I, K):
     from microllm_rocm_b200.kernels import gemm_bf16
     torch.manual_seed(I)
