@@ -11,7 +11,7 @@ using namespace mlb;
 
 constexpr int WARPS = 4;
 constexpr int ROWS_PER_CTA = WARPS * 16;
-constexpr int UNROLL = 8;                      // 32-wide K chunks in flight per thread
+constexpr int BATCH = 4;                       // 32-wide K chunks per register set (two sets in flight)
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
@@ -51,13 +51,69 @@ struct GemvParams {
 // NT: 8-token column blocks (1: M <= 8, 2: M <= 16)
 template <int NT, bool DUAL>
 __global__ void __launch_bounds__(WARPS * 32) gemv_bf16_kernel(GemvParams p) {
-    pdl_prologue();
+    pdl_launch_dependents();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* x_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [NT*8][x_stride]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int k_begin = blockIdx.y * p.k_per_split;
     const int k_end = min(p.K, k_begin + p.k_per_split);
     const int k_len = max(0, k_end - k_begin);
+    const int chunks = k_len / 32;
+
+    const int row0 = blockIdx.x * ROWS_PER_CTA + warp * 16;
+    const bool active = row0 < p.N;
+    // rows past the end read the last row (never stored)
+    const int ra = min(row0 + g, p.N - 1), rb = min(row0 + g + 8, p.N - 1);
+    const __nv_bfloat16* wa = p.w + (size_t)ra * p.ldw + k_begin + t * 8;
+    const __nv_bfloat16* wb = p.w + (size_t)rb * p.ldw + k_begin + t * 8;
+    const __nv_bfloat16* ua = DUAL ? wa + (size_t)p.up_offset * p.ldw : nullptr;
+    const __nv_bfloat16* ub = DUAL ? wb + (size_t)p.up_offset * p.ldw : nullptr;
+    const __nv_bfloat16* xs = x_s + (size_t)g * p.x_stride + t * 8;
+
+    // Two register sets of BATCH chunks each: while one is multiplied the other is in flight.
+    struct Batch { uint4 a[BATCH], b[BATCH], ua[DUAL ? BATCH : 1], ub[DUAL ? BATCH : 1]; };
+    Batch set0, set1;
+    auto load_batch = [&](Batch& s, int c0) {
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u) {
+            if (c0 + u < chunks) {
+                s.a[u] = ldg_stream(wa + (size_t)(c0 + u) * 32);
+                s.b[u] = ldg_stream(wb + (size_t)(c0 + u) * 32);
+                if (DUAL) {
+                    s.ua[u] = ldg_stream(ua + (size_t)(c0 + u) * 32);
+                    s.ub[u] = ldg_stream(ub + (size_t)(c0 + u) * 32);
+                }
+            }
+        }
+    };
+
+    float acc[NT][4], acc_u[DUAL ? NT : 1][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { acc[n][e] = 0.0f; if (DUAL) acc_u[n][e] = 0.0f; }
+    auto mma_batch = [&](const Batch& s, int c0) {
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u) {
+            if (c0 + u < chunks) {
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)n * 8 * p.x_stride + (c0 + u) * 32);
+                    mma_bf16(acc[n], s.a[u].x, s.b[u].x, s.a[u].y, s.b[u].y, xv.x, xv.y);
+                    mma_bf16(acc[n], s.a[u].z, s.b[u].z, s.a[u].w, s.b[u].w, xv.z, xv.w);
+                    if (DUAL) {
+                        mma_bf16(acc_u[n], s.ua[u].x, s.ub[u].x, s.ua[u].y, s.ub[u].y, xv.x, xv.y);
+                        mma_bf16(acc_u[n], s.ua[u].z, s.ub[u].z, s.ua[u].w, s.ub[u].w, xv.z, xv.w);
+                    }
+                }
+            }
+        }
+    };
+
+    // The weights are never written by a kernel: their first loads go out before this kernel
+    // waits for its predecessor, and before the activations are staged.
+    if (active) load_batch(set0, 0);
+    pdl_wait();
 
     // stage this CTA's slice of the activations; rows beyond M are zero
     const int vec_per_row = k_len / 8;
@@ -68,52 +124,13 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_bf16_kernel(GemvParams p) {
         *reinterpret_cast<uint4*>(x_s + (size_t)r * p.x_stride + c) = v;
     }
     __syncthreads();
+    if (!active) return;
 
-    const int row0 = blockIdx.x * ROWS_PER_CTA + warp * 16;
-    if (row0 >= p.N) return;
-    // rows past the end read the last row (never stored)
-    const int ra = min(row0 + g, p.N - 1), rb = min(row0 + g + 8, p.N - 1);
-    const __nv_bfloat16* wa = p.w + (size_t)ra * p.ldw + k_begin + t * 8;
-    const __nv_bfloat16* wb = p.w + (size_t)rb * p.ldw + k_begin + t * 8;
-    const __nv_bfloat16* ua = DUAL ? wa + (size_t)p.up_offset * p.ldw : nullptr;
-    const __nv_bfloat16* ub = DUAL ? wb + (size_t)p.up_offset * p.ldw : nullptr;
-    const __nv_bfloat16* xs = x_s + (size_t)g * p.x_stride + t * 8;
-
-    float acc[NT][4], acc_u[DUAL ? NT : 1][4];
-#pragma unroll
-    for (int n = 0; n < NT; ++n)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) { acc[n][e] = 0.0f; if (DUAL) acc_u[n][e] = 0.0f; }
-
-    const int chunks = k_len / 32;
-    for (int c0 = 0; c0 < chunks; c0 += UNROLL) {
-        uint4 a[UNROLL], b[UNROLL], ua_r[DUAL ? UNROLL : 1], ub_r[DUAL ? UNROLL : 1];
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            if (c0 + u < chunks) {
-                a[u] = ldg_stream(wa + (size_t)(c0 + u) * 32);
-                b[u] = ldg_stream(wb + (size_t)(c0 + u) * 32);
-                if (DUAL) {
-                    ua_r[u] = ldg_stream(ua + (size_t)(c0 + u) * 32);
-                    ub_r[u] = ldg_stream(ub + (size_t)(c0 + u) * 32);
-                }
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            if (c0 + u < chunks) {
-#pragma unroll
-                for (int n = 0; n < NT; ++n) {
-                    const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)n * 8 * p.x_stride + (c0 + u) * 32);
-                    mma_bf16(acc[n], a[u].x, b[u].x, a[u].y, b[u].y, xv.x, xv.y);
-                    mma_bf16(acc[n], a[u].z, b[u].z, a[u].w, b[u].w, xv.z, xv.w);
-                    if (DUAL) {
-                        mma_bf16(acc_u[n], ua_r[u].x, ub_r[u].x, ua_r[u].y, ub_r[u].y, xv.x, xv.y);
-                        mma_bf16(acc_u[n], ua_r[u].z, ub_r[u].z, ua_r[u].w, ub_r[u].w, xv.z, xv.w);
-                    }
-                }
-            }
-        }
+    for (int c0 = 0; c0 < chunks; c0 += 2 * BATCH) {
+        load_batch(set1, c0 + BATCH);
+        mma_batch(set0, c0);
+        load_batch(set0, c0 + 2 * BATCH);
+        mma_batch(set1, c0 + BATCH);
     }
 
     // accumulator element e of column block n: row g (e < 2) or g+8, token n*8 + 2t + (e & 1)

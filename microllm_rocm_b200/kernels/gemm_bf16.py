@@ -60,8 +60,7 @@ def gemv_splits(n: int, k: int):
     return -(-k // k_per_split), k_per_split
 
 
-def gemv_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                  single: bool = False) -> torch.Tensor:
+def gemv_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """[S, M, N] fp32 partial results of x @ weight^T (+ bias, in partial 0); their sum over S,
     taken in order by the kernel that consumes them, is the product."""
     M, K = x.shape

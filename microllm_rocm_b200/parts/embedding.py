@@ -58,8 +58,10 @@ class LMHead(Part):
         if logits.dim() == 3:
             # the few-token kernel: with this many output rows it does not split K, so the one
             # partial result is the product itself
-            if logits.shape[0] != 1:
-                logits = logits.sum(0)
+            if logits.shape[0] != 1:        # a small vocabulary with a long K: add the partial results up
+                total = torch.zeros(logits.shape[1:], dtype=torch.float32, device=logits.device)
+                ops.add_inplace(total, logits)
+                logits = total
             else:
                 logits = logits[0]
         return logits
