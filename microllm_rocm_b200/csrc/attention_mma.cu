@@ -582,22 +582,26 @@ __global__ void __launch_bounds__(WARPS * 32, 2) fa_prefill_kernel(FaParams p) {
 // atomic is needed; the sum over CTAs always runs in rank order.
 constexpr int FRAGS = NB_O * 4;
 constexpr int MAX_SPLITS = 8;
-// shared memory (dynamic): queries | per-warp fragments [WARPS][FRAGS][32] | warp max/sum |
+// shared memory (dynamic): queries | per-warp fragments [DW][FRAGS][32] | warp max/sum |
 // this CTA's merged rows [16][D] with their max and sum | block table
-constexpr size_t DECODE_SMEM = 16 * Q_STRIDE * sizeof(__nv_bfloat16) + (size_t)WARPS * FRAGS * 32 * sizeof(float) +
-                               2 * WARPS * 16 * sizeof(float) + (size_t)16 * D * sizeof(float) + 32 * sizeof(float) +
-                               TABLE_SPAN * sizeof(int);
+constexpr size_t decode_smem(int dw) {
+    return 16 * Q_STRIDE * sizeof(__nv_bfloat16) + (size_t)dw * FRAGS * 32 * sizeof(float) + 2 * dw * 16 * sizeof(float) +
+           (size_t)16 * D * sizeof(float) + 32 * sizeof(float) + TABLE_SPAN * sizeof(int);
+}
 
-__global__ void __launch_bounds__(WARPS * 32, 2) fa_decode_kernel(FaParams p) {
+// DW warps per CTA: 4 (two CTAs per SM, large batches) or 8 (few sequences: more warps, so that each
+// has at most a couple of key tiles and all their loads are in flight at once)
+template <int DW>
+__global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_kernel(FaParams p) {
     pdl_prologue();
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    float* frag = reinterpret_cast<float*>(smem_raw + 16 * Q_STRIDE * sizeof(__nv_bfloat16));   // [WARPS][FRAGS][32]
-    float* warp_m = frag + WARPS * FRAGS * 32;        // [WARPS][16]
-    float* warp_l = warp_m + WARPS * 16;              // [WARPS][16]
-    float* cta_o = warp_l + WARPS * 16;               // [16][D]  this CTA's rows, scaled to cta_m
+    float* frag = reinterpret_cast<float*>(smem_raw + 16 * Q_STRIDE * sizeof(__nv_bfloat16));   // [DW][FRAGS][32]
+    float* warp_m = frag + DW * FRAGS * 32;        // [DW][16]
+    float* warp_l = warp_m + DW * 16;              // [DW][16]
+    float* cta_o = warp_l + DW * 16;               // [16][D]  this CTA's rows, scaled to cta_m
     float* cta_m = cta_o + 16 * D;                    // [16]
     float* cta_l = cta_m + 16;                        // [16]
     int* table_s = reinterpret_cast<int*>(cta_l + 16);
@@ -617,7 +621,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) fa_decode_kernel(FaParams p) {
     const int pos0_load = __ldg(p.seq_pos0 + geo.seq);
     {
         constexpr int VEC_PER_ROW = D / 8;
-        for (int i = threadIdx.x; i < 16 * VEC_PER_ROW; i += WARPS * 32) {
+        for (int i = threadIdx.x; i < 16 * VEC_PER_ROW; i += DW * 32) {
             const int r = i / VEC_PER_ROW, c = (i % VEC_PER_ROW) * 8;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (r < rows_valid) {
@@ -629,7 +633,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) fa_decode_kernel(FaParams p) {
     }
     PageTable pt;
     fill_page_table(pt, table_s, p.block_table + (size_t)geo.seq * p.max_blocks, p.max_blocks, 0, p.max_blocks - 1,
-                    threadIdx.x, WARPS * 32);
+                    threadIdx.x, DW * 32);
     geo.pos0 = pos0_load;
     const int last_pos = geo.pos0;
     const int lo = (p.window > 0 && last_pos - p.window + 1 > 0) ? last_pos - p.window + 1 : 0;
@@ -643,7 +647,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) fa_decode_kernel(FaParams p) {
     __syncthreads();
     RowState st;
     init_state(st);
-    attend<USE_PREFETCH>(p, geo, pt, q_s, tile_begin, tile_end, warp, WARPS, last_pos, st);
+    attend<USE_PREFETCH>(p, geo, pt, q_s, tile_begin, tile_end, warp, DW, last_pos, st);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 1);
@@ -664,16 +668,16 @@ __global__ void __launch_bounds__(WARPS * 32, 2) fa_decode_kernel(FaParams p) {
         warp_l[warp * 16 + g] = st.l[0]; warp_l[warp * 16 + g + 8] = st.l[1];
     }
     __syncthreads();
-    float scale_w[2][WARPS];
+    float scale_w[2][DW];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r = g + 8 * i;
         float m_all = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) m_all = fmaxf(m_all, warp_m[w * 16 + r]);
+        for (int w = 0; w < DW; ++w) m_all = fmaxf(m_all, warp_m[w * 16 + r]);
         float l_all = 0.0f;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) {
+        for (int w = 0; w < DW; ++w) {
             const float mw = warp_m[w * 16 + r];
             scale_w[i][w] = (mw == -INFINITY) ? 0.0f : exp2f(mw - m_all);
             l_all += warp_l[w * 16 + r] * scale_w[i][w];
@@ -681,20 +685,20 @@ __global__ void __launch_bounds__(WARPS * 32, 2) fa_decode_kernel(FaParams p) {
         if (warp == 0 && t == 0) { cta_m[r] = m_all; cta_l[r] = l_all; }
     }
 #pragma unroll
-    for (int k = 0; k < FRAGS / WARPS; ++k) {
-        const int idx = warp + k * WARPS;              // this thread merges fragment idx of all warps
+    for (int k = 0; k < FRAGS / DW; ++k) {
+        const int idx = warp + k * DW;              // this thread merges fragment idx of all warps
         const int nbo = idx >> 2, e = idx & 3, i = e >> 1, r = g + 8 * i;
         const int dim = out_dim(nbo, e, t);
         if (dim >= D || r >= rows_valid) continue;
         float val = 0.0f;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) val += frag[(w * FRAGS + idx) * 32 + lane] * scale_w[i][w];
+        for (int w = 0; w < DW; ++w) val += frag[(w * FRAGS + idx) * 32 + lane] * scale_w[i][w];
         cta_o[r * D + dim] = val;
     }
     // across the cluster: CTA `rank` finishes the slice [rank, rank + 1) * D / splits of every row
     cluster.sync();
     const int slice = D / splits;
-    for (int i = threadIdx.x; i < rows_valid * slice; i += WARPS * 32) {
+    for (int i = threadIdx.x; i < rows_valid * slice; i += DW * 32) {
         const int r = i / slice, dim = rank * slice + i % slice;
         float m_all = -INFINITY;
         float ms[MAX_SPLITS];
@@ -755,17 +759,21 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
         launch_kernel(fa_prefill_kernel, dim3(num_work, num_kv_heads, 1), WARPS * 32, PREFILL_SMEM, stream, p);
         return check_launch("fa_prefill");
     }
+    // a handful of CTAs (one or two sequences): eight warps each; otherwise four warps, two CTAs per SM
+    const bool wide = (long long)num_work * num_kv_heads * splits <= 48;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(4));
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(fa_decode_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(8));
         if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "fa_decode: cannot reserve %d bytes of shared memory: %s",
-                                          (int)DECODE_SMEM, cudaGetErrorString(e));
+                                          (int)decode_smem(8), cudaGetErrorString(e));
         configured = true;
     }
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(num_work, num_kv_heads, splits);
-    config.blockDim = dim3(WARPS * 32);
-    config.dynamicSmemBytes = DECODE_SMEM;
+    config.blockDim = dim3((wide ? 8 : 4) * 32);
+    config.dynamicSmemBytes = wide ? decode_smem(8) : decode_smem(4);
     config.stream = stream;
     cudaLaunchAttribute attributes[2];
     attributes[0].id = cudaLaunchAttributeClusterDimension;
@@ -776,6 +784,7 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
     config.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaLaunchKernelEx(&config, fa_decode_kernel, p);
+    if (wide) cudaLaunchKernelEx(&config, fa_decode_kernel<8>, p);
+    else cudaLaunchKernelEx(&config, fa_decode_kernel<4>, p);
     return check_launch("fa_decode");
 }
