@@ -52,7 +52,7 @@ def prepare_kernels(model=None) -> None:
         for entry in model.cache_entries.values():
             head_dim = getattr(entry.need, "head_dim", None)
             if head_dim:
-                for item in attention.mma_sources(head_dim):
+                for item in attention.mma_sources(head_dim) + attention.tc_sources(head_dim):
                     if item not in sources:
                         sources.append(item)
     kernel_build.compile_many(sources)

@@ -1,15 +1,18 @@
 """Choice of the attention kernel for a step.
 
 fp32: always the plain kernel (fixed summation order, bit-stable across ways of cutting).
-bf16: the tensor-core kernel (`attention_mma.cu`, compiled for the model's head size) when
-the head size is a multiple of 32 and the page size a multiple of 16; the plain kernel
-otherwise.  A step whose sequences all bring one token runs the decode shape (keys split
-over a thread-block cluster that merges through distributed shared memory); any other step
-runs the prefill shape.
+bf16: the tensor-core kernels when the head size is a multiple of 32 and the page size a
+multiple of 16; the plain kernel otherwise.  A step whose sequences all bring one token runs
+the decode shape of `attention_mma.cu` (keys split over a thread-block cluster that merges
+through distributed shared memory).  In any other step every sequence that brings at least
+`TC_MIN_NEW_TOKENS` tokens goes to the tcgen05 kernel (`attention_tc.cu`: 128 query rows per
+CTA, scores and output in tensor memory; head sizes 64 and 128), the others (decoded tokens
+and short portions beside them) to the prefill shape of `attention_mma.cu` with its 16-row
+tiles.  The two launches write disjoint rows of the output.
 """
 from __future__ import annotations
 
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
 import torch
@@ -21,6 +24,15 @@ MAX_HEAD_DIM = 256
 SM_COUNT = 148
 MIN_KEY_TILES_PER_SPLIT = 4         # one 16-key tile per warp at least
 
+TC_HEAD_DIMS = (64, 128)
+TC_KEYS_PER_TILE = 128
+TC_ROWS_PER_TILE = 128
+TC_MIN_NEW_TOKENS = 48              # below this the 16-row tiles of the mma.sync kernel waste less
+
+ops.register_signatures("attention_tc.cu", {
+    "mlb_paged_attention_tc": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+})
 ops.register_signatures("attention_mma.cu", {
     "mlb_paged_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                 c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
@@ -41,22 +53,41 @@ def mma_sources(head_dim: int):
     return [("attention_mma.cu", {"HEAD_DIM": head_dim})] if head_dim % 32 == 0 and 32 <= head_dim <= MAX_HEAD_DIM else []
 
 
-def _plan(ctx, group: int, num_kv_heads: int):
-    """Work list and split choice of a step, shared by every layer with the same group size."""
-    key = ("attention_mma", group, num_kv_heads)
+def tc_supported(head_dim: int, page_size: int, scale: float) -> bool:
+    return (head_dim in TC_HEAD_DIMS and page_size % 8 == 0 and TC_KEYS_PER_TILE % page_size == 0
+            and TC_KEYS_PER_TILE // page_size <= 16 and scale > 0.0)
+
+
+def tc_sources(head_dim: int):
+    return [("attention_tc.cu", {"HEAD_DIM": head_dim})] if head_dim in TC_HEAD_DIMS else []
+
+
+def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
+    """Work lists and split choice of a step, shared by every layer with the same group size."""
+    key = ("attention_mma", group, num_kv_heads, use_tc)
     plan = ctx.extras.get(key)
     if plan is not None:
         return plan
     starts, A = ctx.seq_starts_host, ctx.num_seqs
     decode = ctx.max_new_tokens == 1
-    work = []
+    work, tc_work = [], []
     for a in range(A):
-        tiles = -(-(starts[a + 1] - starts[a]) * group // 16)
+        n_new = starts[a + 1] - starts[a]
+        if use_tc and not decode and n_new >= TC_MIN_NEW_TOKENS:
+            pos0 = ctx.seq_pos0_host[a]
+            for tile in range(-(-n_new // TC_ROWS_PER_TILE)):
+                last_pos = pos0 + min(n_new, (tile + 1) * TC_ROWS_PER_TILE) - 1
+                tc_work.append((last_pos // TC_KEYS_PER_TILE, a, tile))
+            continue
+        tiles = -(-n_new * group // 16)
         work += [(a, first) for first in range(0, tiles, 1 if decode else 4)]
     if not decode:
         # causal work grows with the row tile: start the long ones first so that the tail is short
         work.sort(key=lambda item: -item[1])
-    work_dev = torch.tensor(work, dtype=torch.int32).reshape(-1).to(ctx.positions.device, non_blocking=True)
+        tc_work.sort(key=lambda item: -item[0])
+    device = ctx.positions.device
+    work_dev = torch.tensor(work, dtype=torch.int32).reshape(-1).to(device, non_blocking=True)
+    tc_dev = torch.tensor([(a, t) for _, a, t in tc_work], dtype=torch.int32).reshape(-1).to(device, non_blocking=True)
     splits = 1
     if decode:
         # a cluster of 1, 2, 4 or 8 CTAs shares the keys of one (sequence, kv head): as many as
@@ -67,7 +98,7 @@ def _plan(ctx, group: int, num_kv_heads: int):
             if items * cand <= SM_COUNT * 2 and key_tiles >= cand * MIN_KEY_TILES_PER_SPLIT:
                 splits = cand
                 break
-    plan = (work_dev, len(work), 1 if decode else 0, splits)
+    plan = (work_dev, len(work), 1 if decode else 0, splits, tc_dev, len(tc_work))
     ctx.extras[key] = plan
     return plan
 
@@ -81,8 +112,17 @@ def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx
         return
     if pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("paged_attention: the tensor-core kernel wants bf16 queries, pages and output")
-    T = q.shape[0]
-    work, num_work, mode, splits = _plan(ctx, num_heads // num_kv_heads, num_kv_heads)
+    use_tc = tc_supported(head_dim, page_size, scale) and q.is_contiguous() and out.is_contiguous()
+    work, num_work, mode, splits, tc_work, num_tc = _plan(ctx, num_heads // num_kv_heads, num_kv_heads, use_tc)
+    if num_tc:
+        T = ops.lib("attention_tc.cu", {"HEAD_DIM": head_dim})
+        build.check(T, T.mlb_paged_attention_tc(
+            q.data_ptr(), q.stride(0), pages.data_ptr(), out.data_ptr(), out.stride(0), q.shape[0], ctx.seq_starts.data_ptr(),
+            ctx.seq_pos0.data_ptr(), block_table.data_ptr(), tc_work.data_ptr(), num_tc, block_table.shape[1],
+            pages.shape[0], page_size, num_heads, num_kv_heads, int(window or 0), float(scale), ops._ptr(ctx.error_flag),
+            ops._stream()))
+    if not num_work:
+        return
     L = ops.lib("attention_mma.cu", {"HEAD_DIM": head_dim})
     build.check(L, L.mlb_paged_attention_mma(
         q.data_ptr(), pages.data_ptr(), out.data_ptr(), ctx.seq_starts.data_ptr(), ctx.seq_pos0.data_ptr(), block_table.data_ptr(), work.data_ptr(), num_work,

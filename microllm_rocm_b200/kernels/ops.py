@@ -108,7 +108,7 @@ def all_sources():
     from . import attention
     out = base_sources()
     for d in (32, 64, 128):
-        out += attention.mma_sources(d)
+        out += attention.mma_sources(d) + attention.tc_sources(d)
     from . import gemm_bf16
     return out + gemm_bf16.sources() + [("gemv_noalloc.cu", {})]
 

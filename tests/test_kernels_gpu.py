@@ -135,10 +135,10 @@ def paged_from_dense(k, v, page_size, num_pages, dtype, seed=0):
     return pages.to(dtype), table
 
 
-def run_attention(q_list, k_list, v_list, pos0_list, nh, nkv, d, window, dtype, page_size=16):
+def run_attention(q_list, k_list, v_list, pos0_list, nh, nkv, d, window, dtype, page_size=16, num_pages=64):
     """Queries q_list[s] ([n_s, NH, D]) sit at positions pos0_list[s].. of sequence s whose
     keys are k_list[s]."""
-    pages, table = paged_from_dense(k_list, v_list, page_size, 64, dtype)
+    pages, table = paged_from_dense(k_list, v_list, page_size, num_pages, dtype)
     q = torch.cat([x.reshape(x.shape[0], nh * d) for x in q_list]).to(dtype)
     positions = torch.cat([torch.arange(p, p + x.shape[0], dtype=torch.int32) for p, x in zip(pos0_list, q_list)])
     token_seq = torch.cat([torch.full((x.shape[0],), s, dtype=torch.int32) for s, x in enumerate(q_list)])
@@ -213,6 +213,52 @@ def test_one_far_key_among_hundreds_dominates(dtype):
     # and with a window that just reaches it, visible again
     got_in = run_attention([q], [k], [v], [n - 1], nh, nkv, d, n - far, dtype).reshape(nh, d)
     assert torch.allclose(got_in[0], v[far, 0], atol=3e-2 if dtype == torch.bfloat16 else 1e-4)
+
+
+@pytest.mark.parametrize("nh,nkv,d,window,page_size", [(12, 2, 128, None, 16), (6, 2, 128, 200, 16), (4, 4, 64, None, 32),
+                                                        (5, 1, 64, 129, 8), (2, 1, 128, 64, 128), (3, 3, 128, 1000, 64)])
+def test_tcgen05_prompt_attention_beside_short_portions(nh, nkv, d, window, page_size):
+    """Long prompt portions go through the tcgen05 kernel (128-row tiles, 128-key tiles), short ones
+    and decoded tokens through the mma.sync kernel, in one step.  Portions start at positions that
+    are no multiple of the tile, end inside a page, and unused slots of the pages hold NaN."""
+    torch.manual_seed(nh * d + page_size)
+    lens = [300, 517, 90, 131, 256]          # cached tokens after the step
+    news = [300, 440, 1, 20, 128]            # whole prompt, later portion, decode token, short portion, exact tile
+    ks = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+    vs = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+    qs = [torch.randn(n, nh, d).bfloat16().float() for n in news]
+    pages_needed = sum(-(-n // page_size) for n in lens) + 3
+    got = run_attention(qs, ks, vs, [l - n for l, n in zip(lens, news)], nh, nkv, d, window, torch.bfloat16,
+                        page_size=page_size, num_pages=pages_needed)
+    want = torch.cat([plain_attention_rows(q, k, v, l - n, window).reshape(n, nh * d)
+                      for q, k, v, l, n in zip(qs, ks, vs, lens, news)])
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, **tol(torch.bfloat16)), float((got - want).abs().max())
+
+
+def test_tcgen05_prompt_attention_far_key_and_window_edge():
+    """In a 700-token prompt every query from 400 on is aligned with key 3 (five key tiles back) so that
+    its score stands out; the outputs must be that key's value.  A window that ends one key short of it
+    for the last query only must hide it from that query alone."""
+    torch.manual_seed(11)
+    nh, nkv, d, n = 4, 2, 128, 700
+    k, v = torch.randn(n, nkv, d) * 0.1, torch.randn(n, nkv, d)
+    q = torch.randn(n, nh, d) * 0.1
+    far = 3
+    direction = torch.randn(d)
+    direction /= direction.norm()
+    q[400:, :] = direction * 30
+    k[far, :] = direction * 30
+    k, v, q = (x.bfloat16().float() for x in (k, v, q))
+    got = run_attention([q], [k], [v], [0], nh, nkv, d, None, torch.bfloat16, num_pages=50).reshape(n, nh, d)
+    for h in range(nh):
+        assert torch.allclose(got[400:, h], v[far, h // 2].expand(n - 400, d), atol=3e-2)
+    window = n - 1 - far                      # the last query sees keys far+1..n-1, the one before it sees `far`
+    got_w = run_attention([q], [k], [v], [0], nh, nkv, d, window, torch.bfloat16, num_pages=50).reshape(n, nh, d)
+    want_w = plain_attention_rows(q, k, v, 0, window)
+    assert torch.allclose(got_w, want_w, **tol(torch.bfloat16)), float((got_w - want_w).abs().max())
+    assert torch.allclose(got_w[n - 2, 0], v[far, 0], atol=3e-2)
+    assert not torch.allclose(got_w[n - 1, 0], v[far, 0], atol=0.2)
 
 
 @pytest.mark.parametrize("page_size", [4, 16, 64])
