@@ -593,7 +593,7 @@ constexpr size_t decode_smem(int dw) {
 // has at most a couple of key tiles and all their loads are in flight at once)
 template <int DW>
 __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_kernel(FaParams p) {
-    pdl_prologue();
+    pdl_launch_dependents();       // the wait comes after the sequence's length and block table are on their way
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -617,8 +617,14 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_kernel(FaP
     geo.row0 = (blockIdx.x % tiles_per_seq) * 16;
     const int rows_valid = min(16, p.group - geo.row0);
     const bool upper = rows_valid > 8;
-    // first trip to memory, all at once: the sequence's length, its queries, its block table
+    // First trip to memory: the sequence's length and its block table.  Neither is written by the kernels
+    // just before this one (they come from the host or from the end of the step before), so they are
+    // fetched before the wait for the predecessor; the queries, which it wrote, after it.
     const int pos0_load = __ldg(p.seq_pos0 + geo.seq);
+    PageTable pt;
+    fill_page_table(pt, table_s, p.block_table + (size_t)geo.seq * p.max_blocks, p.max_blocks, 0, p.max_blocks - 1,
+                    threadIdx.x, DW * 32);
+    pdl_wait();
     {
         constexpr int VEC_PER_ROW = D / 8;
         for (int i = threadIdx.x; i < 16 * VEC_PER_ROW; i += DW * 32) {
@@ -631,9 +637,6 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_kernel(FaP
             *reinterpret_cast<uint4*>(q_s + r * Q_STRIDE + c) = v;
         }
     }
-    PageTable pt;
-    fill_page_table(pt, table_s, p.block_table + (size_t)geo.seq * p.max_blocks, p.max_blocks, 0, p.max_blocks - 1,
-                    threadIdx.x, DW * 32);
     geo.pos0 = pos0_load;
     const int last_pos = geo.pos0;
     const int lo = (p.window > 0 && last_pos - p.window + 1 > 0) ? last_pos - p.window + 1 : 0;

@@ -76,14 +76,22 @@ __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_delta, long long delta_stride,
                const float* __restrict__ weight, OutT* __restrict__ out, const int* __restrict__ rows, int width,
                float eps, int vectorised) {
-    pdl_prologue();
+    pdl_launch_dependents();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
-    const size_t src_row = rows ? (size_t)rows[r] : (size_t)r;
-    float* xr = x + src_row * width;
-    OutT* yr = out + (size_t)r * width;
-    float ss = 0.0f;
     if (vectorised) {                       // width % 4 == 0, 16-byte aligned rows, width <= NORM_VECS * 4 * threads
+        // the norm's weight is never written by a kernel: it is fetched before the wait for the predecessor
+        float4 w[NORM_VECS];
+#pragma unroll
+        for (int i = 0; i < NORM_VECS; ++i) {
+            const int c = (threadIdx.x + i * NORM_THREADS) * 4;
+            if (c < width) w[i] = ld4(weight + c);
+        }
+        pdl_wait();
+        const size_t src_row = rows ? (size_t)rows[r] : (size_t)r;
+        float* xr = x + src_row * width;
+        OutT* yr = out + (size_t)r * width;
+        float ss = 0.0f;
         const int nvec = width / 4;
         float4 v[NORM_VECS];
 #pragma unroll
@@ -104,15 +112,19 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_del
         for (int i = 0; i < NORM_VECS; ++i) {
             const int c = (threadIdx.x + i * NORM_THREADS) * 4;
             if (c >= width) break;
-            const float4 w = ld4(weight + c);
-            yr[c + 0] = from_f32<OutT>(v[i].x * inv * w.x);
-            yr[c + 1] = from_f32<OutT>(v[i].y * inv * w.y);
-            yr[c + 2] = from_f32<OutT>(v[i].z * inv * w.z);
-            yr[c + 3] = from_f32<OutT>(v[i].w * inv * w.w);
+            yr[c + 0] = from_f32<OutT>(v[i].x * inv * w[i].x);
+            yr[c + 1] = from_f32<OutT>(v[i].y * inv * w[i].y);
+            yr[c + 2] = from_f32<OutT>(v[i].z * inv * w[i].z);
+            yr[c + 3] = from_f32<OutT>(v[i].w * inv * w[i].w);
         }
         (void)nvec;
         return;
     }
+    pdl_wait();
+    const size_t src_row = rows ? (size_t)rows[r] : (size_t)r;
+    float* xr = x + src_row * width;
+    OutT* yr = out + (size_t)r * width;
+    float ss = 0.0f;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float v = xr[c];
         if (ADD) {

@@ -110,9 +110,9 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_bf16_kernel(GemvParams p) {
         }
     };
 
-    // The weights are never written by a kernel: their first loads go out before this kernel
-    // waits for its predecessor, and before the activations are staged.
-    if (active) load_batch(set0, 0);
+    // The weights are never written by a kernel: the loads of both register sets go out before
+    // this kernel waits for its predecessor, and before the activations are staged.
+    if (active) { load_batch(set0, 0); load_batch(set1, BATCH); }
     pdl_wait();
 
     // stage this CTA's slice of the activations; rows beyond M are zero
@@ -127,10 +127,10 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_bf16_kernel(GemvParams p) {
     if (!active) return;
 
     for (int c0 = 0; c0 < chunks; c0 += 2 * BATCH) {
-        load_batch(set1, c0 + BATCH);
         mma_batch(set0, c0);
         load_batch(set0, c0 + 2 * BATCH);
         mma_batch(set1, c0 + BATCH);
+        load_batch(set1, c0 + 3 * BATCH);
     }
 
     // accumulator element e of column block n: row g (e < 2) or g+8, token n*8 + 2t + (e & 1)

@@ -122,18 +122,42 @@ __device__ __forceinline__ void store4(__nv_bfloat16* dst, const float (&v)[4]) 
 // elements i..i+3 and i+D/2..i+D/2+3 travel as 16-byte pieces.  V heads copy eight elements.
 template <typename QT, typename KVT>
 __global__ void rope_kv_split_half_x4_kernel(RopeKvParams p) {
-    pdl_prologue();
+    // Everything that does not come from the projection before this kernel is fetched and computed before
+    // the wait for it: the position, the angles' sines and cosines, the bias, the page of the cache.
+    pdl_launch_dependents();
     const int half = p.head_dim / 2, quads = half / 4;
     const int heads_all = p.num_heads + 2 * p.num_kv_heads;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (long long)p.tokens * heads_all * quads) return;
+    const bool in_range = idx < (long long)p.tokens * heads_all * quads;
     const int i = (int)(idx % quads) * 4;
-    const int head = (int)((idx / quads) % heads_all);
-    const int t = (int)(idx / ((long long)quads * heads_all));
+    const int head = in_range ? (int)((idx / quads) % heads_all) : 0;
+    const int t = in_range ? (int)(idx / ((long long)quads * heads_all)) : 0;
     const bool is_q = head < p.num_heads;
     const bool is_v = head >= p.num_heads + p.num_kv_heads;
-    if (!is_q && p.pages == nullptr) return;
+    const bool working = in_range && (is_q || p.pages != nullptr);
     const size_t col = (size_t)head * p.head_dim;
+    float4 ba = make_float4(0.f, 0.f, 0.f, 0.f), bb = ba;
+    float sn[4] = {0.f, 0.f, 0.f, 0.f}, cs[4] = {1.f, 1.f, 1.f, 1.f};
+    int pos = 0, page = -1;
+    if (working) {
+        if (p.bias) {
+            ba = *reinterpret_cast<const float4*>(p.bias + col + i);
+            bb = *reinterpret_cast<const float4*>(p.bias + col + i + half);
+        }
+        pos = p.positions[t];
+        if (!is_v) {
+            const float4 f = *reinterpret_cast<const float4*>(p.inv_freq + i);
+            const float fr[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) sincosf((float)pos * fr[k], &sn[k], &cs[k]);
+        }
+        if (!is_q) {
+            const int block = pos / p.page_size;
+            if (pos >= 0 && block < p.max_blocks) page = p.block_table[(size_t)p.token_seq[t] * p.max_blocks + block];
+        }
+    }
+    pdl_wait();
+    if (!working) return;
     const float* src = p.qkv + (size_t)t * p.ld + col;
     // V has nothing to rotate: its two pieces are simply elements i.. and i+half..
     float4 a = *reinterpret_cast<const float4*>(src + i), b = *reinterpret_cast<const float4*>(src + i + half);
@@ -143,21 +167,13 @@ __global__ void rope_kv_split_half_x4_kernel(RopeKvParams p) {
         a.x += a2.x; a.y += a2.y; a.z += a2.z; a.w += a2.w;
         b.x += b2.x; b.y += b2.y; b.z += b2.z; b.w += b2.w;
     }
-    if (p.bias) {
-        const float4 ba = *reinterpret_cast<const float4*>(p.bias + col + i), bb = *reinterpret_cast<const float4*>(p.bias + col + i + half);
-        a.x += ba.x; a.y += ba.y; a.z += ba.z; a.w += ba.w;
-        b.x += bb.x; b.y += bb.y; b.z += bb.z; b.w += bb.w;
-    }
-    const int pos = p.positions[t];
+    a.x += ba.x; a.y += ba.y; a.z += ba.z; a.w += ba.w;
+    b.x += bb.x; b.y += bb.y; b.z += bb.z; b.w += bb.w;
     float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
     if (!is_v) {
-        const float4 f = *reinterpret_cast<const float4*>(p.inv_freq + i);
-        const float fr[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            float s, c;
-            sincosf((float)pos * fr[k], &s, &c);
-            const float ra = av[k] * c - bv[k] * s, rb = av[k] * s + bv[k] * c;
+            const float ra = av[k] * cs[k] - bv[k] * sn[k], rb = av[k] * sn[k] + bv[k] * cs[k];
             av[k] = ra; bv[k] = rb;
         }
     }
@@ -168,9 +184,7 @@ __global__ void rope_kv_split_half_x4_kernel(RopeKvParams p) {
         return;
     }
     const int kvh = is_v ? head - p.num_heads - p.num_kv_heads : head - p.num_heads;
-    const int block = pos / p.page_size, slot = pos % p.page_size;
-    int page = -1;
-    if (pos >= 0 && block < p.max_blocks) page = p.block_table[(size_t)p.token_seq[t] * p.max_blocks + block];
+    const int slot = pos % p.page_size;
     if (page < 0 || page >= p.num_pages) {
         if (p.error_flag) atomicExch(p.error_flag, 1);
         return;
