@@ -234,12 +234,13 @@ __device__ __forceinline__ void consume_keys(const FaParams& p, const __nv_bfloa
 }
 
 // Keys [tile_begin, tile_end) in units of 16, visiting every `stride`-th starting at
-// tile_begin + first.  q_s: this tile's queries, [16][Q_STRIDE] bf16 in shared memory.  With
+// tile_begin + first.  `a` is the register home of the first tile; with a_in_flight the caller has
+// already issued its loads.  q_s: this tile's queries, [16][Q_STRIDE] bf16 in shared memory.  With
 // PREFETCH the loads of the next key tile are in flight while the current one is consumed.
 template <bool PREFETCH>
 __device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& geo, const PageTable& pt,
                                        const __nv_bfloat16* q_s, int tile_begin, int tile_end, int first, int stride,
-                                       int hi_tile, RowState& st) {
+                                       int hi_tile, RowState& st, KeyTile& a, bool a_in_flight) {
     const int lane = threadIdx.x & 31, g = lane >> 2;
     int pos_row[2], lo_row[2];
 #pragma unroll
@@ -256,8 +257,8 @@ __device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& ge
     int kt = tile_begin + first;
     if (kt >= tile_end) return;
     if (PREFETCH) {
-        KeyTile a, b;
-        load_keys(p, geo, pt, kt, hi_tile, a);
+        KeyTile b;
+        if (!a_in_flight) load_keys(p, geo, pt, kt, hi_tile, a);
         while (true) {
             const bool more_b = kt + stride < tile_end;
             if (more_b) load_keys(p, geo, pt, kt + stride, hi_tile, b);
@@ -271,9 +272,9 @@ __device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& ge
             kt += stride;
         }
     } else {
-        KeyTile a;
         for (; kt < tile_end; kt += stride) {
-            load_keys(p, geo, pt, kt, hi_tile, a);
+            if (!a_in_flight) load_keys(p, geo, pt, kt, hi_tile, a);
+            a_in_flight = false;
             consume_keys(p, q_s, a, pos_row, lo_row, st);
         }
     }
@@ -624,6 +625,23 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_kernel(FaP
     PageTable pt;
     fill_page_table(pt, table_s, p.block_table + (size_t)geo.seq * p.max_blocks, p.max_blocks, 0, p.max_blocks - 1,
                     threadIdx.x, DW * 32);
+    geo.pos0 = pos0_load;
+    const int last_pos = geo.pos0;
+    const int lo = (p.window > 0 && last_pos - p.window + 1 > 0) ? last_pos - p.window + 1 : 0;
+    int tile_begin = lo / 16, tile_end = last_pos / 16 + 1;
+    const int splits = (int)gridDim.z, rank = (int)blockIdx.z;
+    if (splits > 1) {                        // this CTA's even share of the sequence's key tiles
+        const int per_split = (tile_end - tile_begin + splits - 1) / splits;
+        tile_begin += rank * per_split;
+        tile_end = min(tile_end, tile_begin + per_split);
+    }
+    __syncthreads();                         // the block table is in shared memory
+    // Second trip, still before the wait: this warp's first key tile, unless it holds the new token's
+    // key, which the kernel before this one is writing.
+    KeyTile first_tile;
+    const int first_kt = tile_begin + warp;
+    const bool early = first_kt < tile_end && first_kt < last_pos / 16;
+    if (early) load_keys(p, geo, pt, first_kt, last_pos, first_tile);
     pdl_wait();
     {
         constexpr int VEC_PER_ROW = D / 8;
@@ -637,20 +655,10 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_kernel(FaP
             *reinterpret_cast<uint4*>(q_s + r * Q_STRIDE + c) = v;
         }
     }
-    geo.pos0 = pos0_load;
-    const int last_pos = geo.pos0;
-    const int lo = (p.window > 0 && last_pos - p.window + 1 > 0) ? last_pos - p.window + 1 : 0;
-    int tile_begin = lo / 16, tile_end = last_pos / 16 + 1;
-    const int splits = (int)gridDim.z, rank = (int)blockIdx.z;
-    if (splits > 1) {                        // this CTA's even share of the sequence's key tiles
-        const int per_split = (tile_end - tile_begin + splits - 1) / splits;
-        tile_begin += rank * per_split;
-        tile_end = min(tile_end, tile_begin + per_split);
-    }
     __syncthreads();
     RowState st;
     init_state(st);
-    attend<USE_PREFETCH>(p, geo, pt, q_s, tile_begin, tile_end, warp, DW, last_pos, st);
+    attend<USE_PREFETCH>(p, geo, pt, q_s, tile_begin, tile_end, warp, DW, last_pos, st, first_tile, early);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 1);
