@@ -234,13 +234,13 @@ __device__ __forceinline__ void consume_keys(const FaParams& p, const __nv_bfloa
 }
 
 // Keys [tile_begin, tile_end) in units of 16, visiting every `stride`-th starting at
-// tile_begin + first.  `a` is the register home of the first tile; with a_in_flight the caller has
-// already issued its loads.  q_s: this tile's queries, [16][Q_STRIDE] bf16 in shared memory.  With
+// tile_begin + first.  `a` and `b` are the register homes of the first and second tile; the caller
+// has already issued the loads of the first `in_flight` of them (b only where PREFETCH).  q_s: this tile's queries, [16][Q_STRIDE] bf16 in shared memory.  With
 // PREFETCH the loads of the next key tile are in flight while the current one is consumed.
 template <bool PREFETCH>
 __device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& geo, const PageTable& pt,
                                        const __nv_bfloat16* q_s, int tile_begin, int tile_end, int first, int stride,
-                                       int hi_tile, RowState& st, KeyTile& a, bool a_in_flight) {
+                                       int hi_tile, RowState& st, KeyTile& a, KeyTile& b, int in_flight) {
     const int lane = threadIdx.x & 31, g = lane >> 2;
     int pos_row[2], lo_row[2];
 #pragma unroll
@@ -257,11 +257,11 @@ __device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& ge
     int kt = tile_begin + first;
     if (kt >= tile_end) return;
     if (PREFETCH) {
-        KeyTile b;
-        if (!a_in_flight) load_keys(p, geo, pt, kt, hi_tile, a);
+        if (in_flight < 1) load_keys(p, geo, pt, kt, hi_tile, a);
         while (true) {
             const bool more_b = kt + stride < tile_end;
-            if (more_b) load_keys(p, geo, pt, kt + stride, hi_tile, b);
+            if (more_b && in_flight < 2) load_keys(p, geo, pt, kt + stride, hi_tile, b);
+            in_flight = 0;
             consume_keys(p, q_s, a, pos_row, lo_row, st);
             if (!more_b) break;
             kt += stride;
@@ -273,8 +273,8 @@ __device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& ge
         }
     } else {
         for (; kt < tile_end; kt += stride) {
-            if (!a_in_flight) load_keys(p, geo, pt, kt, hi_tile, a);
-            a_in_flight = false;
+            if (in_flight < 1) load_keys(p, geo, pt, kt, hi_tile, a);
+            in_flight = 0;
             consume_keys(p, q_s, a, pos_row, lo_row, st);
         }
     }
@@ -638,10 +638,17 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_kernel(FaP
     __syncthreads();                         // the block table is in shared memory
     // Second trip, still before the wait: this warp's first key tile, unless it holds the new token's
     // key, which the kernel before this one is writing.
-    KeyTile first_tile;
+    KeyTile tile_a, tile_b;
     const int first_kt = tile_begin + warp;
-    const bool early = first_kt < tile_end && first_kt < last_pos / 16;
-    if (early) load_keys(p, geo, pt, first_kt, last_pos, first_tile);
+    int early = 0;
+    if (first_kt < tile_end && first_kt < last_pos / 16) {
+        load_keys(p, geo, pt, first_kt, last_pos, tile_a);
+        early = 1;
+        if (USE_PREFETCH && first_kt + DW < tile_end && first_kt + DW < last_pos / 16) {
+            load_keys(p, geo, pt, first_kt + DW, last_pos, tile_b);
+            early = 2;
+        }
+    }
     pdl_wait();
     {
         constexpr int VEC_PER_ROW = D / 8;
@@ -658,7 +665,7 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_kernel(FaP
     __syncthreads();
     RowState st;
     init_state(st);
-    attend<USE_PREFETCH>(p, geo, pt, q_s, tile_begin, tile_end, warp, DW, last_pos, st, first_tile, early);
+    attend<USE_PREFETCH>(p, geo, pt, q_s, tile_begin, tile_end, warp, DW, last_pos, st, tile_a, tile_b, early);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 1);
@@ -736,6 +743,13 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_kernel(FaP
 
 }  // namespace
 
+// up to this many CTAs the decode shape runs eight warps per CTA (MLB_FA_WIDE_LIMIT overrides, for measurements)
+static int wide_limit() {
+    static int limit = -1;
+    if (limit < 0) { const char* e = getenv("MLB_FA_WIDE_LIMIT"); limit = e ? atoi(e) : 48; }
+    return limit;
+}
+
 MLB_EXPORT int mlb_fa_head_dim() { return D; }
 MLB_EXPORT int mlb_fa_max_splits() { return MAX_SPLITS; }
 
@@ -771,7 +785,7 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
         return check_launch("fa_prefill");
     }
     // a handful of CTAs (one or two sequences): eight warps each; otherwise four warps, two CTAs per SM
-    const bool wide = (long long)num_work * num_kv_heads * splits <= 48;
+    const bool wide = (long long)num_work * num_kv_heads * splits <= wide_limit();
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(4));
