@@ -24,6 +24,13 @@ ops.register_signatures("gemv_bf16.cu", {
     "mlb_gemv_bf16": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int,
                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
 })
+ops.register_signatures("gemv_fused.cu", {
+    "mlb_gemv_silu": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_int, c_int,
+                      c_void_p],
+    "mlb_gemv_qkv_rope": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                          c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                          c_void_p],
+})
 ops.register_signatures("gemm_tc.cu", {
     "mlb_gemm_tc": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int,
                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -35,7 +42,7 @@ _error_flags = {}
 
 
 def sources():
-    return [("gemm_tc.cu", {}), ("gemv_bf16.cu", {})]
+    return [("gemm_tc.cu", {}), ("gemv_bf16.cu", {}), ("gemv_fused.cu", {})]
 
 
 # ------------------------------------------------------------------------------ few tokens: weight streaming
@@ -73,15 +80,55 @@ def gemv_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
     return partial
 
 
+GEMV_FUSED_MAX_K = 6144             # the activations of 16 tokens over the whole K must fit shared memory
+
+
+def gemv_fused_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """The few-token kernels that finish their own epilogue (activation; rotation and cache store)."""
+    return gemv_supported(x, weight) and x.shape[1] <= GEMV_FUSED_MAX_K and x.dtype == torch.bfloat16
+
+
 def gemv_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, I] (bf16) = silu(x @ weight[:I]^T) * (x @ weight[I:2I]^T)."""
+    """out[M, I] (bf16) = silu(x @ weight[:I]^T) * (x @ weight[I:2I]^T), one kernel, no partial sums."""
     M, K = x.shape
     I = out.shape[1]
-    if weight.shape != (2 * I, K) or out.shape[0] != M or out.dtype != torch.bfloat16:
+    if weight.shape != (2 * I, K) or out.shape[0] != M or out.dtype != torch.bfloat16 or out.stride(1) != 1:
         raise KernelError("gemv_silu_mul: the weight must hold gate rows then up rows, the output be bf16 [M, I]")
-    L = ops.lib("gemv_bf16.cu")
-    build.check(L, L.mlb_gemv_bf16(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), 2 * I, None, None,
-                                   out.data_ptr(), out.stride(0), 1, I, M, I, K, 1, K, ops._stream()))
+    L = ops.lib("gemv_fused.cu")
+    build.check(L, L.mlb_gemv_silu(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), 2 * I, I, out.data_ptr(),
+                                   out.stride(0), M, I, K, ops._stream()))
+
+
+def gemv_qkv_rope(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
+                  token_seq: torch.Tensor, block_table: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
+                  q_out: torch.Tensor, pages: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
+                  error_flag: Optional[torch.Tensor]) -> None:
+    """Fused q/k/v projection of a few tokens with bias, split-half rotation over the whole head
+    (inv_freq None: no rotation) and the store of keys and values into the paged cache
+    (`pages` None: they are dropped); rotated queries go to q_out [M, NH*D] bf16."""
+    M, K = x.shape
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    if weight.shape != (width, K) or q_out.shape != (M, num_heads * head_dim) or q_out.dtype != torch.bfloat16 \
+            or not q_out.is_contiguous() or positions.shape[0] != M:
+        raise KernelError("gemv_qkv_rope: shapes do not agree")
+    if head_dim % 16:
+        raise KernelError(f"gemv_qkv_rope: head_dim {head_dim} must be a multiple of 16")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.shape[0] * 2 != head_dim):
+        raise KernelError("gemv_qkv_rope: inv_freq must hold head_dim/2 fp32 entries")
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape[0] != width):
+        raise KernelError("gemv_qkv_rope: the bias must be fp32 of the fused width")
+    num_pages = page_size = max_blocks = 0
+    if pages is not None:
+        num_pages, two, nkv, page_size, d = pages.shape
+        if two != 2 or nkv != num_kv_heads or d != head_dim or pages.dtype != torch.bfloat16 or not pages.is_contiguous():
+            raise KernelError(f"gemv_qkv_rope: pages {tuple(pages.shape)} do not match the head geometry")
+        max_blocks = block_table.shape[1]
+    L = ops.lib("gemv_fused.cu")
+    build.check(L, L.mlb_gemv_qkv_rope(
+        x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), ops._ptr(bias), positions.data_ptr(),
+        token_seq.data_ptr(), ops._ptr(block_table), max_blocks, ops._ptr(inv_freq), 1 if inv_freq is not None else 0,
+        q_out.data_ptr(), ops._ptr(pages), num_pages, page_size, M, K, num_heads, num_kv_heads, head_dim,
+        ops._ptr(error_flag), ops._stream()))
 
 
 def _device_scratch(device):

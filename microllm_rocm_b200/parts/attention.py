@@ -18,7 +18,7 @@ from typing import Dict, Optional
 import torch
 
 from ..kernels import attention as attention_kernels
-from ..kernels import ops
+from ..kernels import gemm_bf16, ops
 from ..kernels.linear import linear
 from .base import Mixer, PagedKVNeed, PagedKVView, PositionEncoding, Runtime, StepContext, WeightSpec, register_mixer
 
@@ -71,12 +71,19 @@ class Attention(Mixer):
     # --- compute ------------------------------------------------------------------------
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVView) -> torch.Tensor:
         T = x.shape[0]
-        qkv = linear(x, self.w_qkv, None, torch.float32, partials_ok=True)     # [T, (NH+2NKV)*D] f32, or its partial sums
         q = torch.empty((T, self.nh * self.d), dtype=self.rt.dtype, device=x.device)
         inv_freq, rot, inter = ((self.rotary.inv_freq, self.rotary.rotary_dim, self.rotary.interleaved)
                                 if self.rotary is not None else (self._no_rot, 0, False))
-        ops.rope_kv_write(qkv, self.b_qkv, ctx.positions, ctx.token_seq, cache.block_table, inv_freq, rot, inter,
-                          q, cache.pages if cache.writable else None, self.nh, self.nkv, self.d, ctx.error_flag)
+        pages = cache.pages if cache.writable else None
+        if (x.dtype == torch.bfloat16 and gemm_bf16.gemv_fused_supported(x, self.w_qkv) and self.d % 16 == 0
+                and (rot == 0 or (rot == self.d and not inter))):
+            # a few tokens: projection, bias, rotation and the cache store in one weight-streaming kernel
+            gemm_bf16.gemv_qkv_rope(x, self.w_qkv, self.b_qkv, ctx.positions, ctx.token_seq, cache.block_table,
+                                    inv_freq if rot else None, q, pages, self.nh, self.nkv, self.d, ctx.error_flag)
+        else:
+            qkv = linear(x, self.w_qkv, None, torch.float32, partials_ok=True)  # [T, (NH+2NKV)*D] f32, or its partial sums
+            ops.rope_kv_write(qkv, self.b_qkv, ctx.positions, ctx.token_seq, cache.block_table, inv_freq, rot, inter,
+                              q, pages, self.nh, self.nkv, self.d, ctx.error_flag)
         o = torch.empty_like(q)
         attention_kernels.paged_attention(q, cache.pages, o, ctx, cache.block_table, self.nh, self.nkv, self.d,
                                           self.scale, self.window)

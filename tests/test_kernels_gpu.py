@@ -500,7 +500,7 @@ def test_gemv_partials_sum_to_the_product(M, N, K):
     assert torch.equal(r2, r)
 
 
-@pytest.mark.parametrize("M,I,K", [(8, 1120, 1536), (2, 176, 64), (13, 512, 192)])
+@pytest.mark.parametrize("M,I,K", [(8, 1120, 1536), (2, 176, 64), (13, 512, 192), (1, 1000, 96), (16, 72, 4096), (7, 23, 32)])
 def test_gemv_silu_mul(M, I, K):
     from microllm_rocm_b200.kernels import gemm_bf16
     torch.manual_seed(I + M)
@@ -510,6 +510,60 @@ def test_gemv_silu_mul(M, I, K):
     gemm_bf16.gemv_silu_mul(x.to(DEV), w.to(DEV), out)
     want = plain.swiglu(x.float() @ w[:I].float().t(), x.float() @ w[I:].float().t())
     assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,nh,nkv,d,K,rotate,with_bias", [(8, 12, 2, 128, 1536, True, True), (1, 4, 1, 16, 64, True, False),
+                                                         (13, 5, 5, 48, 160, True, True), (16, 3, 1, 256, 96, False, True),
+                                                         (3, 14, 2, 64, 896, True, True)])
+def test_gemv_qkv_rope_projects_rotates_and_stores(M, nh, nkv, d, K, rotate, with_bias):
+    """Projection, bias, split-half rotation and the paged store in one kernel, against the plain
+    functions; tokens of three sequences at positions around page edges, pages in shuffled order."""
+    from microllm_rocm_b200.kernels import gemm_bf16
+    from microllm_rocm_b200.parts.rotary import inverse_frequencies
+    torch.manual_seed(M + nh + d)
+    theta, page = 1e6, 8
+    width = (nh + 2 * nkv) * d
+    x = (torch.randn(M, K) * 0.5).bfloat16()
+    w = (torch.randn(width, K) * 0.1).bfloat16()
+    bias = torch.randn(width) * 0.3 if with_bias else None
+    positions = torch.tensor(([0, 7, 8, 100, 101, 40, 41, 63, 64, 15, 16, 17, 300, 301, 302, 303])[:M], dtype=torch.int32)
+    token_seq = torch.tensor(([0, 0, 0, 1, 1, 2, 2, 2, 2, 0, 0, 0, 1, 1, 1, 1])[:M], dtype=torch.int32)
+    num_pages, maxb = 64, 40
+    table = torch.full((3, maxb), -1, dtype=torch.int32)
+    perm = list(range(num_pages))
+    random.Random(2).shuffle(perm)
+    for s_, b_ in sorted({(s_, int(p_) // page) for s_, p_ in zip(token_seq.tolist(), positions.tolist())}):
+        table[s_, b_] = perm.pop()
+    pages = torch.zeros(num_pages, 2, nkv, page, d, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.empty(M, nh * d, dtype=torch.bfloat16, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    inv = torch.from_numpy(inverse_frequencies(theta, d)).to(DEV) if rotate else None
+    assert gemm_bf16.gemv_fused_supported(x.to(DEV), w.to(DEV))
+    gemm_bf16.gemv_qkv_rope(x.to(DEV), w.to(DEV), bias.to(DEV) if with_bias else None, positions.to(DEV), token_seq.to(DEV),
+                            table.to(DEV), inv, q_out, pages, nh, nkv, d, flag)
+    assert int(flag.item()) == 0
+    y = x.float() @ w.float().t()
+    if with_bias:
+        y = y + bias
+    y = y.view(M, nh + 2 * nkv, d)
+    rot = (lambda h: plain.rope_split_half(h, positions.tolist(), theta)) if rotate else (lambda h: h)
+    want_q, want_k, want_v = rot(y[:, :nh]), rot(y[:, nh:nh + nkv]), y[:, nh + nkv:]
+    t_ = tol(torch.bfloat16)
+    assert torch.allclose(q_out.float().cpu().view(M, nh, d), want_q, **t_)
+    pc = pages.float().cpu()
+    written = torch.zeros(num_pages, page, dtype=torch.bool)
+    for t in range(M):
+        p_, slot = table[token_seq[t], positions[t] // page], positions[t] % page
+        assert torch.allclose(pc[p_, 0, :, slot], want_k[t], **t_)
+        assert torch.allclose(pc[p_, 1, :, slot], want_v[t], **t_)
+        written[p_, slot] = True
+    assert (pc.abs().sum(dim=(1, 2, 4))[~written] == 0).all()            # nothing else was touched
+    # a token without a page raises the flag and writes nothing
+    table[:] = -1
+    pages.zero_()
+    gemm_bf16.gemv_qkv_rope(x.to(DEV), w.to(DEV), None, positions.to(DEV), token_seq.to(DEV), table.to(DEV), inv, q_out,
+                            pages, nh, nkv, d, flag)
+    assert int(flag.item()) == 1 and float(pages.float().abs().sum()) == 0.0
 
 
 def test_rope_kv_write_adds_partial_projections():
