@@ -80,6 +80,7 @@ def gemv_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
     return partial
 
 
+GEMV_SILU_MAX_TOKENS = 8            # beyond one 8-token column block the fused gate/up kernel loses to partial sums + activation
 GEMV_FUSED_MAX_K = 6144             # the activations of 16 tokens over the whole K must fit shared memory
 
 

@@ -35,11 +35,11 @@ class SwiGLU(FeedForward):
         # activation is evaluated in fp32 and stored bf16, down returns fp32 at the residual
         # boundary -- the reference's policy for its bf16 feed-forward (src/ops/optimized.cpp:676-683).
         act = torch.empty((x.shape[0], self.inter), dtype=self.rt.dtype, device=x.device)
-        if x.dtype == torch.bfloat16 and gemm_bf16.gemv_fused_supported(x, self.w_gate_up):
+        if x.dtype == torch.bfloat16 and x.shape[0] <= gemm_bf16.GEMV_SILU_MAX_TOKENS and gemm_bf16.gemv_fused_supported(x, self.w_gate_up):
             # a few tokens: one weight-streaming kernel, the activation is its epilogue
             gemm_bf16.gemv_silu_mul(x, self.w_gate_up, act)
         elif x.dtype == torch.bfloat16 and gemm_bf16.gemv_supported(x, self.w_gate_up):
-            # a width too large for that kernel: fp32 partial sums, the activation adds them
+            # more tokens, or a width too large for that kernel: fp32 partial sums, the activation adds them
             ops.silu_mul(gemm_bf16.gemv_partials(x, self.w_gate_up), act)
         else:
             gate_up = linear(x, self.w_gate_up, None, self.rt.dtype)
