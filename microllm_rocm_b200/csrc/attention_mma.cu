@@ -582,7 +582,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) fa_prefill_kernel(FaParams p) {
 // distributed shared memory.  Nothing is staged in global memory and no second launch or
 // atomic is needed; the sum over CTAs always runs in rank order.
 constexpr int FRAGS = NB_O * 4;
-constexpr int MAX_SPLITS = 8;
+constexpr int MAX_SPLITS = 16;            // clusters beyond 8 CTAs are the non-portable size, allowed on this GPU
 // shared memory (dynamic): queries | per-warp fragments [DW][FRAGS][32] | warp max/sum |
 // this CTA's merged rows [16][D] with their max and sum | block table
 constexpr size_t decode_smem(int dw) {
@@ -767,8 +767,10 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
         return fail(MLB_UNSUPPORTED_SIZE, "paged_attention_mma: page_size %d must be a multiple of 16", page_size);
     if (num_pages <= 0 || max_blocks <= 0 || window < 0 || num_work < 0)
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: bad cache geometry");
-    if (mode == 1 && !(splits == 1 || splits == 2 || splits == 4 || splits == 8))
-        return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: %d splits, expected 1, 2, 4 or 8", splits);
+    if (mode == 1 && !(splits == 1 || splits == 2 || splits == 4 || splits == 8 || splits == 16))
+        return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: %d splits, expected 1, 2, 4, 8 or 16", splits);
+    if (mode == 1 && D % splits != 0)
+        return fail(MLB_UNSUPPORTED_SIZE, "paged_attention_mma: %d splits do not divide the head size %d", splits, D);
     if (num_work == 0) return MLB_OK;
     FaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, seq_starts, seq_pos0,
                block_table, work, max_blocks, num_pages, page_size, num_heads, num_kv_heads,
@@ -791,6 +793,8 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
         cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(4));
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(fa_decode_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(8));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_decode_kernel<4>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_decode_kernel<8>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "fa_decode: cannot reserve %d bytes of shared memory: %s",
                                           (int)decode_smem(8), cudaGetErrorString(e));
         configured = true;
@@ -809,6 +813,20 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
     config.numAttrs = pdl_enabled() ? 2 : 1;
+    if (splits > 8) {
+        // the non-portable cluster size: ask once whether such a cluster can be resident at all
+        static int clusters16 = -1;
+        if (clusters16 < 0) {
+            cudaLaunchConfig_t probe = config;
+            probe.numAttrs = 1;
+            int n = 0;
+            cudaError_t e = wide ? cudaOccupancyMaxActiveClusters(&n, fa_decode_kernel<8>, &probe)
+                                 : cudaOccupancyMaxActiveClusters(&n, fa_decode_kernel<4>, &probe);
+            clusters16 = (e == cudaSuccess) ? n : 0;
+            cudaGetLastError();
+        }
+        if (clusters16 < 1) return fail(MLB_UNSUPPORTED_SIZE, "fa_decode: clusters of %d CTAs cannot be resident on this device", splits);
+    }
     if (wide) cudaLaunchKernelEx(&config, fa_decode_kernel<8>, p);
     else cudaLaunchKernelEx(&config, fa_decode_kernel<4>, p);
     return check_launch("fa_decode");

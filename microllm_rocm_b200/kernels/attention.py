@@ -12,6 +12,7 @@ tiles.  The two launches write disjoint rows of the output.
 """
 from __future__ import annotations
 
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -23,6 +24,7 @@ from .build import KernelError
 MAX_HEAD_DIM = 256
 SM_COUNT = 148
 MIN_KEY_TILES_PER_SPLIT = 4         # one 16-key tile per warp at least
+DECODE_SPLITS = tuple(int(v) for v in os.environ.get("MLB_FA_DECODE_SPLITS", "8,4,2").split(","))   # cluster sizes tried, largest first
 
 TC_HEAD_DIMS = (64, 128)
 TC_KEYS_PER_TILE = 128
@@ -94,7 +96,7 @@ def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
         # still fit the GPU in one wave (two CTAs per SM) and leave every warp a key tile
         key_tiles = max(1, -(-ctx.max_seq_len // 16))
         items = max(1, len(work) * num_kv_heads)
-        for cand in (8, 4, 2):
+        for cand in DECODE_SPLITS:
             if items * cand <= SM_COUNT * 2 and key_tiles >= cand * MIN_KEY_TILES_PER_SPLIT:
                 splits = cand
                 break
