@@ -59,6 +59,7 @@ struct FaParams {
     int num_heads, num_kv_heads, group;
     int window;
     float scale_log2;               // softmax scale * log2(e)
+    int page_shift;                 // log2(page_size) when it is a power of two, else -1
     int* error_flag;
 };
 
@@ -72,6 +73,14 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
+}
+
+constexpr float RESCALE_STEP = 8.0f;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 __device__ __forceinline__ uint4 load16(const __nv_bfloat16* p) {
@@ -130,7 +139,9 @@ __device__ __forceinline__ void load_keys(const FaParams& p, const TileGeometry&
                                           int hi_tile, KeyTile& kv) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int base = kt * 16;
-    const int page = pt.page_of(base / p.page_size);
+    const int block = p.page_shift >= 0 ? base >> p.page_shift : base / p.page_size;
+    const int slot = p.page_shift >= 0 ? base & (p.page_size - 1) : base % p.page_size;
+    const int page = pt.page_of(block);
     if (page < 0 || page >= p.num_pages) {
         if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 3);
         kv.base = -1;
@@ -138,27 +149,40 @@ __device__ __forceinline__ void load_keys(const FaParams& p, const TileGeometry&
     }
     kv.base = base;
     const size_t page_stride = (size_t)2 * p.num_kv_heads * p.page_size * D;
-    const __nv_bfloat16* kbase = p.pages + (size_t)page * page_stride +
-                                 ((size_t)geo.kvh * p.page_size + (base % p.page_size)) * D;
+    const __nv_bfloat16* kbase = p.pages + (size_t)page * page_stride + ((size_t)geo.kvh * p.page_size + slot) * D;
     const __nv_bfloat16* vbase = kbase + (size_t)p.num_kv_heads * p.page_size * D;
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
         for (int c = 0; c < KCHUNKS; ++c) kv.k[nb][c] = load16(kbase + (size_t)(nb * 8 + g) * D + c * 32 + t * 8);
+    if (base + 15 <= hi_tile) {                        // every key of the tile was written: no predicates
+#pragma unroll
+        for (int vb = 0; vb < VBLOCKS; ++vb) {
+            const int col = vb * 64 + g * 8;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int key = 2 * t + (r & 1) + 8 * (r >> 1);   // this thread's keys: 2t, 2t+1, 2t+8, 2t+9
+                kv.v[vb][r] = (D % 64 == 0 || col < D) ? load16(vbase + (size_t)key * D + col) : make_uint4(0, 0, 0, 0);
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int vb = 0; vb < VBLOCKS; ++vb) {
         const int col = vb * 64 + g * 8;
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-            const int key = 2 * t + (r & 1) + 8 * (r >> 1);       // this thread's keys: 2t, 2t+1, 2t+8, 2t+9
+            const int key = 2 * t + (r & 1) + 8 * (r >> 1);
             kv.v[vb][r] = (col < D && base + key <= hi_tile) ? load16(vbase + (size_t)key * D + col) : make_uint4(0, 0, 0, 0);
         }
     }
 }
 
 // One 16-key tile through scores, running softmax and the value product.
+// first_pos: the smallest position of any real row of the row tile; last_lo: the largest window start.
 __device__ __forceinline__ void consume_keys(const FaParams& p, const __nv_bfloat16* q_s, const KeyTile& kv,
-                                             const int (&pos_row)[2], const int (&lo_row)[2], RowState& st) {
+                                             const int (&pos_row)[2], const int (&lo_row)[2], int first_pos, int last_lo,
+                                             RowState& st) {
     if (kv.base < 0) return;
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     float s[2][4];
@@ -176,43 +200,68 @@ __device__ __forceinline__ void consume_keys(const FaParams& p, const __nv_bfloa
             mma_bf16(s[nb], qa.z, qb.z, qa.w, qb.w, kv.k[nb][c].z, kv.k[nb][c].w);
         }
     }
+    // Masks only where the tile touches an edge (the newest key, the window's start); a padding row
+    // (position -1) of an interior tile keeps finite scores that are never stored.
+    const bool edge = kv.base + 15 > first_pos || kv.base < last_lo;           // uniform over the warp
     float mx[2] = {-INFINITY, -INFINITY};
+    if (edge) {
 #pragma unroll
-    for (int nb = 0; nb < 2; ++nb)
+        for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int i = e >> 1;
-            const int key = kv.base + nb * 8 + 2 * t + (e & 1);
-            const bool ok = key >= lo_row[i] && key <= pos_row[i];
-            s[nb][e] = ok ? s[nb][e] * p.scale_log2 : -INFINITY;
-            mx[i] = fmaxf(mx[i], s[nb][e]);
-        }
+            for (int e = 0; e < 4; ++e) {
+                const int i = e >> 1;
+                const int key = kv.base + nb * 8 + 2 * t + (e & 1);
+                const bool ok = key >= lo_row[i] && key <= pos_row[i];
+                s[nb][e] = ok ? s[nb][e] * p.scale_log2 : -INFINITY;
+                mx[i] = fmaxf(mx[i], s[nb][e]);
+            }
+    } else {
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                s[nb][e] *= p.scale_log2;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
+            }
+    }
+    // The reference maximum of a row moves only when the true maximum has grown by more than 2^8 beyond
+    // it (P, the running sum and the accumulator all use the same reference, so the result is exact):
+    // after the first tiles the accumulator is hardly ever rescaled.
     float corr[2];
+    bool grow = false;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
         mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-        const float m_new = fmaxf(st.m[i], mx[i]);
-        corr[i] = (m_new == -INFINITY) ? 1.0f : exp2f(st.m[i] - m_new);
-        st.m[i] = m_new;
+        const bool g_i = mx[i] > st.m[i] + RESCALE_STEP;          // true as well for the first finite maximum
+        corr[i] = g_i ? (st.m[i] == -INFINITY ? 0.0f : fast_exp2(st.m[i] - mx[i])) : 1.0f;
+        st.m[i] = g_i ? mx[i] : st.m[i];
+        grow |= g_i;
     }
     float rowsum[2] = {0.0f, 0.0f};
 #pragma unroll
-    for (int nb = 0; nb < 2; ++nb)
+    for (int i = 0; i < 2; ++i) {
+        const float ref = st.m[i] == -INFINITY ? 0.0f : st.m[i];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int i = e >> 1;
-            const float pv = (s[nb][e] == -INFINITY) ? 0.0f : exp2f(s[nb][e] - st.m[i]);
-            s[nb][e] = pv;
-            rowsum[i] += pv;
-        }
+        for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
-    for (int i = 0; i < 2; ++i) st.l[i] = st.l[i] * corr[i] + rowsum[i];
-#pragma unroll
-    for (int nbo = 0; nbo < NB_O; ++nbo) {
-        st.o[nbo][0] *= corr[0]; st.o[nbo][1] *= corr[0];
-        st.o[nbo][2] *= corr[1]; st.o[nbo][3] *= corr[1];
+            for (int e2 = 0; e2 < 2; ++e2) {
+                const float pv = fast_exp2(s[nb][2 * i + e2] - ref);      // 2^(-inf) = 0 for masked keys
+                s[nb][2 * i + e2] = pv;
+                rowsum[i] += pv;
+            }
     }
+    if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) st.l[i] *= corr[i];
+#pragma unroll
+        for (int nbo = 0; nbo < NB_O; ++nbo) {
+            st.o[nbo][0] *= corr[0]; st.o[nbo][1] *= corr[0];
+            st.o[nbo][2] *= corr[1]; st.o[nbo][3] *= corr[1];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) st.l[i] += rowsum[i];
     const unsigned pa0 = pack_bf16(s[0][0], s[0][1]);     // row g,   keys 2t, 2t+1
     const unsigned pa1 = pack_bf16(s[0][2], s[0][3]);     // row g+8
     const unsigned pa2 = pack_bf16(s[1][0], s[1][1]);     // row g,   keys 8+2t, 9+2t
@@ -254,6 +303,15 @@ __device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& ge
             lo_row[i] = 0;
         }
     }
+    int first_pos = 0x7fffffff, last_lo = 0;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+        if (pos_row[i] >= 0) { first_pos = min(first_pos, pos_row[i]); last_lo = max(last_lo, lo_row[i]); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        first_pos = min(first_pos, __shfl_xor_sync(0xffffffffu, first_pos, o));
+        last_lo = max(last_lo, __shfl_xor_sync(0xffffffffu, last_lo, o));
+    }
     int kt = tile_begin + first;
     if (kt >= tile_end) return;
     if (PREFETCH) {
@@ -262,12 +320,12 @@ __device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& ge
             const bool more_b = kt + stride < tile_end;
             if (more_b && in_flight < 2) load_keys(p, geo, pt, kt + stride, hi_tile, b);
             in_flight = 0;
-            consume_keys(p, q_s, a, pos_row, lo_row, st);
+            consume_keys(p, q_s, a, pos_row, lo_row, first_pos, last_lo, st);
             if (!more_b) break;
             kt += stride;
             const bool more_a = kt + stride < tile_end;
             if (more_a) load_keys(p, geo, pt, kt + stride, hi_tile, a);
-            consume_keys(p, q_s, b, pos_row, lo_row, st);
+            consume_keys(p, q_s, b, pos_row, lo_row, first_pos, last_lo, st);
             if (!more_a) break;
             kt += stride;
         }
@@ -275,7 +333,7 @@ __device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& ge
         for (; kt < tile_end; kt += stride) {
             if (in_flight < 1) load_keys(p, geo, pt, kt, hi_tile, a);
             in_flight = 0;
-            consume_keys(p, q_s, a, pos_row, lo_row, st);
+            consume_keys(p, q_s, a, pos_row, lo_row, first_pos, last_lo, st);
         }
     }
 }
@@ -774,7 +832,7 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
     if (num_work == 0) return MLB_OK;
     FaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, seq_starts, seq_pos0,
                block_table, work, max_blocks, num_pages, page_size, num_heads, num_kv_heads,
-               num_heads / num_kv_heads, window, scale * LOG2E, error_flag};
+               num_heads / num_kv_heads, window, scale * LOG2E, (page_size & (page_size - 1)) == 0 ? __builtin_ctz((unsigned)page_size) : -1, error_flag};
     if (mode == 0) {
         static bool prefill_configured = false;
         if (!prefill_configured) {
