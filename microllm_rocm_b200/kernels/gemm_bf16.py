@@ -31,6 +31,10 @@ ops.register_signatures("gemv_fused.cu", {
                           c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                           c_void_p],
 })
+ops.register_signatures("gemm_tc2.cu", {
+    "mlb_gemm_pair": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int,
+                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+})
 ops.register_signatures("gemm_tc.cu", {
     "mlb_gemm_tc": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int,
                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -42,7 +46,7 @@ _error_flags = {}
 
 
 def sources():
-    return [("gemm_tc.cu", {}), ("gemv_bf16.cu", {}), ("gemv_fused.cu", {})]
+    return [("gemm_tc.cu", {}), ("gemm_tc2.cu", {}), ("gemv_bf16.cu", {}), ("gemv_fused.cu", {})]
 
 
 # ------------------------------------------------------------------------------ few tokens: weight streaming
@@ -196,6 +200,28 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Opti
                                  ops._ptr(bias), out.data_ptr(), out.stride(0), 1 if out.dtype == torch.bfloat16 else 0,
                                  1 if accumulate else 0, 1 if dual else 0, N if dual else 0, M, N, K, tok_tile, splits,
                                  1 if reduce_here else 0, int(stages), ops._ptr(partial), tickets.data_ptr(), flag.data_ptr(), ops._stream()))
+
+
+def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+              accumulate: bool = False, dual_rows: Optional[int] = None, stages: int = 0, sm_count: int = SM_COUNT) -> None:
+    """The CTA-pair tcgen05 product (`gemm_tc2.cu`) for prompt-sized token counts:
+    out[M, N] = x[M, K] @ weight[:N]^T (+ bias) (+ out), or with dual_rows = I:
+    out[M, I] = silu(x @ weight[:I]^T) * (x @ weight[I:2I]^T)."""
+    M, K = x.shape
+    dual = dual_rows is not None
+    N = dual_rows if dual else weight.shape[0]
+    if weight.shape[1] != K or out.shape != (M, N) or out.stride(1) != 1:
+        raise KernelError(f"gemm_pair: shapes {tuple(x.shape)} x {tuple(weight.shape)}^T -> {tuple(out.shape)} do not agree")
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError("gemm_pair: bf16 operands and an fp32 or bf16 output are expected")
+    if dual and weight.shape[0] < 2 * N:
+        raise KernelError("gemm_pair: a dual product needs gate rows followed by up rows")
+    _, flag = _device_scratch(x.device)
+    L = ops.lib("gemm_tc2.cu")
+    build.check(L, L.mlb_gemm_pair(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), weight.shape[0],
+                                   ops._ptr(bias), out.data_ptr(), out.stride(0), 1 if out.dtype == torch.bfloat16 else 0,
+                                   1 if accumulate else 0, 1 if dual else 0, N if dual else 0, M, N, K, int(stages),
+                                   int(sm_count), flag.data_ptr(), ops._stream()))
 
 
 def library_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,

@@ -462,6 +462,41 @@ def test_tensor_core_dual_product_silu_mul(M, I, K):
     assert int(gemm_bf16.error_flag(torch.device(DEV)).item()) == 0
 
 
+@pytest.mark.parametrize("M,N,K,out_dtype", [(256, 256, 64, torch.float32), (2048, 1536, 1536, torch.float32),
+                                             (300, 520, 200, torch.bfloat16), (1000, 2048, 1536, torch.bfloat16),
+                                             (129, 100, 72, torch.float32), (3000, 300, 4096, torch.bfloat16)])
+def test_cta_pair_product_against_fp32(M, N, K, out_dtype):
+    """tcgen05.mma.cta_group::2: sizes that are no multiple of the 256 x 256 pair tile, more tiles than
+    pairs (the double-buffered accumulator and the ring wrap around), with and without a bias."""
+    from microllm_rocm_b200.kernels import gemm_bf16
+    torch.manual_seed(M + N + K)
+    x, w, bias = (torch.randn(M, K) * 0.5).bfloat16(), (torch.randn(N, K) * 0.5).bfloat16(), torch.randn(N)
+    want = x.double() @ w.double().t() + bias.double()
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    gemm_bf16.gemm_pair(x.to(DEV), w.to(DEV), out, bias=bias.to(DEV))
+    assert int(gemm_bf16.error_flag(torch.device(DEV)).item()) == 0
+    got = out.double().cpu()
+    tol_ = 2e-5 * math.sqrt(K) * 4 if out_dtype == torch.float32 else 2e-2 * want.abs().max().item()
+    assert (got - want).abs().max() <= tol_, float((got - want).abs().max())
+    if out_dtype == torch.float32:                      # accumulate on top of what is there
+        gemm_bf16.gemm_pair(x.to(DEV), w.to(DEV), out, accumulate=True)
+        want2 = want + x.double() @ w.double().t()
+        assert (out.double().cpu() - want2).abs().max() <= 2 * tol_
+
+
+@pytest.mark.parametrize("M,I,K", [(2048, 1120, 1536), (130, 176, 64), (700, 520, 192)])
+def test_cta_pair_dual_product_silu_mul(M, I, K):
+    from microllm_rocm_b200.kernels import gemm_bf16
+    torch.manual_seed(I + M)
+    x = (torch.randn(M, K) * 0.5).bfloat16()
+    w = (torch.randn(2 * I, K) * 0.2).bfloat16()
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    gemm_bf16.gemm_pair(x.to(DEV), w.to(DEV), out, dual_rows=I)
+    want = plain.swiglu(x.float() @ w[:I].float().t(), x.float() @ w[I:].float().t())
+    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2), float((out.float().cpu() - want).abs().max())
+    assert int(gemm_bf16.error_flag(torch.device(DEV)).item()) == 0
+
+
 def test_tensor_core_product_refuses_what_tma_cannot_address():
     from microllm_rocm_b200.kernels import gemm_bf16
     from microllm_rocm_b200.kernels.build import KernelError
