@@ -26,6 +26,7 @@
 
 #include <cooperative_groups.h>
 #include <cuda.h>
+#include <cstdlib>
 
 using namespace mlb;
 
@@ -40,7 +41,7 @@ constexpr int UMMA_K = 16;
 constexpr int A_TILE_BYTES = BLOCK_W * BLOCK_K * 2;
 constexpr int MAX_STAGES = 8;
 constexpr int THREADS = 192;
-constexpr int SPIN_LIMIT = 1 << 24;
+constexpr int SPIN_LIMIT = 1 << 21;          // polls of up to 2 us each
 constexpr int TMEM_COLS = 512;
 
 struct PairParams {
@@ -56,6 +57,7 @@ struct PairParams {
     int dual;                  // 1: silu(gate) * up; W rows n (gate) and up_offset + n (up); N counts gate rows
     int up_offset;
     int n_tiles, m_tiles;
+    int debug;                 // measurement aid: bit 0 skips the stores, bit 1 the accumulator reads too, bit 2 the MMAs, bit 3 the copies
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -74,10 +76,12 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
+// One poll.  The hint lets the hardware park the thread until the phase completes or the time (ns) is up,
+// so that waiting threads do not hammer shared memory while the tensor core reads its operands from it.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(2000u) : "memory");
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code) {
@@ -85,6 +89,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
         if (mbar_try_wait(bar, parity)) return true;
     if (error_flag) atomicExch(error_flag, code);
     return false;
+}
+// a whole warp waits: one lane polls, the others sleep at the warp barrier
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int* error_flag, int code) {
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, error_flag, code);
+    return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+}
+// true in exactly one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+    return pred != 0;
 }
 // this CTA's half of an operand tile; the bytes are counted on `cluster_bar`, which may live in the peer CTA
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t cluster_bar) {
@@ -127,10 +143,10 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t addr, uint32_t (&r)[32
 __device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float silu(float g) {
-    // two-branch sigmoid, as the reference's activation (src/ops/ops.cpp:72-76)
-    if (g >= 0.0f) return g / (1.0f + expf(-g));
-    const float e = expf(g);
-    return g * e / (1.0f + e);
+    // g * sigmoid(g) (src/ops/ops.cpp:72-76, 760-785) in its one-branch form: for very negative g the
+    // exponential overflows to +inf and the quotient is -0, which is the limit; no branch, so that the
+    // 32 elements a thread holds can be evaluated side by side
+    return __fdividef(g, 1.0f + __expf(-g));
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -187,9 +203,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                     const int s = it % p.stages;
                     const uint32_t round = it / p.stages;
+                    if (p.debug & 16) continue;
                     if (round > 0 && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, p.error_flag, 41)) { ok = false; break; }
                     const uint32_t dst = ring + (uint32_t)s * stage_bytes;
                     const uint32_t leader_full = cluster_addr(smem_u32(&full_bar[s]), 0);
+                    if (p.debug & 8) {                 // no copies: the barrier completes on the leader's arrival alone
+                        if (rank == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[s])) : "memory");
+                        continue;
+                    }
                     if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * stage_bytes);
                     const int k = kb * BLOCK_K;
                     tma_load_2d_pair(dst, &map_w, k, n0, leader_full);
@@ -200,33 +221,42 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issue (leader only)
-        if (lane == 0 && rank == 0) {
+        // The whole warp walks the loop converged (its waits park 31 lanes at a warp barrier) and ONE elected lane
+        // issues: descriptors and addresses are then warp-uniform values, as the instruction wants them.
+        if (rank == 0) {
             const uint32_t idesc = umma_idesc(p.tok_tile);
             uint32_t it = 0, local = 0;
             bool ok = true;
             for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
                 const uint32_t buf = local & 1, use = local >> 1;
                 // both epilogues must have drained this buffer (the first use of each buffer passes at once)
-                if (!mbar_wait(smem_u32(&acc_empty[buf]), (use & 1) ^ 1, p.error_flag, 42)) { ok = false; break; }
+                if (!mbar_wait_warp(smem_u32(&acc_empty[buf]), (use & 1) ^ 1, p.error_flag, 42)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem_base + buf * acc_cols;
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                     const int s = it % p.stages;
-                    if (!mbar_wait(smem_u32(&full_bar[s]), (it / p.stages) & 1, p.error_flag, 43)) { ok = false; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    // every lane polls (one broadcast read each time): no shuffle between the barrier and the issue.
+                    // No tcgen05 fence here: the copies and the MMAs that read them are ordered by the mbarrier itself.
+                    if (!(p.debug & 16) && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[s]), (it / p.stages) & 1, p.error_flag, 43))) { ok = false; break; }
                     const uint32_t a_addr = ring + (uint32_t)s * stage_bytes;
-                    const uint32_t b_addr = a_addr + a_bytes;
+                    // descriptors of the stage; a K step of 16 elements moves the start address (16-byte units) by 2
+                    const uint64_t adesc = umma_desc(a_addr), bdesc = umma_desc(a_addr + a_bytes), udesc = umma_desc(a_addr + A_TILE_BYTES);
+                    if (elect_one()) {
+                        if (!(p.debug & 4)) {
+                            umma_pair(acc, adesc, bdesc, idesc, kb > 0 ? 1u : 0u);
+                            if (p.dual) umma_pair(acc + (uint32_t)p.tok_tile, udesc, bdesc, idesc, kb > 0 ? 1u : 0u);
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                        const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-                        const uint64_t bdesc = umma_desc(b_addr + k * UMMA_K * 2);
-                        umma_pair(acc, umma_desc(a_addr + k * UMMA_K * 2), bdesc, idesc, accumulate);
-                        if (p.dual)
-                            umma_pair(acc + (uint32_t)p.tok_tile, umma_desc(a_addr + A_TILE_BYTES + k * UMMA_K * 2), bdesc, idesc, accumulate);
+                            for (int k = 1; k < BLOCK_K / UMMA_K; ++k) {
+                                umma_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc, 1u);
+                                if (p.dual) umma_pair(acc + (uint32_t)p.tok_tile, udesc + 2 * k, bdesc + 2 * k, idesc, 1u);
+                            }
+                        }
+                        if (!(p.debug & 32)) umma_commit_pair(smem_u32(&empty_bar[s]));  // the stage is free in both CTAs once these MMAs have read it
                     }
-                    umma_commit_pair(smem_u32(&empty_bar[s]));      // the stage is free in both CTAs once these MMAs have read it
+                    __syncwarp();
                 }
-                if (ok) umma_commit_pair(smem_u32(&acc_full[buf]));
+                if (ok && elect_one()) umma_commit_pair(smem_u32(&acc_full[buf]));
+                __syncwarp();
             }
         }
     } else {
@@ -238,18 +268,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             const uint32_t buf = local & 1, use = local >> 1;
             const int n0 = (tile / p.m_tiles) * PAIR_W + (int)rank * BLOCK_W, tok0 = (tile % p.m_tiles) * p.tok_tile;
             const int f = n0 + quarter * 32 + lane;
-            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc_full[buf]), use & 1, p.error_flag, 44)) != 0;
+            ok = mbar_wait_warp(smem_u32(&acc_full[buf]), use & 1, p.error_flag, 44);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t lane_addr = tmem_base + buf * acc_cols + ((uint32_t)(quarter * 32) << 16);
             const float bias = (p.bias && f < p.N) ? p.bias[f] : 0.0f;
             for (int c = 0; c < p.tok_tile; c += 32) {
-                if (tok0 + c >= p.M) break;
+                if (tok0 + c >= p.M || (p.debug & 2)) break;
                 uint32_t raw[32], raw_u[32];
                 tmem_ld32_nowait(lane_addr + (uint32_t)c, raw);
                 if (p.dual) tmem_ld32_nowait(lane_addr + (uint32_t)(p.tok_tile + c), raw_u);
                 tmem_wait();
-                if (f >= p.N) continue;
+                if (f >= p.N || (p.debug & 1)) continue;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int tok = tok0 + c + j;
@@ -332,6 +362,11 @@ MLB_EXPORT int mlb_gemm_pair(const void* x, long long ldx, const void* w, long l
     p.tok_tile = dual ? 128 : 256;
     p.k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
     p.out_bf16 = out_bf16; p.accumulate = accumulate; p.dual = dual; p.up_offset = up_offset;
+    {
+        static int debug = -1;
+        if (debug < 0) { const char* e = getenv("MLB_GEMM_DEBUG"); debug = e ? atoi(e) : 0; }
+        p.debug = debug;
+    }
     p.n_tiles = (N + PAIR_W - 1) / PAIR_W;
     p.m_tiles = (M + p.tok_tile - 1) / p.tok_tile;
     const int stage_bytes = (dual ? 2 : 1) * A_TILE_BYTES + (p.tok_tile / 2) * BLOCK_K * 2;
