@@ -43,6 +43,9 @@ constexpr int MAX_STAGES = 8;
 constexpr int THREADS = 192;
 constexpr int SPIN_LIMIT = 1 << 21;          // polls of up to 2 us each
 constexpr int TMEM_COLS = 512;
+#ifndef WAIT_HINT_NS
+#define WAIT_HINT_NS 2000
+#endif
 
 struct PairParams {
     void* out;                 // [M, ldo] fp32 or bf16
@@ -81,7 +84,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(2000u) : "memory");
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"((uint32_t)WAIT_HINT_NS) : "memory");
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code) {

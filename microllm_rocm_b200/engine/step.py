@@ -178,5 +178,14 @@ class Engine:
         code = int(self.error_flag.item())
         if code:
             self.error_flag.zero_()
+            if code >= 10:
+                raise StepError(f"a bounded wait inside a tensor-memory kernel ran out (code {code}); its results are not valid")
             raise StepError(f"a kernel met a token without a valid page (code {code}): the block table and the "
                             "request's length disagree")
+        if self.model.rt.dtype == torch.bfloat16:
+            from ..kernels import gemm_bf16
+            flag = gemm_bf16.error_flag(self.device)
+            code = int(flag.item())
+            if code:
+                flag.zero_()
+                raise StepError(f"a bounded wait inside a tensor-core product ran out (code {code}); its results are not valid")

@@ -244,6 +244,7 @@ def library_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
 # stands (one CTA per tile, one accumulator, epilogue not overlapped), the library is faster
 # on prompt-sized products; it is switched in per token range once it wins there.
 TENSOR_CORE_KERNEL_TOKENS = (0, 0)          # [lo, hi): token counts routed to gemm_tc
+PAIR_MIN_TOKENS = 256                       # from here on the fused gate/up + activation of gemm_tc2 beats library + activation kernel
 
 
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,

@@ -41,6 +41,9 @@ class SwiGLU(FeedForward):
         elif x.dtype == torch.bfloat16 and gemm_bf16.gemv_supported(x, self.w_gate_up):
             # more tokens, or a width too large for that kernel: fp32 partial sums, the activation adds them
             ops.silu_mul(gemm_bf16.gemv_partials(x, self.w_gate_up), act)
+        elif x.dtype == torch.bfloat16 and x.shape[0] >= gemm_bf16.PAIR_MIN_TOKENS and gemm_bf16.supported(x, self.w_gate_up):
+            # a prompt portion: the CTA-pair tcgen05 product with the activation in its epilogue
+            gemm_bf16.gemm_pair(x, self.w_gate_up, act, dual_rows=self.inter)
         else:
             gate_up = linear(x, self.w_gate_up, None, self.rt.dtype)
             ops.silu_mul(gate_up, act)
