@@ -84,7 +84,7 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_del
         float4 w[NORM_VECS];
 #pragma unroll
         for (int i = 0; i < NORM_VECS; ++i) {
-            const int c = (threadIdx.x + i * NORM_THREADS) * 4;
+            const int c = (threadIdx.x + i * blockDim.x) * 4;
             if (c < width) w[i] = ld4(weight + c);
         }
         pdl_wait();
@@ -96,7 +96,7 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_del
         float4 v[NORM_VECS];
 #pragma unroll
         for (int i = 0; i < NORM_VECS; ++i) {
-            const int c = (threadIdx.x + i * NORM_THREADS) * 4;
+            const int c = (threadIdx.x + i * blockDim.x) * 4;
             if (c >= width) break;
             v[i] = ld4(xr + c);
             if (ADD) {
@@ -110,7 +110,7 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_del
         const float inv = 1.0f / sqrtf(ss / (float)width + eps);
 #pragma unroll
         for (int i = 0; i < NORM_VECS; ++i) {
-            const int c = (threadIdx.x + i * NORM_THREADS) * 4;
+            const int c = (threadIdx.x + i * blockDim.x) * 4;
             if (c >= width) break;
             yr[c + 0] = from_f32<OutT>(v[i].x * inv * w[i].x);
             yr[c + 1] = from_f32<OutT>(v[i].y * inv * w[i].y);
@@ -149,13 +149,17 @@ static int launch_rmsnorm(float* x, const float* delta, int n_delta, long long d
     if (n_rows == 0) return MLB_OK;
     const bool aligned = ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && (!delta || (uintptr_t)delta % 16 == 0) &&
                          (delta_stride % 4 == 0);
-    const int vectorised = (width % 4 == 0 && aligned && width <= NORM_VECS * 4 * NORM_THREADS) ? 1 : 0;
+    const int vectorised = (width % 4 == 0 && aligned && width <= NORM_VECS * 4 * NORM_THREADS) ? 1 : 0;   // NORM_THREADS is the widest block
     int threads = NORM_THREADS;
     if (!vectorised) threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-    else if (width <= 4 * 128) threads = 128;
-    else if (width <= 4 * 256) threads = 256;
-    // (the vectorised path strides by NORM_THREADS: smaller blocks simply leave the upper slots unused)
-    if (vectorised) threads = NORM_THREADS;
+    else if (n_rows >= 256 && out_dtype == MLB_BF16) {
+        // many rows (a prompt portion): the smallest block that still covers the row with NORM_VECS float4 per
+        // thread, so that several rows share an SM and every thread has several loads in flight; a few rows
+        // (decoding) keep the widest block, which is the shortest path through one row.  Only on the bf16
+        // path: the fp32 path keeps ONE block size, so that a row's sum never depends on the batch.
+        threads = 128;
+        while (threads * 4 * NORM_VECS < width) threads *= 2;
+    }
     if (out_dtype == MLB_F32)
         launch_kernel(rmsnorm_kernel<float, ADD>, n_rows, threads, 0, stream, x, delta, n_delta, delta_stride, w, (float*)out, rows, width, eps, vectorised);
     else if (out_dtype == MLB_BF16)

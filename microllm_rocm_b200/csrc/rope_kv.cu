@@ -39,6 +39,7 @@ struct RopeKvParams {
     int num_pages, page_size;
     int tokens, num_heads, num_kv_heads, head_dim;
     int* error_flag;         // set to 1 when a token maps to no valid page
+    const float2* cos_sin;   // [T, rot_dim/2] (cos, sin) of every token's angles, or null: computed here
 };
 
 template <typename QT, typename KVT>
@@ -145,7 +146,12 @@ __global__ void rope_kv_split_half_x4_kernel(RopeKvParams p) {
             bb = *reinterpret_cast<const float4*>(p.bias + col + i + half);
         }
         pos = p.positions[t];
-        if (!is_v) {
+        if (!is_v && p.cos_sin) {
+            // a step's table, made once for all layers and heads (written long before this kernel's predecessor)
+            const float4 u = *reinterpret_cast<const float4*>(p.cos_sin + (size_t)t * half + i);
+            const float4 v = *reinterpret_cast<const float4*>(p.cos_sin + (size_t)t * half + i + 2);
+            cs[0] = u.x; sn[0] = u.y; cs[1] = u.z; sn[1] = u.w; cs[2] = v.x; sn[2] = v.y; cs[3] = v.z; sn[3] = v.w;
+        } else if (!is_v) {
             const float4 f = *reinterpret_cast<const float4*>(p.inv_freq + i);
             const float fr[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
@@ -195,7 +201,29 @@ __global__ void rope_kv_split_half_x4_kernel(RopeKvParams p) {
     store4(dst + i + half, bv);
 }
 
+// (cos, sin) of position[t] * inv_freq[i]: the same fp32 expressions as in the rotation kernels
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ cos_sin, int tokens, int half) {
+    pdl_prologue();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)tokens * half) return;
+    const int t = (int)(idx / half), i = (int)(idx % half);
+    float s, c;
+    sincosf((float)positions[t] * inv_freq[i], &s, &c);
+    cos_sin[idx] = make_float2(c, s);
+}
+
 }  // namespace
+
+// cos_sin[T, half] = (cos, sin)(positions[t] * inv_freq[i]): one table per step serves every layer's rotation
+MLB_EXPORT int mlb_rope_table(const int* positions, const float* inv_freq, float* cos_sin, int tokens, int half,
+                              cudaStream_t stream) {
+    if (tokens < 0 || half <= 0) return fail(MLB_INVALID_ARGUMENT, "rope_table: bad sizes");
+    if (tokens == 0) return MLB_OK;
+    const long long total = (long long)tokens * half;
+    launch_kernel(rope_table_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, positions, inv_freq, (float2*)cos_sin, tokens, half);
+    return check_launch("rope_table");
+}
 
 MLB_EXPORT int mlb_rope_kv_write(const float* qkv, long long ld, int n_partials, long long partial_stride,
                                  const float* bias, const int* positions,
@@ -203,7 +231,7 @@ MLB_EXPORT int mlb_rope_kv_write(const float* qkv, long long ld, int n_partials,
                                  const float* inv_freq, int rot_dim, int interleaved, void* q_out, int q_dtype,
                                  void* pages, int kv_dtype, int num_pages, int page_size, int tokens,
                                  int num_heads, int num_kv_heads, int head_dim, int* error_flag,
-                                 cudaStream_t stream) {
+                                 const float* cos_sin, cudaStream_t stream) {
     if (tokens < 0 || num_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || head_dim % 2 != 0)
         return fail(MLB_INVALID_ARGUMENT, "rope_kv_write: bad head sizes");
     if (rot_dim < 0 || rot_dim > head_dim || rot_dim % 2 != 0)
@@ -215,12 +243,13 @@ MLB_EXPORT int mlb_rope_kv_write(const float* qkv, long long ld, int n_partials,
     if (tokens == 0) return MLB_OK;
     if (n_partials < 1) return fail(MLB_INVALID_ARGUMENT, "rope_kv_write: n_partials must be at least 1");
     RopeKvParams p{qkv, ld, n_partials, partial_stride, bias, positions, token_seq, block_table, max_blocks, inv_freq, rot_dim, interleaved,
-                   q_out, pages, num_pages, page_size, tokens, num_heads, num_kv_heads, head_dim, error_flag};
+                   q_out, pages, num_pages, page_size, tokens, num_heads, num_kv_heads, head_dim, error_flag, nullptr};
     const int key = q_dtype * 2 + kv_dtype;
     // the model's own case in 16-byte pieces: split-half over the whole head, eight-element alignment
     const bool wide = rot_dim == head_dim && !interleaved && head_dim % 8 == 0 && ld % 4 == 0 && partial_stride % 4 == 0 &&
                       (uintptr_t)q_out % 16 == 0 && (!pages || (uintptr_t)pages % 16 == 0) && (uintptr_t)qkv % 16 == 0 && (!bias || (uintptr_t)bias % 16 == 0) && (uintptr_t)inv_freq % 16 == 0;
     if (wide) {
+        if (cos_sin && (uintptr_t)cos_sin % 16 == 0 && head_dim % 16 == 0) p.cos_sin = (const float2*)cos_sin;
         const long long total4 = (long long)tokens * (num_heads + 2 * num_kv_heads) * (head_dim / 8);
         const unsigned blocks4 = (unsigned)((total4 + 255) / 256);
         switch (key) {

@@ -62,7 +62,8 @@ _SIGNATURES = {
     "rope_kv.cu": {
         "mlb_rope_kv_write": [c_void_p, c_longlong, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                               c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                              c_int, c_int, c_int, c_void_p, c_void_p],
+                              c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "mlb_rope_table": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     },
     "attention_plain.cu": {
         "mlb_paged_attention_plain": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
@@ -237,10 +238,12 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional
 def rope_kv_write(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
                   token_seq: torch.Tensor, block_table: Optional[torch.Tensor], inv_freq: torch.Tensor,
                   rot_dim: int, interleaved: bool, q_out: torch.Tensor, pages: Optional[torch.Tensor],
-                  num_heads: int, num_kv_heads: int, head_dim: int, error_flag: Optional[torch.Tensor]) -> None:
+                  num_heads: int, num_kv_heads: int, head_dim: int, error_flag: Optional[torch.Tensor],
+                  cos_sin: Optional[torch.Tensor] = None) -> None:
     """Bias, rotation and the K/V store for a fused [T, (NH+2NKV)*D] fp32 projection output
     (or its [S, T, width] partial results, which are summed here).
-    `pages` is [num_pages, 2, NKV, page_size, D]; None makes the call query-only."""
+    `pages` is [num_pages, 2, NKV, page_size, D]; None makes the call query-only.
+    `cos_sin` [T, rot_dim/2, 2] fp32 (from `rope_table`) spares the kernel the sines and cosines."""
     _need(positions, "positions", torch.int32, 1)
     n_partials, partial_stride = 1, 0
     if qkv.dim() == 3:
@@ -256,6 +259,9 @@ def rope_kv_write(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: to
         raise KernelError("rope_kv_write: shapes do not agree")
     if inv_freq.shape[0] * 2 != rot_dim:
         raise KernelError("rope_kv_write: inv_freq must have rot_dim/2 entries")
+    if cos_sin is not None and (cos_sin.dtype != torch.float32 or tuple(cos_sin.shape) != (T, rot_dim // 2, 2)
+                                or not cos_sin.is_contiguous()):
+        raise KernelError("rope_kv_write: cos_sin must be a contiguous fp32 [T, rot_dim/2, 2] table")
     num_pages = page_size = max_blocks = 0
     if pages is not None:
         _need(pages, "pages", dims=5); _need(block_table, "block_table", torch.int32, 2)
@@ -272,7 +278,18 @@ def rope_kv_write(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: to
         qkv.data_ptr(), width, n_partials, partial_stride, _ptr(bias), positions.data_ptr(), token_seq.data_ptr(), _ptr(block_table), max_blocks,
         inv_freq.data_ptr(), rot_dim, 1 if interleaved else 0, q_out.data_ptr(), dtype_tag(q_out),
         _ptr(pages), dtype_tag(pages) if pages is not None else F32, num_pages, page_size, T,
-        num_heads, num_kv_heads, head_dim, _ptr(error_flag), _stream()))
+        num_heads, num_kv_heads, head_dim, _ptr(error_flag), _ptr(cos_sin), _stream()))
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """[T, len(inv_freq), 2] fp32: (cos, sin) of position * inverse frequency, the rotation kernels' own
+    fp32 expressions; made once per step and shared by every layer."""
+    _need(positions, "positions", torch.int32, 1); _need(inv_freq, "inv_freq", torch.float32, 1)
+    out = torch.empty((positions.shape[0], inv_freq.shape[0], 2), dtype=torch.float32, device=positions.device)
+    L = lib("rope_kv.cu")
+    build.check(L, L.mlb_rope_table(positions.data_ptr(), inv_freq.data_ptr(), out.data_ptr(), positions.shape[0],
+                                    inv_freq.shape[0], _stream()))
+    return out
 
 
 # ------------------------------------------------------------------------------ attention

@@ -23,6 +23,9 @@ from ..kernels.linear import linear
 from .base import Mixer, PagedKVNeed, PagedKVView, PositionEncoding, Runtime, StepContext, WeightSpec, register_mixer
 
 
+ROPE_TABLE_MIN_TOKENS = 64          # from here on a step-wide table of sines and cosines pays
+
+
 @register_mixer("attention")
 class Attention(Mixer):
     graph_safe = True
@@ -82,8 +85,15 @@ class Attention(Mixer):
                                     inv_freq if rot else None, q, pages, self.nh, self.nkv, self.d, ctx.error_flag)
         else:
             qkv = linear(x, self.w_qkv, None, torch.float32, partials_ok=True)  # [T, (NH+2NKV)*D] f32, or its partial sums
+            cos_sin = None
+            if rot and T >= ROPE_TABLE_MIN_TOKENS and x.dtype == torch.bfloat16:
+                # a prompt portion: the step's sines and cosines are made once and serve every layer and head
+                key = ("rope_table", id(self.rotary))
+                cos_sin = ctx.extras.get(key)
+                if cos_sin is None:
+                    cos_sin = ctx.extras[key] = ops.rope_table(ctx.positions, inv_freq)
             ops.rope_kv_write(qkv, self.b_qkv, ctx.positions, ctx.token_seq, cache.block_table, inv_freq, rot, inter,
-                              q, pages, self.nh, self.nkv, self.d, ctx.error_flag)
+                              q, pages, self.nh, self.nkv, self.d, ctx.error_flag, cos_sin)
         o = torch.empty_like(q)
         attention_kernels.paged_attention(q, cache.pages, o, ctx, cache.block_table, self.nh, self.nkv, self.d,
                                           self.scale, self.window)

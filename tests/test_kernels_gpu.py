@@ -601,6 +601,31 @@ def test_gemv_qkv_rope_projects_rotates_and_stores(M, nh, nkv, d, K, rotate, wit
     assert int(flag.item()) == 1 and float(pages.float().abs().sum()) == 0.0
 
 
+def test_rope_table_gives_the_same_rotation_bit_for_bit():
+    """The step-wide (cos, sin) table is made with the rotation kernel's own expressions: with it and
+    without it the queries and the cache must be identical."""
+    from microllm_rocm_b200.parts.rotary import inverse_frequencies
+    torch.manual_seed(9)
+    nh, nkv, d, T, page = 6, 2, 64, 300, 16
+    width = (nh + 2 * nkv) * d
+    qkv, bias = torch.randn(T, width, device=DEV), torch.randn(width, device=DEV)
+    inv = torch.from_numpy(inverse_frequencies(1e6, d)).to(DEV)
+    pos = torch.arange(1000, 1000 + T, dtype=torch.int32, device=DEV)
+    seq = torch.zeros(T, dtype=torch.int32, device=DEV)
+    table = torch.arange(90, dtype=torch.int32, device=DEV).flip(0).reshape(1, 90).contiguous()
+    outs = []
+    for use_table in (False, True):
+        pages = torch.zeros(90, 2, nkv, page, d, dtype=torch.bfloat16, device=DEV)
+        q = torch.empty(T, nh * d, dtype=torch.bfloat16, device=DEV)
+        flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+        cs = ops().rope_table(pos, inv) if use_table else None
+        ops().rope_kv_write(qkv, bias, pos, seq, table, inv, d, False, q, pages, nh, nkv, d, flag, cs)
+        assert int(flag.item()) == 0
+        outs.append((q.cpu(), pages.cpu()))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert float(outs[0][1].float().abs().sum()) > 0
+
+
 def test_rope_kv_write_adds_partial_projections():
     from microllm_rocm_b200.parts.rotary import inverse_frequencies
     torch.manual_seed(4)
