@@ -58,7 +58,7 @@ constexpr int SMEM_BYTES = Q_BYTES + SLOTS * KV_BYTES + P_BYTES + 1024;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;               // S0 [0,128)  S1 [128,256)  O [256, 256+D)
 constexpr int O_COL = 2 * BN;
-constexpr int SPIN_LIMIT = 1 << 24;
+constexpr int SPIN_LIMIT = 1 << 21;          // polls of up to 2 us each
 constexpr int MAX_PAGES_PER_TILE = 16;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.0f;         // rescale the accumulator when the maximum grew by 2^8
@@ -89,8 +89,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    // the hint (ns) lets the hardware park the thread until the phase completes instead of spinning on shared memory
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(2000u) : "memory");
     return ok != 0;
 }
 // false when the bound was hit (the caller gives up and the flag tells the host)
@@ -99,6 +100,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
         if (mbar_try_wait(bar, parity)) return true;
     if (error_flag) atomicExch(error_flag, code);
     return false;
+}
+// true in exactly one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -288,50 +295,61 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issue
-        if (lane == 0) {
+        // The whole warp walks the loop converged and ONE elected lane issues, so that descriptors and
+        // addresses are warp-uniform values; every lane polls the barriers (one broadcast read per poll).
+        {
             const uint32_t idesc_qk = idesc(BN, false), idesc_pv = idesc(D, true);
-            bool ok = mbar_wait(smem_u32(&q_full), 0, p.error_flag, 23);
+            auto wait_warp = [&](unsigned long long* bar, uint32_t parity, int code) {
+                return __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, p.error_flag, code)) != 0;
+            };
+            bool ok = wait_warp(&q_full, 0, 23);
             int item = 0;                                  // ring items are consumed in the order they were loaded
             auto issue_qk = [&](int j) {
                 const int slot = item % SLOTS;
-                if (!mbar_wait(smem_u32(&slot_full[slot]), (item / SLOTS) & 1, p.error_flag, 24)) return false;
-                tc_fence_after();
+                if (!wait_warp(&slot_full[slot], (item / SLOTS) & 1, 24)) return false;
                 const uint32_t kb = ring_s + slot * KV_BYTES;
+                if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = (ks / 4) * (BM * ROW_BYTES) + (ks % 4) * 32;
-                    umma(tmem_base + (uint32_t)((j & 1) * BN), desc_k_major(q_s + off), desc_k_major(kb + off), idesc_qk, ks > 0);
+                    for (int ks = 0; ks < D / 16; ++ks) {
+                        const uint32_t off = (ks / 4) * (BM * ROW_BYTES) + (ks % 4) * 32;
+                        umma(tmem_base + (uint32_t)((j & 1) * BN), desc_k_major(q_s + off), desc_k_major(kb + off), idesc_qk, ks > 0);
+                    }
+                    umma_commit(smem_u32(&slot_empty[slot]));
+                    umma_commit(smem_u32(&s_full[j & 1]));
                 }
-                umma_commit(smem_u32(&slot_empty[slot]));
-                umma_commit(smem_u32(&s_full[j & 1]));
+                __syncwarp();
                 ++item;
                 return true;
             };
             for (int j = 0; j < 2 && j < n_tiles && ok; ++j) ok = issue_qk(j);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                ok = mbar_wait(smem_u32(&p_full), j & 1, p.error_flag, 25);
+                ok = wait_warp(&p_full, j & 1, 25);
                 if (!ok) break;
                 const int slot = item % SLOTS;
-                ok = mbar_wait(smem_u32(&slot_full[slot]), (item / SLOTS) & 1, p.error_flag, 26);
+                ok = wait_warp(&slot_full[slot], (item / SLOTS) & 1, 26);
                 if (!ok) break;
-                tc_fence_after();
+                tc_fence_after();                          // P and the rescaled accumulator were written by the softmax warps
                 const uint32_t vb = ring_s + slot * KV_BYTES;
+                if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks) {
-                    const uint32_t a_off = (ks / 4) * (BM * ROW_BYTES) + (ks % 4) * 32;
-                    umma(tmem_base + O_COL, desc_k_major(p_s + a_off), desc_mn_major(vb + ks * 16 * ROW_BYTES, BN * ROW_BYTES),
-                         idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    for (int ks = 0; ks < BN / 16; ++ks) {
+                        const uint32_t a_off = (ks / 4) * (BM * ROW_BYTES) + (ks % 4) * 32;
+                        umma(tmem_base + O_COL, desc_k_major(p_s + a_off), desc_mn_major(vb + ks * 16 * ROW_BYTES, BN * ROW_BYTES),
+                             idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&slot_empty[slot]));
+                    umma_commit(smem_u32(&pv_done));
                 }
-                umma_commit(smem_u32(&slot_empty[slot]));
-                umma_commit(smem_u32(&pv_done));
+                __syncwarp();
                 ++item;
                 if (j + 2 < n_tiles) {
-                    ok = mbar_wait(smem_u32(&s_empty[j & 1]), (j >> 1) & 1, p.error_flag, 27);
+                    ok = wait_warp(&s_empty[j & 1], (j >> 1) & 1, 27);
                     if (!ok) break;
+                    tc_fence_after();                      // the softmax warps have read this score buffer
                     ok = issue_qk(j + 2);
                 }
             }
-            if (!ok) failed_s = 1;
+            if (!ok && lane == 0) failed_s = 1;
         }
     } else {
         // ------------------------------------------------------------------ softmax, one thread per row
