@@ -26,8 +26,14 @@ TINY = {
               intermediate_size=512, max_position_embeddings=512, rope_theta=1e6, rms_norm_eps=1e-5,
               tie_word_embeddings=False, use_sliding_window=True, sliding_window=32, max_window_layers=1,
               torch_dtype="float32"),
+    # sized for the tensor-memory kernels (head size 64, prompts of several hundred tokens); used by the tests
+    # that must reach them, not by the whole matrix of cuts
+    "c": dict(vocab_size=500, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              intermediate_size=392, max_position_embeddings=1024, rope_theta=1e5, rms_norm_eps=1e-6,
+              tie_word_embeddings=False, use_sliding_window=True, sliding_window=200, max_window_layers=1,
+              torch_dtype="float32"),
 }
-SEEDS = {"a": 0, "b": 1}
+SEEDS = {"a": 0, "b": 1, "c": 2}
 
 # fp32: engine and plain differ only by summation order.  bf16: both round to bf16 at the
 # same places, so what remains is summation order times bf16 steps of the intermediate values.

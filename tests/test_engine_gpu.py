@@ -62,6 +62,31 @@ def test_mixed_batches_with_reused_pages(folders, key, dtype):
         assert stats["pages_released_by_window"] > 0
 
 
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
+def test_prompts_of_hundreds_of_tokens_reach_the_tensor_memory_kernels(tmp_path_factory, cut):
+    """Configuration c (head size 64, window 200 in the second layer): prompt portions of 48 tokens and
+    more go through the tcgen05 attention kernel, portions of 256 and more through the CTA-pair product
+    with the activation in its epilogue; decoded tokens beside them through the fused few-token kernels."""
+    from microllm_rocm_b200.kernels import ops
+    folder = make_folder(tmp_path_factory, "c", "float32")
+    vocab = tiny_config("c").vocab_size
+    reqs = {f"c{i}": random_tokens(n, vocab, 31 * i + n) for i, n in enumerate([300, 520, 77, 260])}
+    if cut == "mixed":
+        steps, peak = steps_mixed(reqs, max_live=3, seed=5, decode_tail=6)
+        # larger portions than the tiny configurations use, so that some reach the 128-row tiles
+        engine = engine_for(folder, "bfloat16", max_tokens=peak)
+    else:
+        steps = {"whole": steps_whole, "tail": steps_prefill_then_decode,
+                 "portions": lambda r: steps_portions(r, sizes=(260, 7, 130, 2, 64, 300, 49))}[cut](reqs)
+        engine = engine_for(folder, "bfloat16", max_tokens=2048)
+    got = collect(engine, steps)
+    compare_with_plain(got, folder, reqs, "bfloat16")
+    loaded = {source for source, _ in ops._libs}
+    assert "attention_tc.cu" in loaded
+    if cut != "mixed":
+        assert "gemm_tc2.cu" in loaded
+
+
 @pytest.mark.parametrize("key", ["a", "b"])
 def test_fp32_is_bit_stable_across_cuts(folders, key):
     """In the fp32 path every summation order is fixed by the token's own position, so the
