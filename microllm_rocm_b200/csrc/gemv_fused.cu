@@ -3,6 +3,7 @@
 //
 //   mlb_gemv_silu      act[M, I]  = silu(x Wg^T) * (x Wu^T)                     (gate/up + activation)
 //   mlb_gemv_qkv_rope  q, k, v    = x Wqkv^T + b;  q, k rotated;  k, v stored into the paged cache
+//   mlb_gemv_split     partial[S] = x W^T over S ranges of K                    (few partial sums for the consumer)
 //
 // Both stream the weights exactly like gemv_bf16_kernel (16-byte loads straight into
 // mma.sync.m16n8k16 fragments, two register sets in flight, the first loads issued before the
@@ -257,6 +258,65 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) gemv_qkv_rope_kernel(QkvParams
     dst[pair + half] = __float2bfloat16_rn(rb);
 }
 
+// ------------------------------------------------------------------------------ plain product, K split inside the CTA
+// partial[split, M, N] = x[:, k range of the split] * W[:, the same]^T.  The grid is (16-row tiles, splits):
+// the warps of a CTA share the split's K range, so a product needs far fewer partial results than with one
+// warp per K range (the consumer adds them up), and most of a warp's weights are on their way before the wait.
+struct SplitParams {
+    const __nv_bfloat16* x;      // [M, ldx]
+    const __nv_bfloat16* w;      // [N, ldw]
+    const float* bias;           // [N] or null; added by split 0
+    float* partial;              // [splits, M, N]
+    long long ldx, ldw;
+    int M, N, K, k_per_cta, x_stride;
+};
+
+constexpr int SPLIT_WARPS = 8;
+constexpr int SPLIT_BATCH = 4;
+
+template <int NT>
+__global__ void __launch_bounds__(SPLIT_WARPS * 32) gemv_split_kernel(SplitParams p) {
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* x_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)NT * 8 * p.x_stride * 2);     // [W][NT*4][32]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int f0 = blockIdx.x * 16;
+    const int k_begin = blockIdx.y * p.k_per_cta, k_len = max(0, min(p.K, k_begin + p.k_per_cta) - k_begin);
+    const int total_chunks = k_len / 32, per_warp = (total_chunks + SPLIT_WARPS - 1) / SPLIT_WARPS;
+    const int c_begin = min(total_chunks, warp * per_warp);
+    const int ra = min(f0 + g, p.N - 1), rb = min(f0 + g + 8, p.N - 1);       // rows past the end read the last row (never stored)
+
+    Streamer<NT, false, SPLIT_BATCH> st;
+    st.chunks = min(total_chunks, c_begin + per_warp) - c_begin;
+    st.wa = p.w + (size_t)ra * p.ldw + k_begin + c_begin * 32 + t * 8;
+    st.wb = p.w + (size_t)rb * p.ldw + k_begin + c_begin * 32 + t * 8;
+    st.ua = st.ub = nullptr;
+    st.clear();
+    st.preload();
+    pdl_wait();
+    stage_x<NT>(x_s, p.x + k_begin, p.ldx, p.M, k_len, p.x_stride, SPLIT_WARPS * 32);
+    __syncthreads();
+    st.run(x_s + (size_t)g * p.x_stride + c_begin * 32 + t * 8, p.x_stride);
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) red[((warp * NT + n) * 4 + e) * 32 + lane] = st.acc[n][e];
+    __syncthreads();
+    // element e of column block n of lane (g, t): row g (e < 2) or g+8, token n*8 + 2t + (e & 1)
+    for (int o = threadIdx.x; o < NT * 4 * 32; o += SPLIT_WARPS * 32) {
+        const int ne = o >> 5, l2 = o & 31, n = ne >> 2, e = ne & 3;
+        const int row = f0 + (l2 >> 2) + 8 * (e >> 1), tok = n * 8 + 2 * (l2 & 3) + (e & 1);
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < SPLIT_WARPS; ++w) v += red[((w * NT + n) * 4 + e) * 32 + l2];
+        if (row < p.N && tok < p.M) {
+            if (p.bias && blockIdx.y == 0) v += p.bias[row];
+            p.partial[((size_t)blockIdx.y * p.M + tok) * p.N + row] = v;
+        }
+    }
+}
+
 int x_pitch(int K) {
     int x_stride = K + 8;                                   // pitch in bytes = 64 mod 128: 16-byte row loads
     while ((x_stride * 2) % 128 != 64) x_stride += 8;       // of two neighbouring rows hit different banks
@@ -344,4 +404,31 @@ MLB_EXPORT int mlb_gemv_qkv_rope(const void* x, long long ldx, const void* w, lo
         launch_kernel(gemv_qkv_rope_kernel<2>, blocks, QKV_WARPS * 32, smem, stream, p);
     }
     return check_launch("gemv_qkv_rope");
+}
+
+// partial[splits, M, N] (fp32) = x * W^T cut into `splits` K ranges of k_per_cta elements (a multiple of 32;
+// bias, if given, goes into split 0); their sum over the splits, taken in order by the consumer, is the product.
+MLB_EXPORT int mlb_gemv_split(const void* x, long long ldx, const void* w, long long ldw, int w_rows, const float* bias,
+                              float* partial, int M, int N, int K, int splits, int k_per_cta, cudaStream_t stream) {
+    int status = check_operands("gemv_split", x, ldx, w, ldw, M, K);
+    if (status != MLB_OK) return status;
+    if (N <= 0 || N > w_rows || !partial) return fail(MLB_INVALID_ARGUMENT, "gemv_split: bad output");
+    if (splits < 1 || splits > 65535 || k_per_cta <= 0 || k_per_cta % 32 != 0 || (long long)splits * k_per_cta < K)
+        return fail(MLB_INVALID_ARGUMENT, "gemv_split: %d splits of %d do not cover K=%d in steps of 32", splits, k_per_cta, K);
+    if (k_per_cta > mlb_gemv_fused_max_k()) return fail(MLB_UNSUPPORTED_SIZE, "gemv_split: a K range of %d per CTA is more than %d", k_per_cta, mlb_gemv_fused_max_k());
+    const int nt = M <= 8 ? 1 : 2;
+    SplitParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, partial, ldx, ldw, M, N, K, k_per_cta, x_pitch(k_per_cta)};
+    const size_t smem = (size_t)nt * 8 * p.x_stride * 2 + (size_t)SPLIT_WARPS * nt * 4 * 32 * sizeof(float);
+    static size_t configured1 = 0, configured2 = 0;
+    const dim3 grid((unsigned)((N + 15) / 16), (unsigned)splits);
+    if (nt == 1) {
+        status = reserve(gemv_split_kernel<1>, smem, configured1, "gemv_split");
+        if (status != MLB_OK) return status;
+        launch_kernel(gemv_split_kernel<1>, grid, SPLIT_WARPS * 32, smem, stream, p);
+    } else {
+        status = reserve(gemv_split_kernel<2>, smem, configured2, "gemv_split");
+        if (status != MLB_OK) return status;
+        launch_kernel(gemv_split_kernel<2>, grid, SPLIT_WARPS * 32, smem, stream, p);
+    }
+    return check_launch("gemv_split");
 }

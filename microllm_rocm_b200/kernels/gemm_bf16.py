@@ -8,6 +8,7 @@ as `library_linear` for comparisons.
 """
 from __future__ import annotations
 
+import os
 from ctypes import c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -25,6 +26,8 @@ ops.register_signatures("gemv_bf16.cu", {
                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
 })
 ops.register_signatures("gemv_fused.cu", {
+    "mlb_gemv_split": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                       c_int, c_void_p],
     "mlb_gemv_silu": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_int, c_int,
                       c_void_p],
     "mlb_gemv_qkv_rope": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -41,6 +44,7 @@ ops.register_signatures("gemm_tc.cu", {
 })
 
 USE_TENSOR_CORE_KERNEL = True
+USE_GEMV_SPLIT = os.environ.get("MLB_GEMV_SPLIT", "1") != "0"
 _tickets = {}
 _error_flags = {}
 
@@ -76,6 +80,9 @@ def gemv_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
     taken in order by the kernel that consumes them, is the product."""
     M, K = x.shape
     N = weight.shape[0]
+    plan = gemv_split_plan(N, K) if x.dtype == torch.bfloat16 and USE_GEMV_SPLIT and M >= GEMV_SPLIT_MIN_TOKENS else None
+    if plan is not None:
+        return gemv_split_partials(x, weight, bias, *plan)
     splits, k_per_split = gemv_splits(N, K)
     partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
     L = ops.lib("gemv_bf16.cu")
@@ -91,6 +98,36 @@ GEMV_FUSED_MAX_K = 6144             # the activations of 16 tokens over the whol
 def gemv_fused_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
     """The few-token kernels that finish their own epilogue (activation; rotation and cache store)."""
     return gemv_supported(x, weight) and x.shape[1] <= GEMV_FUSED_MAX_K and x.dtype == torch.bfloat16
+
+
+GEMV_SPLIT_TARGET_CTAS = int(os.environ.get("MLB_GEMV_SPLIT_CTAS", str(2 * SM_COUNT)))   # eight-warp CTAs, two per SM
+GEMV_SPLIT_MIN_TOKENS = 5               # measured: below this the one-warp-per-range kernel is the faster one
+GEMV_SPLIT_MAX_TILES = 4 * SM_COUNT     # beyond this many 16-row tiles the one-warp-per-range kernel streams better
+
+
+def gemv_split_plan(n: int, k: int):
+    """(splits, k_per_cta) for the kernel that splits K inside the CTA, or None when the other kernel suits better."""
+    tiles = -(-n // 16)
+    if tiles > GEMV_SPLIT_MAX_TILES:
+        return None
+    splits = max(1, min(GEMV_SPLIT_TARGET_CTAS // tiles, k // GEMV_MIN_K_PER_SPLIT))
+    k_per_cta = -(-(-(-k // splits)) // 32) * 32
+    while k_per_cta > GEMV_FUSED_MAX_K:
+        splits += 1
+        k_per_cta = -(-(-(-k // splits)) // 32) * 32
+    return -(-k // k_per_cta), k_per_cta
+
+
+def gemv_split_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], splits: int,
+                        k_per_cta: int) -> torch.Tensor:
+    """[S, M, N] fp32 partial results from the kernel whose warps share a CTA's K range (few partials)."""
+    M, K = x.shape
+    N = weight.shape[0]
+    partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+    L = ops.lib("gemv_fused.cu")
+    build.check(L, L.mlb_gemv_split(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), N, ops._ptr(bias),
+                                    partial.data_ptr(), M, N, K, splits, k_per_cta, ops._stream()))
+    return partial
 
 
 def gemv_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:

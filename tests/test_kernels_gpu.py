@@ -511,7 +511,7 @@ def test_tensor_core_product_refuses_what_tma_cannot_address():
 
 # ------------------------------------------------------------------------------ few-token weight streaming
 @pytest.mark.parametrize("M,N,K", [(1, 64, 32), (8, 2048, 1536), (8, 1536, 8960), (3, 200, 96), (16, 384, 192),
-                                   (9, 1000, 1024), (5, 70, 4096)])
+                                   (9, 1000, 1024), (5, 70, 4096), (4, 9616, 96), (11, 12000, 160), (2, 1536, 8960)])
 def test_gemv_partials_sum_to_the_product(M, N, K):
     from microllm_rocm_b200.kernels import gemm_bf16
     torch.manual_seed(M * 7 + N + K)
