@@ -82,6 +82,7 @@ class CacheManager:
         self.slots = SlotPool(max_requests)
         self.requests: Dict[Hashable, _Request] = {}
         self.pages_released_by_window = 0
+        self.tables_version = 0          # grows whenever any block table changes: lets a reader skip a comparison
 
     # ----- requests -------------------------------------------------------------------------
     def add(self, request: Hashable) -> bool:
@@ -92,6 +93,7 @@ class CacheManager:
         if slot is None:
             return False
         self.requests[request] = _Request(0, {k: [] for k in self.groups}, slot)
+        self.tables_version += 1
         return True
 
     def has(self, request: Hashable) -> bool:
@@ -125,6 +127,7 @@ class CacheManager:
                 if page is None:                                   # cannot happen after the check above
                     raise PageError("pool ran dry inside a checked reservation")
                 r.tables[k].append(page)
+                self.tables_version += 1
         return True
 
     def commit(self, request: Hashable, new_len: int) -> None:
@@ -145,9 +148,11 @@ class CacheManager:
                     self.groups[k].pool.free(table[b])
                     table[b] = RELEASED
                     self.pages_released_by_window += 1
+                    self.tables_version += 1
 
     def release(self, request: Hashable) -> None:
         r = self.requests.pop(request)
+        self.tables_version += 1
         for k, table in r.tables.items():
             for page in table:
                 if page != RELEASED:

@@ -291,20 +291,45 @@ MLB_EXPORT int mlb_cast_f32_bf16(const float* in, void* out, long long n, cudaSt
 // positions, the per-sequence extents and the per-request draw counters on the device, so
 // that the same captured step can run again without the host touching its inputs.
 __global__ void decode_advance_kernel(int* __restrict__ positions, int* __restrict__ seq_pos0,
-                                      int* __restrict__ seq_lens, long long* __restrict__ draw, int n) {
+                                      int* __restrict__ seq_lens, long long* __restrict__ draw, int n,
+                                      const int* __restrict__ tokens, const int* __restrict__ error_flag,
+                                      int* __restrict__ result) {
     pdl_prologue();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i == 0 && result) result[n] = error_flag ? *error_flag : 0;
     if (i >= n) return;
     positions[i] += 1;
     seq_pos0[i] += 1;
     seq_lens[i] += 1;
     draw[i] += 1;
+    if (result) result[i] = tokens[i];
 }
 
+// `result` (may be null): n + 1 ints that receive the step's selected tokens and then the error flag, so
+// that one device -> host copy brings everything the host wants to see of a step.
 MLB_EXPORT int mlb_decode_advance(int* positions, int* seq_pos0, int* seq_lens, long long* draw, int n,
-                                  cudaStream_t stream) {
+                                  const int* tokens, const int* error_flag, int* result, cudaStream_t stream) {
     if (n < 0) return fail(MLB_INVALID_ARGUMENT, "decode_advance: negative size");
+    if (result && !tokens) return fail(MLB_INVALID_ARGUMENT, "decode_advance: a result buffer needs the tokens");
     if (n == 0) return MLB_OK;
-    launch_kernel(decode_advance_kernel, (n + 127) / 128, 128, 0, stream, positions, seq_pos0, seq_lens, draw, n);
+    launch_kernel(decode_advance_kernel, (n + 127) / 128, 128, 0, stream, positions, seq_pos0, seq_lens, draw, n, tokens,
+                  error_flag, result);
     return check_launch("decode_advance");
+}
+
+// ------------------------------------------------------------------ small copies without a framework in between
+// A decode step moves a few dozen bytes each way; the launch path of a tensor library costs more
+// than the copy.  Host memory must be pinned for the copy to be asynchronous.
+MLB_EXPORT int mlb_copy_async(void* dst, const void* src, long long bytes, int to_device, cudaStream_t stream) {
+    if (bytes < 0 || (bytes > 0 && (!dst || !src))) return fail(MLB_INVALID_ARGUMENT, "copy_async: bad arguments");
+    if (bytes == 0) return MLB_OK;
+    cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "copy_async: %s", cudaGetErrorString(e));
+    return MLB_OK;
+}
+
+MLB_EXPORT int mlb_stream_synchronize(cudaStream_t stream) {
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "stream_synchronize: %s", cudaGetErrorString(e));
+    return MLB_OK;
 }

@@ -59,7 +59,10 @@ class DecodeGraph:
         self.host = torch.zeros(self.total, dtype=torch.int32, pin_memory=True)
         self.dev = torch.zeros(self.total, dtype=torch.int32, device=dev)
         self.out_host = torch.zeros(A + 1, dtype=torch.int32, pin_memory=True)     # tokens, then the error flag
-        self._upload_done: Optional[torch.cuda.Event] = None
+        self.out_dev = torch.zeros(A + 1, dtype=torch.int32, device=dev)           # gathered by the step's last kernel
+        self._upload_pending = False
+        self._token_views = None
+        self._tables_version = -1
         d = lambda name: self.dev[self._s[name][0]:self._s[name][1]]
         self.temperature = d("temperature").view(torch.float32)
         self.top_k = d("top_k")
@@ -104,19 +107,21 @@ class DecodeGraph:
         self._h("seed").view(np.int64)[:] = [c.seed for c in configs]
         self._h("draw").view(np.int64)[:] = list(draws)
         self._fill_tables()
+        self._tables_version = cache.tables_version
         self.dev.copy_(self.host, non_blocking=True)
         self._mark_upload()
         self.ctx.max_seq_len = max(lengths) + 1
 
     def _mark_upload(self) -> None:
-        if self._upload_done is None:
-            self._upload_done = torch.cuda.Event()
-        self._upload_done.record()
+        self._upload_pending = True
 
     def _wait_upload(self) -> None:
-        """The staging buffer may be rewritten only once the last copy out of it has run."""
-        if self._upload_done is not None:
-            self._upload_done.synchronize()
+        """The staging buffer may be rewritten only once the last copy out of it has run.  Every step ends
+        with a synchronisation (the token read), which clears the mark; only a second upload without a
+        step in between has to wait here."""
+        if self._upload_pending:
+            ops.stream_synchronize()
+            self._upload_pending = False
 
     def _fill_tables(self) -> bool:
         """Write the requests' block tables into the staging buffer; True if they changed."""
@@ -137,6 +142,9 @@ class DecodeGraph:
         """After the host reserved pages (or a window released some): bring the device tables up
         to date.  Only the table region travels."""
         cache = self.engine.cache
+        if cache.tables_version == self._tables_version:
+            return                                        # no table of the pool has changed since the last look
+        self._tables_version = cache.tables_version
         if all(self._table_state.get(g) == [tuple(cache.requests[q].tables[g]) for q in self.requests]
                for g in self._tables):
             return
@@ -151,9 +159,13 @@ class DecodeGraph:
         replay would find the same values where the sampler left them; sending them keeps the
         host the owner of what the model is fed."""
         self._wait_upload()
-        a, b = self._s["tokens"]
-        self.host.numpy()[a:b] = tokens
-        self.dev[a:b].copy_(self.host[a:b], non_blocking=True)
+        if self._token_views is None:
+            a, b = self._s["tokens"]
+            ops.copy_async(self.dev[a:b], self.host[a:b])         # checked once; from now on by raw pointers
+            self._token_views = (self.host.numpy()[a:b], self.host[a:b].data_ptr(), self.dev[a:b].data_ptr(), 4 * (b - a))
+        array, pinned, device, nbytes = self._token_views
+        array[:] = tokens
+        ops.copy_raw(device, pinned, nbytes, True)
         self._mark_upload()
 
     def fits(self, requests: Sequence[Hashable]) -> bool:
@@ -164,7 +176,8 @@ class DecodeGraph:
     def _body(self) -> None:
         logits = self.engine.model.forward(self.ctx, self.views)
         ops.sample_rows(logits, self.temperature, self.top_k, self.seed, self.draw, self.ctx.token_ids)
-        ops.decode_advance(self.ctx.positions, self.ctx.seq_pos0, self.ctx.seq_lens, self.draw)
+        ops.decode_advance(self.ctx.positions, self.ctx.seq_pos0, self.ctx.seq_lens, self.draw, self.ctx.token_ids,
+                           self.engine.error_flag, self.out_dev)
 
     def capture(self) -> None:
         """Run the step once eagerly (plans launches, warms libraries), then record it.  The
@@ -189,9 +202,9 @@ class DecodeGraph:
     def read_tokens(self) -> List[int]:
         """The tokens the last replay selected (one device -> host copy, synchronising)."""
         A = self.batch
-        self.out_host[:A].copy_(self.ctx.token_ids, non_blocking=True)
-        self.out_host[A:].copy_(self.engine.error_flag, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        ops.copy_raw(self.out_host.data_ptr(), self.out_dev.data_ptr(), 4 * (A + 1), False)
+        ops.stream_synchronize()
+        self._upload_pending = False                      # everything queued before has run
         host = self.out_host.tolist()
         if host[A]:
             self.engine.error_flag.zero_()

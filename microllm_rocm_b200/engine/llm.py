@@ -104,13 +104,14 @@ class LLM:
             graph.upload_tokens([e.request.token(e.begin) for e in plan.entries])
             self.h2d_bytes += 4 * len(ids)
         graph.replay()
-        tokens = graph.read_tokens()
-        self.d2h_bytes += 4 * (len(ids) + 1)
-        self.graph_steps += 1
+        # what does not need the step's tokens happens while the GPU runs
         for e in plan.entries:
             self.engine.cache.commit(e.request.id, e.begin + 1)
+        self.d2h_bytes += 4 * (len(ids) + 1)
+        self.graph_steps += 1
         self.engine.steps_run += 1
         self.engine.tokens_run += len(ids)
+        tokens = graph.read_tokens()
         finished = self.scheduler.update(plan, tokens)
         if finished:
             self._graph = None

@@ -32,6 +32,7 @@ TC_ROWS_PER_TILE = 128
 TC_MIN_NEW_TOKENS = 48              # below this the 16-row tiles of the mma.sync kernel waste less
 
 ops.register_signatures("attention_tc.cu", {
+    "mlb_fa_tc_supported": [c_int, c_float],
     "mlb_paged_attention_tc": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
 })

@@ -53,7 +53,9 @@ _SIGNATURES = {
         "mlb_add_inplace": [c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p],
         "mlb_silu_mul": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
         "mlb_cast_f32_bf16": [c_void_p, c_void_p, c_longlong, c_void_p],
-        "mlb_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+        "mlb_copy_async": [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
+        "mlb_stream_synchronize": [c_void_p],
+        "mlb_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     },
     "gemm_f32.cu": {
         "mlb_gemm_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -203,17 +205,56 @@ def cast_f32_bf16(x: torch.Tensor, out: torch.Tensor) -> None:
     build.check(L, L.mlb_cast_f32_bf16(x.data_ptr(), out.data_ptr(), x.numel(), _stream()))
 
 
-def decode_advance(positions: torch.Tensor, seq_pos0: torch.Tensor, seq_lens: torch.Tensor, draw: torch.Tensor) -> None:
+def decode_advance(positions: torch.Tensor, seq_pos0: torch.Tensor, seq_lens: torch.Tensor, draw: torch.Tensor,
+                   tokens: Optional[torch.Tensor] = None, error_flag: Optional[torch.Tensor] = None,
+                   result: Optional[torch.Tensor] = None) -> None:
     """Every sequence of a captured decode step has grown by one token: advance its position,
-    extents and draw counter on the device."""
+    extents and draw counter on the device.  With `result` ([n + 1] int32) the step's selected
+    `tokens` and the error flag are gathered there, for one device -> host copy."""
     n = positions.shape[0]
     _need(positions, "positions", torch.int32, 1); _need(seq_pos0, "seq_pos0", torch.int32, 1)
     _need(seq_lens, "seq_lens", torch.int32, 1); _need(draw, "draw", torch.int64, 1)
     if not (seq_pos0.shape[0] == seq_lens.shape[0] == draw.shape[0] == n):
         raise KernelError("decode_advance: one entry per sequence in every array")
+    if result is not None:
+        _need(result, "result", torch.int32, 1); _need(tokens, "tokens", torch.int32, 1)
+        if result.shape[0] != n + 1 or tokens.shape[0] != n:
+            raise KernelError("decode_advance: result holds one int per sequence and one more for the error flag")
     L = lib("basic.cu")
     build.check(L, L.mlb_decode_advance(positions.data_ptr(), seq_pos0.data_ptr(), seq_lens.data_ptr(), draw.data_ptr(),
-                                        n, _stream()))
+                                        n, _ptr(tokens), _ptr(error_flag), _ptr(result), _stream()))
+
+
+def copy_async(dst: torch.Tensor, src: torch.Tensor) -> None:
+    """A small contiguous copy between pinned host memory and the device on the current stream, through the
+    runtime directly (a tensor library's copy costs several microseconds of dispatch for a few bytes)."""
+    nbytes = src.numel() * src.element_size()
+    if dst.numel() * dst.element_size() != nbytes or not dst.is_contiguous() or not src.is_contiguous():
+        raise KernelError("copy_async: both sides must be contiguous and of the same size")
+    if dst.is_cuda == src.is_cuda:
+        raise KernelError("copy_async: one side on the device, the other in pinned host memory")
+    host = src if dst.is_cuda else dst
+    if not host.is_pinned():
+        raise KernelError("copy_async: the host side must be pinned")
+    L = lib("basic.cu")
+    status = L.mlb_copy_async(dst.data_ptr(), src.data_ptr(), nbytes, 1 if dst.is_cuda else 0, _stream())
+    if status != 0:
+        build.check(L, status)
+
+
+def copy_raw(dst: int, src: int, nbytes: int, to_device: bool) -> None:
+    """`copy_async` for a caller that keeps the two addresses of buffers it owns (pinned host, device)."""
+    L = lib("basic.cu")
+    status = L.mlb_copy_async(dst, src, nbytes, 1 if to_device else 0, _stream())
+    if status != 0:
+        build.check(L, status)
+
+
+def stream_synchronize() -> None:
+    L = lib("basic.cu")
+    status = L.mlb_stream_synchronize(_stream())
+    if status != 0:
+        build.check(L, status)
 
 
 # ------------------------------------------------------------------------------ fp32 GEMM
