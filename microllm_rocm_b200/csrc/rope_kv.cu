@@ -128,11 +128,12 @@ __global__ void rope_kv_split_half_x4_kernel(RopeKvParams p) {
     pdl_launch_dependents();
     const int half = p.head_dim / 2, quads = half / 4;
     const int heads_all = p.num_heads + 2 * p.num_kv_heads;
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const bool in_range = idx < (long long)p.tokens * heads_all * quads;
-    const int i = (int)(idx % quads) * 4;
-    const int head = in_range ? (int)((idx / quads) % heads_all) : 0;
-    const int t = in_range ? (int)(idx / ((long long)quads * heads_all)) : 0;
+    // grid (tokens, blocks of a token's items): no 64-bit divisions on the way to (token, head, element)
+    const int item = blockIdx.y * blockDim.x + threadIdx.x;
+    const bool in_range = item < heads_all * quads;
+    const int i = (item % quads) * 4;
+    const int head = in_range ? item / quads : 0;
+    const int t = blockIdx.x;
     const bool is_q = head < p.num_heads;
     const bool is_v = head >= p.num_heads + p.num_kv_heads;
     const bool working = in_range && (is_q || p.pages != nullptr);
@@ -250,13 +251,14 @@ MLB_EXPORT int mlb_rope_kv_write(const float* qkv, long long ld, int n_partials,
                       (uintptr_t)q_out % 16 == 0 && (!pages || (uintptr_t)pages % 16 == 0) && (uintptr_t)qkv % 16 == 0 && (!bias || (uintptr_t)bias % 16 == 0) && (uintptr_t)inv_freq % 16 == 0;
     if (wide) {
         if (cos_sin && (uintptr_t)cos_sin % 16 == 0 && head_dim % 16 == 0) p.cos_sin = (const float2*)cos_sin;
-        const long long total4 = (long long)tokens * (num_heads + 2 * num_kv_heads) * (head_dim / 8);
-        const unsigned blocks4 = (unsigned)((total4 + 255) / 256);
+        const int per_token = (num_heads + 2 * num_kv_heads) * (head_dim / 8);
+        const int threads4 = per_token >= 256 ? 256 : ((per_token + 31) / 32) * 32;
+        const dim3 blocks4((unsigned)tokens, (unsigned)((per_token + threads4 - 1) / threads4));
         switch (key) {
-            case MLB_F32 * 2 + MLB_F32: launch_kernel(rope_kv_split_half_x4_kernel<float, float>, blocks4, 256, 0, stream, p); break;
-            case MLB_BF16 * 2 + MLB_BF16: launch_kernel(rope_kv_split_half_x4_kernel<__nv_bfloat16, __nv_bfloat16>, blocks4, 256, 0, stream, p); break;
-            case MLB_F32 * 2 + MLB_BF16: launch_kernel(rope_kv_split_half_x4_kernel<float, __nv_bfloat16>, blocks4, 256, 0, stream, p); break;
-            case MLB_BF16 * 2 + MLB_F32: launch_kernel(rope_kv_split_half_x4_kernel<__nv_bfloat16, float>, blocks4, 256, 0, stream, p); break;
+            case MLB_F32 * 2 + MLB_F32: launch_kernel(rope_kv_split_half_x4_kernel<float, float>, blocks4, threads4, 0, stream, p); break;
+            case MLB_BF16 * 2 + MLB_BF16: launch_kernel(rope_kv_split_half_x4_kernel<__nv_bfloat16, __nv_bfloat16>, blocks4, threads4, 0, stream, p); break;
+            case MLB_F32 * 2 + MLB_BF16: launch_kernel(rope_kv_split_half_x4_kernel<float, __nv_bfloat16>, blocks4, threads4, 0, stream, p); break;
+            case MLB_BF16 * 2 + MLB_F32: launch_kernel(rope_kv_split_half_x4_kernel<__nv_bfloat16, float>, blocks4, threads4, 0, stream, p); break;
             default: return fail(MLB_INVALID_ARGUMENT, "rope_kv_write: unknown dtypes %d/%d", q_dtype, kv_dtype);
         }
         return check_launch("rope_kv_write");
