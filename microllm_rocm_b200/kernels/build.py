@@ -149,7 +149,21 @@ def compile_object(source: str, defines: Optional[Dict[str, object]] = None, ext
     if verbose:
         print(proc.stderr, file=sys.stderr)
     os.replace(tmp, out)          # atomic: another process building the same object just wins or loses
+    _prune_older_builds(out)
     return out
+
+
+def _prune_older_builds(current: str) -> None:
+    """Objects of the same source and defines built from an earlier state of the sources (another hash) are
+    of no use any more; a process that still has one loaded keeps its mapping."""
+    folder, name = os.path.split(current)
+    prefix = name[:name.rfind("-") + 1]                   # "<stem><defines>-"
+    for other in os.listdir(folder):
+        if other != name and other.startswith(prefix) and other.endswith(".so") and len(other) == len(name):
+            try:
+                os.remove(os.path.join(folder, other))
+            except OSError:
+                pass
 
 
 def compile_many(items: Iterable[Tuple[str, Dict[str, object]]], jobs: int = 0) -> Dict[Tuple[str, tuple], str]:
