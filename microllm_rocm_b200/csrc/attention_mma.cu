@@ -799,6 +799,275 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_kernel(FaP
     cluster.sync();                          // nobody leaves while its shared memory may still be read
 }
 
+
+// ---------------------------------------------------------------------------------- decode, keys on the M side
+// The same work as fa_decode_kernel for groups of at most 8 query heads, with the roles of the MMA
+// operands swapped so that the 16-row side carries KEYS and the 8-column side the group's heads:
+//     S^T[16 keys, 8 heads] = K[16 keys, D] Q^T          (K straight from the page as the A operand, as a
+//                                                        weight in the streaming products; Q^T from shared memory)
+//     O^T[D, 8 heads]      += V^T[D, 16 keys] P^T        (V^T fragments by byte permutes of the same 16-byte loads;
+//                                                        P^T moves from accumulator to B-operand layout by 4 shuffles)
+// A 16-row tile of the other kernel carries 6 real rows for this model; here nothing is padding but two of
+// eight columns: half the MMAs, half the accumulator registers, half the exponentials per key.
+constexpr int NPAIR = (VBLOCKS + 1) / 2;    // pairs of 64-element value blocks: one MMA covers 16 rows = 8 + 8 elements
+constexpr int FRAGS_T = NPAIR * 8 * 4;
+
+struct RowStateT {
+    float m[2];               // reference maximum of heads 2t and 2t+1 (equal in all lanes of the same t)
+    float l[2];               // this thread's share (its own keys) of the running sums
+    float o[NPAIR * 8][4];    // [pair*8 + j]: e < 2: element vb0*64 + 8g + j, e >= 2: element vb1*64 + 8g + j; head 2t + (e & 1)
+};
+
+__device__ __forceinline__ void consume_keys_t(const FaParams& p, const __nv_bfloat16* q_s, const KeyTile& kv, int last_pos,
+                                               int lo, RowStateT& st) {
+    if (kv.base < 0) return;
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    float s0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s1[4] = {0.0f, 0.0f, 0.0f, 0.0f};     // two chains
+#pragma unroll
+    for (int c = 0; c < KCHUNKS; ++c) {
+        const uint4 q = *reinterpret_cast<const uint4*>(q_s + g * Q_STRIDE + c * 32 + t * 8);       // head g
+        mma_bf16(s0, kv.k[0][c].x, kv.k[1][c].x, kv.k[0][c].y, kv.k[1][c].y, q.x, q.y);
+        mma_bf16(s1, kv.k[0][c].z, kv.k[1][c].z, kv.k[0][c].w, kv.k[1][c].w, q.z, q.w);
+    }
+    // s[0], s[1]: key base + g, heads 2t, 2t+1;   s[2], s[3]: key base + g + 8
+    float s[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[e] = (s0[e] + s1[e]) * p.scale_log2;
+    if (kv.base + 15 > last_pos || kv.base < lo) {         // an edge tile (uniform over the warp)
+        const int key0 = kv.base + g, key1 = key0 + 8;
+        if (key0 < lo || key0 > last_pos) s[0] = s[1] = -INFINITY;
+        if (key1 < lo || key1 > last_pos) s[2] = s[3] = -INFINITY;
+    }
+    float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
+    float corr[2];
+    bool grow = false;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 4));
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 8));
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 16));
+        const bool g_i = mx[i] > st.m[i] + RESCALE_STEP;          // true as well for the first finite maximum
+        corr[i] = g_i ? (st.m[i] == -INFINITY ? 0.0f : fast_exp2(st.m[i] - mx[i])) : 1.0f;
+        st.m[i] = g_i ? mx[i] : st.m[i];
+        grow |= g_i;
+    }
+    const float ref0 = st.m[0] == -INFINITY ? 0.0f : st.m[0], ref1 = st.m[1] == -INFINITY ? 0.0f : st.m[1];
+    const float p0 = fast_exp2(s[0] - ref0), p1 = fast_exp2(s[1] - ref1), p2 = fast_exp2(s[2] - ref0), p3 = fast_exp2(s[3] - ref1);
+    if (__any_sync(0xffffffffu, grow)) {
+        st.l[0] *= corr[0];
+        st.l[1] *= corr[1];
+#pragma unroll
+        for (int k = 0; k < NPAIR * 8; ++k) {
+            st.o[k][0] *= corr[0]; st.o[k][1] *= corr[1];
+            st.o[k][2] *= corr[0]; st.o[k][3] *= corr[1];
+        }
+    }
+    st.l[0] += p0 + p2;
+    st.l[1] += p1 + p3;
+    // P^T from accumulator layout (keys on g, heads on t) to B-operand layout (keys on t, head g): lane (g, t)
+    // takes head g's probabilities of keys 2t, 2t+8 from lane (2t, g/2) and of keys 2t+1, 2t+9 from lane (2t+1, g/2)
+    const unsigned u_even = pack_bf16(p0, p2), u_odd = pack_bf16(p1, p3);      // (key g, key g+8) of head 2t / 2t+1
+    const int src1 = (2 * t) * 4 + (g >> 1), src2 = src1 + 4;
+    const unsigned e1 = __shfl_sync(0xffffffffu, u_even, src1), o1 = __shfl_sync(0xffffffffu, u_odd, src1);
+    const unsigned e2 = __shfl_sync(0xffffffffu, u_even, src2), o2 = __shfl_sync(0xffffffffu, u_odd, src2);
+    const unsigned w1 = (g & 1) ? o1 : e1, w2 = (g & 1) ? o2 : e2;
+    const unsigned b0 = __byte_perm(w1, w2, 0x5410u);       // keys 2t, 2t+1
+    const unsigned b1 = __byte_perm(w1, w2, 0x7632u);       // keys 2t+8, 2t+9
+#pragma unroll
+    for (int pp = 0; pp < NPAIR; ++pp) {
+        const int vb0 = 2 * pp, vb1 = 2 * pp + 1;
+        const unsigned* x0 = reinterpret_cast<const unsigned*>(&kv.v[vb0][0]);
+        const unsigned* x1 = reinterpret_cast<const unsigned*>(&kv.v[vb0][1]);
+        const unsigned* x2 = reinterpret_cast<const unsigned*>(&kv.v[vb0][2]);
+        const unsigned* x3 = reinterpret_cast<const unsigned*>(&kv.v[vb0][3]);
+        const unsigned* y0 = reinterpret_cast<const unsigned*>(&kv.v[vb1 < VBLOCKS ? vb1 : vb0][0]);
+        const unsigned* y1 = reinterpret_cast<const unsigned*>(&kv.v[vb1 < VBLOCKS ? vb1 : vb0][1]);
+        const unsigned* y2 = reinterpret_cast<const unsigned*>(&kv.v[vb1 < VBLOCKS ? vb1 : vb0][2]);
+        const unsigned* y3 = reinterpret_cast<const unsigned*>(&kv.v[vb1 < VBLOCKS ? vb1 : vb0][3]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const unsigned sel = (j & 1) ? 0x7632u : 0x5410u;       // high or low bf16 of both words
+            const unsigned a0 = __byte_perm(x0[j >> 1], x1[j >> 1], sel);     // element vb0*64 + 8g + j of keys 2t, 2t+1
+            const unsigned a2 = __byte_perm(x2[j >> 1], x3[j >> 1], sel);     // ... of keys 2t+8, 2t+9
+            const unsigned a1 = vb1 < VBLOCKS ? __byte_perm(y0[j >> 1], y1[j >> 1], sel) : 0u;
+            const unsigned a3 = vb1 < VBLOCKS ? __byte_perm(y2[j >> 1], y3[j >> 1], sel) : 0u;
+            mma_bf16(st.o[pp * 8 + j], a0, a1, a2, a3, b0, b1);
+        }
+    }
+}
+
+// shared memory (dynamic): queries | per-warp fragments [DW][FRAGS_T][32] | warp max/sum per head |
+// this CTA's merged heads [8][D] with their max and sum | block table
+constexpr size_t decode_t_smem(int dw) {
+    return 16 * Q_STRIDE * sizeof(__nv_bfloat16) + (size_t)dw * FRAGS_T * 32 * sizeof(float) + 2 * dw * 8 * sizeof(float) +
+           (size_t)8 * D * sizeof(float) + 16 * sizeof(float) + TABLE_SPAN * sizeof(int);
+}
+
+template <int DW>
+__global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_t_kernel(FaParams p) {
+    pdl_launch_dependents();       // the wait comes after the sequence's length, block table and first keys are on their way
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);                             // [8 heads used of 16][Q_STRIDE]
+    float* frag = reinterpret_cast<float*>(smem_raw + 16 * Q_STRIDE * sizeof(__nv_bfloat16));   // [DW][FRAGS_T][32]
+    float* warp_m = frag + DW * FRAGS_T * 32;      // [DW][8]
+    float* warp_l = warp_m + DW * 8;               // [DW][8]
+    float* cta_o = warp_l + DW * 8;                // [8][D]  this CTA's heads, scaled to cta_m
+    float* cta_m = cta_o + 8 * D;                  // [8]
+    float* cta_l = cta_m + 8;                      // [8]
+    int* table_s = reinterpret_cast<int*>(cta_l + 8);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+
+    // one token per sequence and at most 8 heads per group: the work item is the sequence = blockIdx.x
+    TileGeometry geo;
+    geo.seq = blockIdx.x;
+    geo.kvh = blockIdx.y;
+    geo.token0 = geo.seq;
+    geo.n_new = 1;
+    geo.row0 = 0;
+    const int heads = p.group;                     // <= 8
+    const int pos0_load = __ldg(p.seq_pos0 + geo.seq);
+    PageTable pt;
+    fill_page_table(pt, table_s, p.block_table + (size_t)geo.seq * p.max_blocks, p.max_blocks, 0, p.max_blocks - 1,
+                    threadIdx.x, DW * 32);
+    geo.pos0 = pos0_load;
+    const int last_pos = geo.pos0;
+    const int lo = (p.window > 0 && last_pos - p.window + 1 > 0) ? last_pos - p.window + 1 : 0;
+    int tile_begin = lo / 16, tile_end = last_pos / 16 + 1;
+    const int splits = (int)gridDim.z, rank = (int)blockIdx.z;
+    if (splits > 1) {                        // this CTA's even share of the sequence's key tiles
+        const int per_split = (tile_end - tile_begin + splits - 1) / splits;
+        tile_begin += rank * per_split;
+        tile_end = min(tile_end, tile_begin + per_split);
+    }
+    __syncthreads();                         // the block table is in shared memory
+    // still before the wait: this warp's first key tiles, unless they hold the new token's key
+    KeyTile tile_a, tile_b;
+    int kt = tile_begin + warp;
+    int in_flight = 0;
+    if (kt < tile_end && kt < last_pos / 16) {
+        load_keys(p, geo, pt, kt, last_pos, tile_a);
+        in_flight = 1;
+        if (USE_PREFETCH && kt + DW < tile_end && kt + DW < last_pos / 16) {
+            load_keys(p, geo, pt, kt + DW, last_pos, tile_b);
+            in_flight = 2;
+        }
+    }
+    pdl_wait();
+    {
+        constexpr int VEC_PER_ROW = D / 8;
+        for (int i = threadIdx.x; i < 8 * VEC_PER_ROW; i += DW * 32) {
+            const int r = i / VEC_PER_ROW, c = (i % VEC_PER_ROW) * 8;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < heads) v = load16(p.q + ((size_t)geo.token0 * p.num_heads + geo.kvh * p.group + r) * D + c);
+            *reinterpret_cast<uint4*>(q_s + r * Q_STRIDE + c) = v;
+        }
+    }
+    __syncthreads();
+    RowStateT st;
+    st.m[0] = st.m[1] = -INFINITY;
+    st.l[0] = st.l[1] = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NPAIR * 8; ++k)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) st.o[k][e] = 0.0f;
+    if (kt < tile_end) {
+        if (USE_PREFETCH) {
+            if (in_flight < 1) load_keys(p, geo, pt, kt, last_pos, tile_a);
+            while (true) {
+                const bool more_b = kt + DW < tile_end;
+                if (more_b && in_flight < 2) load_keys(p, geo, pt, kt + DW, last_pos, tile_b);
+                in_flight = 0;
+                consume_keys_t(p, q_s, tile_a, last_pos, lo, st);
+                if (!more_b) break;
+                kt += DW;
+                const bool more_a = kt + DW < tile_end;
+                if (more_a) load_keys(p, geo, pt, kt + DW, last_pos, tile_a);
+                consume_keys_t(p, q_s, tile_b, last_pos, lo, st);
+                if (!more_a) break;
+                kt += DW;
+            }
+        } else {
+            for (; kt < tile_end; kt += DW) {
+                if (in_flight < 1) load_keys(p, geo, pt, kt, last_pos, tile_a);
+                in_flight = 0;
+                consume_keys_t(p, q_s, tile_a, last_pos, lo, st);
+            }
+        }
+    }
+    // a head's sum over this warp's keys: the lanes of equal t hold its shares
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 4);
+        st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 8);
+        st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 16);
+    }
+    // every warp publishes its fragments, then each thread merges a share of them
+#pragma unroll
+    for (int k = 0; k < NPAIR * 8; ++k)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) frag[(warp * FRAGS_T + k * 4 + e) * 32 + lane] = st.o[k][e];
+    if (g == 0) {
+        warp_m[warp * 8 + 2 * t] = st.m[0]; warp_m[warp * 8 + 2 * t + 1] = st.m[1];
+        warp_l[warp * 8 + 2 * t] = st.l[0]; warp_l[warp * 8 + 2 * t + 1] = st.l[1];
+    }
+    __syncthreads();
+    float scale_w[2][DW];                    // of heads 2t and 2t+1
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int h = 2 * t + i;
+        float m_all = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DW; ++w) m_all = fmaxf(m_all, warp_m[w * 8 + h]);
+        float l_all = 0.0f;
+#pragma unroll
+        for (int w = 0; w < DW; ++w) {
+            const float mw = warp_m[w * 8 + h];
+            scale_w[i][w] = (mw == -INFINITY) ? 0.0f : exp2f(mw - m_all);
+            l_all += warp_l[w * 8 + h] * scale_w[i][w];
+        }
+        if (warp == 0 && g == 0) { cta_m[h] = m_all; cta_l[h] = l_all; }
+    }
+#pragma unroll
+    for (int k = 0; k < FRAGS_T / DW; ++k) {
+        const int idx = warp + k * DW;              // this thread merges fragment idx of all warps
+        const int kk = idx >> 2, e = idx & 3, i = e & 1, h = 2 * t + i;
+        const int dim = (2 * (kk >> 3) + (e >> 1)) * 64 + 8 * g + (kk & 7);
+        if (dim >= D || h >= heads) continue;
+        float val = 0.0f;
+#pragma unroll
+        for (int w = 0; w < DW; ++w) val += frag[(w * FRAGS_T + idx) * 32 + lane] * scale_w[i][w];
+        cta_o[h * D + dim] = val;
+    }
+    // across the cluster: CTA `rank` finishes the slice [rank, rank + 1) * D / splits of every head
+    cluster.sync();
+    const int slice = D / splits;
+    for (int i = threadIdx.x; i < heads * slice; i += DW * 32) {
+        const int r = i / slice, dim = rank * slice + i % slice;
+        float m_all = -INFINITY;
+        float ms[MAX_SPLITS];
+#pragma unroll
+        for (int s2 = 0; s2 < MAX_SPLITS; ++s2) {
+            ms[s2] = -INFINITY;
+            if (s2 < splits) ms[s2] = *cluster.map_shared_rank(cta_m + r, s2);
+            m_all = fmaxf(m_all, ms[s2]);
+        }
+        float acc = 0.0f, l_all = 0.0f;
+#pragma unroll
+        for (int s2 = 0; s2 < MAX_SPLITS; ++s2) {
+            if (s2 < splits && ms[s2] != -INFINITY) {
+                const float w = exp2f(ms[s2] - m_all);
+                acc += w * *cluster.map_shared_rank(cta_o + r * D + dim, s2);
+                l_all += w * *cluster.map_shared_rank(cta_l + r, s2);
+            }
+        }
+        const int head = geo.kvh * p.group + r;
+        p.out[((size_t)geo.token0 * p.num_heads + head) * D + dim] = __float2bfloat16_rn(l_all > 0.0f ? acc / l_all : 0.0f);
+    }
+    cluster.sync();                          // nobody leaves while its shared memory may still be read
+}
+
 }  // namespace
 
 // up to this many CTAs the decode shape runs eight warps per CTA (MLB_FA_WIDE_LIMIT overrides, for measurements)
@@ -806,6 +1075,13 @@ static int wide_limit() {
     static int limit = -1;
     if (limit < 0) { const char* e = getenv("MLB_FA_WIDE_LIMIT"); limit = e ? atoi(e) : 48; }
     return limit;
+}
+
+// MLB_FA_KEYS_ON_M=0 keeps groups of up to 8 heads on the kernel with queries on the 16-row side (for measurements)
+static bool keys_on_m_enabled() {
+    static int on = -1;
+    if (on < 0) { const char* e = getenv("MLB_FA_KEYS_ON_M"); on = (e && e[0] == '0') ? 0 : 1; }
+    return on == 1;
 }
 
 MLB_EXPORT int mlb_fa_head_dim() { return D; }
@@ -846,6 +1122,8 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
     }
     // a handful of CTAs (one or two sequences): eight warps each; otherwise four warps, two CTAs per SM
     const bool wide = (long long)num_work * num_kv_heads * splits <= wide_limit();
+    // groups of at most 8 heads: the kernel with keys on the 16-row side of the MMA (half the work per key)
+    const bool keys_on_m = p.group <= 8 && D % 64 == 0 && keys_on_m_enabled();
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(4));
@@ -853,6 +1131,10 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
             e = cudaFuncSetAttribute(fa_decode_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(8));
         if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_decode_kernel<4>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_decode_kernel<8>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_decode_t_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_t_smem(4));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_decode_t_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_t_smem(8));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_decode_t_kernel<4>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_decode_t_kernel<8>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "fa_decode: cannot reserve %d bytes of shared memory: %s",
                                           (int)decode_smem(8), cudaGetErrorString(e));
         configured = true;
@@ -860,7 +1142,7 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(num_work, num_kv_heads, splits);
     config.blockDim = dim3((wide ? 8 : 4) * 32);
-    config.dynamicSmemBytes = wide ? decode_smem(8) : decode_smem(4);
+    config.dynamicSmemBytes = keys_on_m ? (wide ? decode_t_smem(8) : decode_t_smem(4)) : (wide ? decode_smem(8) : decode_smem(4));
     config.stream = stream;
     cudaLaunchAttribute attributes[2];
     attributes[0].id = cudaLaunchAttributeClusterDimension;
@@ -879,11 +1161,16 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
             probe.numAttrs = 1;
             int n = 0;
             cudaError_t e = wide ? cudaOccupancyMaxActiveClusters(&n, fa_decode_kernel<8>, &probe)
-                                 : cudaOccupancyMaxActiveClusters(&n, fa_decode_kernel<4>, &probe);
+                                 : cudaOccupancyMaxActiveClusters(&n, fa_decode_kernel<4>, &probe);      // the larger of the two kernels
             clusters16 = (e == cudaSuccess) ? n : 0;
             cudaGetLastError();
         }
         if (clusters16 < 1) return fail(MLB_UNSUPPORTED_SIZE, "fa_decode: clusters of %d CTAs cannot be resident on this device", splits);
+    }
+    if (keys_on_m) {
+        if (wide) cudaLaunchKernelEx(&config, fa_decode_t_kernel<8>, p);
+        else cudaLaunchKernelEx(&config, fa_decode_t_kernel<4>, p);
+        return check_launch("fa_decode_t");
     }
     if (wide) cudaLaunchKernelEx(&config, fa_decode_kernel<8>, p);
     else cudaLaunchKernelEx(&config, fa_decode_kernel<4>, p);
