@@ -1123,7 +1123,7 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
     // a handful of CTAs (one or two sequences): eight warps each; otherwise four warps, two CTAs per SM
     const bool wide = (long long)num_work * num_kv_heads * splits <= wide_limit();
     // groups of at most 8 heads: the kernel with keys on the 16-row side of the MMA (half the work per key)
-    const bool keys_on_m = p.group <= 8 && D % 64 == 0 && keys_on_m_enabled();
+    const bool keys_on_m = p.group <= 8 && D % 64 == 0 && USE_PREFETCH && keys_on_m_enabled();   // two key tiles in registers
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(4));
