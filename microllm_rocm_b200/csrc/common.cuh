@@ -105,29 +105,9 @@ inline bool pdl_enabled() {
     return enabled == 1;
 }
 
-// One shared-memory carve-out for every kernel of the library.  Kernels that prefer different splits of the
-// SM's 256 KB between L1 and shared memory cannot be resident on an SM together, and a kernel whose CTAs
-// cannot become resident while its predecessor runs loses what programmatic dependent launch gives.
-// MLB_CARVEOUT (percent of shared memory, default: not set, the driver chooses per kernel).
-inline int carveout_percent() {
-    static int value = -2;
-    if (value == -2) { const char* e = getenv("MLB_CARVEOUT"); value = e ? atoi(e) : -1; }
-    return value;
-}
-inline void prefer_carveout(const void* kernel) {
-    const int percent = carveout_percent();
-    if (percent < 0) return;
-    static const void* seen[64];
-    static int n_seen = 0;
-    for (int i = 0; i < n_seen; ++i) if (seen[i] == kernel) return;
-    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, percent);
-    if (n_seen < 64) seen[n_seen++] = kernel;
-}
-
 template <typename... KArgs, typename... Args>
 inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                           Args&&... args) {
-    prefer_carveout((const void*)kernel);
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = block;
