@@ -93,6 +93,7 @@ struct SampleParams {
     const unsigned long long* seed;      // [rows]
     const unsigned long long* draw;      // [rows]   how many tokens this request has drawn so far
     int* out;                            // [rows]
+    int skip_greedy;                     // 1: greedy rows were already selected by argmax_split_kernel
 };
 
 __global__ void __launch_bounds__(THREADS) sample_rows_kernel(SampleParams p) {
@@ -109,6 +110,7 @@ __global__ void __launch_bounds__(THREADS) sample_rows_kernel(SampleParams p) {
     const int row = blockIdx.x, tid = threadIdx.x;
     const float* x = p.logits + (size_t)row * p.ld;
     const int V = p.vocab;
+    if (p.skip_greedy && ((p.temperature ? p.temperature[row] : 0.0f) == 0.0f || (p.top_k ? p.top_k[row] : 0) == 1)) return;
 
     // pass 1: maximum, its first index, finiteness
     if (tid == 0) { s_flag = 0; s_pick = 0x7fffffff; }
@@ -243,12 +245,95 @@ __global__ void __launch_bounds__(THREADS) argmax_rows_kernel(const float* __res
     if (tid == 0) out[row] = s_flag ? -1 : best_i;
 }
 
+// ------------------------------------------------------------------------------ greedy selection over a large vocabulary
+// One block per row reads 600 KB of logits alone; here a row is cut into `parts` slices, one block each.  Every
+// block leaves (maximum, first index, finiteness) of its slice; the block that arrives last at the row's ticket
+// merges them (largest value, smallest index on ties: the result does not depend on which block is last) and
+// resets the ticket.  The scratch is a file-scope device array: launches on different streams would share it.
+constexpr int SPLIT_THREADS = 256;
+constexpr int SPLIT_MAX_ROWS = 4096;
+constexpr int SPLIT_MAX_PARTS = 32;
+constexpr int SPLIT_MIN_VOCAB = 16384;
+constexpr int SPLIT_SLICE = 8192;
+
+__device__ float g_part_val[SPLIT_MAX_ROWS * SPLIT_MAX_PARTS];
+__device__ int g_part_idx[SPLIT_MAX_ROWS * SPLIT_MAX_PARTS];
+__device__ int g_part_bad[SPLIT_MAX_ROWS * SPLIT_MAX_PARTS];
+__device__ int g_tickets[SPLIT_MAX_ROWS];
+
+__global__ void __launch_bounds__(SPLIT_THREADS) argmax_split_kernel(const float* __restrict__ logits, long long ld, int vocab,
+                                                                     int parts, const float* __restrict__ temperature,
+                                                                     const int* __restrict__ top_k, int* __restrict__ out) {
+    pdl_prologue();
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    __shared__ int s_flag, s_last;
+    const int row = blockIdx.x, part = blockIdx.y, tid = threadIdx.x;
+    // with per-row settings, only greedy rows are selected here (the sampling kernel takes the others)
+    if (temperature && temperature[row] != 0.0f && !(top_k && top_k[row] == 1)) return;
+    const int per = (vocab + parts - 1) / parts;
+    const int begin = part * per, end = min(vocab, begin + per);
+    const float* x = logits + (size_t)row * ld;
+    if (tid == 0) s_flag = 0;
+    __syncthreads();
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    bool bad = false;
+    for (int i = begin + tid; i < end; i += SPLIT_THREADS) {
+        const float v = x[i];
+        if (!isfinite(v)) bad = true;
+        if (v > best) { best = v; best_i = i; }        // strided walk visits indices in increasing order
+    }
+    if (bad) atomicExch(&s_flag, 1);
+    block_argmax(best, best_i, s_val, s_idx);
+    __syncthreads();
+    if (tid == 0) {
+        const int slot = row * SPLIT_MAX_PARTS + part;
+        g_part_val[slot] = best; g_part_idx[slot] = best_i; g_part_bad[slot] = s_flag;
+        __threadfence();
+        s_last = atomicAdd(&g_tickets[row], 1) == parts - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_last || tid >= 32) return;
+    __threadfence();
+    float v = -INFINITY;
+    int idx = 0x7fffffff, any_bad = 0;
+    if (tid < parts) {
+        const int slot = row * SPLIT_MAX_PARTS + tid;
+        v = __ldcg(&g_part_val[slot]); idx = __ldcg(&g_part_idx[slot]); any_bad = __ldcg(&g_part_bad[slot]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        any_bad |= __shfl_xor_sync(0xffffffffu, any_bad, o);
+        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+    if (tid == 0) {
+        out[row] = any_bad ? -1 : idx;
+        g_tickets[row] = 0;
+    }
+}
+
+int split_parts(int rows, int vocab) {
+    if (vocab < SPLIT_MIN_VOCAB || rows > SPLIT_MAX_ROWS) return 0;
+    int parts = vocab / SPLIT_SLICE;
+    if (parts > SPLIT_MAX_PARTS) parts = SPLIT_MAX_PARTS;
+    return parts < 2 ? 0 : parts;
+}
+
 }  // namespace
 
 MLB_EXPORT int mlb_argmax_rows(const float* logits, long long ld, int rows, int vocab, int* out,
                                cudaStream_t stream) {
     if (rows < 0 || vocab <= 0 || ld < vocab) return fail(MLB_INVALID_ARGUMENT, "argmax_rows: bad sizes");
     if (rows == 0) return MLB_OK;
+    const int parts = split_parts(rows, vocab);
+    if (parts) {
+        launch_kernel(argmax_split_kernel, dim3(rows, parts), SPLIT_THREADS, 0, stream, logits, ld, vocab, parts,
+                      (const float*)nullptr, (const int*)nullptr, out);
+        return check_launch("argmax_split");
+    }
     launch_kernel(argmax_rows_kernel, rows, THREADS, 0, stream, logits, ld, vocab, out);
     return check_launch("argmax_rows");
 }
@@ -259,7 +344,15 @@ MLB_EXPORT int mlb_sample_rows(const float* logits, long long ld, int rows, int 
     if (rows < 0 || vocab <= 0 || ld < vocab) return fail(MLB_INVALID_ARGUMENT, "sample_rows: bad sizes");
     if (!seed || !draw) return fail(MLB_INVALID_ARGUMENT, "sample_rows: seed and draw arrays are required");
     if (rows == 0) return MLB_OK;
-    SampleParams p{logits, ld, vocab, temperature, top_k, seed, draw, out};
+    SampleParams p{logits, ld, vocab, temperature, top_k, seed, draw, out, 0};
+    const int parts = split_parts(rows, vocab);
+    if (parts && temperature) {
+        // greedy rows by many blocks per row; the rows that sample by the one-block-per-row kernel, which then skips the others
+        launch_kernel(argmax_split_kernel, dim3(rows, parts), SPLIT_THREADS, 0, stream, logits, ld, vocab, parts, temperature, top_k, out);
+        int status = check_launch("argmax_split");
+        if (status != MLB_OK) return status;
+        p.skip_greedy = 1;
+    }
     launch_kernel(sample_rows_kernel, rows, THREADS, 0, stream, p);
     return check_launch("sample_rows");
 }

@@ -356,15 +356,22 @@ def test_rope_kv_write_refuses_to_write_without_a_page():
 
 
 # ------------------------------------------------------------------------------ selection
-def test_argmax_ties_and_non_finite():
-    x = torch.randn(5, 1003)
-    x[0, 7] = x[0, 500] = 50.0                         # tie: the smaller index wins
-    x[1, 1002] = 60.0                                  # last element
-    x[2, 10] = float("nan")
+@pytest.mark.parametrize("vocab", [1003, 151936, 20000])
+def test_argmax_ties_and_non_finite(vocab):
+    """Small vocabularies go through one block per row, large ones through several blocks per row that
+    meet at a ticket: ties across slices, the very last element, and non-finite values far from the maximum."""
+    torch.manual_seed(vocab)
+    x = torch.randn(7, vocab)
+    x[0, 7] = x[0, vocab - 500] = 50.0                 # tie, possibly in different slices: the smaller index wins
+    x[1, vocab - 1] = 60.0                             # last element
+    x[2, vocab // 2 + 10] = float("nan")
     x[3, 0] = float("inf")
-    out = torch.empty(5, dtype=torch.int32, device=DEV)
-    ops().argmax_rows(x.to(DEV), out)
-    assert out.tolist() == [7, 1002, -1, -1, int(x[4].argmax())]
+    x[5, vocab - 3] = float("-inf")                    # not finite, though far from the maximum
+    x[6, 9000 % vocab] = x[6, 8191 % vocab] = x[6, 8192 % vocab] = 70.0    # ties on both sides of a slice edge
+    out = torch.full((7,), -7, dtype=torch.int32, device=DEV)
+    for _ in range(3):                                 # the tickets must be left ready for the next launch
+        ops().argmax_rows(x.to(DEV), out)
+        assert out.tolist() == [7, vocab - 1, -1, -1, int(x[4].argmax()), -1, min(9000 % vocab, 8191 % vocab, 8192 % vocab)]
 
 
 @pytest.mark.parametrize("vocab", [97, 1003, 40000])
