@@ -84,7 +84,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 __device__ __forceinline__ uint4 load16(const __nv_bfloat16* p) {
-    return __ldg(reinterpret_cast<const uint4*>(p));
+    // keys and values are read once per step: they need no line in L1
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
 }
 
 struct RowState {
