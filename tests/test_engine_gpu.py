@@ -87,6 +87,23 @@ def test_prompts_of_hundreds_of_tokens_reach_the_tensor_memory_kernels(tmp_path_
         assert "gemm_tc2.cu" in loaded
 
 
+@pytest.mark.parametrize("page_size", [16, 64, 128])
+def test_head_size_128_with_six_heads_per_kv_head(tmp_path_factory, page_size):
+    """Configuration d has the benchmark model's head geometry (head size 128, six query heads on one kv head):
+    the tcgen05 attention kernel and the keys-on-M decode kernel at the sizes they are compiled for in the
+    benchmark, over pages of 16, 64 and 128 tokens, against the plain implementation."""
+    folder = make_folder(tmp_path_factory, "d", "float32")
+    vocab = tiny_config("d").vocab_size
+    reqs = {f"d{i}": random_tokens(n, vocab, 17 * i + n) for i, n in enumerate([330, 129, 64])}
+    engine = engine_for(folder, "bfloat16", max_tokens=2048, page_size=page_size)
+    got = collect(engine, steps_prefill_then_decode(reqs, tail=24))
+    compare_with_plain(got, folder, reqs, "bfloat16")
+    steps, peak = steps_mixed(reqs, max_live=3, seed=9, decode_tail=5)
+    live = sum(-(-len(t) // page_size) * page_size for t in reqs.values())       # all three may be live at once
+    engine = engine_for(folder, "bfloat16", max_tokens=live, page_size=page_size)
+    compare_with_plain(collect(engine, steps), folder, reqs, "bfloat16")
+
+
 @pytest.mark.parametrize("key", ["a", "b"])
 def test_fp32_is_bit_stable_across_cuts(folders, key):
     """In the fp32 path every summation order is fixed by the token's own position, so the
