@@ -104,6 +104,40 @@ def test_head_size_128_with_six_heads_per_kv_head(tmp_path_factory, page_size):
     compare_with_plain(collect(engine, steps), folder, reqs, "bfloat16")
 
 
+def test_benchmark_shape_bf16_tracks_the_true_fp32_path():
+    """The Qwen2.5-1.5B shape with random weights (28 layers, the kernels and tile sizes the benchmark runs):
+    a prompt portion of 304 tokens beside one of 100, then a decode token beside a portion, then decode
+    steps.  No plain implementation at this size; the bf16 path is held against the engine's own true fp32
+    path.  bf16 rounds at about six places per layer to 2^-8 relative: over 28 layers the logits' relative
+    L2 distance is expected near 0.4 % * sqrt(170) = 5 %, measured 2.3-3.4 %; a wrong tile, a dropped key
+    range or a misplaced head shows as tens of percent."""
+    from microllm_rocm_b200.config import preset
+    from microllm_rocm_b200.engine.loading import random_engine
+    from microllm_rocm_b200.engine.step import StepEntry
+    cfg = preset("qwen2.5-1.5b")
+    gen = torch.Generator().manual_seed(1)
+    a = torch.randint(0, cfg.vocab_size, (310,), generator=gen).tolist()
+    b = torch.randint(0, cfg.vocab_size, (140,), generator=gen).tolist()
+
+    def run(dtype):
+        engine = random_engine(cfg, seed=0, dtype=dtype, page_size=64, max_tokens=1024, max_requests=4, draw_on_device=True)
+        engine.cache.add("a")
+        engine.cache.add("b")
+        outs = [engine.step([StepEntry("a", a[:304], [301, 302, 303]), StepEntry("b", b[:100], [99])]),
+                engine.step([StepEntry("a", a[304:305], [0]), StepEntry("b", b[100:135], [34])])]
+        for i in range(5):
+            outs.append(engine.step([StepEntry("a", a[305 + i:306 + i], [0]), StepEntry("b", b[135 + i:136 + i], [0])]))
+        engine.check_device_errors()
+        return torch.cat([o.float().cpu() for o in outs])
+
+    want = run("float32")
+    torch.cuda.empty_cache()
+    got = run("bfloat16")
+    assert torch.isfinite(got).all() and got.shape == want.shape == (16, cfg.vocab_size)
+    distance = (got - want).norm(dim=1) / want.norm(dim=1)
+    assert float(distance.max()) < 0.08, distance.tolist()
+
+
 @pytest.mark.parametrize("key", ["a", "b"])
 def test_fp32_is_bit_stable_across_cuts(folders, key):
     """In the fp32 path every summation order is fixed by the token's own position, so the
