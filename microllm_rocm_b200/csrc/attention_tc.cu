@@ -6,18 +6,20 @@
 // lo..hi that any of them may see in tiles of 128 keys, whose edges sit at multiples of 128
 // of the absolute position.  Six warps:
 //     warp 0     TMA producer.  The Q tile once; then the K and V tiles in the order the tensor
-//                core needs them (K0 K1 V0 K2 V1 ...) into one ring of five 32 KB slots, so that
-//                loads run two to three key tiles ahead.  Lane g looks up page g of a tile in
+//                core needs them (K0 K1 V0 K2 V1 ...) into one ring of 32 KB slots (six at head
+//                size 128), so that loads run two to three key tiles ahead.  Lane g looks up page g of a tile in
 //                the block table (one tile ahead of use) and issues that page's
 //                cp.async.bulk.tensor copies, one per 64-element column span, 128-byte swizzled.
 //     warp 1     one thread issues tcgen05.mma (kind::f16, bf16 in, fp32 in tensor memory):
-//                S = Q K^T into one of two score buffers, O += P V into the output accumulator.
+//                S = Q K^T into one of two score buffers, O += P V into the output accumulator,
+//                with P read from tensor memory (the A operand may live there) and V from the ring.
 //                S of tile j+1 is issued before P V of tile j, so the tensor pipe works on
 //                the next scores while the softmax warps turn the current ones into P.
 //     warps 2-5  softmax, one thread per query row: tcgen05.ld brings the row's 128 scores,
 //                mask (only in tiles that touch the causal or window edge), running maximum and
-//                sum in fp32 with base-2 exponentials, P rounded to bf16 into shared memory in
-//                the swizzled operand layout.  The accumulator in tensor memory is rescaled
+//                sum in fp32 with base-2 exponentials, P rounded to bf16 and written back to
+//                tensor memory (tcgen05.st, two buffers, two keys per column): it never touches
+//                shared memory.  The accumulator in tensor memory is rescaled
 //                only when a row's maximum has grown by more than 2^8 since the last rescale:
 //                P and the row sum use the same (stale) reference, so the quotient is exact.
 //                V rows of keys that no row of the tile may see are cleared in shared memory, so
@@ -48,16 +50,17 @@ static_assert(D == 64 || D == 128, "HEAD_DIM must be 64 or 128");
 constexpr int BM = 128;                      // query rows per CTA (MMA M)
 constexpr int BN = 128;                      // keys per tile
 constexpr int SPANS = D / 64;                // 64-element (128-byte) column spans of a Q/K/V row
-constexpr int KEY_SPANS = BN / 64;           // the same for a row of P
 constexpr int ROW_BYTES = 128;               // one swizzle span
 constexpr int Q_BYTES = SPANS * BM * ROW_BYTES;
 constexpr int KV_BYTES = SPANS * BN * ROW_BYTES;
-constexpr int P_BYTES = KEY_SPANS * BM * ROW_BYTES;
-constexpr int SLOTS = (226 * 1024 - 1024 - Q_BYTES - P_BYTES) / KV_BYTES > 8 ? 8 : (226 * 1024 - 1024 - Q_BYTES - P_BYTES) / KV_BYTES;
-constexpr int SMEM_BYTES = Q_BYTES + SLOTS * KV_BYTES + P_BYTES + 1024;
+constexpr int RING_BUDGET = 226 * 1024 - 1024 - Q_BYTES;
+constexpr int SLOTS = RING_BUDGET / KV_BYTES > 8 ? 8 : RING_BUDGET / KV_BYTES;
+constexpr int SMEM_BYTES = Q_BYTES + SLOTS * KV_BYTES + 1024;
 constexpr int THREADS = 192;
-constexpr int TMEM_COLS = 512;               // S0 [0,128)  S1 [128,256)  O [256, 256+D)
+constexpr int TMEM_COLS = 512;               // S0 [0,128)  S1 [128,256)  O [256, 256+D)  P0 [384,448)  P1 [448,512)
 constexpr int O_COL = 2 * BN;
+constexpr int P_COL = 384;                   // P as bf16 pairs: 64 columns per buffer, two buffers
+static_assert(O_COL + D <= P_COL, "the accumulator must end before the P buffers");
 constexpr int SPIN_LIMIT = 1 << 21;          // polls of up to 2 us each
 constexpr int MAX_PAGES_PER_TILE = 16;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -144,6 +147,12 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, ui
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(a), "l"(b), "r"(id), "r"(accumulate) : "memory");
 }
+// the same with the A operand in tensor memory (lane = row, a 32-bit column = two neighbouring bf16 of the contraction)
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t id, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(id), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -184,7 +193,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, TcParams p) {
     pdl_launch_dependents();
     extern __shared__ unsigned char smem_dyn[];
-    __shared__ __align__(8) unsigned long long q_full, slot_full[SLOTS], slot_empty[SLOTS], s_full[2], s_empty[2], p_full, pv_done;
+    __shared__ __align__(8) unsigned long long q_full, slot_full[SLOTS], slot_empty[SLOTS], s_full[2], s_empty[2], p_full, pv_done[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int failed_s;
 
@@ -192,7 +201,6 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;     // the swizzle pattern wants 1024-byte alignment
     const uint32_t q_s = base;
     const uint32_t ring_s = q_s + Q_BYTES;
-    const uint32_t p_s = ring_s + SLOTS * KV_BYTES;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&q_full), 1);
@@ -205,7 +213,8 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             mbar_init(smem_u32(&s_empty[s]), 4);          // one arrival per softmax warp
         }
         mbar_init(smem_u32(&p_full), 4);
-        mbar_init(smem_u32(&pv_done), 1);
+        mbar_init(smem_u32(&pv_done[0]), 1);        // P V of the even tiles, and of the odd ones: one per P buffer
+        mbar_init(smem_u32(&pv_done[1]), 1);
         failed_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -332,13 +341,11 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 const uint32_t vb = ring_s + slot * KV_BYTES;
                 if (elect_one()) {
 #pragma unroll
-                    for (int ks = 0; ks < BN / 16; ++ks) {
-                        const uint32_t a_off = (ks / 4) * (BM * ROW_BYTES) + (ks % 4) * 32;
-                        umma(tmem_base + O_COL, desc_k_major(p_s + a_off), desc_mn_major(vb + ks * 16 * ROW_BYTES, BN * ROW_BYTES),
-                             idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                    }
+                    for (int ks = 0; ks < BN / 16; ++ks)          // 16 keys = 8 columns of P
+                        umma_ts(tmem_base + O_COL, tmem_base + (uint32_t)(P_COL + (j & 1) * (BN / 2) + ks * 8),
+                                desc_mn_major(vb + ks * 16 * ROW_BYTES, BN * ROW_BYTES), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                     umma_commit(smem_u32(&slot_empty[slot]));
-                    umma_commit(smem_u32(&pv_done));
+                    umma_commit(smem_u32(&pv_done[j & 1]));
                 }
                 __syncwarp();
                 ++item;
@@ -396,11 +403,9 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             const float m_new = fmaxf(m_used, mx * p.scale_log2);
             const bool grow = m_new > m_used + RESCALE_STEP;          // also true for the first finite maximum
             const float alpha = grow ? (m_used == -INFINITY ? 0.0f : fast_exp2(m_used - m_new)) : 1.0f;
-            bool waited = false;
             if (j > 0 && __any_sync(0xffffffffu, grow)) {
-                ok = wait_all(&pv_done, (j - 1) & 1, 29);      // O holds tiles 0..j-1
+                ok = wait_all(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, 29);      // O holds tiles 0..j-1
                 if (!ok) break;
-                waited = true;
                 tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < D / 32; ++c) {
@@ -427,8 +432,8 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             }
             const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             l += sum;
-            if (j > 0 && !waited) {                       // the P buffer is free once P V of the tile before is done
-                ok = wait_all(&pv_done, (j - 1) & 1, 30);
+            if (j > 1) {                                  // this P buffer is free once P V of the tile before the last is done
+                ok = wait_all(&pv_done[j & 1], ((j - 2) >> 1) & 1, 30);
                 if (!ok) break;
             }
             // Keys outside lo..hi of the whole tile have P = 0, but 0 * V must not be NaN whatever an unused
@@ -447,20 +452,17 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
                 }
             }
-            // row r of P: 16-byte chunk c of a 128-byte span lands at chunk c ^ (r % 8)
+            // row r of P goes to tensor memory, where the second product reads it as its A operand
+            // (lane = row, a column = two neighbouring keys as bf16): no shared memory, no swizzle, no proxy fence
 #pragma unroll
-            for (int c = 0; c < BN / 8; ++c) {
-                const uint32_t addr = p_s + (c / 8) * (BM * ROW_BYTES) + r * ROW_BYTES + (((c % 8) ^ (r & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                             ::"r"(addr), "r"(packed[4 * c]), "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3])
-                             : "memory");
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            for (int c = 0; c < BN / 64; ++c) tmem_st32(lane_base + (uint32_t)(P_COL + buf * (BN / 2) + c * 32), packed + c * 32);
+            tmem_wait_st();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the cleared V rows, for the tensor core
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&p_full));
         }
-        if (ok && n_tiles > 0) ok = wait_all(&pv_done, (n_tiles - 1) & 1, 31);
+        if (ok && n_tiles > 0) ok = wait_all(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, 31);
         if (ok && n_tiles > 0) {
             tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
