@@ -54,7 +54,10 @@ def sources():
 
 
 # ------------------------------------------------------------------------------ few tokens: weight streaming
-GEMV_MAX_TOKENS = 16
+GEMV_MAX_TOKENS = 16                  # what the weight-streaming kernels can take
+# ...and up to where the engine sends them: from 9 tokens on (a second 8-token column block per fragment) the
+# library's product with separate rotation / activation kernels is faster (1.63 ms against 1.88 for a batch-9 step)
+GEMV_ROUTE_MAX_TOKENS = int(os.environ.get("MLB_GEMV_ROUTE_MAX_TOKENS", "8"))
 GEMV_TARGET_CTAS = SM_COUNT * 4
 GEMV_MIN_K_PER_SPLIT = 256
 
@@ -93,6 +96,11 @@ def gemv_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
 
 GEMV_SILU_MAX_TOKENS = 8            # beyond one 8-token column block the fused gate/up kernel loses to partial sums + activation
 GEMV_FUSED_MAX_K = 6144             # the activations of 16 tokens over the whole K must fit shared memory
+
+
+def gemv_preferred(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """The weight-streaming kernels can take this product and are the faster way for it."""
+    return x.shape[0] <= GEMV_ROUTE_MAX_TOKENS and gemv_supported(x, weight)
 
 
 def gemv_fused_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -287,7 +295,7 @@ PAIR_MIN_TOKENS = 256                       # from here on the fused gate/up + a
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
                 out: Optional[torch.Tensor], partials_ok: bool = False) -> torch.Tensor:
     m = x.shape[0]
-    if partials_ok and out is None and out_dtype == torch.float32 and gemv_supported(x, weight):
+    if partials_ok and out is None and out_dtype == torch.float32 and gemv_preferred(x, weight):
         return gemv_partials(x, weight, bias)
     lo, hi = TENSOR_CORE_KERNEL_TOKENS
     if lo <= m < hi and supported(x, weight):

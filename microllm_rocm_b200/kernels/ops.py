@@ -26,7 +26,15 @@ def dtype_tag(t: torch.Tensor) -> int:
         raise KernelError(f"unsupported tensor dtype {t.dtype}") from None
 
 
+# The current stream's handle straight from the runtime's binding: the Stream object that
+# torch.cuda.current_stream() builds costs more host time than a short kernel runs.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_current_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
+    if _raw_stream is not None and _current_device is not None:
+        return _raw_stream(_current_device())
     return torch.cuda.current_stream().cuda_stream
 
 

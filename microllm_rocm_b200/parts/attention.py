@@ -78,7 +78,8 @@ class Attention(Mixer):
         inv_freq, rot, inter = ((self.rotary.inv_freq, self.rotary.rotary_dim, self.rotary.interleaved)
                                 if self.rotary is not None else (self._no_rot, 0, False))
         pages = cache.pages if cache.writable else None
-        if (x.dtype == torch.bfloat16 and gemm_bf16.gemv_fused_supported(x, self.w_qkv) and self.d % 16 == 0
+        if (x.dtype == torch.bfloat16 and gemm_bf16.gemv_preferred(x, self.w_qkv)
+                and gemm_bf16.gemv_fused_supported(x, self.w_qkv) and self.d % 16 == 0
                 and (rot == 0 or (rot == self.d and not inter))):
             # a few tokens: projection, bias, rotation and the cache store in one weight-streaming kernel
             gemm_bf16.gemv_qkv_rope(x, self.w_qkv, self.b_qkv, ctx.positions, ctx.token_seq, cache.block_table,

@@ -38,7 +38,7 @@ class SwiGLU(FeedForward):
         if x.dtype == torch.bfloat16 and x.shape[0] <= gemm_bf16.GEMV_SILU_MAX_TOKENS and gemm_bf16.gemv_fused_supported(x, self.w_gate_up):
             # a few tokens: one weight-streaming kernel, the activation is its epilogue
             gemm_bf16.gemv_silu_mul(x, self.w_gate_up, act)
-        elif x.dtype == torch.bfloat16 and gemm_bf16.gemv_supported(x, self.w_gate_up):
+        elif x.dtype == torch.bfloat16 and gemm_bf16.gemv_preferred(x, self.w_gate_up):
             # more tokens, or a width too large for that kernel: fp32 partial sums, the activation adds them
             ops.silu_mul(gemm_bf16.gemv_partials(x, self.w_gate_up), act)
         elif x.dtype == torch.bfloat16 and x.shape[0] >= gemm_bf16.PAIR_MIN_TOKENS and gemm_bf16.supported(x, self.w_gate_up):
