@@ -34,6 +34,11 @@ ops.register_signatures("gemv_fused.cu", {
                           c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                           c_void_p],
 })
+ops.register_signatures("gemm_lib.cu", {
+    "mlb_lt_available": [],
+    "mlb_lt_matmul": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
+                      c_void_p, c_longlong, c_void_p],
+})
 ops.register_signatures("gemm_tc2.cu", {
     "mlb_gemm_pair": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int,
                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
@@ -49,8 +54,14 @@ _tickets = {}
 _error_flags = {}
 
 
+USE_DIRECT_LIBRARY = os.environ.get("MLB_DIRECT_CUBLASLT", "1") != "0"
+LIBRARY_WORKSPACE_BYTES = 32 << 20
+_workspaces = {}
+_direct_ok = None
+
+
 def sources():
-    return [("gemm_tc.cu", {}), ("gemm_tc2.cu", {}), ("gemv_bf16.cu", {}), ("gemv_fused.cu", {})]
+    return [("gemm_tc.cu", {}), ("gemm_tc2.cu", {}), ("gemv_bf16.cu", {}), ("gemv_fused.cu", {}), ("gemm_lib.cu", {})]
 
 
 # ------------------------------------------------------------------------------ few tokens: weight streaming
@@ -269,10 +280,34 @@ def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Op
                                    int(sm_count), flag.data_ptr(), ops._stream()))
 
 
+def _direct_library(device) -> bool:
+    """Whether cuBLASLt can be called without the tensor framework in between (csrc/gemm_lib.cu)."""
+    global _direct_ok
+    if _direct_ok is None:
+        _direct_ok = bool(USE_DIRECT_LIBRARY and ops.lib("gemm_lib.cu").mlb_lt_available())
+    return _direct_ok
+
+
 def library_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
-                   out: Optional[torch.Tensor]) -> torch.Tensor:
-    """cuBLASLt: bf16 operands, fp32 accumulate, output written in out_dtype."""
+                   out: Optional[torch.Tensor], alloc=None) -> torch.Tensor:
+    """cuBLASLt: bf16 operands, fp32 accumulate, output written in out_dtype.  `alloc(shape, dtype)` supplies
+    the output when `out` is not given (default: a new tensor)."""
     LaunchCounter.library += 1
+    if (bias is None and x.is_cuda and x.stride(1) == 1 and weight.stride(1) == 1 and x.shape[0] > 0
+            and (out is None or (out.dtype == out_dtype and out.stride(1) == 1)) and _direct_library(x.device)):
+        M, K = x.shape
+        N = weight.shape[0]
+        if out is None:
+            out = alloc((M, N), out_dtype) if alloc is not None else torch.empty((M, N), dtype=out_dtype, device=x.device)
+        key = str(x.device)
+        work = _workspaces.get(key)
+        if work is None:
+            work = _workspaces[key] = torch.empty(LIBRARY_WORKSPACE_BYTES, dtype=torch.uint8, device=x.device)
+        L = ops.lib("gemm_lib.cu")
+        build.check(L, L.mlb_lt_matmul(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), out.data_ptr(),
+                                       out.stride(0), 1 if out_dtype == torch.bfloat16 else 0, 0, M, N, K,
+                                       work.data_ptr(), LIBRARY_WORKSPACE_BYTES, ops._stream()))
+        return out
     if out_dtype == torch.bfloat16:
         y = torch.mm(x, weight.t()) if out is None else torch.mm(x, weight.t(), out=out)
     else:
@@ -293,7 +328,7 @@ PAIR_MIN_TOKENS = 256                       # from here on the fused gate/up + a
 
 
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
-                out: Optional[torch.Tensor], partials_ok: bool = False) -> torch.Tensor:
+                out: Optional[torch.Tensor], partials_ok: bool = False, alloc=None) -> torch.Tensor:
     m = x.shape[0]
     if partials_ok and out is None and out_dtype == torch.float32 and gemv_preferred(x, weight):
         return gemv_partials(x, weight, bias)
@@ -303,4 +338,4 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
             out = torch.empty((m, weight.shape[0]), dtype=out_dtype, device=x.device)
         gemm_tc(x, weight, out, bias=bias)
         return out
-    return library_linear(x, weight, bias, out_dtype, out)
+    return library_linear(x, weight, bias, out_dtype, out, alloc)

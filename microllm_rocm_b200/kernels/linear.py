@@ -19,10 +19,11 @@ from .build import KernelError
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: torch.dtype = torch.float32, out: Optional[torch.Tensor] = None,
-           partials_ok: bool = False) -> torch.Tensor:
+           partials_ok: bool = False, alloc=None) -> torch.Tensor:
     """x [M,K] and weight [N,K] in the same dtype (f32 or bf16); returns [M,N] in `out_dtype`.
     With partials_ok the caller accepts [S, M, N] fp32 partial results instead (a product whose
-    K range was split over CTAs) and adds them up itself, in order, where it reads them."""
+    K range was split over CTAs) and adds them up itself, in order, where it reads them.
+    `alloc(shape, dtype)`: where a plain [M,N] result comes from when `out` is not given (a step's scratch)."""
     if x.dtype != weight.dtype:
         raise KernelError(f"linear: activations are {x.dtype} but the weight is {weight.dtype}")
     M, N = x.shape[0], weight.shape[0]
@@ -30,7 +31,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         if out_dtype != torch.float32:
             raise KernelError("linear: the fp32 path produces fp32")
         if out is None:
-            out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+            out = alloc((M, N), torch.float32) if alloc is not None else torch.empty((M, N), dtype=torch.float32, device=x.device)
         ops.gemm_f32(x, weight, out, bias=bias)
         return out
     if x.dtype != torch.bfloat16:
@@ -38,4 +39,4 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if not x.is_cuda:
         raise KernelError("linear: there is no CPU path")
     from . import gemm_bf16
-    return gemm_bf16.linear_bf16(x, weight, bias, out_dtype, out, partials_ok=partials_ok)
+    return gemm_bf16.linear_bf16(x, weight, bias, out_dtype, out, partials_ok=partials_ok, alloc=alloc)

@@ -74,7 +74,7 @@ class Attention(Mixer):
     # --- compute ------------------------------------------------------------------------
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVView) -> torch.Tensor:
         T = x.shape[0]
-        q = torch.empty((T, self.nh * self.d), dtype=self.rt.dtype, device=x.device)
+        q = ctx.buffer("attention.q", (T, self.nh * self.d), self.rt.dtype)
         inv_freq, rot, inter = ((self.rotary.inv_freq, self.rotary.rotary_dim, self.rotary.interleaved)
                                 if self.rotary is not None else (self._no_rot, 0, False))
         pages = cache.pages if cache.writable else None
@@ -85,7 +85,8 @@ class Attention(Mixer):
             gemm_bf16.gemv_qkv_rope(x, self.w_qkv, self.b_qkv, ctx.positions, ctx.token_seq, cache.block_table,
                                     inv_freq if rot else None, q, pages, self.nh, self.nkv, self.d, ctx.error_flag)
         else:
-            qkv = linear(x, self.w_qkv, None, torch.float32, partials_ok=True)  # [T, (NH+2NKV)*D] f32, or its partial sums
+            qkv = linear(x, self.w_qkv, None, torch.float32, partials_ok=True,    # [T, (NH+2NKV)*D] f32, or its partial sums
+                         alloc=lambda shape, dtype: ctx.buffer("attention.qkv", shape, dtype))
             cos_sin = None
             if rot and T >= ROPE_TABLE_MIN_TOKENS and x.dtype == torch.bfloat16:
                 # a prompt portion: the step's sines and cosines are made once and serve every layer and head
@@ -95,7 +96,7 @@ class Attention(Mixer):
                     cos_sin = ctx.extras[key] = ops.rope_table(ctx.positions, inv_freq)
             ops.rope_kv_write(qkv, self.b_qkv, ctx.positions, ctx.token_seq, cache.block_table, inv_freq, rot, inter,
                               q, pages, self.nh, self.nkv, self.d, ctx.error_flag, cos_sin)
-        o = torch.empty_like(q)
+        o = ctx.buffer("attention.o", (T, self.nh * self.d), self.rt.dtype)
         attention_kernels.paged_attention(q, cache.pages, o, ctx, cache.block_table, self.nh, self.nkv, self.d,
                                           self.scale, self.window)
         return linear(o, self.w_o, self.b_o, torch.float32, partials_ok=True)  # [T, H] f32, or its partial sums

@@ -116,6 +116,25 @@ class StepContext:
     def decode_only(self) -> bool:
         return self.max_new_tokens == 1
 
+    def buffer(self, role: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """Scratch of this step for one role ("attention.q", "block.normed", ...): the same tensor every time
+        the role, shape and dtype come back, so the layers of a model share it (each is done with it before the
+        next one writes) and a step costs one allocation per role instead of one per layer.  A part names its
+        roles after itself, and may only ask for a buffer whose content nobody reads after the part has returned
+        and the next part has consumed what it returned."""
+        key = (role, shape, dtype)
+        t = self.extras.get(key)
+        if t is None:
+            t = self.extras[key] = torch.empty(shape, dtype=dtype, device=self.token_ids.device)
+        return t
+
+
+def scratch(ctx: Optional[StepContext], role: str, shape: Tuple[int, ...], dtype: torch.dtype, device) -> torch.Tensor:
+    """ctx.buffer(...), or a fresh tensor for a part that is run without a step around it."""
+    if ctx is None:
+        return torch.empty(shape, dtype=dtype, device=device)
+    return ctx.buffer(role, shape, dtype)
+
 
 # ----------------------------------------------------------------------------- part kinds
 class Part:

@@ -19,12 +19,12 @@ class PreNormResidualBlock(Block):
         self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward = mixer_norm, mixer, ffn_norm, feed_forward
 
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext, cache):
-        normed = torch.empty(residual.shape, dtype=self.rt.dtype, device=residual.device)
+        normed = ctx.buffer("block.normed", tuple(residual.shape), self.rt.dtype)
         if delta is None:
             self.mixer_norm.forward(residual, normed)
         else:
             self.mixer_norm.add_forward(residual, delta, normed)
         mixed = self.mixer.forward(normed, ctx, cache)
-        normed2 = torch.empty_like(normed)
+        normed2 = ctx.buffer("block.normed2", tuple(residual.shape), self.rt.dtype)
         self.ffn_norm.add_forward(residual, mixed, normed2)
         return residual, self.feed_forward.forward(normed2, ctx)

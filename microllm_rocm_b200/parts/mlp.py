@@ -9,7 +9,7 @@ import torch
 
 from ..kernels import gemm_bf16, ops
 from ..kernels.linear import linear
-from .base import FeedForward, Runtime, StepContext, WeightSpec, register_feed_forward
+from .base import FeedForward, Runtime, StepContext, WeightSpec, register_feed_forward, scratch
 
 
 @register_feed_forward("swiglu")
@@ -34,7 +34,7 @@ class SwiGLU(FeedForward):
         # fp32 path: everything f32.  bf16 path: gate/up leave the product as bf16, the
         # activation is evaluated in fp32 and stored bf16, down returns fp32 at the residual
         # boundary -- the reference's policy for its bf16 feed-forward (src/ops/optimized.cpp:676-683).
-        act = torch.empty((x.shape[0], self.inter), dtype=self.rt.dtype, device=x.device)
+        act = scratch(ctx, "swiglu.act", (x.shape[0], self.inter), self.rt.dtype, x.device)
         if x.dtype == torch.bfloat16 and x.shape[0] <= gemm_bf16.GEMV_SILU_MAX_TOKENS and gemm_bf16.gemv_fused_supported(x, self.w_gate_up):
             # a few tokens: one weight-streaming kernel, the activation is its epilogue
             gemm_bf16.gemv_silu_mul(x, self.w_gate_up, act)
@@ -45,6 +45,7 @@ class SwiGLU(FeedForward):
             # a prompt portion: the CTA-pair tcgen05 product with the activation in its epilogue
             gemm_bf16.gemm_pair(x, self.w_gate_up, act, dual_rows=self.inter)
         else:
-            gate_up = linear(x, self.w_gate_up, None, self.rt.dtype)
+            gate_up = linear(x, self.w_gate_up, None, self.rt.dtype,
+                             alloc=lambda shape, dtype: scratch(ctx, "swiglu.gate_up", shape, dtype, x.device))
             ops.silu_mul(gate_up, act)
         return linear(act, self.w_down, None, torch.float32, partials_ok=True)

@@ -504,6 +504,27 @@ def test_cta_pair_dual_product_silu_mul(M, I, K):
     assert int(gemm_bf16.error_flag(torch.device(DEV)).item()) == 0
 
 
+@pytest.mark.parametrize("M,N,K,out_dtype", [(2048, 1536, 8960, torch.float32), (300, 520, 136, torch.bfloat16),
+                                             (17, 2048, 1536, torch.float32), (1, 72, 40, torch.float32),
+                                             (700, 17920, 1536, torch.bfloat16)])
+def test_library_product_called_directly(M, N, K, out_dtype):
+    """cuBLASLt through the package's own C entry point (no tensor framework in between): against fp32,
+    into a given output with a row pitch of its own, and the same bits as a second call."""
+    from microllm_rocm_b200.kernels import gemm_bf16
+    torch.manual_seed(M + N)
+    x, w = (torch.randn(M, K) * 0.5).bfloat16().to(DEV), (torch.randn(N, K) * 0.5).bfloat16().to(DEV)
+    assert gemm_bf16._direct_library(torch.device(DEV))
+    before = gemm_bf16.LaunchCounter.library
+    y = gemm_bf16.library_linear(x, w, None, out_dtype, None)
+    assert gemm_bf16.LaunchCounter.library == before + 1 and y.dtype == out_dtype and y.shape == (M, N)
+    want = x.double().cpu() @ w.double().cpu().t()
+    tol_ = 2e-5 * math.sqrt(K) * 4 if out_dtype == torch.float32 else 1e-2 * want.abs().max().item()
+    assert (y.double().cpu() - want).abs().max() <= tol_
+    wide = torch.full((M, N + 8), 7.0, dtype=out_dtype, device=DEV)
+    gemm_bf16.library_linear(x, w, None, out_dtype, wide[:, :N])
+    assert torch.equal(wide[:, :N], y) and float(wide[:, N:].float().min()) == 7.0
+
+
 def test_tensor_core_product_refuses_what_tma_cannot_address():
     from microllm_rocm_b200.kernels import gemm_bf16
     from microllm_rocm_b200.kernels.build import KernelError
