@@ -1,10 +1,12 @@
 """bf16 x bf16 -> fp32-accumulated products of the serving path.
 
-The hand-written tcgen05 kernel (`gemm_tc.cu`) takes every product whose K and row pitches
-are multiples of 8 elements (what TMA can address); it picks the token tile from the number
-of tokens and splits K over CTAs when the output has too few tiles to fill the GPU.  Anything
-else falls to the library product (cuBLASLt through torch.mm), which also stays available
-as `library_linear` for comparisons.
+Who takes which product (`linear_bf16`, and the parts for their fused forms):
+  up to 8 tokens     the weight-streaming kernels (`gemv_bf16.cu`, `gemv_fused.cu`)
+  256 tokens and up  gate/up with its activation: the CTA-pair tcgen05 kernel (`gemm_tc2.cu`)
+  everything else    the library product, cuBLASLt called through `gemm_lib.cu` (or through torch.mm
+                     when a bias has to be added or cuBLASLt cannot be taken from the process)
+`gemm_tc.cu` (tcgen05, one CTA per tile) takes every product whose K and row pitches are multiples of
+8 elements; it is kept for comparison and is not on the engine's path.
 """
 from __future__ import annotations
 

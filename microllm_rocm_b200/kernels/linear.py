@@ -2,7 +2,7 @@
 
 fp32 path: the hand-written CUDA-core kernel (`gemm_f32.cu`), plain fp32 FMA, fixed
 summation order.  bf16 path: bf16 operands with fp32 accumulation; the library product
-(cuBLASLt through torch.mm) stands where the reference calls hipBLASLt for the same
+(cuBLASLt, see gemm_bf16.library_linear) stands where the reference calls hipBLASLt for the same
 projections (src/ops/optimized.cpp:349-403, BF16 x BF16 with 32-bit compute), and the
 hand-written small-batch kernel takes over for decode-sized batches when it is enabled.
 Weights stay in the checkpoint's [out, in] layout.
