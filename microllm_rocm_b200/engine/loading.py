@@ -48,7 +48,7 @@ def prepare_kernels(model=None) -> None:
     sources = ops.base_sources()
     if model is not None and model.rt.dtype == torch.bfloat16:
         from ..kernels import gemm_bf16
-        sources += gemm_bf16.sources()
+        sources += gemm_bf16.sources(engine_only=True)
         for entry in model.cache_entries.values():
             head_dim = getattr(entry.need, "head_dim", None)
             if head_dim:

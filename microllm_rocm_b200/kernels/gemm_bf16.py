@@ -62,8 +62,10 @@ _workspaces = {}
 _direct_ok = None
 
 
-def sources():
-    return [("gemm_tc.cu", {}), ("gemm_tc2.cu", {}), ("gemv_bf16.cu", {}), ("gemv_fused.cu", {}), ("gemm_lib.cu", {})]
+def sources(engine_only: bool = False):
+    """The objects of this module; with engine_only just those that a model's step can reach."""
+    used = [("gemm_tc2.cu", {}), ("gemv_bf16.cu", {}), ("gemv_fused.cu", {}), ("gemm_lib.cu", {})]
+    return used if engine_only else [("gemm_tc.cu", {})] + used
 
 
 # ------------------------------------------------------------------------------ few tokens: weight streaming
