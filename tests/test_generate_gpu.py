@@ -166,3 +166,10 @@ def test_captured_decode_steps_equal_launched_ones(folders, dtype):
         for i, t in enumerate(got[0]):
             assert float(ref[i].max() - ref[i, t]) <= 0.03 * float(ref[i].abs().max()), (i, t)
     graphed.engine.cache.check()
+
+
+def test_the_driver_entry_point_generates_and_compares():
+    """`__graft_entry__.smoke()` is what runs first on a fresh GPU box: it must import, generate a few tokens
+    in fp32 and bf16 and agree with the plain implementation."""
+    import __graft_entry__ as entry
+    entry.smoke()
