@@ -35,14 +35,14 @@ class Model:
         self.final_norm = make(NORMS, "norm", spec.final_norm, rt)
         self.head = make(HEADS, "head", spec.head, rt)
         self.blocks = []
-        self._parts: List[Tuple[str, Part]] = [("", self.embedding), ("", self.position),
+        self._parts: List[Tuple[str, Part]] = [("", self.embedding), (spec.position.params.get("prefix", ""), self.position),
                                                (spec.final_norm.params.get("prefix", ""), self.final_norm),
                                                ("", self.head)]
         for layer in spec.layers:
             position = self.position
             if "position" in layer.mixer.params:                 # a layer may bring its own encoding
                 position = make(POSITION_ENCODINGS, "position encoding", layer.mixer.params["position"], rt)
-                self._parts.append(("", position))
+                self._parts.append((layer.prefix + layer.mixer.params["position"].params.get("prefix", ""), position))
             mixer_cls = MIXERS.get(layer.mixer.kind)
             if mixer_cls is None:
                 raise KeyError(f"unknown mixer kind {layer.mixer.kind!r}; registered: {', '.join(sorted(MIXERS))}")

@@ -291,3 +291,172 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     mixed = collect(load_engine(folder, dtype="float32", page_size=16, max_tokens=peak, max_requests=3), steps)
     for key, row in whole.items():
         assert torch.allclose(mixed[key], row, atol=3e-5), key
+
+
+# --------------------------------------------------------------------------------- more toy parts: routing, positions, a norm
+def register_toy_routed():
+    """Three more kinds defined in the test: a feed-forward that ROUTES every token to one of E small experts
+    (top-1 of a linear router, fp32 softmax weight on the chosen expert), a position encoding that ADDS a
+    learned vector per absolute position to the embedded tokens (and gives the attention nothing to rotate),
+    and a norm that subtracts the mean (LayerNorm with weight and bias).  The framework's files know none
+    of them; they meet the framework's attention, block, embedding and head in one model."""
+    from microllm_rocm_b200.config import Architecture, register_architecture
+    from microllm_rocm_b200.config.spec import LayerSpec, ModelSpec, PartSpec, RunSpec
+    from microllm_rocm_b200.parts import (FeedForward, Norm, PositionEncoding, WeightSpec, register_feed_forward,
+                                          register_norm, register_position_encoding)
+
+    @register_feed_forward("toy_routed", replace=True)
+    class Routed(FeedForward):
+        def __init__(self, params, rt):
+            self.prefix, self.rt = params.get("prefix", ""), rt
+            self.h, self.i, self.e = int(params["hidden_size"]), int(params["intermediate_size"]), int(params["experts"])
+
+        def weight_specs(self):
+            specs = {"router.weight": WeightSpec((self.e, self.h), init=("normal", 0.5))}
+            for e in range(self.e):
+                specs[f"experts.{e}.up.weight"] = WeightSpec((self.i, self.h), init=("normal", 0.2))
+                specs[f"experts.{e}.down.weight"] = WeightSpec((self.h, self.i), init=("normal", 0.2))
+            return specs
+
+        def bind(self, tensors):
+            self.router = tensors["router.weight"]
+            self.up = [tensors[f"experts.{e}.up.weight"] for e in range(self.e)]
+            self.down = [tensors[f"experts.{e}.down.weight"] for e in range(self.e)]
+
+        def forward(self, x, ctx):
+            x = x.float()
+            weights = torch.softmax(x @ self.router.float().t(), dim=-1)           # router logits and softmax in fp32
+            chosen = weights.argmax(-1)
+            out = torch.zeros_like(x)
+            for e in range(self.e):
+                rows = (chosen == e).nonzero().flatten()
+                if rows.numel():
+                    hidden = torch.relu(x[rows] @ self.up[e].float().t())
+                    out[rows] = weights[rows, e, None] * (hidden @ self.down[e].float().t())
+            return out
+
+    @register_position_encoding("toy_learned", replace=True)
+    class Learned(PositionEncoding):
+        def __init__(self, params, rt):
+            self.prefix, self.n, self.h = params.get("prefix", ""), int(params["positions"]), int(params["hidden_size"])
+
+        def weight_specs(self):
+            return {"table.weight": WeightSpec((self.n, self.h), init=("normal", 0.3))}
+
+        def bind(self, tensors):
+            self.table = tensors["table.weight"]
+
+        def on_embedding(self, x, ctx):
+            x += self.table.float()[ctx.positions.long()]
+
+    @register_norm("toy_layernorm", replace=True)
+    class LayerNorm(Norm):
+        def __init__(self, params, rt):
+            self.prefix, self.size, self.eps = params.get("prefix", ""), int(params["size"]), float(params["eps"])
+
+        def weight_specs(self):
+            return {"weight": WeightSpec((self.size,), role="vector", init=("one_plus_normal", 0.1)),
+                    "bias": WeightSpec((self.size,), role="vector", init=("normal", 0.1))}
+
+        def bind(self, tensors):
+            self.weight, self.bias = tensors["weight"], tensors["bias"]
+
+        def forward(self, x, out, rows=None):
+            x = x if rows is None else x[rows.long()]
+            out.copy_(torch.nn.functional.layer_norm(x.float(), (self.size,), self.weight, self.bias, self.eps))
+
+        def add_forward(self, residual, delta, out):
+            residual += delta if delta.dim() == 2 else delta.sum(0)       # a delta may be partial sums [S, T, H]
+            self.forward(residual, out)
+
+    @dataclasses.dataclass(frozen=True)
+    class RoutedConfig:
+        vocab_size: int
+        hidden_size: int
+        intermediate_size: int
+        experts: int
+        layers: int
+        num_heads: int = 2
+        eps: float = 1e-5
+        max_position_embeddings: int = 128
+        torch_dtype: str = "float32"
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["vocab_size"], raw["hidden_size"], raw["intermediate_size"], raw["experts"], raw["layers"],
+                       raw.get("num_heads", 2), raw.get("eps", 1e-5), raw.get("max_position_embeddings", 128))
+
+        def to_dict(self):
+            return dict(dataclasses.asdict(self), architectures=["ToyRoutedForCausalLM"])
+
+    def build_spec(cfg):
+        h = cfg.hidden_size
+        norm = lambda sub: PartSpec("toy_layernorm", dict(prefix=sub, size=h, eps=cfg.eps))
+        layers = [LayerSpec(prefix=f"layers.{l}.", block=PartSpec("pre_norm_residual"), mixer_norm=norm("n1."),
+                            mixer=PartSpec("attention", dict(prefix="attn.", hidden_size=h, num_heads=cfg.num_heads, num_kv_heads=1,
+                                                             head_dim=h // cfg.num_heads, qkv_bias=True, window=None)),
+                            ffn_norm=norm("n2."),
+                            feed_forward=PartSpec("toy_routed", dict(prefix="ff.", hidden_size=h, experts=cfg.experts,
+                                                                     intermediate_size=cfg.intermediate_size)))
+                  for l in range(cfg.layers)]
+        return ModelSpec(architecture="ToyRoutedForCausalLM", hidden_size=h, vocab_size=cfg.vocab_size,
+                         max_position=cfg.max_position_embeddings,
+                         embedding=PartSpec("token_embedding", dict(name="embed.weight", vocab_size=cfg.vocab_size, hidden_size=h)),
+                         position=PartSpec("toy_learned", dict(prefix="positions.", positions=cfg.max_position_embeddings, hidden_size=h)),
+                         layers=layers, order=[RunSpec(l) for l in range(len(layers))], final_norm=norm("final."),
+                         head=PartSpec("lm_head", dict(name="head.weight", vocab_size=cfg.vocab_size, hidden_size=h, tied_to=None)))
+
+    arch = Architecture("ToyRoutedForCausalLM", RoutedConfig, build_spec)
+    register_architecture(arch, replace=True)
+    return arch, RoutedConfig
+
+
+def plain_routed_forward(w, cfg, toks):
+    T, H, NH = len(toks), cfg.hidden_size, cfg.num_heads
+    D = H // NH
+    ln = lambda x, p: torch.nn.functional.layer_norm(x, (H,), w[p + "weight"], w[p + "bias"], cfg.eps)
+    x = plain.embedding(w["embed.weight"], toks) + w["positions.table.weight"][:T]
+    for l in range(cfg.layers):
+        p = f"layers.{l}."
+        h = ln(x, p + "n1.")
+        q = (plain.linear(h, w[p + "attn.q_proj.weight"]) + w[p + "attn.q_proj.bias"]).view(T, NH, D)
+        k = (plain.linear(h, w[p + "attn.k_proj.weight"]) + w[p + "attn.k_proj.bias"]).view(T, 1, D)
+        v = (plain.linear(h, w[p + "attn.v_proj.weight"]) + w[p + "attn.v_proj.bias"]).view(T, 1, D)
+        x = x + plain.linear(plain.causal_gqa_attention(q, k, v, None).reshape(T, H), w[p + "attn.o_proj.weight"])
+        h = ln(x, p + "n2.")
+        weights = torch.softmax(plain.linear(h, w[p + "ff.router.weight"]), -1)
+        out = torch.zeros_like(h)
+        for t in range(T):
+            e = int(weights[t].argmax())
+            hidden = torch.relu(plain.linear(h[t:t + 1], w[p + f"ff.experts.{e}.up.weight"]))
+            out[t] = weights[t, e] * plain.linear(hidden, w[p + f"ff.experts.{e}.down.weight"])[0]
+        x = x + out
+    return plain.linear(ln(x, "final."), w["head.weight"])
+
+
+def test_toy_routing_positions_and_norm_are_registered_built_and_stepped(tmp_path):
+    """A routed feed-forward, learned positions and a layer norm, all defined in this file, build into a model
+    beside the framework's attention (which then rotates nothing), load from a folder written by the
+    random-weights mode, and step whole and in mixed portions to the same logits as a plain forward."""
+    from microllm_rocm_b200.engine.loading import load_engine
+    from microllm_rocm_b200.weights import write_random_model
+    arch, RoutedConfig = register_toy_routed()
+    cfg = RoutedConfig(vocab_size=70, hidden_size=48, intermediate_size=40, experts=3, layers=2, num_heads=3)
+    folder = write_random_model(arch, cfg, 7, str(tmp_path / "routed"), "float32")
+    engine = load_engine(folder, dtype="float32", page_size=16, max_tokens=256, max_requests=3)
+    reqs = {f"q{i}": random_tokens(n, cfg.vocab_size, 3 * n) for i, n in enumerate([33, 50, 12, 41])}
+    w = plain.read_safetensors(os.path.join(folder, "model.safetensors"))
+    whole = collect(engine, steps_whole(reqs))
+    experts_used = set()
+    for rid, toks in reqs.items():
+        want = plain_routed_forward(w, cfg, toks)
+        for p in range(len(toks)):
+            assert torch.allclose(whole[(rid, p)], want[p], atol=5e-5), (rid, p)
+        h0 = torch.nn.functional.layer_norm(plain.embedding(w["embed.weight"], toks) + w["positions.table.weight"][:len(toks)],
+                                            (cfg.hidden_size,), w["layers.0.n1.weight"], w["layers.0.n1.bias"], cfg.eps)
+        experts_used |= set(plain.linear(h0, w["layers.0.ff.router.weight"]).argmax(-1).tolist())
+    assert len(experts_used) > 1                      # the router really sends tokens to different experts
+    steps, peak = steps_mixed(reqs, max_live=3, seed=4)
+    mixed = collect(load_engine(folder, dtype="float32", page_size=16, max_tokens=peak, max_requests=3), steps)
+    for key, row in whole.items():
+        assert torch.allclose(mixed[key], row, atol=5e-5), key
