@@ -118,6 +118,12 @@ class CacheManager:
         r = self.requests[request]
         if new_len < r.length:
             raise ValueError("a request cannot shrink")
+        want = (new_len + self.page_size - 1) // self.page_size
+        for table in r.tables.values():
+            if len(table) < want:
+                break
+        else:
+            return True                                   # the usual decode step: the last page still has room
         needed = self.pages_needed(request, new_len)
         if any(n > self.groups[k].pool.free_count for k, n in needed.items()):
             return False
