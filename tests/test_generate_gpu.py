@@ -173,3 +173,37 @@ def test_the_driver_entry_point_generates_and_compares():
     in fp32 and bf16 and agree with the plain implementation."""
     import __graft_entry__ as entry
     entry.smoke()
+
+
+@pytest.mark.parametrize("key,pool,budget,seed,preempts", [("b", 320, 2048, 0, True), ("b", 400, 64, 7, False),
+                                                          ("a", 0, 37, 1, False)])
+def test_many_requests_through_a_tight_pool_equal_one_by_one(folders, key, pool, budget, seed, preempts):
+    """Thirty requests of assorted lengths, greedy and sampled, submitted in bursts while the engine steps,
+    through a pool so small that running requests are preempted and recomputed, with prompts cut by a small
+    token budget: in fp32 every request must get exactly the tokens it gets alone in a roomy pool (which the
+    tests above tie to the plain implementation), and the cache must end empty and consistent."""
+    import random
+    from microllm_rocm_b200 import GenerationConfig
+    cfg = tiny_config(key)
+    rng = random.Random(seed)
+    cap = cfg.max_position_embeddings
+    lens = [n for n in [1, 2, 3, 7, 15, 16, 17, 31, 33, 64, 100, 150] if n + 64 <= cap]
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(rng.choice(lens))] for _ in range(30)]
+    cfgs = [GenerationConfig(max_new_tokens=rng.choice([1, 2, 5, 17, 40, 64]), temperature=0.0 if i % 3 else 0.8,
+                             top_k=0 if i % 2 else 5, seed=i) for i in range(30)]
+    roomy = llm_for(folders[key], "float32", max_tokens=8192)
+    want = [roomy.generate([p], c)[0] for p, c in zip(prompts, cfgs)]
+    tight = llm_for(folders[key], "float32", max_tokens=pool or cap + 64, max_tokens_per_step=budget)
+    pending, ids = list(zip(prompts, cfgs)), []
+    while pending or tight.has_work():
+        for _ in range(rng.randrange(0, 4)):
+            if pending:
+                ids.append(tight.submit(*pending.pop(0)))
+        if tight.has_work():
+            tight.step()
+    assert [list(tight.poll(i).generated) for i in ids] == want
+    metrics = tight.metrics()
+    assert metrics["cache"]["live_requests"] == 0
+    if preempts:
+        assert metrics["preemptions"] > 0               # the pool really was too small for the load
+    tight.engine.cache.check()
