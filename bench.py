@@ -35,7 +35,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
-BASELINE_DECODE_B8 = 435.0      # reference, DeepSeek-R1-Distill-Qwen-1.5B, T2048 B8, MI300X
+BASELINE_DECODE_B8 = 435.0      # the reference's published figure: DeepSeek-R1-Distill-Qwen-1.5B, T2048 B8, on an MI300X
 
 
 def peaks():

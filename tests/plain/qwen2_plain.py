@@ -182,7 +182,7 @@ def block(x, w, prefix, cfg, positions, window, rnd):
 def forward_logits(weights: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int],
                    precision: str = "float32", dtype: torch.dtype = torch.float32) -> torch.Tensor:
     """Logits [T, V] for every position of one whole sequence (positions 0..T-1)
-    (src/model/model.cpp:1043-1087; pseudocode of the whole pass in the survey of that file)."""
+    (src/model/model.cpp:1043-1087)."""
     rnd = Rounding(precision)
     w = {}
     for name, t in weights.items():
