@@ -138,6 +138,41 @@ def test_benchmark_shape_bf16_tracks_the_true_fp32_path():
     assert float(distance.max()) < 0.08, distance.tolist()
 
 
+@pytest.mark.parametrize("name", ["qwen2.5-7b", "qwen2.5-14b"])
+def test_wider_layer_shapes_bf16_tracks_the_true_fp32_path(name):
+    """Two layers of the 7B shape (width 3,584, 28/4 heads, intermediate 18,944, untied head) and of the 14B
+    shape (width 5,120, 40/8 heads, intermediate 13,824): widths and K ranges that the few-token kernels split
+    differently from the benchmark's.  Prompt portions of 600, 100 and 30 tokens, a step that mixes a decode
+    token with two portions, decode steps at batch 3; bf16 against the engine's fp32 path."""
+    from microllm_rocm_b200.config import preset
+    from microllm_rocm_b200.engine.loading import random_engine
+    from microllm_rocm_b200.engine.step import StepEntry
+    cfg = preset(name, num_hidden_layers=2)
+    gen = torch.Generator().manual_seed(1)
+    reqs = {k: torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist() for k, n in (("a", 700), ("b", 140), ("c", 40))}
+
+    def run(dtype):
+        engine = random_engine(cfg, seed=0, dtype=dtype, page_size=64, max_tokens=2048, max_requests=4, draw_on_device=True)
+        for k in reqs:
+            engine.cache.add(k)
+        outs = [engine.step([StepEntry("a", reqs["a"][:600], [599]), StepEntry("b", reqs["b"][:100], [99])]),
+                engine.step([StepEntry("a", reqs["a"][600:601], [0]), StepEntry("b", reqs["b"][100:135], [34]),
+                             StepEntry("c", reqs["c"][:30], [29])])]
+        for i in range(5):
+            outs.append(engine.step([StepEntry("a", reqs["a"][601 + i:602 + i], [0]), StepEntry("b", reqs["b"][135 + i:136 + i], [0]),
+                                     StepEntry("c", reqs["c"][30 + i:31 + i], [0])]))
+        engine.check_device_errors()
+        return torch.cat([o.float().cpu() for o in outs])
+
+    want = run("float32")
+    torch.cuda.empty_cache()
+    got = run("bfloat16")
+    torch.cuda.empty_cache()
+    assert torch.isfinite(got).all() and got.shape == want.shape == (20, cfg.vocab_size)
+    distance = (got - want).norm(dim=1) / want.norm(dim=1)
+    assert float(distance.max()) < 0.05, distance.tolist()      # two layers: measured 1.9 % and 2.2 %
+
+
 @pytest.mark.parametrize("key", ["a", "b"])
 def test_fp32_is_bit_stable_across_cuts(folders, key):
     """In the fp32 path every summation order is fixed by the token's own position, so the
