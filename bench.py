@@ -124,9 +124,9 @@ def run_ours(args):
     from microllm_rocm_b200.sampling import GenerationConfig
 
     pk = peaks()
-    full = preset("qwen2.5-1.5b")
+    full = preset(args.model)
     layers = args.layers or full.num_hidden_layers
-    cfg = preset("qwen2.5-1.5b", num_hidden_layers=layers)
+    cfg = preset(args.model, num_hidden_layers=layers)
     prompt_len, context, page = args.prompt, args.context, 64
     max_batch = max(args.batch, 64 if not (args.skip_points or args.only) else args.batch)
     tokens_needed = max_batch * (context + page)
@@ -224,16 +224,19 @@ def run_ours(args):
            "h2d_bytes_per_step": (llm.h2d_bytes - h2d0) // args.steps, "d2h_bytes_per_step": (llm.d2h_bytes - d2h0) // args.steps}
 
     out = {
-        "metric": "decode tokens/s (Qwen2.5-1.5B shape, bf16, batch 8, 2048-token prompts)", "value": value,
+        "metric": f"decode tokens/s ({args.model[:1].upper() + args.model[1:-1] + args.model[-1:].upper()} shape, bf16, "
+                  f"batch {args.batch}, {prompt_len}-token prompts)", "value": value,
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": value / BASELINE_DECODE_B8, "dtype": "bf16",
+        "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": value / BASELINE_DECODE_B8 if (args.model, args.batch, prompt_len) == ("qwen2.5-1.5b", 8, 2048) else None,
+        "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02) seed 0, uniform random token ids", "impl": "ours",
-        "config": {"model": "qwen2.5-1.5b-shape", "layers": layers, "layers_of_model": full.num_hidden_layers,
+        "config": {"model": args.model + "-shape", "layers": layers, "layers_of_model": full.num_hidden_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_size, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "tied": cfg.tie_word_embeddings, "global_batch": args.batch, "seq_len": prompt_len,
                    "context": context, "decode_context": ctx_len, "page_size": page, "parallelism": "single-gpu",
-                   "l2": "step reads >3 GB, larger than L2", "peaks": pk["source"]},
+                   "l2": f"step reads {bytes_step / 1e9:.1f} GB, larger than L2", "peaks": pk["source"]},
         "e2e": e2e, "gpu_launches": launches, "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "bytes_per_step": bytes_step},
@@ -249,6 +252,7 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="qwen2.5-1.5b", help="a preset's layer shapes (default: the benchmark model)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--context", type=int, default=4096)

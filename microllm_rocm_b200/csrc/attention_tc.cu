@@ -101,7 +101,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code) {
     for (int i = 0; i < SPIN_LIMIT; ++i)
         if (mbar_try_wait(bar, parity)) return true;
-    if (error_flag) atomicExch(error_flag, code);
+    if (error_flag) atomicCAS(error_flag, 0, code);          // the first failure is the one worth reporting
     return false;
 }
 // true in exactly one lane of the (converged) warp
@@ -580,6 +580,12 @@ MLB_EXPORT int mlb_paged_attention_tc(const void* q, long long ldq, const void* 
                                           (int)SMEM_BYTES, cudaGetErrorString(e));
         configured = true;
     }
-    launch_kernel(fa_tc_prefill_kernel, dim3(num_heads, num_work, 1), THREADS, SMEM_BYTES, stream, map_q, map_kv, p);
+    // Launched WITHOUT programmatic early start.  A CTA of this kernel takes a whole SM (225 KB of shared memory, all
+    // of the tensor memory) from its first instruction; started early it sits on that SM, in front of its dependency
+    // wait, while the kernels it waits for still need SMs.  Measured with 28 heads, 4 KV heads and a width of 3,584
+    // (library projections of several waves) and the host far ahead of the GPU: started early, bounded waits inside
+    // this kernel ran out in most runs (first codes 21, 27, 30, i.e. the whole CTA stalled); started after its
+    // predecessor, in none.  The mechanism is not established; what an early start hides here is ~2 us of 36.
+    fa_tc_prefill_kernel<<<dim3(num_heads, num_work, 1), THREADS, SMEM_BYTES, stream>>>(map_q, map_kv, p);
     return check_launch("fa_tc_prefill");
 }

@@ -22,7 +22,7 @@ import torch
 from ..kernels import ops
 from ..parts.base import StepContext
 from ..sampling.config import GenerationConfig
-from .step import Engine, OutOfPages, StepError
+from .step import Engine, OutOfPages, StepError, device_error_text
 
 
 def graph_capable(engine: Engine) -> bool:
@@ -208,7 +208,7 @@ class DecodeGraph:
         host = self.out_host.tolist()
         if host[A]:
             self.engine.error_flag.zero_()
-            raise StepError(f"a kernel met a token without a valid page (code {host[A]})")
+            raise StepError(device_error_text(host[A]))
         return host[:A]
 
 

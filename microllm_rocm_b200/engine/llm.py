@@ -18,7 +18,7 @@ from ..sampling.sampler import Sampler
 from .decode_graph import DecodeGraph, DecodeGraphPool, graph_capable
 from .loading import DEFAULT_PAGE_SIZE, load_engine
 from .scheduler import Request, Scheduler, StepPlan
-from .step import Engine, StepEntry, StepError
+from .step import Engine, StepEntry, StepError, device_error_text
 
 
 class LLM:
@@ -80,7 +80,7 @@ class LLM:
         self.d2h_bytes += 4 * (R + 1)
         if host[R]:
             self.engine.error_flag.zero_()
-            raise StepError(f"a kernel met a token without a valid page (code {host[R]})")
+            raise StepError(device_error_text(host[R]))
         return self.scheduler.update(plan, host[:R])
 
     def _graph_step(self, plan: StepPlan) -> List[Request]:

@@ -37,6 +37,13 @@ class StepEntry:
     want: Sequence[int] = ()          # places among `tokens` whose logits are asked for
 
 
+def device_error_text(code: int) -> str:
+    """What a non-zero device error flag means."""
+    if code >= 10:
+        return f"a bounded wait inside a tensor-memory kernel ran out (code {code}); the step's results are not valid"
+    return f"a kernel met a token without a valid page (code {code}): the block table and the request's length disagree"
+
+
 class Engine:
     """A model, its cache, and step().  Owns no policy: who runs when is the scheduler's."""
 
@@ -178,10 +185,7 @@ class Engine:
         code = int(self.error_flag.item())
         if code:
             self.error_flag.zero_()
-            if code >= 10:
-                raise StepError(f"a bounded wait inside a tensor-memory kernel ran out (code {code}); its results are not valid")
-            raise StepError(f"a kernel met a token without a valid page (code {code}): the block table and the "
-                            "request's length disagree")
+            raise StepError(device_error_text(code))
         if self.model.rt.dtype == torch.bfloat16:
             from ..kernels import gemm_bf16
             flag = gemm_bf16.error_flag(self.device)
