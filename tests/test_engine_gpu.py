@@ -173,6 +173,30 @@ def test_wider_layer_shapes_bf16_tracks_the_true_fp32_path(name):
     assert float(distance.max()) < 0.05, distance.tolist()      # two layers: measured 1.9 % and 2.2 %
 
 
+def test_prompt_steps_issued_back_to_back_leave_no_device_error():
+    """Four layers of the 7B shape, three prompts of 2,048 tokens stepped one after the other WITHOUT a
+    synchronisation in between, so that the host runs far ahead of the GPU and every kernel that may start
+    early does.  (The tensor-memory attention kernel, started early in this situation, had bounded waits run
+    out; it is launched after its predecessor now.)  The device error flag must stay clear and the logits finite."""
+    from microllm_rocm_b200.config import preset
+    from microllm_rocm_b200.engine.loading import random_engine
+    from microllm_rocm_b200.engine.step import StepEntry
+    cfg = preset("qwen2.5-7b", num_hidden_layers=4)
+    engine = random_engine(cfg, seed=0, dtype="bfloat16", page_size=64, max_tokens=8 * 2368, max_requests=8, draw_on_device=True)
+    gen = torch.Generator().manual_seed(0)
+    outs = []
+    for _ in range(2):
+        for i in range(3):
+            toks = torch.randint(0, cfg.vocab_size, (2048,), generator=gen).tolist()
+            engine.cache.add(f"p{i}")
+            outs.append(engine.step([StepEntry(f"p{i}", toks, [2047])]))
+        for i in range(3):
+            engine.cache.release(f"p{i}")
+    torch.cuda.synchronize()
+    engine.check_device_errors()
+    assert all(torch.isfinite(o).all() for o in outs)
+
+
 @pytest.mark.parametrize("key", ["a", "b"])
 def test_fp32_is_bit_stable_across_cuts(folders, key):
     """In the fp32 path every summation order is fixed by the token's own position, so the
