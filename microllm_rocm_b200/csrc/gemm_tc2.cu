@@ -398,15 +398,16 @@ MLB_EXPORT int mlb_gemm_pair(const void* x, long long ldx, const void* w, long l
     config.blockDim = dim3(THREADS);
     config.dynamicSmemBytes = smem;
     config.stream = stream;
-    cudaLaunchAttribute attributes[2];
+    // No programmatic early start: a CTA of this kernel holds a whole SM and all of its tensor memory from its first
+    // instruction, and the prompt attention kernel, which does the same, stalled when it sat early in front of its
+    // dependency wait (see attention_tc.cu).  This kernel never did; an early start would hide ~2 us of ~100.
+    cudaLaunchAttribute attributes[1];
     attributes[0].id = cudaLaunchAttributeClusterDimension;
     attributes[0].val.clusterDim.x = 2;
     attributes[0].val.clusterDim.y = 1;
     attributes[0].val.clusterDim.z = 1;
-    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
-    config.numAttrs = pdl_enabled() ? 2 : 1;
+    config.numAttrs = 1;
     cudaLaunchKernelEx(&config, gemm_pair_kernel, map_w, map_x, p);
     return check_launch("gemm_pair");
 }
