@@ -585,7 +585,8 @@ MLB_EXPORT int mlb_paged_attention_tc(const void* q, long long ldq, const void* 
     // wait, while the kernels it waits for still need SMs.  Measured with 28 heads, 4 KV heads and a width of 3,584
     // (library projections of several waves) and the host far ahead of the GPU: started early, bounded waits inside
     // this kernel ran out in most runs (first codes 21, 27, 30, i.e. the whole CTA stalled); started after its
-    // predecessor, in none.  The mechanism is not established; what an early start hides here is ~2 us of 36.
+    // predecessor, in none (nor with this kernel early and the CTA-pair product, which holds SMs the same way, not:
+    // the stall seems to need both).  The mechanism is not established; an early start hides ~2 us of 36 here.
     fa_tc_prefill_kernel<<<dim3(num_heads, num_work, 1), THREADS, SMEM_BYTES, stream>>>(map_q, map_kv, p);
     return check_launch("fa_tc_prefill");
 }
