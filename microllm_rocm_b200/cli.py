@@ -7,7 +7,13 @@ Flags with the reference's names keep the reference's meaning (hf_infer.cpp:32-7
 top logits to print), --logits-output, --cache-logits-output, --cache-prefill-mode
 full|token, --bf16-ffn/--bf16-attention, --kv-cache-dtype, --cache-capacity,
 --continuous-slots, --continuous-prompt-lengths, --continuous-new-token-lengths,
---continuous-prompt-offsets, --continuous-arrival-steps.  The reference's command line is
+--continuous-prompt-offsets, --continuous-arrival-steps.  Flags that choose between code paths the reference has
+and this engine does not are read and checked as the reference checks them, and accepted with the one value
+that describes this engine: --use-cache true (there is no uncached path), --prefill-logits last,
+--batch-argmax-mode device, --decode-mode generation, --continuous-prefill-batch true,
+--continuous-diagnostics false; any other legal value is refused with a sentence that says so, and
+--continuous-cache-buckets (a paged cache has no buckets), --kv-cache-fp32-layers, --trace-output and the
+tokenizer flags (--text, --vocab, --merges, --tokenizer-family, --chat-user) are refused by name.  The reference's command line is
 always greedy and has no random-weights mode; added here: --model DIR (config.json and
 model.safetensors in one folder), --dtype fp32|bf16, --temperature, --sampling-top-k, --seed,
 --stop-tokens, --page-size, --num-pages, --max-tokens-per-step, --max-seqs, and
@@ -33,6 +39,31 @@ DEFAULTS: Dict[str, object] = {
     "continuous-prompt-offsets": "", "continuous-arrival-steps": "",
     "temperature": 0.0, "sampling-top-k": 0, "seed": 1, "stop-tokens": "", "page-size": 16, "num-pages": 0,
     "max-tokens-per-step": 2048, "max-seqs": 64, "random-config": "", "random-seed": 0, "write-model": "",
+    # the reference's switches between code paths: only the value that describes this engine is accepted
+    "use-cache": "true", "prefill-logits": "last", "batch-argmax-mode": "device", "decode-mode": "generation",
+    "continuous-prefill-batch": "true", "continuous-diagnostics": "false",
+}
+
+# flag -> (legal values in the reference, the one this engine has, what the others would need)
+ONE_WAY = {
+    "use-cache": (("true", "false"), "true", "there is no uncached forward pass"),
+    "prefill-logits": (("last", "full"), "last", "logits of every prompt position come from bin/trace_run"),
+    "batch-argmax-mode": (("device", "host"), "device", "tokens are always selected on the device"),
+    "decode-mode": (("generation", "steady"), "generation", "steady decoding of a fixed batch is what bench.py measures"),
+    "continuous-prefill-batch": (("true", "false"), "true", "prompt portions always share a step"),
+    "continuous-diagnostics": (("true", "false"), "false", "the scheduler's metrics are in the JSON line already"),
+}
+NOT_HERE = {
+    "continuous-cache-buckets": "a paged cache has no capacity buckets",
+    "kv-cache-fp32-layers": "the cache has the compute dtype in every layer",
+    "trace-output": "tensor traces are not built; bin/trace_run replays token traces and writes logits",
+    "trace-max-elements": "tensor traces are not built",
+    "bf16-algorithm-index": "the library chooses its own algorithm",
+    "text": "tokenizers are not part of this engine: give --tokens",
+    "vocab": "tokenizers are not part of this engine: give --tokens",
+    "merges": "tokenizers are not part of this engine: give --tokens",
+    "tokenizer-family": "tokenizers are not part of this engine: give --tokens",
+    "chat-user": "tokenizers are not part of this engine: give --tokens",
 }
 
 
@@ -46,6 +77,8 @@ def parse(argv: List[str]) -> Dict[str, object]:
         raise UsageError("missing CLI value")
     for i in range(0, len(argv), 2):
         name, value = argv[i], argv[i + 1]
+        if name.startswith("--") and name[2:] in NOT_HERE:
+            raise UsageError(f"{name} is an option of the reference that this engine does not have: {NOT_HERE[name[2:]]}")
         if not name.startswith("--") or name[2:] not in DEFAULTS:
             raise UsageError(f"unknown CLI option: {name}")
         key = name[2:]
@@ -76,6 +109,11 @@ def int_list(text: str, what: str) -> List[int]:
 
 
 def validate(o: Dict[str, object]) -> None:
+    for key, (legal, ours, why) in ONE_WAY.items():
+        if o[key] not in legal:
+            raise UsageError(f"--{key} must be {' or '.join(legal)}")
+        if o[key] != ours:
+            raise UsageError(f"--{key} {o[key]} is not available in this engine ({why}); only --{key} {ours}")
     if o["random-config"] and o["write-model"]:
         return
     if not o["model"] and not (o["config"] and o["weights"]):
