@@ -4,13 +4,13 @@
 Flags with the reference's names keep the reference's meaning (hf_infer.cpp:32-73, rules
 :179-285): --config/--weights, --tokens, --device, --workload both|prefill|decode|continuous,
 --new-tokens, --batch, --warmup/--steps, --prefill-warmup/--prefill-steps, --top-k (how many
-top logits to print), --logits-output, --cache-logits-output, --cache-prefill-mode
+top logits to print), --logits-output, --prefill-logits last|full (full: the head is applied at every prompt
+position and --logits-output holds [tokens, vocab]; the top logits are the last position's either way), --cache-logits-output, --cache-prefill-mode
 full|token, --bf16-ffn/--bf16-attention, --kv-cache-dtype, --cache-capacity,
 --continuous-slots, --continuous-prompt-lengths, --continuous-new-token-lengths,
 --continuous-prompt-offsets, --continuous-arrival-steps.  Flags that choose between code paths the reference has
 and this engine does not are read and checked as the reference checks them, and accepted with the one value
-that describes this engine: --use-cache true (there is no uncached path), --prefill-logits last,
---batch-argmax-mode device, --decode-mode generation, --continuous-prefill-batch true,
+that describes this engine: --use-cache true (there is no uncached path), --batch-argmax-mode device, --decode-mode generation, --continuous-prefill-batch true,
 --continuous-diagnostics false; any other legal value is refused with a sentence that says so, and
 --continuous-cache-buckets (a paged cache has no buckets), --kv-cache-fp32-layers, --trace-output and the
 tokenizer flags (--text, --vocab, --merges, --tokenizer-family, --chat-user) are refused by name.  The reference's command line is
@@ -47,7 +47,6 @@ DEFAULTS: Dict[str, object] = {
 # flag -> (legal values in the reference, the one this engine has, what the others would need)
 ONE_WAY = {
     "use-cache": (("true", "false"), "true", "there is no uncached forward pass"),
-    "prefill-logits": (("last", "full"), "last", "logits of every prompt position come from bin/trace_run"),
     "batch-argmax-mode": (("device", "host"), "device", "tokens are always selected on the device"),
     "decode-mode": (("generation", "steady"), "generation", "steady decoding of a fixed batch is what bench.py measures"),
     "continuous-prefill-batch": (("true", "false"), "true", "prompt portions always share a step"),
@@ -109,6 +108,8 @@ def int_list(text: str, what: str) -> List[int]:
 
 
 def validate(o: Dict[str, object]) -> None:
+    if o["prefill-logits"] not in ("last", "full"):
+        raise UsageError("--prefill-logits must be last or full")
     for key, (legal, ours, why) in ONE_WAY.items():
         if o[key] not in legal:
             raise UsageError(f"--{key} must be {' or '.join(legal)}")
@@ -236,7 +237,9 @@ def run(o) -> int:
         torch.cuda.synchronize()
         return r, (time.perf_counter() - a) * 1e3
 
-    def prefill_once(want_all_rows=False):
+    full_logits = o["prefill-logits"] == "full"
+
+    def prefill_once():
         cache = engine.cache
         rows = [f"p{b}" for b in range(batch)]
         for r in rows:
@@ -244,10 +247,16 @@ def run(o) -> int:
         try:
             if o["cache-prefill-mode"] == "token":          # the prompt one token at a time
                 logits = None
+                pieces = []
                 for i, t in enumerate(ids):
-                    logits = engine.step([StepEntry(r, [t], [0] if i == len(ids) - 1 else []) for r in rows])
+                    logits = engine.step([StepEntry(r, [t], [0] if (full_logits or i == len(ids) - 1) else []) for r in rows])
+                    if full_logits:
+                        pieces.append(logits[:1])
+                if full_logits:
+                    logits = torch.cat(pieces)                # the first request's rows, one per position
             else:
-                logits = engine.step([StepEntry(r, ids, [len(ids) - 1]) for r in rows])
+                want = list(range(len(ids))) if full_logits else [len(ids) - 1]
+                logits = engine.step([StepEntry(r, ids, want) for r in rows])
             engine.check_device_errors()
             return logits
         finally:
@@ -261,11 +270,13 @@ def run(o) -> int:
         for _ in range(o["prefill-steps"]):
             logits, ms = timed(prefill_once)
             total += ms
-        row = logits[0].to("cpu")
+        first = logits[:len(ids)].to("cpu") if full_logits else logits[:1].to("cpu")     # the first request's rows
+        row = first[-1]
         if o["logits-output"]:
-            row.numpy().astype("<f4").tofile(o["logits-output"])
+            (first if full_logits else row).numpy().astype("<f4").tofile(o["logits-output"])
         top = torch.topk(row, min(o["top-k"], row.numel()))
         out.update({"prefill_warmup": o["prefill-warmup"], "prefill_steps": o["prefill-steps"],
+                    "prefill_logits_mode": o["prefill-logits"],
                     "forward_ms": total / o["prefill-steps"],
                     "prefill_tokens_per_second": batch * len(ids) * o["prefill-steps"] / (total / 1e3),
                     "top_logits": [{"token": int(i), "logit": float(v)} for v, i in zip(top.values, top.indices)]})

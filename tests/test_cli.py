@@ -45,9 +45,12 @@ def test_rules_of_the_reference(argv, message):
 
 
 def test_switches_between_paths_this_engine_does_not_have():
+    check(BASE + ["--prefill-logits", "full"])
+    with pytest.raises(cli.UsageError, match="--prefill-logits must be last or full"):
+        check(BASE + ["--prefill-logits", "all"])
     check(BASE + ["--use-cache", "true", "--prefill-logits", "last", "--batch-argmax-mode", "device",
                   "--decode-mode", "generation", "--continuous-prefill-batch", "true", "--continuous-diagnostics", "false"])
-    for flag, value in (("--use-cache", "false"), ("--prefill-logits", "full"), ("--batch-argmax-mode", "host"),
+    for flag, value in (("--use-cache", "false"), ("--batch-argmax-mode", "host"),
                         ("--decode-mode", "steady"), ("--continuous-prefill-batch", "false"), ("--continuous-diagnostics", "true")):
         with pytest.raises(cli.UsageError, match="not available in this engine"):
             check(BASE + [flag, value])

@@ -129,6 +129,18 @@ def test_command_line(folders, tmp_path):
     assert [t["token"] for t in info["top_logits"]] == torch.topk(last, 3).indices.tolist()
     cached = torch.from_numpy(np.fromfile(cached_file, dtype="<f4"))
     assert torch.allclose(cached, plain_logits(folders[key], prompt + want[:-1])[-1], atol=2e-5)
+    # --prefill-logits full: the head at every prompt position, whole prompt or token by token
+    for mode in ("full", "token"):
+        full_file = tmp_path / f"full_{mode}.f32"
+        cmd = [sys.executable, os.path.join(ROOT, "bin", "microllm_hf_infer"), "--model", folders[key], "--tokens",
+               ",".join(map(str, prompt)), "--workload", "prefill", "--prefill-logits", "full", "--cache-prefill-mode", mode,
+               "--logits-output", str(full_file), "--top-k", "3"]
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        info = json.loads(proc.stdout.strip().splitlines()[-1])
+        every = torch.from_numpy(np.fromfile(full_file, dtype="<f4")).view(len(prompt), -1)
+        assert torch.allclose(every, plain_logits(folders[key], prompt), atol=2e-5)
+        assert info["prefill_logits_mode"] == "full" and [t["token"] for t in info["top_logits"]] == torch.topk(every[-1], 3).indices.tolist()
     # continuous workload: delayed arrivals over two slots
     cmd = [sys.executable, os.path.join(ROOT, "bin", "microllm_hf_infer"), "--model", folders[key], "--workload", "continuous",
            "--tokens", ",".join(map(str, prompt)), "--continuous-slots", "2", "--continuous-prompt-lengths", "4,9,6",
