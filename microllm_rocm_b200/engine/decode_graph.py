@@ -168,6 +168,17 @@ class DecodeGraph:
         ops.copy_raw(device, pinned, nbytes, True)
         self._mark_upload()
 
+    def stale(self, max_seq_len: int) -> bool:
+        """The captured step was cut for another context length than the one it is about to serve."""
+        from ..kernels import attention
+        return self.graph is not None and attention.decode_plan_stale(self.ctx, max_seq_len)
+
+    def invalidate(self) -> None:
+        """Forget the captured step and the launch plans frozen into it; the next capture plans anew."""
+        from ..kernels import attention
+        self.graph = None
+        attention.forget_plans(self.ctx)
+
     def fits(self, requests: Sequence[Hashable]) -> bool:
         cache = self.engine.cache
         return all(len(cache.requests[q].tables[g]) <= w for g, w in self.widths.items() for q in requests)

@@ -88,9 +88,14 @@ class LLM:
         decode step instead of launching it kernel by kernel."""
         ids = [e.request.id for e in plan.entries]
         graph = self._graph
+        longest = max(e.begin for e in plan.entries) + 1
+        if graph is not None and graph.stale(longest):
+            graph = None                                 # the context outgrew the way the captured step cuts the keys
         if graph is None or graph.requests != ids or not graph.fits(ids):
             remaining = max(e.request.config.max_new_tokens - len(e.request.generated) for e in plan.entries)
             graph = self.graphs.get(ids, headroom_tokens=remaining)
+            if graph.stale(longest):
+                graph.invalidate()                       # captured for another context length: plan and capture anew
             state = ([e.request.token(e.begin) for e in plan.entries], [e.begin for e in plan.entries],
                      [e.request.config for e in plan.entries], [len(e.request.generated) for e in plan.entries])
             graph.load(ids, *state)

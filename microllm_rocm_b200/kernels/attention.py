@@ -66,6 +66,35 @@ def tc_sources(head_dim: int):
     return [("attention_tc.cu", {"HEAD_DIM": head_dim})] if head_dim in TC_HEAD_DIMS else []
 
 
+def decode_splits(items: int, max_seq_len: int) -> int:
+    """How many CTAs (one thread-block cluster) share the keys of one (sequence, kv head) in a decode step:
+    as many as still fit the GPU in one wave (two CTAs per SM) and leave every warp a key tile."""
+    key_tiles = max(1, -(-max_seq_len // 16))
+    items = max(1, items)
+    for cand in DECODE_SPLITS:
+        if cand > 8 and items * cand > WIDE_CLUSTER_CTAS:
+            continue          # clusters of 16 pay only while the whole grid is a handful of (eight-warp) CTAs
+        if items * cand <= SM_COUNT * 2 and key_tiles >= cand * MIN_KEY_TILES_PER_SPLIT:
+            return cand
+    return 1
+
+
+def decode_plan_stale(ctx, max_seq_len: int) -> bool:
+    """Whether a decode step planned for `ctx` (its plans are kept in ctx.extras, and frozen into a captured
+    graph) would be cut differently at this context length: a step captured at a short context has one CTA
+    per (sequence, kv head) and must not serve a context of thousands that way."""
+    for key, plan in ctx.extras.items():
+        if isinstance(key, tuple) and key and key[0] == "attention_mma" and plan[2] == 1:
+            if decode_splits(plan[1] * key[2], max_seq_len) != plan[3]:
+                return True
+    return False
+
+
+def forget_plans(ctx) -> None:
+    for key in [k for k in ctx.extras if isinstance(k, tuple) and k and k[0] == "attention_mma"]:
+        del ctx.extras[key]
+
+
 def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
     """Work lists and split choice of a step, shared by every layer with the same group size."""
     key = ("attention_mma", group, num_kv_heads, use_tc)
@@ -92,18 +121,7 @@ def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
     device = ctx.positions.device
     work_dev = torch.tensor(work, dtype=torch.int32).reshape(-1).to(device, non_blocking=True)
     tc_dev = torch.tensor([(a, t) for _, a, t in tc_work], dtype=torch.int32).reshape(-1).to(device, non_blocking=True)
-    splits = 1
-    if decode:
-        # a cluster of 1, 2, 4 or 8 CTAs shares the keys of one (sequence, kv head): as many as
-        # still fit the GPU in one wave (two CTAs per SM) and leave every warp a key tile
-        key_tiles = max(1, -(-ctx.max_seq_len // 16))
-        items = max(1, len(work) * num_kv_heads)
-        for cand in DECODE_SPLITS:
-            if cand > 8 and items * cand > WIDE_CLUSTER_CTAS:
-                continue          # clusters of 16 pay only while the whole grid is a handful of (eight-warp) CTAs
-            if items * cand <= SM_COUNT * 2 and key_tiles >= cand * MIN_KEY_TILES_PER_SPLIT:
-                splits = cand
-                break
+    splits = decode_splits(len(work) * num_kv_heads, ctx.max_seq_len) if decode else 1
     plan = (work_dev, len(work), 1 if decode else 0, splits, tc_dev, len(tc_work))
     ctx.extras[key] = plan
     return plan

@@ -219,3 +219,22 @@ def test_many_requests_through_a_tight_pool_equal_one_by_one(folders, key, pool,
     if preempts:
         assert metrics["preemptions"] > 0               # the pool really was too small for the load
     tight.engine.cache.check()
+
+
+def test_a_long_generation_from_a_short_prompt_is_cut_anew_as_it_grows(folders):
+    """A captured decode step freezes how many CTAs share a sequence's keys.  Captured after a 3-token prompt
+    that is one; 200 tokens later the step must have been planned and captured again (several CTAs), and the
+    tokens must still be those of the kernel-by-kernel path."""
+    from microllm_rocm_b200 import GenerationConfig
+    key = "b"
+    prompt = random_tokens(3, tiny_config(key).vocab_size, 11)
+    cfg = GenerationConfig(max_new_tokens=200, temperature=0.0)
+    want = llm_for(folders[key], "float32", max_tokens=1024, cuda_graphs=False).generate([prompt], cfg)[0]
+    graphed = llm_for(folders[key], "float32", max_tokens=1024)
+    assert graphed.generate([prompt], cfg)[0] == want             # (the fp32 attention kernel has no key split to re-plan)
+    bf16 = llm_for(folders[key], "bfloat16", max_tokens=1024)
+    got = bf16.generate([prompt], cfg)[0]
+    assert bf16.graphs.captures >= 2, bf16.graphs.captures
+    ref = plain_logits(folders[key], prompt + got[:-1], "bfloat16")[len(prompt) - 1:]
+    for i, t in enumerate(got):                                    # each pick is a (near) maximum of the plain bf16 logits
+        assert float(ref[i].max() - ref[i, t]) <= 0.03 * float(ref[i].abs().max()), (i, t)

@@ -187,6 +187,22 @@ def test_paged_attention_prompts_and_decodes_in_one_batch(dtype, nh, nkv, d, win
     assert torch.allclose(got, want, **tol(dtype)), float((got - want).abs().max())
 
 
+@pytest.mark.parametrize("nh,nkv,d", [(12, 2, 128), (4, 4, 64), (6, 1, 64)])
+def test_decode_step_of_long_and_short_sequences_shares_one_key_split(nh, nkv, d):
+    """One decode step for sequences of 1,500, 20, 300 and 1 cached tokens: the number of CTAs that share a
+    (sequence, kv head) is chosen for the longest, so the short sequences leave most of those CTAs without
+    a single key tile; their empty shares must drop out of the merge."""
+    torch.manual_seed(nh + d)
+    lens = [1500, 20, 300, 1]
+    ks = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+    vs = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+    qs = [torch.randn(1, nh, d).bfloat16().float() for _ in lens]
+    got = run_attention(qs, ks, vs, [n - 1 for n in lens], nh, nkv, d, None, torch.bfloat16, num_pages=130)
+    want = torch.cat([plain_attention_rows(q, k, v, n - 1, None).reshape(1, nh * d) for q, k, v, n in zip(qs, ks, vs, lens)])
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, **tol(torch.bfloat16)), float((got - want).abs().max())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_one_far_key_among_hundreds_dominates(dtype):
     """Query and one key far back are scaled so that their score stands out: the output must
