@@ -195,3 +195,49 @@ def test_window_group_lets_a_long_request_run_in_a_small_pool():
     h.run()
     assert h.s.requests[rid].generated == oracle(list(range(30)), cfg)
     assert h.cache.pages_released_by_window > 0
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_arrivals_cancellations_and_tight_pools_keep_the_books_and_the_tokens(seed):
+    """Random prompts, lengths, stop tokens, arrival times and cancellations against pools of random
+    tightness (some with a window group): after every step the cache's books are consistent; every request
+    that was not cancelled ends with exactly the oracle's tokens, whatever was preempted and recomputed on
+    the way; in the end nothing is held."""
+    import random
+    rng = random.Random(seed)
+    page = rng.choice([2, 4, 8])
+    longest = 60
+    window = rng.choice([None, None, 8, 16])
+    pages = rng.randint(-(-(longest + 24) // page) + 1, 3 * (longest + 24) // page)
+    h = Harness(num_pages=pages, page_size=page, max_requests=rng.randint(2, 6), budget=rng.choice([3, 8, 16, 64]),
+                max_seqs=rng.randint(2, 6), window=window)
+    todo = []
+    for _ in range(25):
+        prompt = [rng.randrange(VOCAB) for _ in range(rng.randint(1, longest))]
+        stops = tuple(rng.sample(range(VOCAB), rng.choice([0, 0, 3])))
+        todo.append((prompt, GenerationConfig(max_new_tokens=rng.randint(0, 24), temperature=0.0, stop_tokens=stops)))
+    submitted, cancelled = [], set()
+    steps = 0
+    while todo or h.s.has_work():
+        for _ in range(rng.randrange(0, 3)):
+            if todo:
+                prompt, cfg = todo.pop()
+                submitted.append((h.s.submit(prompt, cfg), prompt, cfg))
+        if submitted and rng.random() < 0.08:
+            rid = rng.choice(submitted)[0]
+            if h.s.requests[rid].state in (RequestState.WAITING, RequestState.RUNNING) and h.s.cancel(rid):
+                cancelled.add(rid)
+                h.fed.pop(rid, None)
+        if h.s.has_work():
+            h.step()
+        steps += 1
+        assert steps < 20000, "the scheduler makes no progress"
+    for rid, prompt, cfg in submitted:
+        r = h.s.requests[rid]
+        if rid in cancelled:
+            assert r.state == RequestState.CANCELLED and r.generated == oracle(prompt, cfg)[:len(r.generated)]
+        else:
+            assert r.state == RequestState.COMPLETED and r.generated == oracle(prompt, cfg), (rid, r.preemptions)
+    h.cache.check()
+    stats = h.cache.stats()
+    assert not h.cache.requests and all(stats[g]["used"] == 0 for g in h.cache.groups)
