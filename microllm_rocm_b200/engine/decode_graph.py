@@ -22,7 +22,7 @@ import torch
 from ..kernels import ops
 from ..parts.base import StepContext
 from ..sampling.config import GenerationConfig
-from .step import Engine, OutOfPages, StepError, device_error_text
+from .step import Engine, StepError, device_error_text
 
 
 def graph_capable(engine: Engine) -> bool:

@@ -33,7 +33,7 @@ import enum
 import time
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Deque, Dict, List, Optional, Sequence
 
 from ..sampling.config import GenerationConfig
 

@@ -14,7 +14,6 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..config.spec import ModelSpec
-from . import base
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Part, Runtime,
                    StepContext, WeightSpec, make)
 
