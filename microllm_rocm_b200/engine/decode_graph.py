@@ -224,11 +224,13 @@ class DecodeGraph:
 
 
 class DecodeGraphPool:
-    """Captured decode steps by batch size and table width; built on first use."""
+    """Captured decode steps by batch size and table width; built on first use.  At most `max_graphs` are
+    kept (each owns its activations and a captured graph): the one used longest ago goes first."""
 
-    def __init__(self, engine: Engine):
+    def __init__(self, engine: Engine, max_graphs: int = 32):
         self.engine = engine
-        self.graphs: Dict[tuple, DecodeGraph] = {}
+        self.max_graphs = max(1, int(max_graphs))
+        self.graphs: Dict[tuple, DecodeGraph] = {}          # insertion order = order of last use
         self.captures = 0
 
     def get(self, requests: Sequence[Hashable], headroom_tokens: int = 0) -> DecodeGraph:
@@ -239,10 +241,12 @@ class DecodeGraphPool:
             need = max(need, max(len(cache.requests[q].tables[g]) for q in requests))
             widths[g] = max(8, _round_up_pow2(need))
         key = (len(requests), tuple(sorted(widths.items())))
-        graph = self.graphs.get(key)
+        graph = self.graphs.pop(key, None)
         if graph is None:
+            while len(self.graphs) >= self.max_graphs:
+                del self.graphs[next(iter(self.graphs))]
             graph = DecodeGraph(self.engine, len(requests), widths)
-            self.graphs[key] = graph
+        self.graphs[key] = graph                             # (re)inserted last: most recently used
         return graph
 
     def ensure_captured(self, graph: DecodeGraph) -> None:
