@@ -72,7 +72,8 @@ class CacheManager:
                 self.entry_group[name] = key
                 if device is not None:
                     self.kv_storage[name] = torch.zeros(
-                        (num_pages, 2, need.num_kv_heads, page_size, need.head_dim), dtype=kv_dtype, device=device)
+                        (num_pages, 2, need.num_kv_heads, page_size, need.head_dim), dtype=need.dtype or kv_dtype,
+                        device=device)
             elif isinstance(need, FixedStateNeed):
                 self.state_needs[name] = need
                 if device is not None:

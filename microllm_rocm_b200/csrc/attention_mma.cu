@@ -1074,19 +1074,9 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_t_kernel(F
 
 }  // namespace
 
-// up to this many CTAs the decode shape runs eight warps per CTA (MLB_FA_WIDE_LIMIT overrides, for measurements)
-static int wide_limit() {
-    static int limit = -1;
-    if (limit < 0) { const char* e = getenv("MLB_FA_WIDE_LIMIT"); limit = e ? atoi(e) : 48; }
-    return limit;
-}
-
-// MLB_FA_KEYS_ON_M=0 keeps groups of up to 8 heads on the kernel with queries on the 16-row side (for measurements)
-static bool keys_on_m_enabled() {
-    static int on = -1;
-    if (on < 0) { const char* e = getenv("MLB_FA_KEYS_ON_M"); on = (e && e[0] == '0') ? 0 : 1; }
-    return on == 1;
-}
+// up to this many CTAs the decode shape runs eight warps per CTA (measured: one sequence of two kv heads gains,
+// eight sequences lose)
+constexpr int WIDE_LIMIT_CTAS = 48;
 
 MLB_EXPORT int mlb_fa_head_dim() { return D; }
 MLB_EXPORT int mlb_fa_max_splits() { return MAX_SPLITS; }
@@ -1114,7 +1104,8 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
                block_table, work, max_blocks, num_pages, page_size, num_heads, num_kv_heads,
                num_heads / num_kv_heads, window, scale * LOG2E, (page_size & (page_size - 1)) == 0 ? __builtin_ctz((unsigned)page_size) : -1, error_flag};
     if (mode == 0) {
-        static bool prefill_configured = false;
+        static bool prefill_configured_on[MAX_DEVICES] = {false};
+        bool& prefill_configured = prefill_configured_on[device_index()];
         if (!prefill_configured) {
             cudaError_t e = cudaFuncSetAttribute(fa_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM);
             if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "fa_prefill: cannot reserve %d bytes of shared memory: %s",
@@ -1125,10 +1116,11 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
         return check_launch("fa_prefill");
     }
     // a handful of CTAs (one or two sequences): eight warps each; otherwise four warps, two CTAs per SM
-    const bool wide = (long long)num_work * num_kv_heads * splits <= wide_limit();
+    const bool wide = (long long)num_work * num_kv_heads * splits <= WIDE_LIMIT_CTAS;
     // groups of at most 8 heads: the kernel with keys on the 16-row side of the MMA (half the work per key)
-    const bool keys_on_m = p.group <= 8 && D % 64 == 0 && USE_PREFETCH && keys_on_m_enabled();   // two key tiles in registers
-    static bool configured = false;
+    const bool keys_on_m = p.group <= 8 && D % 64 == 0 && USE_PREFETCH;   // two key tiles in registers
+    static bool configured_on[MAX_DEVICES] = {false};
+    bool& configured = configured_on[device_index()];
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(4));
         if (e == cudaSuccess)
@@ -1159,7 +1151,11 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
     config.numAttrs = pdl_enabled() ? 2 : 1;
     if (splits > 8) {
         // the non-portable cluster size: ask once whether such a cluster can be resident at all
-        static int clusters16 = -1;
+        static int clusters16_on[MAX_DEVICES];
+        static bool clusters16_asked[MAX_DEVICES] = {false};
+        const int dev = device_index();
+        if (!clusters16_asked[dev]) { clusters16_on[dev] = -1; clusters16_asked[dev] = true; }
+        int& clusters16 = clusters16_on[dev];
         if (clusters16 < 0) {
             cudaLaunchConfig_t probe = config;
             probe.numAttrs = 1;

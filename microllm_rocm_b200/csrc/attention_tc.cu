@@ -573,7 +573,8 @@ MLB_EXPORT int mlb_paged_attention_tc(const void* q, long long ldq, const void* 
 
     TcParams p{(__nv_bfloat16*)out, ldo, seq_starts, seq_pos0, block_table, work, max_blocks, num_pages, page_size,
                BN / page_size, num_heads, num_kv_heads, num_heads / num_kv_heads, window, scale * LOG2E, error_flag};
-    static bool configured = false;
+    static bool configured_on[MAX_DEVICES] = {false};         // the attribute belongs to the device
+    bool& configured = configured_on[device_index()];
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(fa_tc_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "attention_tc: cannot reserve %d bytes of shared memory: %s",

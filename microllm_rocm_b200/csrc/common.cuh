@@ -49,6 +49,30 @@ inline int check_launch(const char* what) {
     return MLB_OK;
 }
 
+// ---- per-device facts -----------------------------------------------------------------
+// Function attributes (the dynamic shared memory a kernel may use, cluster sizes) and the number of
+// multiprocessors belong to a DEVICE, not to the process: whatever a launcher sets up once, it sets up once
+// per device, in arrays indexed by device_index().
+constexpr int MAX_DEVICES = 64;
+
+inline int device_index() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= MAX_DEVICES) d = 0;
+    return d;
+}
+
+// multiprocessors of the current device
+inline int sm_count() {
+    static int counts[MAX_DEVICES] = {0};
+    const int d = device_index();
+    if (counts[d] <= 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || n <= 0) return 1;
+        counts[d] = n;
+    }
+    return counts[d];
+}
+
 // ---- element access: all arithmetic happens in fp32 ------------------------------------
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

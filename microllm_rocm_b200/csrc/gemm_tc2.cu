@@ -1,7 +1,7 @@
 // Prompt-sized bf16 products on the fifth-generation tensor cores with CTA PAIRS:
 //     y[M, N] = x[M, K] * W[N, K]^T   (+ bias), or   y[M, I] = silu(x Wg^T) * (x Wu^T).
 //
-// Computed transposed, like gemm_tc.cu: the 256-row side of the instruction is a tile of 256
+// Computed transposed, like gemm_stream.cu: the 256-row side of the instruction is a tile of 256
 // WEIGHT rows, its N side a tile of 128 or 256 TOKENS.  A thread-block cluster of two CTAs (one
 // per SM of a TPC) shares every tile through tcgen05.mma.cta_group::2: each CTA stages HALF of
 // both operands (its 128 weight rows, its half of the tokens) and keeps its 128 accumulator
@@ -60,7 +60,6 @@ struct PairParams {
     int dual;                  // 1: silu(gate) * up; W rows n (gate) and up_offset + n (up); N counts gate rows
     int up_offset;
     int n_tiles, m_tiles;
-    int debug;                 // measurement aid: bit 0 skips the stores, bit 1 the accumulator reads too, bit 2 the MMAs, bit 3 the copies
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -206,14 +205,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                     const int s = it % p.stages;
                     const uint32_t round = it / p.stages;
-                    if (p.debug & 16) continue;
                     if (round > 0 && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, p.error_flag, 41)) { ok = false; break; }
                     const uint32_t dst = ring + (uint32_t)s * stage_bytes;
                     const uint32_t leader_full = cluster_addr(smem_u32(&full_bar[s]), 0);
-                    if (p.debug & 8) {                 // no copies: the barrier completes on the leader's arrival alone
-                        if (rank == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[s])) : "memory");
-                        continue;
-                    }
                     if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * stage_bytes);
                     const int k = kb * BLOCK_K;
                     tma_load_2d_pair(dst, &map_w, k, n0, leader_full);
@@ -240,21 +234,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                     const int s = it % p.stages;
                     // every lane polls (one broadcast read each time): no shuffle between the barrier and the issue.
                     // No tcgen05 fence here: the copies and the MMAs that read them are ordered by the mbarrier itself.
-                    if (!(p.debug & 16) && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[s]), (it / p.stages) & 1, p.error_flag, 43))) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[s]), (it / p.stages) & 1, p.error_flag, 43))) { ok = false; break; }
                     const uint32_t a_addr = ring + (uint32_t)s * stage_bytes;
                     // descriptors of the stage; a K step of 16 elements moves the start address (16-byte units) by 2
                     const uint64_t adesc = umma_desc(a_addr), bdesc = umma_desc(a_addr + a_bytes), udesc = umma_desc(a_addr + A_TILE_BYTES);
                     if (elect_one()) {
-                        if (!(p.debug & 4)) {
-                            umma_pair(acc, adesc, bdesc, idesc, kb > 0 ? 1u : 0u);
-                            if (p.dual) umma_pair(acc + (uint32_t)p.tok_tile, udesc, bdesc, idesc, kb > 0 ? 1u : 0u);
+                        umma_pair(acc, adesc, bdesc, idesc, kb > 0 ? 1u : 0u);
+                        if (p.dual) umma_pair(acc + (uint32_t)p.tok_tile, udesc, bdesc, idesc, kb > 0 ? 1u : 0u);
 #pragma unroll
-                            for (int k = 1; k < BLOCK_K / UMMA_K; ++k) {
-                                umma_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc, 1u);
-                                if (p.dual) umma_pair(acc + (uint32_t)p.tok_tile, udesc + 2 * k, bdesc + 2 * k, idesc, 1u);
-                            }
+                        for (int k = 1; k < BLOCK_K / UMMA_K; ++k) {
+                            umma_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc, 1u);
+                            if (p.dual) umma_pair(acc + (uint32_t)p.tok_tile, udesc + 2 * k, bdesc + 2 * k, idesc, 1u);
                         }
-                        if (!(p.debug & 32)) umma_commit_pair(smem_u32(&empty_bar[s]));  // the stage is free in both CTAs once these MMAs have read it
+                        umma_commit_pair(smem_u32(&empty_bar[s]));  // the stage is free in both CTAs once these MMAs have read it
                     }
                     __syncwarp();
                 }
@@ -277,12 +269,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             const uint32_t lane_addr = tmem_base + buf * acc_cols + ((uint32_t)(quarter * 32) << 16);
             const float bias = (p.bias && f < p.N) ? p.bias[f] : 0.0f;
             for (int c = 0; c < p.tok_tile; c += 32) {
-                if (tok0 + c >= p.M || (p.debug & 2)) break;
+                if (tok0 + c >= p.M) break;
                 uint32_t raw[32], raw_u[32];
                 tmem_ld32_nowait(lane_addr + (uint32_t)c, raw);
                 if (p.dual) tmem_ld32_nowait(lane_addr + (uint32_t)(p.tok_tile + c), raw_u);
                 tmem_wait();
-                if (f >= p.N || (p.debug & 1)) continue;
+                if (f >= p.N) continue;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int tok = tok0 + c + j;
@@ -365,11 +357,6 @@ MLB_EXPORT int mlb_gemm_pair(const void* x, long long ldx, const void* w, long l
     p.tok_tile = dual ? 128 : 256;
     p.k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
     p.out_bf16 = out_bf16; p.accumulate = accumulate; p.dual = dual; p.up_offset = up_offset;
-    {
-        static int debug = -1;
-        if (debug < 0) { const char* e = getenv("MLB_GEMM_DEBUG"); debug = e ? atoi(e) : 0; }
-        p.debug = debug;
-    }
     p.n_tiles = (N + PAIR_W - 1) / PAIR_W;
     p.m_tiles = (M + p.tok_tile - 1) / p.tok_tile;
     const int stage_bytes = (dual ? 2 : 1) * A_TILE_BYTES + (p.tok_tile / 2) * BLOCK_K * 2;
@@ -384,7 +371,8 @@ MLB_EXPORT int mlb_gemm_pair(const void* x, long long ldx, const void* w, long l
     status = make_map(&map_x, x, M, K, ldx, p.tok_tile / 2);
     if (status != MLB_OK) return status;
 
-    static bool configured = false;
+    static bool configured_on[MAX_DEVICES] = {false};         // the attribute belongs to the device
+    bool& configured = configured_on[device_index()];
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(220 * 1024));
         if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "gemm_pair: cannot reserve shared memory: %s", cudaGetErrorString(e));

@@ -16,9 +16,9 @@
 // With DUAL two weight row blocks (gate rows r.., up rows up_offset + r..) run against the
 // same activations and silu(gate) * up is stored as bf16 (no split: the activation is not linear).
 //
-// The tensor-memory kernel (gemm_tc.cu) pays a fixed price per 64-wide K block (barrier
-// hand-offs and one dependent tcgen05.mma chain) that only amortises over larger token
-// tiles; for M <= 16 this kernel reaches a higher share of the memory bandwidth.  The
+// The tensor-memory kernel (gemm_stream.cu) pays a fixed price per launch (barrier set-up,
+// tensor-memory allocation, one dependent tcgen05.mma chain) that amortises over larger token
+// counts; up to 8 tokens this kernel is the one the engine uses.  The
 // reference calls hipBLASLt for every projection whatever the batch
 // (src/ops/optimized.cpp:44-70).
 #include "common.cuh"
@@ -34,7 +34,8 @@ namespace {
 
 template <int NT, bool DUAL>
 int launch(const GemvParams& p, int splits, size_t smem, cudaStream_t stream) {
-    static size_t configured = 0;
+    static size_t configured_on[MAX_DEVICES] = {0};            // the attribute belongs to the device
+    size_t& configured = configured_on[device_index()];
     if (smem > 48 * 1024 && smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(gemv_bf16_kernel<NT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "gemv_bf16: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));

@@ -357,7 +357,9 @@ MLB_EXPORT int mlb_gemv_silu(const void* x, long long ldx, const void* w, long l
     const int nt = M <= 8 ? 1 : 2;
     SiluParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldx, ldw, ldo, M, I, K, up_offset, x_pitch(K)};
     const size_t smem = (size_t)nt * 8 * p.x_stride * 2 + (size_t)SILU_WARPS * 2 * nt * 4 * 32 * sizeof(float);
-    static size_t configured1 = 0, configured2 = 0;
+    static size_t configured1_on[MAX_DEVICES] = {0}, configured2_on[MAX_DEVICES] = {0};   // per device, as the attribute is
+    size_t& configured1 = configured1_on[device_index()];
+    size_t& configured2 = configured2_on[device_index()];
     const unsigned blocks = (unsigned)((I + 15) / 16);
     if (nt == 1) {
         status = reserve(gemv_silu_kernel<1>, smem, configured1, "gemv_silu");
@@ -392,7 +394,9 @@ MLB_EXPORT int mlb_gemv_qkv_rope(const void* x, long long ldx, const void* w, lo
                 inv_freq, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pages, max_blocks, num_pages, page_size, num_heads, num_kv_heads,
                 head_dim, rotate ? 1 : 0, error_flag};
     const size_t smem = (size_t)nt * 8 * p.x_stride * 2 + (size_t)QKV_WARPS * nt * 4 * 32 * sizeof(float);
-    static size_t configured1 = 0, configured2 = 0;
+    static size_t configured1_on[MAX_DEVICES] = {0}, configured2_on[MAX_DEVICES] = {0};   // per device, as the attribute is
+    size_t& configured1 = configured1_on[device_index()];
+    size_t& configured2 = configured2_on[device_index()];
     const unsigned blocks = (unsigned)((num_heads + 2 * num_kv_heads) * (head_dim / 16));
     if (nt == 1) {
         status = reserve(gemv_qkv_rope_kernel<1>, smem, configured1, "gemv_qkv_rope");
@@ -419,7 +423,9 @@ MLB_EXPORT int mlb_gemv_split(const void* x, long long ldx, const void* w, long 
     const int nt = M <= 8 ? 1 : 2;
     SplitParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, partial, ldx, ldw, M, N, K, k_per_cta, x_pitch(k_per_cta)};
     const size_t smem = (size_t)nt * 8 * p.x_stride * 2 + (size_t)SPLIT_WARPS * nt * 4 * 32 * sizeof(float);
-    static size_t configured1 = 0, configured2 = 0;
+    static size_t configured1_on[MAX_DEVICES] = {0}, configured2_on[MAX_DEVICES] = {0};   // per device, as the attribute is
+    size_t& configured1 = configured1_on[device_index()];
+    size_t& configured2 = configured2_on[device_index()];
     const dim3 grid((unsigned)((N + 15) / 16), (unsigned)splits);
     if (nt == 1) {
         status = reserve(gemv_split_kernel<1>, smem, configured1, "gemv_split");

@@ -17,8 +17,20 @@
  *     in the regular path).  A product that needs more is refused with
  *     MLB_UNSUPPORTED_SIZE and a message; nothing is launched.
  *   - The first call on a device looks up the array's device address
- *     (cudaGetSymbolAddress) and remembers it.  Make that first call outside any CUDA stream
- *     capture.
+ *     (cudaGetSymbolAddress), the device's multiprocessor count and, for long K ranges, raises
+ *     the kernel's shared-memory limit, and remembers all three (behind a mutex: first calls
+ *     from several host threads are safe).  Make that first call outside any CUDA stream
+ *     capture.  With CUDA's default lazy module loading it is also the moment the driver
+ *     loads this library's module on that device and backs the 16 MiB array: that one call
+ *     therefore does reserve device memory, may synchronise, and can fail for lack of memory.
+ *     Treat it as a warm-up to make at initialisation, while allocating is still allowed;
+ *     every later call on that device allocates nothing.
+ *   - The kernel is launched with programmatic stream serialisation and fetches W before it
+ *     waits for the kernel in front of it on the stream (x, bias and out are touched only
+ *     after that wait).  W must therefore not be written by the kernel launched immediately
+ *     before this call on the same stream (a dequantisation or a weight copy, say); if it is,
+ *     put another launch or an event in between, or set MLB_PDL=0 in the environment, which
+ *     turns the early start off for the whole library.
  *   - All calls share the one array, and it keeps whatever the last call left in it.  Nothing
  *     in it has to be zero: every element a call reads it has written first.  Two calls that
  *     may run at the same time on the GPU (different streams, no ordering between them) race
@@ -37,11 +49,13 @@ extern "C" {
 #define MLB_GEMV_NOALLOC_SCRATCH_FLOATS (4u << 20)
 
 /* x: [M, ldx] bf16, w: [N, ldw] bf16, bias: [N] fp32 or NULL, out: [M, ldo] fp32.
- * K a multiple of 32, ldx and ldw multiples of 8, x and w 16-byte aligned. */
+ * K a multiple of 32, ldx and ldw multiples of 8, x and w 16-byte aligned; a NULL x, w or out is
+ * refused with MLB_INVALID_ARGUMENT before anything is launched. */
 int mlb_gemv_bf16_noalloc(const void* x, long long ldx, const void* w, long long ldw, const float* bias, float* out,
                           long long ldo, int M, int N, int K, cudaStream_t stream);
 
-/* Floats of scratch the product above would need, or -1 if its sizes are refused anyway. */
+/* Floats of scratch the product above would need on the current device (the split follows its
+ * multiprocessor count), or -1 if its sizes are refused anyway. */
 long long mlb_gemv_bf16_noalloc_scratch_needed(int M, int N, int K);
 
 #ifdef __cplusplus

@@ -123,8 +123,8 @@ __device__ __forceinline__ void store4(__nv_bfloat16* dst, const float (&v)[4]) 
 // elements i..i+3 and i+D/2..i+D/2+3 travel as 16-byte pieces.  V heads copy eight elements.
 template <typename QT, typename KVT>
 __global__ void rope_kv_split_half_x4_kernel(RopeKvParams p) {
-    // Everything that does not come from the projection before this kernel is fetched and computed before
-    // the wait for it: the position, the angles' sines and cosines, the bias, the page of the cache.
+    // Everything that no kernel of this step writes is fetched and computed before the wait: the position, the
+    // bias, the page of the cache, and the angles' sines and cosines when they are computed here.
     pdl_launch_dependents();
     const int half = p.head_dim / 2, quads = half / 4;
     const int heads_all = p.num_heads + 2 * p.num_kv_heads;
@@ -147,12 +147,7 @@ __global__ void rope_kv_split_half_x4_kernel(RopeKvParams p) {
             bb = *reinterpret_cast<const float4*>(p.bias + col + i + half);
         }
         pos = p.positions[t];
-        if (!is_v && p.cos_sin) {
-            // a step's table, made once for all layers and heads (written long before this kernel's predecessor)
-            const float4 u = *reinterpret_cast<const float4*>(p.cos_sin + (size_t)t * half + i);
-            const float4 v = *reinterpret_cast<const float4*>(p.cos_sin + (size_t)t * half + i + 2);
-            cs[0] = u.x; sn[0] = u.y; cs[1] = u.z; sn[1] = u.w; cs[2] = v.x; sn[2] = v.y; cs[3] = v.z; sn[3] = v.w;
-        } else if (!is_v) {
+        if (!is_v && !p.cos_sin) {
             const float4 f = *reinterpret_cast<const float4*>(p.inv_freq + i);
             const float fr[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
@@ -165,6 +160,14 @@ __global__ void rope_kv_split_half_x4_kernel(RopeKvParams p) {
     }
     pdl_wait();
     if (!working) return;
+    if (!is_v && p.cos_sin) {
+        // A step's table, made once for all layers and heads.  It is written by a kernel of THIS step (in the first
+        // layer by the kernel launched just before this one), so it may only be read behind the wait: kernels
+        // that sit in front of their waits can all be resident while the table's kernel has not run yet.
+        const float4 u = *reinterpret_cast<const float4*>(p.cos_sin + (size_t)t * half + i);
+        const float4 v = *reinterpret_cast<const float4*>(p.cos_sin + (size_t)t * half + i + 2);
+        cs[0] = u.x; sn[0] = u.y; cs[1] = u.z; sn[1] = u.w; cs[2] = v.x; sn[2] = v.y; cs[3] = v.z; sn[3] = v.w;
+    }
     const float* src = p.qkv + (size_t)t * p.ld + col;
     // V has nothing to rotate: its two pieces are simply elements i.. and i+half..
     float4 a = *reinterpret_cast<const float4*>(src + i), b = *reinterpret_cast<const float4*>(src + i + half);

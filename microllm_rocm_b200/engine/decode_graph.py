@@ -170,14 +170,13 @@ class DecodeGraph:
 
     def stale(self, max_seq_len: int) -> bool:
         """The captured step was cut for another context length than the one it is about to serve."""
-        from ..kernels import attention
-        return self.graph is not None and attention.decode_plan_stale(self.ctx, max_seq_len)
+        return self.graph is not None and any(b.mixer.plan_stale(self.ctx, max_seq_len) for b in self.engine.model.blocks)
 
     def invalidate(self) -> None:
         """Forget the captured step and the launch plans frozen into it; the next capture plans anew."""
-        from ..kernels import attention
         self.graph = None
-        attention.forget_plans(self.ctx)
+        for block in self.engine.model.blocks:
+            block.mixer.forget_plans(self.ctx)
 
     def fits(self, requests: Sequence[Hashable]) -> bool:
         cache = self.engine.cache

@@ -44,17 +44,12 @@ def require_gpu(device: Optional[str] = None) -> torch.device:
 
 def prepare_kernels(model=None) -> None:
     """Compile, at once and in parallel, every kernel object this model will ask for."""
-    from ..kernels import attention
     sources = ops.base_sources()
-    if model is not None and model.rt.dtype == torch.bfloat16:
-        from ..kernels import gemm_bf16
-        sources += gemm_bf16.sources(engine_only=True)
-        for entry in model.cache_entries.values():
-            head_dim = getattr(entry.need, "head_dim", None)
-            if head_dim:
-                for item in attention.mma_sources(head_dim) + attention.tc_sources(head_dim):
-                    if item not in sources:
-                        sources.append(item)
+    if model is not None:
+        for part in model.parts():
+            for item in part.kernel_sources():
+                if item not in sources:
+                    sources.append(item)
     kernel_build.compile_many(sources)
 
 

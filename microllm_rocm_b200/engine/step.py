@@ -186,10 +186,3 @@ class Engine:
         if code:
             self.error_flag.zero_()
             raise StepError(device_error_text(code))
-        if self.model.rt.dtype == torch.bfloat16:
-            from ..kernels import gemm_bf16
-            flag = gemm_bf16.error_flag(self.device)
-            code = int(flag.item())
-            if code:
-                flag.zero_()
-                raise StepError(f"a bounded wait inside a tensor-core product ran out (code {code}); its results are not valid")

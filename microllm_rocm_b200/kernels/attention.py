@@ -12,7 +12,6 @@ tiles.  The two launches write disjoint rows of the output.
 """
 from __future__ import annotations
 
-import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -20,11 +19,11 @@ import torch
 
 from . import build, ops
 from .build import KernelError
+from .device import DEFAULT_SM_COUNT, sm_count
 
 MAX_HEAD_DIM = 256
-SM_COUNT = 148
 MIN_KEY_TILES_PER_SPLIT = 4         # one 16-key tile per warp at least
-DECODE_SPLITS = tuple(int(v) for v in os.environ.get("MLB_FA_DECODE_SPLITS", "16,8,4,2").split(","))   # cluster sizes tried, largest first
+DECODE_SPLITS = (16, 8, 4, 2)       # cluster sizes tried, largest first
 WIDE_CLUSTER_CTAS = 48              # measured: one sequence of two kv heads gains 3 % from clusters of 16, eight sequences lose 10 %
 
 TC_HEAD_DIMS = (64, 128)
@@ -66,26 +65,27 @@ def tc_sources(head_dim: int):
     return [("attention_tc.cu", {"HEAD_DIM": head_dim})] if head_dim in TC_HEAD_DIMS else []
 
 
-def decode_splits(items: int, max_seq_len: int) -> int:
+def decode_splits(items: int, max_seq_len: int, sms: int = DEFAULT_SM_COUNT) -> int:
     """How many CTAs (one thread-block cluster) share the keys of one (sequence, kv head) in a decode step:
-    as many as still fit the GPU in one wave (two CTAs per SM) and leave every warp a key tile."""
+    as many as still fit the GPU's `sms` multiprocessors in one wave (two CTAs per SM) and leave every warp a
+    key tile."""
     key_tiles = max(1, -(-max_seq_len // 16))
     items = max(1, items)
     for cand in DECODE_SPLITS:
         if cand > 8 and items * cand > WIDE_CLUSTER_CTAS:
             continue          # clusters of 16 pay only while the whole grid is a handful of (eight-warp) CTAs
-        if items * cand <= SM_COUNT * 2 and key_tiles >= cand * MIN_KEY_TILES_PER_SPLIT:
+        if items * cand <= sms * 2 and key_tiles >= cand * MIN_KEY_TILES_PER_SPLIT:
             return cand
     return 1
 
 
-def decode_plan_stale(ctx, max_seq_len: int) -> bool:
+def decode_plan_stale(ctx, max_seq_len: int, sms: int = DEFAULT_SM_COUNT) -> bool:
     """Whether a decode step planned for `ctx` (its plans are kept in ctx.extras, and frozen into a captured
     graph) would be cut differently at this context length: a step captured at a short context has one CTA
     per (sequence, kv head) and must not serve a context of thousands that way."""
     for key, plan in ctx.extras.items():
         if isinstance(key, tuple) and key and key[0] == "attention_mma" and plan[2] == 1:
-            if decode_splits(plan[1] * key[2], max_seq_len) != plan[3]:
+            if decode_splits(plan[1] * key[2], max_seq_len, sms) != plan[3]:
                 return True
     return False
 
@@ -121,7 +121,7 @@ def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
     device = ctx.positions.device
     work_dev = torch.tensor(work, dtype=torch.int32).reshape(-1).to(device, non_blocking=True)
     tc_dev = torch.tensor([(a, t) for _, a, t in tc_work], dtype=torch.int32).reshape(-1).to(device, non_blocking=True)
-    splits = decode_splits(len(work) * num_kv_heads, ctx.max_seq_len) if decode else 1
+    splits = decode_splits(len(work) * num_kv_heads, ctx.max_seq_len, sm_count(device)) if decode else 1
     plan = (work_dev, len(work), 1 if decode else 0, splits, tc_dev, len(tc_work))
     ctx.extras[key] = plan
     return plan

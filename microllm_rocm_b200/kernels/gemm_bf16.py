@@ -1,16 +1,16 @@
 """bf16 x bf16 -> fp32-accumulated products of the serving path.
 
 Who takes which product (`linear_bf16`, and the parts for their fused forms):
-  up to 8 tokens     the weight-streaming kernels (`gemv_bf16.cu`, `gemv_fused.cu`)
-  256 tokens and up  gate/up with its activation: the CTA-pair tcgen05 kernel (`gemm_tc2.cu`)
-  everything else    the library product, cuBLASLt called through `gemm_lib.cu` (or through torch.mm
-                     when a bias has to be added or cuBLASLt cannot be taken from the process)
-`gemm_tc.cu` (tcgen05, one CTA per tile) takes every product whose K and row pitches are multiples of
-8 elements; it is kept for comparison and is not on the engine's path.
+  up to 8 tokens      the weight-streaming mma.sync kernels (`gemv_bf16.cu`, `gemv_fused.cu`)
+  9 to 128 tokens     the weight-streaming tcgen05 kernel (`gemm_stream.cu`): fp32 partial results for QKV, O,
+                      down and the head; gate/up with its activation as the epilogue
+  256 tokens and up   gate/up with its activation: the CTA-pair tcgen05 kernel (`gemm_tc2.cu`)
+  everything else     the library product, cuBLASLt called through `gemm_lib.cu` (or through torch.mm when a
+                      bias has to be added or cuBLASLt cannot be taken from the process)
+Grid sizes and K splits follow the multiprocessor count of the device the operands live on.
 """
 from __future__ import annotations
 
-import os
 from ctypes import c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -18,10 +18,7 @@ import torch
 
 from . import build, ops
 from .build import KernelError, LaunchCounter
-
-SM_COUNT = 148
-MAX_SPLITS = 32
-MIN_K_BLOCKS_PER_SPLIT = 4          # 256 elements of K per CTA at least
+from .device import DEFAULT_SM_COUNT, sm_count
 
 ops.register_signatures("gemv_bf16.cu", {
     "mlb_gemv_bf16": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int,
@@ -45,18 +42,17 @@ ops.register_signatures("gemm_tc2.cu", {
     "mlb_gemm_pair": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int,
                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
 })
-ops.register_signatures("gemm_tc.cu", {
-    "mlb_gemm_tc": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int,
-                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+ops.register_signatures("gemm_stream.cu", {
+    "mlb_gemm_stream_max_tokens": [],
+    "mlb_gemm_stream_splits": [c_int, c_int],
+    "mlb_gemm_stream": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                        c_int, c_void_p, c_void_p],
+    "mlb_gemm_stream_silu": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_int,
+                             c_int, c_int, c_void_p, c_void_p],
 })
 
-USE_TENSOR_CORE_KERNEL = True
-USE_GEMV_SPLIT = os.environ.get("MLB_GEMV_SPLIT", "1") != "0"
-_tickets = {}
 _error_flags = {}
 
-
-USE_DIRECT_LIBRARY = os.environ.get("MLB_DIRECT_CUBLASLT", "1") != "0"
 LIBRARY_WORKSPACE_BYTES = 32 << 20
 _workspaces = {}
 _direct_ok = None
@@ -64,16 +60,15 @@ _direct_ok = None
 
 def sources(engine_only: bool = False):
     """The objects of this module; with engine_only just those that a model's step can reach."""
-    used = [("gemm_tc2.cu", {}), ("gemv_bf16.cu", {}), ("gemv_fused.cu", {}), ("gemm_lib.cu", {})]
-    return used if engine_only else [("gemm_tc.cu", {})] + used
+    return [("gemm_tc2.cu", {}), ("gemm_stream.cu", {}), ("gemv_bf16.cu", {}), ("gemv_fused.cu", {}), ("gemm_lib.cu", {})]
 
 
 # ------------------------------------------------------------------------------ few tokens: weight streaming
-GEMV_MAX_TOKENS = 16                  # what the weight-streaming kernels can take
+GEMV_MAX_TOKENS = 16                  # what the mma.sync weight-streaming kernels can take
 # ...and up to where the engine sends them: from 9 tokens on (a second 8-token column block per fragment) the
-# library's product with separate rotation / activation kernels is faster (1.63 ms against 1.88 for a batch-9 step)
-GEMV_ROUTE_MAX_TOKENS = int(os.environ.get("MLB_GEMV_ROUTE_MAX_TOKENS", "8"))
-GEMV_TARGET_CTAS = SM_COUNT * 4
+# tcgen05 streaming kernel is the faster one
+GEMV_ROUTE_MAX_TOKENS = 8
+GEMV_CTAS_PER_SM = 4                  # CTAs the one-warp-per-range kernel aims at
 GEMV_MIN_K_PER_SPLIT = 256
 
 
@@ -83,10 +78,10 @@ def gemv_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.stride(1) == 1 and weight.stride(1) == 1 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def gemv_splits(n: int, k: int):
+def gemv_splits(n: int, k: int, sms: int = DEFAULT_SM_COUNT):
     """(splits, k_per_split): enough CTAs to fill the GPU, K ranges of whole 32-element chunks."""
     row_blocks = -(-n // 64)
-    splits = max(1, min(-(-GEMV_TARGET_CTAS // row_blocks), k // GEMV_MIN_K_PER_SPLIT))
+    splits = max(1, min(-(-GEMV_CTAS_PER_SM * sms // row_blocks), k // GEMV_MIN_K_PER_SPLIT))
     k_per_split = -(-(-(-k // splits)) // 32) * 32
     while k_per_split * 2 * 16 > 160 * 1024:                 # the staged activations must fit shared memory
         k_per_split = -(-(k_per_split // 2) // 32) * 32
@@ -98,10 +93,11 @@ def gemv_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
     taken in order by the kernel that consumes them, is the product."""
     M, K = x.shape
     N = weight.shape[0]
-    plan = gemv_split_plan(N, K) if x.dtype == torch.bfloat16 and USE_GEMV_SPLIT and M >= GEMV_SPLIT_MIN_TOKENS else None
+    sms = sm_count(x.device)
+    plan = gemv_split_plan(N, K, sms) if x.dtype == torch.bfloat16 and M >= GEMV_SPLIT_MIN_TOKENS else None
     if plan is not None:
         return gemv_split_partials(x, weight, bias, *plan)
-    splits, k_per_split = gemv_splits(N, K)
+    splits, k_per_split = gemv_splits(N, K, sms)
     partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
     L = ops.lib("gemv_bf16.cu")
     build.check(L, L.mlb_gemv_bf16(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), N, ops._ptr(bias),
@@ -123,17 +119,17 @@ def gemv_fused_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
     return gemv_supported(x, weight) and x.shape[1] <= GEMV_FUSED_MAX_K and x.dtype == torch.bfloat16
 
 
-GEMV_SPLIT_TARGET_CTAS = int(os.environ.get("MLB_GEMV_SPLIT_CTAS", str(2 * SM_COUNT)))   # eight-warp CTAs, two per SM
+GEMV_SPLIT_CTAS_PER_SM = 2              # eight-warp CTAs, two per SM
 GEMV_SPLIT_MIN_TOKENS = 8               # measured: below this the one-warp-per-range kernel is the faster one (1.205 against 1.226 ms at batch 6)
-GEMV_SPLIT_MAX_TILES = 4 * SM_COUNT     # beyond this many 16-row tiles the one-warp-per-range kernel streams better
+GEMV_SPLIT_MAX_TILES_PER_SM = 4         # beyond this many 16-row tiles the one-warp-per-range kernel streams better
 
 
-def gemv_split_plan(n: int, k: int):
+def gemv_split_plan(n: int, k: int, sms: int = DEFAULT_SM_COUNT):
     """(splits, k_per_cta) for the kernel that splits K inside the CTA, or None when the other kernel suits better."""
     tiles = -(-n // 16)
-    if tiles > GEMV_SPLIT_MAX_TILES:
+    if tiles > GEMV_SPLIT_MAX_TILES_PER_SM * sms:
         return None
-    splits = max(1, min(GEMV_SPLIT_TARGET_CTAS // tiles, k // GEMV_MIN_K_PER_SPLIT))
+    splits = max(1, min(GEMV_SPLIT_CTAS_PER_SM * sms // tiles, k // GEMV_MIN_K_PER_SPLIT))
     k_per_cta = -(-(-(-k // splits)) // 32) * 32
     while k_per_cta > GEMV_FUSED_MAX_K:
         splits += 1
@@ -196,74 +192,87 @@ def gemv_qkv_rope(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
         ops._ptr(error_flag), ops._stream()))
 
 
-def _device_scratch(device):
-    key = str(device)
-    if key not in _tickets:
-        _tickets[key] = torch.zeros(1 << 16, dtype=torch.int32, device=device)      # left zero by every launch
-        _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _tickets[key], _error_flags[key]
+# ------------------------------------------------------------------------------ 9 to 128 tokens: tcgen05 weight streaming
+STREAM_MAX_TOKENS = 128               # the token side of one tcgen05.mma tile
+STREAM_MIN_K_BLOCKS_PER_SPLIT = 4     # 256 elements of K per CTA at least
+STREAM_MAX_SPLITS = 16
 
 
-def error_flag(device) -> torch.Tensor:
-    """Raised by the kernel when a bounded wait ran out (codes 11-13)."""
-    return _device_scratch(device)[1]
+def stream_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """What TMA can address: K and the row pitches multiples of 8 elements, bases 16-byte aligned."""
+    m, k = x.shape
+    return (0 < m <= STREAM_MAX_TOKENS and k % 8 == 0 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
+            and x.stride(1) == 1 and weight.stride(1) == 1 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+            and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16)
 
 
-def token_tile(m: int, dual: bool = False) -> int:
-    for t in (16, 32, 64, 128):
-        if m <= t:
-            return t
-    return 128 if dual else 256
+def stream_preferred(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return GEMV_ROUTE_MAX_TOKENS < x.shape[0] <= STREAM_MAX_TOKENS and stream_supported(x, weight)
 
 
-def choose_splits(m: int, n: int, k: int, tok_tile: int) -> int:
-    tiles = -(-n // 128) * -(-m // tok_tile)
+def stream_splits(n: int, k: int, sms: int = DEFAULT_SM_COUNT) -> int:
+    """K ranges per 128-row tile: as many as give every SM a CTA, each at least 256 elements of K long, none empty."""
+    tiles = -(-n // 128)
     k_blocks = -(-k // 64)
-    if tiles >= SM_COUNT:
-        return 1
-    return max(1, min(SM_COUNT // tiles, k_blocks // MIN_K_BLOCKS_PER_SPLIT, MAX_SPLITS))
+    splits = max(1, min(sms // tiles, k_blocks // STREAM_MIN_K_BLOCKS_PER_SPLIT, STREAM_MAX_SPLITS))
+    per = -(-k_blocks // splits)
+    return -(-k_blocks // per)
+
+
+def stream_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, splits: Optional[int] = None,
+                    stages: int = 0, error_flag: Optional[torch.Tensor] = None, alloc=None) -> torch.Tensor:
+    """[S, M, N] fp32 partial results of x @ weight^T (+ bias, in partial 0) from the tcgen05 streaming kernel."""
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise KernelError(f"stream_partials: shapes {tuple(x.shape)} x {tuple(weight.shape)}^T do not agree")
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape[0] != N):
+        raise KernelError("stream_partials: the bias must be fp32 of length N")
+    L = ops.lib("gemm_stream.cu")
+    splits = L.mlb_gemm_stream_splits(K, splits if splits is not None else stream_splits(N, K, sm_count(x.device)))
+    shape = (splits, M, N)
+    partial = alloc(shape, torch.float32) if alloc is not None else torch.empty(shape, dtype=torch.float32, device=x.device)
+    flag = error_flag if error_flag is not None else device_error_flag(x.device)
+    build.check(L, L.mlb_gemm_stream(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), N, ops._ptr(bias),
+                                     partial.data_ptr(), M, N, K, splits, int(stages), flag.data_ptr(), ops._stream()))
+    return partial
+
+
+def stream_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, stages: int = 0,
+                    error_flag: Optional[torch.Tensor] = None) -> None:
+    """out[M, I] (bf16) = silu(x @ weight[:I]^T) * (x @ weight[I:2I]^T), the activation as the product's epilogue."""
+    M, K = x.shape
+    I = out.shape[1]
+    if weight.shape != (2 * I, K) or out.shape[0] != M or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise KernelError("stream_silu_mul: the weight must hold gate rows then up rows, the output be bf16 [M, I]")
+    flag = error_flag if error_flag is not None else device_error_flag(x.device)
+    L = ops.lib("gemm_stream.cu")
+    build.check(L, L.mlb_gemm_stream_silu(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), 2 * I, I,
+                                          out.data_ptr(), out.stride(0), M, I, K, int(stages), flag.data_ptr(), ops._stream()))
+
+
+# ------------------------------------------------------------------------------ prompt portions: CTA pairs
+def device_error_flag(device) -> torch.Tensor:
+    """Where the tensor-memory kernels raise a code when one of their bounded waits ran out and the caller named
+    no flag of its own (a part run outside a step).  Inside a step the parts pass the step's flag."""
+    key = str(device)
+    if key not in _error_flags:
+        _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_flags[key]
+
+
+error_flag = device_error_flag
 
 
 def supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
     k = x.shape[1]
-    return (USE_TENSOR_CORE_KERNEL and k % 8 == 0 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
+    return (k % 8 == 0 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
             and x.stride(1) == 1 and weight.stride(1) == 1 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            accumulate: bool = False, dual_rows: Optional[int] = None, splits: Optional[int] = None,
-            tok_tile: Optional[int] = None, partial: Optional[torch.Tensor] = None, stages: int = 0) -> None:
-    """out[M, N] = x[M, K] @ weight[:N, K]^T (+ bias) (+ out), or with dual_rows = I:
-    out[M, I] = silu(x @ weight[:I]^T) * (x @ weight[I:2I]^T)."""
-    M, K = x.shape
-    dual = dual_rows is not None
-    N = dual_rows if dual else weight.shape[0]
-    if weight.shape[1] != K or out.shape != (M, N) or out.stride(1) != 1:
-        raise KernelError(f"gemm_tc: shapes {tuple(x.shape)} x {tuple(weight.shape)}^T -> {tuple(out.shape)} do not agree")
-    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype not in (torch.float32, torch.bfloat16):
-        raise KernelError("gemm_tc: bf16 operands and an fp32 or bf16 output are expected")
-    if dual and weight.shape[0] < 2 * N:
-        raise KernelError("gemm_tc: a dual product needs gate rows followed by up rows")
-    tok_tile = tok_tile or token_tile(M, dual)
-    if splits is None:
-        splits = 1 if dual else choose_splits(M, N, K, tok_tile)
-    tickets, flag = _device_scratch(x.device)
-    reduce_here = partial is None
-    if splits > 1 and reduce_here:
-        if -(-N // 128) * -(-M // tok_tile) > tickets.numel():
-            raise KernelError("gemm_tc: too many output tiles for a split product")
-        partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
-    if partial is not None and splits > 1 and (partial.shape != (splits, M, N) or partial.dtype != torch.float32):
-        raise KernelError("gemm_tc: the partial buffer must be fp32 [splits, M, N]")
-    L = ops.lib("gemm_tc.cu")
-    build.check(L, L.mlb_gemm_tc(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), weight.shape[0],
-                                 ops._ptr(bias), out.data_ptr(), out.stride(0), 1 if out.dtype == torch.bfloat16 else 0,
-                                 1 if accumulate else 0, 1 if dual else 0, N if dual else 0, M, N, K, tok_tile, splits,
-                                 1 if reduce_here else 0, int(stages), ops._ptr(partial), tickets.data_ptr(), flag.data_ptr(), ops._stream()))
-
-
 def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-              accumulate: bool = False, dual_rows: Optional[int] = None, stages: int = 0, sm_count: int = SM_COUNT) -> None:
+              accumulate: bool = False, dual_rows: Optional[int] = None, stages: int = 0, sms: Optional[int] = None,
+              error_flag: Optional[torch.Tensor] = None) -> None:
     """The CTA-pair tcgen05 product (`gemm_tc2.cu`) for prompt-sized token counts:
     out[M, N] = x[M, K] @ weight[:N]^T (+ bias) (+ out), or with dual_rows = I:
     out[M, I] = silu(x @ weight[:I]^T) * (x @ weight[I:2I]^T)."""
@@ -276,19 +285,21 @@ def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Op
         raise KernelError("gemm_pair: bf16 operands and an fp32 or bf16 output are expected")
     if dual and weight.shape[0] < 2 * N:
         raise KernelError("gemm_pair: a dual product needs gate rows followed by up rows")
-    _, flag = _device_scratch(x.device)
+    flag = error_flag if error_flag is not None else device_error_flag(x.device)
+    sms = sms if sms is not None else sm_count(x.device)
+    sms -= sms % 2                                      # whole pairs
     L = ops.lib("gemm_tc2.cu")
     build.check(L, L.mlb_gemm_pair(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), weight.shape[0],
                                    ops._ptr(bias), out.data_ptr(), out.stride(0), 1 if out.dtype == torch.bfloat16 else 0,
                                    1 if accumulate else 0, 1 if dual else 0, N if dual else 0, M, N, K, int(stages),
-                                   int(sm_count), flag.data_ptr(), ops._stream()))
+                                   int(sms), flag.data_ptr(), ops._stream()))
 
 
 def _direct_library(device) -> bool:
     """Whether cuBLASLt can be called without the tensor framework in between (csrc/gemm_lib.cu)."""
     global _direct_ok
     if _direct_ok is None:
-        _direct_ok = bool(USE_DIRECT_LIBRARY and ops.lib("gemm_lib.cu").mlb_lt_available())
+        _direct_ok = bool(ops.lib("gemm_lib.cu").mlb_lt_available())
     return _direct_ok
 
 
@@ -324,22 +335,15 @@ def library_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
     return y
 
 
-# Which kernel takes which product.  The tcgen05 kernel is correct for every size but, as it
-# stands (one CTA per tile, one accumulator, epilogue not overlapped), the library is faster
-# on prompt-sized products; it is switched in per token range once it wins there.
-TENSOR_CORE_KERNEL_TOKENS = (0, 0)          # [lo, hi): token counts routed to gemm_tc
 PAIR_MIN_TOKENS = 256                       # from here on the fused gate/up + activation of gemm_tc2 beats library + activation kernel
 
 
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
-                out: Optional[torch.Tensor], partials_ok: bool = False, alloc=None) -> torch.Tensor:
-    m = x.shape[0]
-    if partials_ok and out is None and out_dtype == torch.float32 and gemv_preferred(x, weight):
-        return gemv_partials(x, weight, bias)
-    lo, hi = TENSOR_CORE_KERNEL_TOKENS
-    if lo <= m < hi and supported(x, weight):
-        if out is None:
-            out = torch.empty((m, weight.shape[0]), dtype=out_dtype, device=x.device)
-        gemm_tc(x, weight, out, bias=bias)
-        return out
+                out: Optional[torch.Tensor], partials_ok: bool = False, alloc=None,
+                error_flag: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if partials_ok and out is None and out_dtype == torch.float32:
+        if gemv_preferred(x, weight):
+            return gemv_partials(x, weight, bias)
+        if stream_preferred(x, weight):
+            return stream_partials(x, weight, bias, error_flag=error_flag)
     return library_linear(x, weight, bias, out_dtype, out, alloc)

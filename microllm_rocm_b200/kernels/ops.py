@@ -330,11 +330,17 @@ def rope_kv_write(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: to
         num_heads, num_kv_heads, head_dim, _ptr(error_flag), _ptr(cos_sin), _stream()))
 
 
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """[T, len(inv_freq), 2] fp32: (cos, sin) of position * inverse frequency, the rotation kernels' own
     fp32 expressions; made once per step and shared by every layer."""
     _need(positions, "positions", torch.int32, 1); _need(inv_freq, "inv_freq", torch.float32, 1)
-    out = torch.empty((positions.shape[0], inv_freq.shape[0], 2), dtype=torch.float32, device=positions.device)
+    shape = (positions.shape[0], inv_freq.shape[0], 2)
+    if out is None:
+        out = torch.empty(shape, dtype=torch.float32, device=positions.device)
+    else:
+        _need(out, "out", torch.float32, 3)
+        if tuple(out.shape) != shape:
+            raise KernelError("rope_table: the output must be [T, len(inv_freq), 2]")
     L = lib("rope_kv.cu")
     build.check(L, L.mlb_rope_table(positions.data_ptr(), inv_freq.data_ptr(), out.data_ptr(), positions.shape[0],
                                     inv_freq.shape[0], _stream()))

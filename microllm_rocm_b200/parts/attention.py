@@ -71,6 +71,20 @@ class Attention(Mixer):
         self.w_o = tensors["o_proj.weight"]
         self.b_o = tensors.get("o_proj.bias")
 
+    def kernel_sources(self):
+        if self.rt.is_fp32:
+            return []
+        return (gemm_bf16.sources(engine_only=True) + attention_kernels.mma_sources(self.d)
+                + attention_kernels.tc_sources(self.d))
+
+    # --- launch plans frozen into a captured decode step ----------------------------------
+    def plan_stale(self, ctx: StepContext, max_seq_len: int) -> bool:
+        from ..kernels.device import sm_count
+        return attention_kernels.decode_plan_stale(ctx, max_seq_len, sm_count(self.rt.device))
+
+    def forget_plans(self, ctx: StepContext) -> None:
+        attention_kernels.forget_plans(ctx)
+
     # --- compute ------------------------------------------------------------------------
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVView) -> torch.Tensor:
         T = x.shape[0]
@@ -86,17 +100,20 @@ class Attention(Mixer):
                                     inv_freq if rot else None, q, pages, self.nh, self.nkv, self.d, ctx.error_flag)
         else:
             qkv = linear(x, self.w_qkv, None, torch.float32, partials_ok=True,    # [T, (NH+2NKV)*D] f32, or its partial sums
-                         alloc=lambda shape, dtype: ctx.buffer("attention.qkv", shape, dtype))
+                         alloc=lambda shape, dtype: ctx.buffer("attention.qkv", shape, dtype), error_flag=ctx.error_flag)
             cos_sin = None
             if rot and T >= ROPE_TABLE_MIN_TOKENS and x.dtype == torch.bfloat16:
                 # a prompt portion: the step's sines and cosines are made once and serve every layer and head
+                # (a result of this step's positions: it lives in step_values, which every forward starts empty,
+                # so a context that outlives its step -- a captured decode step -- never reads old angles)
                 key = ("rope_table", id(self.rotary))
-                cos_sin = ctx.extras.get(key)
+                cos_sin = ctx.step_values.get(key)
                 if cos_sin is None:
-                    cos_sin = ctx.extras[key] = ops.rope_table(ctx.positions, inv_freq)
+                    table = ctx.buffer("attention.rope_table", (T, rot // 2, 2), torch.float32)
+                    cos_sin = ctx.step_values[key] = ops.rope_table(ctx.positions, inv_freq, out=table)
             ops.rope_kv_write(qkv, self.b_qkv, ctx.positions, ctx.token_seq, cache.block_table, inv_freq, rot, inter,
                               q, pages, self.nh, self.nkv, self.d, ctx.error_flag, cos_sin)
         o = ctx.buffer("attention.o", (T, self.nh * self.d), self.rt.dtype)
         attention_kernels.paged_attention(q, cache.pages, o, ctx, cache.block_table, self.nh, self.nkv, self.d,
                                           self.scale, self.window)
-        return linear(o, self.w_o, self.b_o, torch.float32, partials_ok=True)  # [T, H] f32, or its partial sums
+        return linear(o, self.w_o, self.b_o, torch.float32, partials_ok=True, error_flag=ctx.error_flag)  # [T, H] f32, or its partial sums

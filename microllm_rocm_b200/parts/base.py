@@ -59,10 +59,12 @@ class WeightSpec:
 @dataclass(frozen=True)
 class PagedKVNeed:
     """Keys and values that grow with the tokens.  `window`: only the last `window` keys are
-    ever read (pages behind it may be given back while the request lives); None: all keys."""
+    ever read (pages behind it may be given back while the request lives); None: all keys.
+    `dtype`: what the pages store; None: the runtime's compute dtype."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    dtype: Optional[torch.dtype] = None
 
 
 @dataclass(frozen=True)
@@ -110,7 +112,10 @@ class StepContext:
     state_slots_host: List[int] = field(default_factory=list)
     max_new_tokens: int = 0        # longest run of new tokens of one sequence
     max_seq_len: int = 0           # longest sequence after the step
-    extras: Dict[str, Any] = field(default_factory=dict)   # per-step scratch shared by parts
+    extras: Dict[str, Any] = field(default_factory=dict)   # scratch buffers and launch plans shared by parts
+    # results computed from the step's device state (a table of this step's angles, say): valid for ONE forward;
+    # the model empties it before every forward, also when the context itself lives on (a captured decode step)
+    step_values: Dict[Any, Any] = field(default_factory=dict)
 
     @property
     def decode_only(self) -> bool:
@@ -146,6 +151,11 @@ class Part:
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         pass
+
+    def kernel_sources(self) -> List[Tuple[str, dict]]:
+        """(source file, defines) of the kernel objects this part will ask for beyond those every model needs,
+        so that they are compiled together, in parallel, before the first step instead of one by one inside it."""
+        return []
 
 
 class Norm(Part):
@@ -187,6 +197,18 @@ class Mixer(Part):
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
         raise NotImplementedError
+
+    # A mixer may plan its launches on the host from the lengths of the step's sequences and keep the plan in
+    # ctx.extras; a captured decode step freezes that plan while the sequences grow.  The two hooks let whoever
+    # holds such a context ask whether the plan still suits, and drop it, without knowing what the plan is.
+    def plan_stale(self, ctx: StepContext, max_seq_len: int) -> bool:
+        """Whether launches planned in `ctx` would be cut differently once the longest sequence holds
+        `max_seq_len` tokens.  Default: the mixer plans nothing that depends on lengths."""
+        return False
+
+    def forget_plans(self, ctx: StepContext) -> None:
+        """Drop this mixer's plans from `ctx`; the next forward plans anew."""
+        return None
 
 
 class FeedForward(Part):

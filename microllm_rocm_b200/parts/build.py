@@ -76,6 +76,15 @@ class Model:
             self.run_cache.append((name, owns))
         self.bound = False
 
+    def parts(self) -> List[Part]:
+        """Every part of the model, each once."""
+        seen, out = set(), []
+        for _, part in self._parts:
+            if id(part) not in seen:
+                seen.add(id(part))
+                out.append(part)
+        return out
+
     # --- weights ----------------------------------------------------------------------
     def expected_tensors(self) -> Dict[str, WeightSpec]:
         out: Dict[str, WeightSpec] = {}
@@ -109,6 +118,7 @@ class Model:
         ctx.logit_rows.  `caches`: cache name -> writable view for this step."""
         if not self.bound:
             raise RuntimeError("model weights are not bound")
+        ctx.step_values.clear()              # nothing computed from an earlier step's positions or tokens survives
         residual = self.embedding.forward(ctx.token_ids)
         self.position.on_embedding(residual, ctx)
         delta = None
@@ -128,7 +138,7 @@ class Model:
             ops.add_inplace(residual, delta)
         rows = torch.empty((R, self.spec.hidden_size), dtype=self.rt.dtype, device=residual.device)
         self.final_norm.forward(residual, rows, rows=ctx.logit_rows)
-        return self.head.forward(rows)
+        return self.head.forward(rows, ctx.error_flag)
 
 
 def _read_only(view):

@@ -52,11 +52,17 @@ class LMHead(Part):
     def bind(self, tensors):
         self.weight = tensors[self.tied_to if self.tied_to is not None else self.name]
 
-    def forward(self, rows: torch.Tensor) -> torch.Tensor:
-        """rows [R, H] in the compute dtype -> logits [R, V] fp32."""
-        logits = linear(rows, self.weight, None, torch.float32, partials_ok=True)
+    def kernel_sources(self):
+        if self.rt.is_fp32:
+            return []
+        from ..kernels import gemm_bf16
+        return gemm_bf16.sources(engine_only=True)
+
+    def forward(self, rows: torch.Tensor, error_flag: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """rows [R, H] in the compute dtype -> logits [R, V] fp32.  `error_flag`: the step's device flag."""
+        logits = linear(rows, self.weight, None, torch.float32, partials_ok=True, error_flag=error_flag)
         if logits.dim() == 3:
-            # the few-token kernel: with this many output rows it does not split K, so the one
+            # a weight-streaming kernel: with this many output rows it does not split K, so the one
             # partial result is the product itself
             if logits.shape[0] != 1:        # a small vocabulary with a long K: add the partial results up
                 total = torch.zeros(logits.shape[1:], dtype=torch.float32, device=logits.device)

@@ -26,6 +26,9 @@ class SwiGLU(FeedForward):
                 "up_proj.weight": WeightSpec((self.inter, self.hidden)),
                 "down_proj.weight": WeightSpec((self.hidden, self.inter))}
 
+    def kernel_sources(self):
+        return [] if self.rt.is_fp32 else gemm_bf16.sources(engine_only=True)
+
     def bind(self, tensors):
         self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], 0).contiguous()
         self.w_down = tensors["down_proj.weight"]
@@ -35,17 +38,21 @@ class SwiGLU(FeedForward):
         # activation is evaluated in fp32 and stored bf16, down returns fp32 at the residual
         # boundary -- the reference's policy for its bf16 feed-forward (src/ops/optimized.cpp:676-683).
         act = scratch(ctx, "swiglu.act", (x.shape[0], self.inter), self.rt.dtype, x.device)
+        flag = ctx.error_flag if ctx is not None else None      # one flag covers the step: whoever reads it sees every kernel's
         if x.dtype == torch.bfloat16 and x.shape[0] <= gemm_bf16.GEMV_SILU_MAX_TOKENS and gemm_bf16.gemv_fused_supported(x, self.w_gate_up):
             # a few tokens: one weight-streaming kernel, the activation is its epilogue
             gemm_bf16.gemv_silu_mul(x, self.w_gate_up, act)
         elif x.dtype == torch.bfloat16 and gemm_bf16.gemv_preferred(x, self.w_gate_up):
             # more tokens, or a width too large for that kernel: fp32 partial sums, the activation adds them
             ops.silu_mul(gemm_bf16.gemv_partials(x, self.w_gate_up), act)
+        elif gemm_bf16.stream_preferred(x, self.w_gate_up):
+            # up to 128 tokens: the tcgen05 weight-streaming product, the activation is its epilogue
+            gemm_bf16.stream_silu_mul(x, self.w_gate_up, act, error_flag=flag)
         elif x.dtype == torch.bfloat16 and x.shape[0] >= gemm_bf16.PAIR_MIN_TOKENS and gemm_bf16.supported(x, self.w_gate_up):
             # a prompt portion: the CTA-pair tcgen05 product with the activation in its epilogue
-            gemm_bf16.gemm_pair(x, self.w_gate_up, act, dual_rows=self.inter)
+            gemm_bf16.gemm_pair(x, self.w_gate_up, act, dual_rows=self.inter, error_flag=flag)
         else:
             gate_up = linear(x, self.w_gate_up, None, self.rt.dtype,
                              alloc=lambda shape, dtype: scratch(ctx, "swiglu.gate_up", shape, dtype, x.device))
             ops.silu_mul(gate_up, act)
-        return linear(act, self.w_down, None, torch.float32, partials_ok=True)
+        return linear(act, self.w_down, None, torch.float32, partials_ok=True, error_flag=flag)

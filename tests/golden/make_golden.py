@@ -5,7 +5,7 @@ What it does: writes a very small random Qwen2 model (model.safetensors + config
 this folder), runs walkinglabs/microLLM-rocm's `microllm_hf_infer` built for the CPU
 (-DMICROLLM_ENABLE_HIP=OFF) on a few prompts with `--workload prefill --logits-output`, and
 stores the last-position logits it wrote in `reference_logits.json`, together with the
-logits after a cached decode step (`--workload both --new-tokens 2 --cache-logits-output`).
+logits after a cached decode step (`--workload both --new-tokens 3 --cache-logits-output`).
 tests/test_plain.py then checks the plain implementation against these files; the reference
 binary is not needed again.
 

@@ -180,6 +180,110 @@ def test_captured_decode_steps_equal_launched_ones(folders, dtype):
     graphed.engine.cache.check()
 
 
+def test_captured_decode_step_of_64_requests_rotates_with_the_present_positions(folders):
+    """64 requests decoding in bf16: the step is large enough for the path that makes one table of the step's
+    sines and cosines.  A captured step lives on from one replay to the next while the positions move on the
+    device, so whatever it computes from the positions must be computed inside every replay.  Two engines are fed
+    the SAME tokens, one through replays of a captured step, one through plain steps; their caches (the rotated
+    keys every step stored) must agree, and so must the tokens they select."""
+    from microllm_rocm_b200.engine.decode_graph import DecodeGraphPool
+    from microllm_rocm_b200.engine.loading import load_engine
+    from microllm_rocm_b200.engine.step import StepEntry
+    from microllm_rocm_b200.kernels import ops
+    from microllm_rocm_b200.kernels.build import LaunchCounter
+    from microllm_rocm_b200 import GenerationConfig
+    key, batch, steps = "b", 64, 7
+    vocab = tiny_config(key).vocab_size
+    prompts = [random_tokens(3 + (i * 7) % 40, vocab, 1000 + i) for i in range(batch)]
+    forced = [[random_tokens(steps + 1, vocab, 5000 + i)[s] for i in range(batch)] for s in range(steps + 1)]
+    ids = [f"q{i}" for i in range(batch)]
+
+    def fresh():
+        engine = load_engine(folders[key], dtype="bfloat16", page_size=16, max_tokens=batch * 64, max_requests=batch)
+        for rid, p in zip(ids, prompts):
+            assert engine.cache.add(rid)
+        engine.step([StepEntry(rid, p, []) for rid, p in zip(ids, prompts)])
+        return engine
+
+    # plain steps: forced tokens in, selected tokens out
+    plain_engine = fresh()
+    picked = torch.empty(batch, dtype=torch.int32, device="cuda")
+    want_tokens = []
+    for s in range(steps):
+        logits = plain_engine.step([StepEntry(rid, [forced[s][i]], [0]) for i, rid in enumerate(ids)])
+        ops.argmax_rows(logits, picked)
+        want_tokens.append(picked.tolist())
+
+    # the same through a captured step
+    engine = fresh()
+    cache = engine.cache
+    lengths = [cache.length(rid) for rid in ids]
+    for rid, n in zip(ids, lengths):
+        assert cache.reserve(rid, n + 1)
+    pool = DecodeGraphPool(engine)
+    graph = pool.get(ids, headroom_tokens=steps + 1)
+    greedy = GenerationConfig(max_new_tokens=steps + 1, temperature=0.0)
+    state = (forced[0], lengths, [greedy] * batch, [0] * batch)
+    graph.load(ids, *state)
+    before = LaunchCounter.own
+    pool.ensure_captured(graph)
+    graph.load(ids, *state)
+    got_tokens = []
+    for s in range(steps):
+        for i, rid in enumerate(ids):
+            assert cache.reserve(rid, lengths[i] + 1)
+        graph.refresh_tables()
+        if s:
+            graph.upload_tokens(forced[s])
+        graph.replay()
+        got_tokens.append(graph.read_tokens())
+        for i, rid in enumerate(ids):
+            lengths[i] += 1
+            cache.commit(rid, lengths[i])
+    engine.check_device_errors()
+    # same requests added in the same order to pools of the same size: the two caches use the same pages
+    assert [cache.requests[r].tables for r in ids] == [plain_engine.cache.requests[r].tables for r in ids]
+    for name, pages in cache.kv_storage.items():
+        other = plain_engine.cache.kv_storage[name]
+        for i, rid in enumerate(ids):
+            for group, table in cache.requests[rid].tables.items():
+                if cache.entry_group[name] != group:
+                    continue
+                for block, page in enumerate(table):
+                    if page < 0:
+                        continue
+                    n = min(16, lengths[i] - 16 * block)
+                    a, b = pages[page, :, :, :n].float(), other[page, :, :, :n].float()
+                    assert torch.allclose(a, b, atol=2e-2, rtol=2e-2), (name, rid, block, float((a - b).abs().max()))
+    agree = sum(g == w for gs, ws in zip(got_tokens, want_tokens) for g, w in zip(gs, ws))
+    assert agree >= 0.97 * batch * steps, agree          # bf16 near-ties may fall the other way; stale angles would not leave 97 %
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_raised_device_flag_ends_the_step_with_an_error(folders, dtype):
+    """Every kernel of a step reports through ONE device flag (a token without a page, a bounded wait of a
+    tensor-memory kernel that ran out).  Whatever raised it, the step that reads it must fail instead of handing
+    out tokens, both when it launches kernel by kernel and when it replays a captured decode step, and the flag
+    must be clear again afterwards."""
+    from microllm_rocm_b200 import GenerationConfig
+    from microllm_rocm_b200.engine.step import StepError
+    llm = llm_for(folders["a"], dtype, max_tokens=256)
+    rid = llm.submit(random_tokens(9, tiny_config("a").vocab_size, 4), GenerationConfig(max_new_tokens=8, temperature=0.0))
+    llm.engine.error_flag.fill_(43)                     # as a bounded wait inside a product would
+    with pytest.raises(StepError, match="bounded wait"):
+        llm.step()                                      # the prompt's step, launched kernel by kernel
+    assert int(llm.engine.error_flag.item()) == 0
+    llm.cancel(rid)
+    rid = llm.submit(random_tokens(9, tiny_config("a").vocab_size, 4), GenerationConfig(max_new_tokens=8, temperature=0.0))
+    llm.step()
+    llm.step()
+    assert llm.graph_steps >= 1
+    llm.engine.error_flag.fill_(2)                      # as a kernel that met a token without a page would
+    with pytest.raises(StepError, match="page"):
+        llm.step()                                      # a replayed decode step
+    assert int(llm.engine.error_flag.item()) == 0
+
+
 def test_the_driver_entry_point_generates_and_compares():
     """`__graft_entry__.smoke()` is what runs first on a fresh GPU box: it must import, generate a few tokens
     in fp32 and bf16 and agree with the plain implementation."""

@@ -431,58 +431,69 @@ def test_kernels_refuse_bad_sizes_with_a_clear_error():
 
 
 # ------------------------------------------------------------------------------ tcgen05 products
-@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 2048, 1536), (8, 1536, 8960), (5, 200, 264), (64, 384, 192),
-                                   (300, 520, 136), (2048, 1536, 1536), (17, 1000, 72), (130, 130, 8),
-                                   (2048, 4096, 256), (700, 9000, 200), (2100, 2500, 1536)])   # > 148 tiles: persistent CTAs
-@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-def test_tensor_core_product_against_fp32(M, N, K, out_dtype):
+@pytest.mark.parametrize("M,N,K,splits,stages", [
+    (9, 2048, 1536, None, 0), (16, 1536, 8960, None, 0), (33, 1000, 264, 2, 0), (64, 1536, 8960, None, 0),
+    (64, 384, 192, 3, 2), (128, 130, 72, 1, 0), (100, 19000, 1536, None, 3), (17, 200, 8, None, 0), (1, 128, 64, 1, 0),
+    (64, 17920, 1536, 1, 0), (48, 2500, 1000, 7, 2)])
+def test_stream_partials_sum_to_the_product(M, N, K, splits, stages):
+    """The tcgen05 weight-streaming product at 1..128 tokens: widths and K that are no multiple of the tile, K cut
+    into ranges of uneven length, a ring of two or three stages that wraps many times, and more row tiles than
+    SMs (each CTA then walks several tiles with its accumulator double-buffered).  The partial results, added in
+    split order, are the product; a second call gives the same bits."""
     from microllm_rocm_b200.kernels import gemm_bf16
     torch.manual_seed(M + N + K)
-    x = torch.randn(M, K).bfloat16()
-    w = torch.randn(N, K).bfloat16()
-    bias = torch.randn(N)
+    x = torch.randn(M, K).bfloat16().to(DEV)
+    w = torch.randn(N, K).bfloat16().to(DEV)
+    bias = torch.randn(N, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert gemm_bf16.stream_supported(x, w)
+    part = gemm_bf16.stream_partials(x, w, bias, splits=splits, stages=stages, error_flag=flag)
+    assert part.dim() == 3 and part.shape[1:] == (M, N) and (splits is None or part.shape[0] <= splits)
+    again = gemm_bf16.stream_partials(x, w, bias, splits=splits, stages=stages, error_flag=flag)
+    assert int(flag.item()) == 0
+    assert torch.equal(part, again)
+    got = part[0].double()
+    for i in range(1, part.shape[0]):
+        got += part[i].double()
     want = x.double() @ w.double().t() + bias.double()
-    out = torch.empty(M, N, dtype=out_dtype, device=DEV)
-    gemm_bf16.gemm_tc(x.to(DEV), w.to(DEV), out, bias=bias.to(DEV))
-    assert int(gemm_bf16.error_flag(torch.device(DEV)).item()) == 0
-    got = out.double().cpu()
-    scale = math.sqrt(K)
-    tol_abs = (2e-5 if out_dtype == torch.float32 else 1e-2) * scale
-    assert (got - want).abs().max() <= tol_abs + (4e-3 if out_dtype == torch.bfloat16 else 0) * want.abs().max(), \
-        float((got - want).abs().max())
+    assert (got - want).abs().max().item() <= 2e-5 * math.sqrt(K) * 4, float((got - want).abs().max())
 
 
-@pytest.mark.parametrize("splits,tok_tile", [(1, 16), (4, 16), (3, 32), (7, 64), (2, 256)])
-def test_tensor_core_product_split_k_tiles_and_accumulate(splits, tok_tile):
+@pytest.mark.parametrize("M,I,K,stages", [(64, 1120, 1536, 0), (9, 176, 64, 0), (33, 520, 192, 2), (128, 2240, 1536, 0),
+                                          (100, 9600, 192, 3), (16, 8960, 1536, 0), (17, 23, 40, 0)])
+def test_stream_silu_mul(M, I, K, stages):
+    """Gate/up with the activation as the epilogue: 64 gate rows stacked on 64 up rows per tile, the halves
+    exchanged through shared memory; token counts that end inside a 16- and a 32-token chunk, an intermediate
+    size that ends inside a tile, and more tiles than SMs."""
     from microllm_rocm_b200.kernels import gemm_bf16
-    torch.manual_seed(splits)
-    M, N, K = 40, 300, 1000
-    x, w = torch.randn(M, K).bfloat16(), torch.randn(N, K).bfloat16()
-    base = torch.randn(M, N)
-    out = base.to(DEV).clone()
-    gemm_bf16.gemm_tc(x.to(DEV), w.to(DEV), out, accumulate=True, splits=splits, tok_tile=tok_tile)
-    want = base.double() + x.double() @ w.double().t()
-    assert (out.double().cpu() - want).abs().max() <= 2e-5 * math.sqrt(K) * 4
-    # the same call again gives the same bits: the split sum has a fixed order
-    again = base.to(DEV).clone()
-    gemm_bf16.gemm_tc(x.to(DEV), w.to(DEV), again, accumulate=True, splits=splits, tok_tile=tok_tile)
-    assert torch.equal(out, again)
-    assert int(gemm_bf16.error_flag(torch.device(DEV)).item()) == 0
-
-
-@pytest.mark.parametrize("M,I,K", [(8, 8960 // 8, 1536), (3, 176, 64), (200, 512, 192), (1200, 2100, 192)])
-def test_tensor_core_dual_product_silu_mul(M, I, K):
-    from microllm_rocm_b200.kernels import gemm_bf16
-    torch.manual_seed(I)
+    torch.manual_seed(I + M)
     x = (torch.randn(M, K) * 0.5).bfloat16()
     w = (torch.randn(2 * I, K) * 0.2).bfloat16()
-    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
-    gemm_bf16.gemm_tc(x.to(DEV), w.to(DEV), out, dual_rows=I)
-    g = x.float() @ w[:I].float().t()
-    u = x.float() @ w[I:].float().t()
-    want = plain.swiglu(g, u)
-    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2), float((out.float().cpu() - want).abs().max())
-    assert int(gemm_bf16.error_flag(torch.device(DEV)).item()) == 0
+    w[0, :] = x[0].float() * 4                           # one large positive and one large negative gate value:
+    w[1, :] = -x[0].float() * 4                          # both branches of the sigmoid
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    gemm_bf16.stream_silu_mul(x.to(DEV), w.to(DEV), out, stages=stages, error_flag=flag)
+    assert int(flag.item()) == 0
+    want = plain.swiglu(x.float() @ w[:I].float().t(), x.float() @ w[I:].float().t())
+    got = out.float().cpu()
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), float((got - want).abs().max())
+
+
+def test_stream_product_refuses_what_it_cannot_take():
+    from microllm_rocm_b200.kernels import gemm_bf16
+    from microllm_rocm_b200.kernels.build import KernelError
+    x, w = torch.randn(12, 20, device=DEV).bfloat16(), torch.randn(8, 20, device=DEV).bfloat16()
+    assert not gemm_bf16.stream_supported(x, w)                       # K is no multiple of 8: TMA cannot address it
+    with pytest.raises(KernelError, match="multiples of 8"):
+        gemm_bf16.stream_partials(x, w)
+    # the dispatcher sends such a product to the library instead of failing
+    y = gemm_bf16.linear_bf16(x, w, None, torch.float32, None, partials_ok=True)
+    assert y.dim() == 2 and torch.allclose(y.cpu(), x.float().cpu() @ w.float().cpu().t(), atol=1e-2)
+    big = torch.randn(129, 64, device=DEV).bfloat16()
+    with pytest.raises(KernelError, match="1..128"):
+        gemm_bf16.stream_partials(big, torch.randn(8, 64, device=DEV).bfloat16())
 
 
 @pytest.mark.parametrize("M,N,K,out_dtype", [(256, 256, 64, torch.float32), (2048, 1536, 1536, torch.float32),
@@ -539,18 +550,6 @@ def test_library_product_called_directly(M, N, K, out_dtype):
     wide = torch.full((M, N + 8), 7.0, dtype=out_dtype, device=DEV)
     gemm_bf16.library_linear(x, w, None, out_dtype, wide[:, :N])
     assert torch.equal(wide[:, :N], y) and float(wide[:, N:].float().min()) == 7.0
-
-
-def test_tensor_core_product_refuses_what_tma_cannot_address():
-    from microllm_rocm_b200.kernels import gemm_bf16
-    from microllm_rocm_b200.kernels.build import KernelError
-    x, w = torch.randn(4, 20, device=DEV).bfloat16(), torch.randn(8, 20, device=DEV).bfloat16()
-    assert not gemm_bf16.supported(x, w)
-    with pytest.raises(KernelError, match="multiples of 8"):
-        gemm_bf16.gemm_tc(x, w, torch.empty(4, 8, device=DEV))
-    # the dispatcher sends such a product to the library instead of failing
-    y = gemm_bf16.linear_bf16(x, w, None, torch.float32, None)
-    assert torch.allclose(y.cpu(), x.float().cpu() @ w.float().cpu().t(), atol=1e-2)
 
 
 # ------------------------------------------------------------------------------ few-token weight streaming

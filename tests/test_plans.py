@@ -2,6 +2,8 @@
 within what the kernels' shared memory takes (no GPU needed)."""
 import pytest
 
+from microllm_rocm_b200.kernels.device import DEFAULT_SM_COUNT
+
 
 @pytest.mark.parametrize("n,k", [(1536, 1536), (1536, 8960), (2048, 1536), (17920, 1536), (151936, 1536), (3584, 18944),
                                  (5120, 13824), (64, 32), (80, 96), (300, 12288), (7, 64)])
@@ -15,17 +17,31 @@ def test_k_ranges_cover_the_product(n, k):
         splits, per = plan
         assert splits >= 1 and per % 32 == 0 and (splits - 1) * per < k <= splits * per
         assert per <= gemm_bf16.GEMV_FUSED_MAX_K
-        assert -(-n // 16) <= gemm_bf16.GEMV_SPLIT_MAX_TILES
+        assert -(-n // 16) <= gemm_bf16.GEMV_SPLIT_MAX_TILES_PER_SM * DEFAULT_SM_COUNT
     else:
-        assert -(-n // 16) > gemm_bf16.GEMV_SPLIT_MAX_TILES
+        assert -(-n // 16) > gemm_bf16.GEMV_SPLIT_MAX_TILES_PER_SM * DEFAULT_SM_COUNT
+    # the tcgen05 streaming product: whole 64-element blocks of K, no empty range, at most one CTA per SM and tile
+    for sms in (DEFAULT_SM_COUNT, 132, 16):
+        s = gemm_bf16.stream_splits(n, k, sms)
+        blocks = -(-k // 64)
+        per = -(-blocks // s)
+        assert 1 <= s <= gemm_bf16.STREAM_MAX_SPLITS and (s - 1) * per < blocks <= s * per
+        assert s == 1 or (s * -(-n // 128) <= sms and per >= gemm_bf16.STREAM_MIN_K_BLOCKS_PER_SPLIT - 1)
 
 
-def test_token_tiles_and_routing_limits():
+def test_plans_follow_the_device_they_are_made_for():
+    """A part with fewer multiprocessors gets fewer CTAs per product and smaller clusters per sequence."""
+    from microllm_rocm_b200.kernels import attention, gemm_bf16
+    assert gemm_bf16.gemv_splits(1536, 8960, 148)[0] > gemm_bf16.gemv_splits(1536, 8960, 32)[0]
+    assert gemm_bf16.stream_splits(1536, 8960, 148) > gemm_bf16.stream_splits(1536, 8960, 24)
+    assert attention.decode_splits(16, 2048, 148) == 8 and attention.decode_splits(16, 2048, 60) == 4
+
+
+def test_routing_limits():
     from microllm_rocm_b200.kernels import gemm_bf16
-    assert [gemm_bf16.token_tile(m) for m in (1, 16, 17, 64, 65, 128, 129, 5000)] == [16, 16, 32, 64, 128, 128, 256, 256]
-    assert gemm_bf16.token_tile(5000, dual=True) == 128
     assert gemm_bf16.GEMV_ROUTE_MAX_TOKENS <= gemm_bf16.GEMV_MAX_TOKENS
     assert gemm_bf16.GEMV_SILU_MAX_TOKENS <= gemm_bf16.GEMV_MAX_TOKENS
+    assert gemm_bf16.GEMV_ROUTE_MAX_TOKENS < gemm_bf16.STREAM_MAX_TOKENS < gemm_bf16.PAIR_MIN_TOKENS
 
 
 def test_decode_key_split_grows_with_the_context_and_fits_one_wave():
@@ -35,7 +51,7 @@ def test_decode_key_split_grows_with_the_context_and_fits_one_wave():
         for context in (1, 48, 64, 113, 241, 497, 1009, 4000, 100000):
             splits = attention.decode_splits(items, context)
             assert splits >= max(1, last) or splits == last            # never fewer CTAs for a longer context
-            assert splits == 1 or (items * splits <= 2 * attention.SM_COUNT and -(-context // 16) >= 4 * splits)
+            assert splits == 1 or (items * splits <= 2 * DEFAULT_SM_COUNT and -(-context // 16) >= 4 * splits)
             last = splits
     assert attention.decode_splits(16, 16) == 1 and attention.decode_splits(16, 2048) == 8
     assert attention.decode_splits(2, 32768) == 16 and attention.decode_splits(128, 2048) == 2

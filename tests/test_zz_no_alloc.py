@@ -81,3 +81,8 @@ def test_no_alloc_product_refuses_what_its_scratch_cannot_hold():
     assert "scratch" in message and "mlb_gemv_bf16" in message
     assert lib.mlb_gemv_bf16_noalloc(x.data_ptr(), 64, w.data_ptr(), 64, None, out.data_ptr(), 8, 17, 8, 64, stream) != 0
     assert "1..16" in lib.mlb_last_error().decode()
+    # a missing operand is an error code on the host, never an address for the kernel
+    for args in [(None, w.data_ptr(), out.data_ptr()), (x.data_ptr(), None, out.data_ptr()), (x.data_ptr(), w.data_ptr(), None)]:
+        assert lib.mlb_gemv_bf16_noalloc(args[0], 64, args[1], 64, None, args[2], 8, 16, 8, 64, stream) == 1
+        assert "null" in lib.mlb_last_error().decode()
+    torch.cuda.synchronize()
