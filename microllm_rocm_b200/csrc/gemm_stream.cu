@@ -46,7 +46,10 @@ constexpr int MAX_STAGES = 12;
 constexpr int MAX_TOKENS = 128;
 constexpr int THREADS = 192;
 constexpr int SPIN_LIMIT = 1 << 22;          // polls of up to 1 us each
-constexpr int XBUF_BYTES = 2 * 32 * HALF_W * 4;   // two exchange buffers of 32 tokens x 64 rows fp32
+constexpr int XBUF_BYTES = 2 * 16 * HALF_W * 4;   // two exchange buffers of 16 tokens x 64 rows fp32
+// Shared memory a CTA takes unless the caller asks for a deeper ring: less than half an SM's, so that the CTAs of
+// the NEXT kernel of the step become resident beside this one's and fetch their first weights meanwhile.
+constexpr int SMEM_BUDGET = 110 * 1024;
 
 enum Mode : int { MODE_PARTIAL = 0, MODE_SILU = 1 };
 
@@ -128,10 +131,11 @@ __device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.syn
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 __device__ __forceinline__ float silu(float g) {
-    // two-branch sigmoid, as the reference's activation (src/ops/ops.cpp:72-76)
-    if (g >= 0.0f) return g / (1.0f + expf(-g));
-    const float e = expf(g);
-    return g * e / (1.0f + e);
+    // g * sigmoid(g) (src/ops/ops.cpp:72-76, 760-785) in its one-branch form: for very negative g the
+    // exponential overflows to +inf and the quotient is -0, which is the limit.  No branch and the fast
+    // exponential and reciprocal: the epilogue of a one-tile CTA is not hidden behind anything, and the
+    // result is rounded to bf16 right away.
+    return __fdividef(g, 1.0f + __expf(-g));
 }
 
 // Where the 128 rows of work item `tile` come from: two boxes of 64 weight rows.
@@ -281,56 +285,78 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t lane_addr = tmem_base + buf * (uint32_t)p.tok_tile + ((uint32_t)(quarter * 32) << 16);
+            const int limit = min(p.tok_tile, (p.M + 15) / 16 * 16);       // columns that hold tokens
             if (p.mode == MODE_PARTIAL) {
                 const int f = tile * BLOCK_W + quarter * 32 + lane;          // this thread's output feature
                 const float bias = (p.bias && split == 0 && f < p.N) ? p.bias[f] : 0.0f;
                 float* dst = p.partial + (size_t)split * p.M * p.N + f;
-                for (int c = 0; c < p.tok_tile && c < p.M; c += 16) {
-                    uint32_t raw[16];
-                    tmem_ld16_nowait(lane_addr + (uint32_t)c, raw);
-                    tmem_wait();
+                // two 16-column loads in turn: the next one travels while this one is stored
+                uint32_t a[16], b[16];
+                tmem_ld16_nowait(lane_addr, a);
+                tmem_wait();
+                for (int c = 0; c < limit; c += 32) {
+                    if (c + 16 < limit) tmem_ld16_nowait(lane_addr + (uint32_t)(c + 16), b);
                     if (f < p.N) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
-                            if (c + j < p.M) dst[(size_t)(c + j) * p.N] = __uint_as_float(raw[j]) + bias;
+                            if (c + j < p.M) dst[(size_t)(c + j) * p.N] = __uint_as_float(a[j]) + bias;
                     }
+                    tmem_wait();
+                    if (c + 16 >= limit) break;
+                    if (c + 32 < limit) tmem_ld16_nowait(lane_addr + (uint32_t)(c + 32), a);
+                    if (f < p.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (c + 16 + j < p.M) dst[(size_t)(c + 16 + j) * p.N] = __uint_as_float(b[j]) + bias;
+                    }
+                    tmem_wait();
                 }
             } else if (p.mode == MODE_SILU) {
-                // lanes 0-63 of the tile hold gate rows, lanes 64-127 the up rows of the same features.  Of every 32
-                // tokens the gate side finishes the first 16 and the up side the last 16; each sends the other what
+                // lanes 0-63 of the tile hold gate rows, lanes 64-127 the up rows of the same features.  Of every 16
+                // tokens the gate side finishes the first 8 and the up side the last 8; each sends the other what
                 // it needs through shared memory (token-major, so both sides touch consecutive words).
                 const bool up_side = quarter >= 2;
                 const int i = (quarter & 1) * 32 + lane;                  // row within the 64
                 const int f = tile * HALF_W + i;
-                int chunk = 0;
-                for (int c = 0; c < p.tok_tile && c < p.M; c += 32, ++chunk) {
-                    uint32_t lo[16], hi[16];
-                    tmem_ld16_nowait(lane_addr + (uint32_t)c, lo);
-                    const bool has_hi = c + 16 < p.tok_tile;
-                    if (has_hi) tmem_ld16_nowait(lane_addr + (uint32_t)(c + 16), hi);
-                    tmem_wait();
-                    float* xb = xbuf + (size_t)(chunk & 1) * 32 * HALF_W;
-                    if (up_side) {
+                auto finish = [&](const uint32_t (&raw)[16], int c, int chunk) {
+                    float* xb = xbuf + (size_t)(chunk & 1) * 16 * HALF_W;
+                    if (up_side) {                      // the gate side finishes tokens 0..7 of the chunk and needs their up values
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) xb[j * HALF_W + i] = __uint_as_float(lo[j]);
-                    } else if (has_hi) {
+                        for (int j = 0; j < 8; ++j) xb[j * HALF_W + i] = __uint_as_float(raw[j]);
+                    } else {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) xb[(16 + j) * HALF_W + i] = __uint_as_float(hi[j]);
+                        for (int j = 8; j < 16; ++j) xb[j * HALF_W + i] = __uint_as_float(raw[j]);
                     }
                     epilogue_sync();
-                    if (f < p.N) {
-                        if (!up_side) {
+                    if (f >= p.N) return;
+                    // all eight results first, without conditions, so that their exponentials and reciprocals overlap;
+                    // then the stores
+                    float res[8];
+                    if (!up_side) {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (c + j < p.M)
-                                    p.out[(size_t)(c + j) * p.ldo + f] = __float2bfloat16_rn(silu(__uint_as_float(lo[j])) * xb[j * HALF_W + i]);
-                        } else if (has_hi) {
+                        for (int j = 0; j < 8; ++j) res[j] = silu(__uint_as_float(raw[j])) * xb[j * HALF_W + i];
+                    } else {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (c + 16 + j < p.M)
-                                    p.out[(size_t)(c + 16 + j) * p.ldo + f] = __float2bfloat16_rn(silu(xb[(16 + j) * HALF_W + i]) * __uint_as_float(hi[j]));
-                        }
+                        for (int j = 0; j < 8; ++j) res[j] = silu(xb[(8 + j) * HALF_W + i]) * __uint_as_float(raw[8 + j]);
                     }
+                    __nv_bfloat16* dst = p.out + (size_t)(c + (up_side ? 8 : 0)) * p.ldo + f;
+                    const int left = p.M - c - (up_side ? 8 : 0);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (j < left) dst[(size_t)j * p.ldo] = __float2bfloat16_rn(res[j]);
+                };
+                uint32_t a[16], b[16];
+                tmem_ld16_nowait(lane_addr, a);
+                tmem_wait();
+                int chunk = 0;
+                for (int c = 0; c < limit; c += 32, chunk += 2) {
+                    if (c + 16 < limit) tmem_ld16_nowait(lane_addr + (uint32_t)(c + 16), b);
+                    finish(a, c, chunk);
+                    tmem_wait();
+                    if (c + 16 >= limit) break;
+                    if (c + 32 < limit) tmem_ld16_nowait(lane_addr + (uint32_t)(c + 32), a);
+                    finish(b, c + 16, chunk + 1);
+                    tmem_wait();
                 }
                 epilogue_sync();          // the exchange buffers are free for the next tile
             }
@@ -421,13 +447,18 @@ int launch(StreamParams& p, const void* x, long long ldx, const void* w, long lo
     p.k_blocks_per_split = (p.k_blocks + p.splits - 1) / p.splits;
     p.splits = (p.k_blocks + p.k_blocks_per_split - 1) / p.k_blocks_per_split;      // no empty split
     p.items = p.n_tiles * p.splits;
+    const int ctas = p.items < sm_count() ? p.items : sm_count();
+    // a CTA with one work item needs one accumulator; with more, two, so that a tile drains while the next one runs
     p.tmem_cols = 32;
-    while (p.tmem_cols < 2 * p.tok_tile) p.tmem_cols *= 2;
+    while (p.tmem_cols < (p.items > ctas ? 2 : 1) * p.tok_tile) p.tmem_cols *= 2;
     const int stage_bytes = A_TILE_BYTES + p.tok_tile * BLOCK_K * 2;
     const int xbuf = p.mode == MODE_PARTIAL ? 0 : XBUF_BYTES;
     int most = (200 * 1024 - xbuf) / stage_bytes;
     if (most > MAX_STAGES) most = MAX_STAGES;
-    p.stages = stages > 0 ? (stages < most ? stages : most) : most;
+    int usual = (SMEM_BUDGET - 1024 - xbuf) / stage_bytes;
+    if (p.items > ctas) usual = most;                 // a long stream (the head): nothing to share the SM with for a while
+    if (usual > most) usual = most;
+    p.stages = stages > 0 ? (stages < most ? stages : most) : usual;
     if (p.stages < 2) p.stages = 2;
     const size_t smem = (size_t)p.stages * stage_bytes + xbuf + 1024;
 
@@ -444,7 +475,6 @@ int launch(StreamParams& p, const void* x, long long ldx, const void* w, long lo
         if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "gemm_stream: cannot reserve shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
-    const int ctas = p.items < sm_count() ? p.items : sm_count();
     launch_kernel(gemm_stream_kernel, dim3(ctas), dim3(THREADS), smem, stream, map_w, map_x, p);
     return check_launch("gemm_stream");
 }
@@ -457,7 +487,7 @@ MLB_EXPORT int mlb_gemm_stream_max_tokens() { return MAX_TOKENS; }
 // given, goes into split 0); splits' = mlb_gemm_stream_splits(K, splits) <= splits is what the kernel really
 // uses (no empty range).  Their sum over the splits, taken in order by the consumer, is the product.
 // x and W are bf16 with row pitches ldx, ldw (elements); K and the pitches must be multiples of 8 and the
-// bases 16-byte aligned (TMA).  stages: 0 = as deep a ring as fits.
+// bases 16-byte aligned (TMA).  stages: 0 = a ring that leaves half of the SM's shared memory to the next kernel.
 MLB_EXPORT int mlb_gemm_stream_splits(int K, int splits) {
     const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
     if (splits < 1) splits = 1;
