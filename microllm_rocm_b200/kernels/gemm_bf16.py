@@ -88,17 +88,22 @@ def gemv_splits(n: int, k: int, sms: int = DEFAULT_SM_COUNT):
     return -(-k // k_per_split), k_per_split
 
 
-def gemv_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+def _empty(shape, dtype, device, alloc):
+    return alloc(shape, dtype) if alloc is not None else torch.empty(shape, dtype=dtype, device=device)
+
+
+def gemv_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, alloc=None) -> torch.Tensor:
     """[S, M, N] fp32 partial results of x @ weight^T (+ bias, in partial 0); their sum over S,
-    taken in order by the kernel that consumes them, is the product."""
+    taken in order by the kernel that consumes them, is the product.  `alloc(shape, dtype)`: where the
+    result comes from (a step's scratch; default: a new tensor)."""
     M, K = x.shape
     N = weight.shape[0]
     sms = sm_count(x.device)
     plan = gemv_split_plan(N, K, sms) if x.dtype == torch.bfloat16 and M >= GEMV_SPLIT_MIN_TOKENS else None
     if plan is not None:
-        return gemv_split_partials(x, weight, bias, *plan)
+        return gemv_split_partials(x, weight, bias, *plan, alloc=alloc)
     splits, k_per_split = gemv_splits(N, K, sms)
-    partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+    partial = _empty((splits, M, N), torch.float32, x.device, alloc)
     L = ops.lib("gemv_bf16.cu")
     build.check(L, L.mlb_gemv_bf16(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), N, ops._ptr(bias),
                                    partial.data_ptr(), None, 0, 0, 0, M, N, K, splits, k_per_split, ops._stream()))
@@ -138,11 +143,11 @@ def gemv_split_plan(n: int, k: int, sms: int = DEFAULT_SM_COUNT):
 
 
 def gemv_split_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], splits: int,
-                        k_per_cta: int) -> torch.Tensor:
+                        k_per_cta: int, alloc=None) -> torch.Tensor:
     """[S, M, N] fp32 partial results from the kernel whose warps share a CTA's K range (few partials)."""
     M, K = x.shape
     N = weight.shape[0]
-    partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+    partial = _empty((splits, M, N), torch.float32, x.device, alloc)
     L = ops.lib("gemv_fused.cu")
     build.check(L, L.mlb_gemv_split(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), N, ops._ptr(bias),
                                     partial.data_ptr(), M, N, K, splits, k_per_cta, ops._stream()))
@@ -343,7 +348,7 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
                 error_flag: Optional[torch.Tensor] = None) -> torch.Tensor:
     if partials_ok and out is None and out_dtype == torch.float32:
         if gemv_preferred(x, weight):
-            return gemv_partials(x, weight, bias)
+            return gemv_partials(x, weight, bias, alloc=alloc)
         if stream_preferred(x, weight):
-            return stream_partials(x, weight, bias, error_flag=error_flag)
+            return stream_partials(x, weight, bias, error_flag=error_flag, alloc=alloc)
     return library_linear(x, weight, bias, out_dtype, out, alloc)

@@ -95,10 +95,17 @@ def lib(source: str, defines=None) -> ctypes.CDLL:
     got = _libs.get(key)
     if got is None:
         got = build.load(source, defines)
+        from .replay import Launcher
         for name, argtypes in _SIGNATURES.get(source, {}).items():
             fn = getattr(got, name)
+            if isinstance(fn, Launcher):
+                continue
             fn.argtypes = argtypes
             fn.restype = c_int
+            if argtypes and argtypes[-1] is c_void_p:
+                # a launcher (its last argument is the stream): calls through; a recorder may listen (kernels/replay.py).
+                # Queries (split counts, limits) return numbers, not a status, and are never recorded.
+                setattr(got, name, Launcher(got, fn, argtypes))
         _libs[key] = got
     return got
 
@@ -110,7 +117,7 @@ def register_signatures(source: str, signatures) -> None:
 def base_sources():
     """(source, defines) of every kernel that any model needs."""
     return [("basic.cu", {}), ("gemm_f32.cu", {}), ("rope_kv.cu", {}), ("attention_plain.cu", {}),
-            ("sampling.cu", {})]
+            ("sampling.cu", {}), ("replay.cu", {})]
 
 
 def all_sources():

@@ -77,6 +77,17 @@ class Attention(Mixer):
         return (gemm_bf16.sources(engine_only=True) + attention_kernels.mma_sources(self.d)
                 + attention_kernels.tc_sources(self.d))
 
+    def replay_key(self):
+        if self.out_bias:
+            return None                  # a bias on the output projection is added by a tensor-framework operation
+        if not self.rt.is_fp32 and not gemm_bf16._direct_library(self.rt.device):
+            return None                  # the library product would go through the tensor framework
+        rotary = None if self.rotary is None else (self.rotary.inv_freq.data_ptr(), self.rotary.rotary_dim, self.rotary.interleaved)
+        return ("attention", self.hidden, self.nh, self.nkv, self.d, self.qkv_bias, self.window, self.scale, rotary)
+
+    def own_tensors(self):
+        return [self.w_qkv, self.b_qkv, self.w_o]
+
     # --- launch plans frozen into a captured decode step ----------------------------------
     def plan_stale(self, ctx: StepContext, max_seq_len: int) -> bool:
         from ..kernels.device import sm_count
@@ -116,4 +127,5 @@ class Attention(Mixer):
         o = ctx.buffer("attention.o", (T, self.nh * self.d), self.rt.dtype)
         attention_kernels.paged_attention(q, cache.pages, o, ctx, cache.block_table, self.nh, self.nkv, self.d,
                                           self.scale, self.window)
-        return linear(o, self.w_o, self.b_o, torch.float32, partials_ok=True, error_flag=ctx.error_flag)  # [T, H] f32, or its partial sums
+        return linear(o, self.w_o, self.b_o, torch.float32, partials_ok=True, error_flag=ctx.error_flag,      # [T, H] f32, or its partial sums
+                      alloc=lambda shape, dtype: ctx.buffer("attention.out", shape, dtype))

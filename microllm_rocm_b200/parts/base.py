@@ -157,6 +157,20 @@ class Part:
         so that they are compiled together, in parallel, before the first step instead of one by one inside it."""
         return []
 
+    # Layers of equal structure issue the same launches; only their own tensors differ.  A part that says so lets
+    # the model record one layer's launches and issue them again, natively, for the others (kernels/replay.py).
+    def replay_key(self):
+        """A hashable description of everything but the part's own tensors that decides which launches its
+        forward makes and with which arguments (sizes, constants, options), or None: this part's forward does
+        work that a recording of launcher calls would miss (tensor-framework operations, host-side state), so
+        its layers always run call by call.  Default: None."""
+        return None
+
+    def own_tensors(self) -> List[Optional[torch.Tensor]]:
+        """The device tensors this part owns, in a fixed order (None for an absent optional one): what differs
+        between two parts with the same replay_key."""
+        return []
+
 
 class Norm(Part):
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
@@ -226,6 +240,15 @@ class Block:
 
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext, cache):
         raise NotImplementedError
+
+    def replay_key(self):
+        """As Part.replay_key, for the whole block; in addition the block promises that with equal keys its
+        forward returns the same (residual, delta) tensors for every layer of a step (scratch by role from
+        ctx.buffer, never a fresh tensor).  Default: None."""
+        return None
+
+    def own_tensors(self) -> List[Optional[torch.Tensor]]:
+        return []
 
 
 # ----------------------------------------------------------------------------- registries

@@ -18,6 +18,13 @@ class PreNormResidualBlock(Block):
         self.rt = rt
         self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward = mixer_norm, mixer, ffn_norm, feed_forward
 
+    def replay_key(self):
+        keys = [p.replay_key() for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)]
+        return None if any(k is None for k in keys) else ("pre_norm_residual", self.rt.dtype, *keys)
+
+    def own_tensors(self):
+        return [t for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward) for t in p.own_tensors()]
+
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext, cache):
         normed = ctx.buffer("block.normed", tuple(residual.shape), self.rt.dtype)
         if delta is None:

@@ -75,6 +75,11 @@ class Model:
                     raise ValueError(f"order[{i}] reads cache {name!r} of another kind than its mixer needs")
             self.run_cache.append((name, owns))
         self.bound = False
+        # Layers of equal structure are recorded once per step and issued again natively (kernels/replay.py);
+        # False runs every layer call by call.
+        self.replay_layers = True
+        self.layers_replayed = 0             # runs issued from a recording so far
+        self._replay_keys: Optional[List[object]] = None
 
     def parts(self) -> List[Part]:
         """Every part of the model, each once."""
@@ -84,6 +89,26 @@ class Model:
                 seen.add(id(part))
                 out.append(part)
         return out
+
+    # --- layers of equal structure --------------------------------------------------------
+    def _layer_replay_keys(self) -> List[object]:
+        """Per run of the execution list: what decides its launches besides its own tensors, or None."""
+        if self._replay_keys is None:
+            keys = []
+            for i, run in enumerate(self.spec.order):
+                key = self.blocks[run.layer].replay_key()
+                name, owns = self.run_cache[i]
+                group = None
+                if name is not None:
+                    need = self.cache_entries[name].need
+                    group = (type(need).__name__, getattr(need, "window", None), getattr(need, "dtype", None))
+                keys.append(None if key is None else (key, owns, group))
+            self._replay_keys = keys
+        return self._replay_keys
+
+    @staticmethod
+    def _run_pointers(block, view) -> List[int]:
+        return [0 if t is None else t.data_ptr() for t in list(block.own_tensors()) + _view_tensors(view)]
 
     # --- weights ----------------------------------------------------------------------
     def expected_tensors(self) -> Dict[str, WeightSpec]:
@@ -122,6 +147,8 @@ class Model:
         residual = self.embedding.forward(ctx.token_ids)
         self.position.on_embedding(residual, ctx)
         delta = None
+        keys = self._layer_replay_keys() if self.replay_layers else None
+        recordings = {}                      # structure of a run -> (recording, the recorded run's own pointers) | None
         for i, run in enumerate(self.spec.order):
             name, owns = self.run_cache[i]
             view = None
@@ -129,7 +156,33 @@ class Model:
                 view = caches[name]
                 if not owns:
                     view = _read_only(view)
-            residual, delta = self.blocks[run.layer].forward(residual, delta, ctx, view)
+            block = self.blocks[run.layer]
+            key = keys[i] if keys is not None and i > 0 and delta is not None else None
+            if key is None:
+                # the first run of a step plans launches and makes the step's tables: it always runs call by call
+                residual, delta = block.forward(residual, delta, ctx, view)
+                continue
+            pointers = self._run_pointers(block, view)
+            if key not in recordings:
+                from ..kernels.replay import Recorder, Recording
+                with Recorder() as recorder:
+                    out_residual, out_delta = block.forward(residual, delta, ctx, view)
+                recording = None
+                if (out_residual is residual and out_delta is not None and delta is not None
+                        and out_delta.data_ptr() == delta.data_ptr() and recorder.unrecordable is None):
+                    recording = Recording(recorder)
+                    if not _swappable(recording, block, view):
+                        recording = None
+                recordings[key] = (recording, pointers) if recording is not None else None
+                residual, delta = out_residual, out_delta
+                continue
+            entry = recordings[key]
+            if entry is None:
+                residual, delta = block.forward(residual, delta, ctx, view)
+                continue
+            recording, base = entry
+            recording.replay(list(zip(base, pointers)))
+            self.layers_replayed += 1
         R = ctx.logit_rows.shape[0]
         if R == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=residual.device)
@@ -139,6 +192,25 @@ class Model:
         rows = torch.empty((R, self.spec.hidden_size), dtype=self.rt.dtype, device=residual.device)
         self.final_norm.forward(residual, rows, rows=ctx.logit_rows)
         return self.head.forward(rows, ctx.error_flag)
+
+
+def _view_tensors(view) -> List[Optional[torch.Tensor]]:
+    if view is None:
+        return []
+    return [getattr(view, "pages", None), getattr(view, "storage", None)]
+
+
+def _swappable(recording, block, view) -> bool:
+    """Every pointer a recorded launch takes into a tensor the layer owns must be that tensor's base address:
+    only those can be replaced by another layer's tensor.  (A launcher handed `weight + offset` would keep
+    reading the recorded layer's weight.)"""
+    owned = [t for t in list(block.own_tensors()) + _view_tensors(view) if t is not None]
+    ranges = [(t.data_ptr(), t.data_ptr() + t.numel() * t.element_size()) for t in owned]
+    for p in recording.pointers:
+        for lo, hi in ranges:
+            if lo < p < hi:
+                return False
+    return True
 
 
 def _read_only(view):

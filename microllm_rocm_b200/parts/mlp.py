@@ -33,6 +33,14 @@ class SwiGLU(FeedForward):
         self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], 0).contiguous()
         self.w_down = tensors["down_proj.weight"]
 
+    def replay_key(self):
+        if not self.rt.is_fp32 and not gemm_bf16._direct_library(self.rt.device):
+            return None                  # the library product would go through the tensor framework
+        return ("swiglu", self.hidden, self.inter)
+
+    def own_tensors(self):
+        return [self.w_gate_up, self.w_down]
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         # fp32 path: everything f32.  bf16 path: gate/up leave the product as bf16, the
         # activation is evaluated in fp32 and stored bf16, down returns fp32 at the residual
@@ -44,7 +52,8 @@ class SwiGLU(FeedForward):
             gemm_bf16.gemv_silu_mul(x, self.w_gate_up, act)
         elif x.dtype == torch.bfloat16 and gemm_bf16.gemv_preferred(x, self.w_gate_up):
             # more tokens, or a width too large for that kernel: fp32 partial sums, the activation adds them
-            ops.silu_mul(gemm_bf16.gemv_partials(x, self.w_gate_up), act)
+            ops.silu_mul(gemm_bf16.gemv_partials(x, self.w_gate_up, alloc=lambda shape, dtype: scratch(
+                ctx, "swiglu.gate_up_partials", shape, dtype, x.device)), act)
         elif gemm_bf16.stream_preferred(x, self.w_gate_up):
             # up to 128 tokens: the tcgen05 weight-streaming product, the activation is its epilogue
             gemm_bf16.stream_silu_mul(x, self.w_gate_up, act, error_flag=flag)
@@ -55,4 +64,5 @@ class SwiGLU(FeedForward):
             gate_up = linear(x, self.w_gate_up, None, self.rt.dtype,
                              alloc=lambda shape, dtype: scratch(ctx, "swiglu.gate_up", shape, dtype, x.device))
             ops.silu_mul(gate_up, act)
-        return linear(act, self.w_down, None, torch.float32, partials_ok=True, error_flag=flag)
+        return linear(act, self.w_down, None, torch.float32, partials_ok=True, error_flag=flag,
+                      alloc=lambda shape, dtype: scratch(ctx, "swiglu.out", shape, dtype, x.device))

@@ -25,6 +25,12 @@ class RMSNorm(Norm):
     def bind(self, tensors):
         self.weight = tensors["weight"]
 
+    def replay_key(self):
+        return ("rmsnorm", self.size, self.eps)
+
+    def own_tensors(self):
+        return [self.weight]
+
     def forward(self, x, out, rows=None):
         ops.rmsnorm(x, self.weight, self.eps, out, rows=rows)
 

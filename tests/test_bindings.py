@@ -3,7 +3,7 @@ differs from the C declaration would make ctypes pass the extra pointers as 32-b
 import os
 import re
 
-from microllm_rocm_b200.kernels import attention, gemm_bf16, ops  # noqa: F401  (they register their signatures)
+from microllm_rocm_b200.kernels import attention, gemm_bf16, ops, replay  # noqa: F401  (they register their signatures)
 
 CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "microllm_rocm_b200", "csrc")
 EXPORT = re.compile(r"MLB_EXPORT\s+int\s+(\w+)\s*\(([^)]*)\)", re.S)

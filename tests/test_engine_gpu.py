@@ -104,6 +104,44 @@ def test_head_size_128_with_six_heads_per_kv_head(tmp_path_factory, page_size):
     compare_with_plain(collect(engine, steps), folder, reqs, "bfloat16")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_issued_from_a_recording_give_the_bits_of_layers_called_one_by_one(tmp_path_factory, dtype):
+    """Six layers, three with all keys and three with a window: the first layer of a step always runs call by
+    call, the first layer of each structure after it is recorded, the others are issued natively from that
+    recording with their own weights and pages swapped in.  Steps of every size class (a prompt portion large
+    enough for the step-wide table of angles, one for the tensor-memory streaming products, single tokens), in
+    one engine with the recording on and in one with it off: the logits must be the same bits."""
+    from microllm_rocm_b200.config import Qwen2Config, get_architecture
+    from microllm_rocm_b200.engine.loading import load_engine
+    from microllm_rocm_b200.engine.step import StepEntry
+    from microllm_rocm_b200.weights import write_random_model
+    cfg = Qwen2Config.from_dict(dict(helpers.TINY["b"], num_hidden_layers=6, max_window_layers=3))
+    folder = str(tmp_path_factory.mktemp("six_layers"))
+    write_random_model(get_architecture("Qwen2ForCausalLM"), cfg, 9, folder, "float32")
+    a = random_tokens(200, cfg.vocab_size, 1)
+    b = random_tokens(120, cfg.vocab_size, 2)
+
+    def run(replay):
+        engine = load_engine(folder, dtype=dtype, page_size=16, max_tokens=512, max_requests=4)
+        engine.model.replay_layers = replay
+        engine.cache.add("a")
+        engine.cache.add("b")
+        outs = [engine.step([StepEntry("a", a[:100], [0, 50, 99])]),
+                engine.step([StepEntry("a", a[100:130], [29]), StepEntry("b", b[:20], [19])]),      # 50 tokens
+                engine.step([StepEntry("a", a[130:131], [0]), StepEntry("b", b[20:90], [0, 69])]),   # 71 tokens
+                engine.step([StepEntry("a", a[131:132], [0]), StepEntry("b", b[90:91], [0])])]
+        for i in range(3):
+            outs.append(engine.step([StepEntry("a", a[132 + i:133 + i], [0])]))
+        engine.check_device_errors()
+        return torch.cat([o.float().cpu() for o in outs]), engine.model.layers_replayed
+
+    want, none = run(False)
+    got, replayed = run(True)
+    assert none == 0 and replayed == 7 * 3            # per step: layers 2, 4 and 5
+    assert torch.isfinite(got).all()
+    assert torch.equal(got, want)
+
+
 def test_benchmark_shape_bf16_tracks_the_true_fp32_path():
     """The Qwen2.5-1.5B shape with random weights (28 layers, the kernels and tile sizes the benchmark runs):
     a prompt portion of 304 tokens beside one of 100, then a decode token beside a portion, then decode
