@@ -1,6 +1,8 @@
 """Decode throughput of the engine on one B200, with prefill and roofline figures.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+                    [--model PRESET] [--batch B] [--prompt P] [--context C]
+                    [--workload decode|mixed] [--requests R] [--new-tokens N] [--chunk T]
 
 The model has the layer sizes of the Qwen2.5-1.5B shape (BASELINE.json configs[2]) with
 random bf16 weights; the default run decodes a batch of 8 requests that hold 2,048-token
@@ -14,11 +16,23 @@ new token from one pass through the model.  It prints ONE JSON line:
   prefill      one 2,048-token prompt: tokens/s, ms, fraction of the bf16 tensor peak
   roofline     bytes the decode step must read (every weight once + the live cache) / time
   points       decode tokens/s at batch 1 and 64
+  families     share of the decode step's kernel time by kernel family (products, attention, norms and rotation,
+               sampling), from the device's own kernel records of a few replays; null where they cannot be had
   clocks       SM clock and throttle reasons sampled with nvidia-smi during the timed region
+
+`--workload mixed` is the serving workload of BASELINE.json's configs[3]: R requests (64) with prompt lengths
+uniform in [128, 2048], prompts cut into portions under a budget of T tokens a step (512) beside the decode tokens
+of the requests already running, N new tokens each (128), all through LLM.submit/step.  It prints one line with
+generated and processed tokens per second, steps, preemptions, and two views of who waits for whom: the share of the
+wall time the host spent blocked in a step's device-to-host read (the GPU was busy for all of that; the rest is the
+host preparing and issuing steps, during which the GPU may or may not have work queued) and the driver's own
+utilisation samples (coarse: its sampling window is a good part of a second).
+`--model qwen2.5-14b --prompt 8192 --context 8448` gives configs[4] (decode at context 8,192, prefill of 2,048).
 
 Each decode step reads ~3 GB of weights, far more than the 126 MB L2, so no L2 flush is
 needed between timed iterations.  The reference (walkinglabs/microLLM-rocm) is HIP/ROCm
-code without a CUDA path, so `--impl reference` reports that it is unavailable.
+code without a CUDA path; its CPU build is single-threaded scalar code that needs minutes for one layer of this
+shape, so `--impl reference` reports that it is unavailable and why.
 """
 from __future__ import annotations
 
@@ -36,7 +50,14 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
-BASELINE_DECODE_B8 = 435.0      # the reference's published figure: DeepSeek-R1-Distill-Qwen-1.5B, T2048 B8, on an MI300X
+# The reference's own published steady-decode figure for this layer shape (DeepSeek-R1-Distill-Qwen-1.5B, context
+# 2,048, batch 8, BF16 weights) -- measured on an AMD MI300X with a real checkpoint: other hardware, orientation only.
+BASELINE_DECODE_B8 = 435.0
+BASELINE_NOTE = "reference's published steady decode, same layer shape, context 2048, batch 8, on an AMD MI300X (other hardware; orientation, not a like-for-like ratio)"
+REFERENCE_UNAVAILABLE = ("walkinglabs/microLLM-rocm is a CMake C++/HIP project for ROCm (gfx942) with no CUDA path and no "
+                         "pip-installable package, so its GPU path cannot run on a B200; its CPU build (-DMICROLLM_ENABLE_HIP=OFF) "
+                         "runs single-threaded scalar loops and took 103 s for one pass of a 256-token prompt plus 4 tokens through "
+                         "ONE layer of this shape, so 28 layers with 8 x 2048-token prompts are far outside the time limit")
 
 
 def peaks():
@@ -44,17 +65,19 @@ def peaks():
     if os.path.exists(path):
         try:
             raw = json.load(open(path))
-            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw.get("bf16_tflops_sustained", raw["bf16_tflops"])),
-                    "bf16_tflops_burst": float(raw["bf16_tflops"]), "source": "measured"}
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(raw.get("bf16_tflops_sustained", raw["bf16_tflops"])), "source": "measured"}
         except Exception:
             pass
-    return dict(FALLBACK_PEAKS)
+    out = dict(FALLBACK_PEAKS)
+    out["bf16_tflops_sustained"] = 1400.0
+    return out
 
 
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons every 20 ms while the timed region runs."""
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,utilization.gpu")
 
     def __init__(self):
         self.samples, self.proc = [], None
@@ -91,6 +114,11 @@ class ClockSampler:
         reasons = [n for i, n in enumerate(names) if any(s[3 + i].lower().startswith("active") for s in self.samples)]
         return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": float(self.samples[0][1]),
                 "reasons": reasons, "samples": len(self.samples)}
+
+    def utilization(self):
+        """Mean of the driver's `utilization.gpu` samples (share of each sampling period with a kernel running)."""
+        values = [float(s[7]) for s in self.samples if len(s) > 7 and s[7].replace(".", "").isdigit()]
+        return sum(values) / len(values) / 100.0 if values else None
 
 
 def decode_bytes(cfg, layers, batch, context, dtype_bytes=2):
@@ -195,6 +223,113 @@ def count_launches(session: DecodeSession) -> int:
     return LaunchCounter.own - before
 
 
+FAMILIES = (("attention", ("fa_", "paged_attention")), ("products", ("gemv", "gemm", "nvjet", "cutlass", "sm100", "sm90")),
+            ("norm_rope_act", ("rmsnorm", "rope", "silu", "add_inplace", "embed")), ("sampling", ("argmax", "sample", "decode_advance")))
+
+
+def kernel_families(session):
+    """Share of a decode step's kernel time by family, from the device's kernel records (CUPTI through the
+    tensor framework's profiler) of three replays.  Kernels of a step overlap at their edges, so the shares are of
+    the SUM of kernel durations, given beside that sum; None when the records cannot be had."""
+    try:
+        import torch
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                session.step()
+            torch.cuda.synchronize()
+        totals, total = {}, 0.0
+        for event in prof.key_averages():
+            us = float(getattr(event, "device_time_total", 0.0) or getattr(event, "cuda_time_total", 0.0))
+            if us <= 0:
+                continue
+            name = event.key.lower()
+            family = next((f for f, marks in FAMILIES if any(m in name for m in marks)), "other")
+            totals[family] = totals.get(family, 0.0) + us
+            total += us
+        if total <= 0:
+            return None
+        out = {f: round(v / total, 4) for f, v in sorted(totals.items())}
+        out["kernel_ms_per_step"] = round(total / 3 / 1e3, 4)
+        return out
+    except Exception:
+        return None
+
+
+def run_mixed(args):
+    """BASELINE.json configs[3]: many requests of assorted prompt lengths through the scheduler, prompts in portions
+    under a token budget beside the decode tokens of the others."""
+    import random
+
+    import torch
+
+    from microllm_rocm_b200.config import preset
+    from microllm_rocm_b200.engine.llm import LLM
+    from microllm_rocm_b200.engine.loading import random_engine
+    from microllm_rocm_b200.kernels.build import LaunchCounter
+    from microllm_rocm_b200.sampling import GenerationConfig
+
+    full = preset(args.model)
+    layers = args.layers or full.num_hidden_layers
+    cfg = preset(args.model, num_hidden_layers=layers)
+    page = 64
+    rng = random.Random(args.seed)
+    lengths = [rng.randint(args.min_prompt, args.max_prompt) for _ in range(args.requests)]
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in lengths]
+    tokens_needed = sum(-(-(n + args.new_tokens) // page) * page for n in lengths) + page
+    if args.pool_tokens:
+        tokens_needed = args.pool_tokens
+    engine = random_engine(cfg, seed=0, dtype="bfloat16", page_size=page, max_tokens=tokens_needed,
+                           max_requests=args.requests, draw_on_device=True)
+    llm = LLM(engine, max_tokens_per_step=args.chunk, max_seqs=args.requests)
+    config = GenerationConfig(max_new_tokens=args.new_tokens, temperature=0.0)
+
+    def run_once():
+        ids = [llm.submit(p, config) for p in prompts]
+        launches0, steps, wait0 = LaunchCounter.own, 0, llm.wait_s
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        while llm.has_work():
+            llm.step()
+            steps += 1
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        generated = sum(len(llm.poll(i).generated) for i in ids)
+        for i in ids:
+            del llm.scheduler.requests[i]
+        return wall, steps, generated, LaunchCounter.own - launches0, llm.wait_s - wait0
+
+    run_once()                                   # warm-up: compiles nothing new afterwards, captures the decode steps
+    metrics0 = dict(llm.metrics())
+    sampler = ClockSampler()
+    with sampler:
+        time.sleep(0.3)
+        wall, steps, generated, launches, waited = run_once()
+    metrics = llm.metrics()
+    processed = sum(lengths) + generated
+    out = {
+        "metric": f"mixed serving: generated tokens/s ({args.model}-shape, bf16, {args.requests} requests, prompts "
+                  f"U[{args.min_prompt},{args.max_prompt}], {args.new_tokens} new tokens, {args.chunk}-token steps)",
+        "value": generated / wall, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": 1,
+        "ms_per_step": wall / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": f"synthetic: random weights N(0,0.02) seed 0, uniform random token ids, prompt lengths from seed {args.seed}",
+        "impl": "ours",
+        "config": {"model": args.model + "-shape", "layers": layers, "layers_of_model": full.num_hidden_layers,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_size, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "requests": args.requests, "min_prompt": args.min_prompt, "max_prompt": args.max_prompt,
+                   "new_tokens": args.new_tokens, "max_tokens_per_step": args.chunk, "page_size": page,
+                   "pool_tokens": tokens_needed, "parallelism": "single-gpu"},
+        "processed_tokens_per_s": processed / wall, "prompt_tokens": sum(lengths), "generated_tokens": generated,
+        "wall_s": wall, "host_waits_for_gpu_frac": waited / wall, "gpu_utilization_sampled": sampler.utilization(),
+        "gpu_launches": launches,
+        "preemptions": metrics.get("preemptions", 0) - metrics0.get("preemptions", 0),
+        "graph_steps": llm.graph_steps, "clocks": sampler.summary(),
+    }
+    print(json.dumps(out))
+    return 0
+
+
 def run_ours(args):
     import torch
 
@@ -241,16 +376,22 @@ def run_ours(args):
         print(json.dumps({"only": "prefill", "ms": prefill_ms, "tokens": args.prefill_tokens, "layers": layers}))
         return 0
     pf_flops = prefill_flops(cfg, layers, args.prefill_tokens)
+    # one step of a few milliseconds timed alone is the burst case of the tensor peak; the sustained figure beside it
     prefill = {"value": args.prefill_tokens / (prefill_ms / 1e3), "tokens": args.prefill_tokens, "ms": prefill_ms,
-               "frac": pf_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+               "frac": pf_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12),
+               "frac_of_sustained_peak": pf_flops / (prefill_ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12)}
 
     # ---- decode, device-timed ------------------------------------------------------------------
-    def decode_device(batch, steps, warmup, sampler=None):
-        session = DecodeSession(engine, prompts(batch), steps + warmup + 1)
+    family_shares = {}
+
+    def decode_device(batch, steps, warmup, sampler=None, families=False):
+        session = DecodeSession(engine, prompts(batch), steps + warmup + 1 + (4 if families else 0))
         for _ in range(warmup):
             session.step()
         torch.cuda.synchronize()
         launches = count_launches(session)
+        if families:
+            family_shares.update(kernel_families(session) or {})
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         if sampler:
             sampler.__enter__()
@@ -268,7 +409,7 @@ def run_ours(args):
         return ms, launches * steps, ctx
 
     sampler = ClockSampler()
-    ms_per_step, launches, ctx_len = decode_device(args.batch, args.steps, args.warmup, sampler)
+    ms_per_step, launches, ctx_len = decode_device(args.batch, args.steps, args.warmup, sampler, families=not args.only)
     value = args.batch / (ms_per_step / 1e3)
     bytes_step = decode_bytes(cfg, layers, args.batch, ctx_len)
     achieved = bytes_step / (ms_per_step / 1e3) / 1e9
@@ -310,6 +451,7 @@ def run_ours(args):
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak",
         "vs_baseline": value / BASELINE_DECODE_B8 if (args.model, args.batch, prompt_len) == ("qwen2.5-1.5b", 8, 2048) else None,
+        "baseline": {"value": BASELINE_DECODE_B8, "unit": "tokens/s", "what": BASELINE_NOTE},
         "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02) seed 0, uniform random token ids", "impl": "ours",
         "config": {"model": args.model + "-shape", "layers": layers, "layers_of_model": full.num_hidden_layers,
@@ -321,7 +463,7 @@ def run_ours(args):
         "e2e": e2e, "gpu_launches": launches, "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "bytes_per_step": bytes_step},
-        "points": points, "clocks": sampler.summary(),
+        "points": points, "families": family_shares or None, "clocks": sampler.summary(),
     }
     print(json.dumps(out))
     return 0
@@ -342,16 +484,25 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="run just one timed part and print a short line (for profiler captures)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed"])
+    ap.add_argument("--requests", type=int, default=64, help="mixed: how many requests")
+    ap.add_argument("--min-prompt", type=int, default=128)
+    ap.add_argument("--max-prompt", type=int, default=2048)
+    ap.add_argument("--new-tokens", type=int, default=128, help="mixed: tokens generated per request")
+    ap.add_argument("--chunk", type=int, default=512, help="mixed: token budget of a step (max_tokens_per_step)")
+    ap.add_argument("--pool-tokens", type=int, default=0, help="mixed: size the page pool for this many tokens (0: all requests fit)")
+    ap.add_argument("--seed", type=int, default=0)
     args = ap.parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": "walkinglabs/microLLM-rocm is a CMake C++/HIP project "
-                          "for ROCm (gfx942) with no CUDA path and no pip-installable package: it cannot run on a B200"}))
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "mixed":
+        return run_mixed(args)
     return run_ours(args)
 
 

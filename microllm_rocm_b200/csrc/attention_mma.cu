@@ -61,6 +61,8 @@ struct FaParams {
     float scale_log2;               // softmax scale * log2(e)
     int page_shift;                 // log2(page_size) when it is a power of two, else -1
     int* error_flag;
+    int listed;                     // decode shape: 1 = work item i is sequence work[i] (a step that also holds prompt
+                                    // portions), 0 = work item i is sequence i and token i (every sequence brings one token)
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -674,8 +676,9 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_kernel(FaP
     const int tiles_per_seq = (p.group + 15) / 16;
     TileGeometry geo;
     geo.seq = blockIdx.x / tiles_per_seq;
+    if (p.listed) geo.seq = __ldg(p.work + geo.seq);          // (the step's own lists come from the host: no wait needed)
     geo.kvh = blockIdx.y;
-    geo.token0 = geo.seq;
+    geo.token0 = p.listed ? __ldg(p.seq_starts + geo.seq) : geo.seq;
     geo.n_new = 1;
     geo.row0 = (blockIdx.x % tiles_per_seq) * 16;
     const int rows_valid = min(16, p.group - geo.row0);
@@ -925,9 +928,9 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_t_kernel(F
 
     // one token per sequence and at most 8 heads per group: the work item is the sequence = blockIdx.x
     TileGeometry geo;
-    geo.seq = blockIdx.x;
+    geo.seq = p.listed ? __ldg(p.work + blockIdx.x) : (int)blockIdx.x;   // (the step's own lists come from the host: no wait needed)
     geo.kvh = blockIdx.y;
-    geo.token0 = geo.seq;
+    geo.token0 = p.listed ? __ldg(p.seq_starts + geo.seq) : geo.seq;
     geo.n_new = 1;
     geo.row0 = 0;
     const int heads = p.group;                     // <= 8
@@ -1083,7 +1086,9 @@ MLB_EXPORT int mlb_fa_max_splits() { return MAX_SPLITS; }
 
 // mode 0: prefill shape (work items name the first of 4 row tiles of a sequence).
 // mode 1: decode shape: every sequence brings one token (num_work = sequences * ceil(group / 16));
-// the keys are cut `splits` ways (1, 2, 4 or 8; D / splits must be whole) over a thread-block cluster.
+// the keys are cut `splits` ways (1, 2, 4, 8 or 16; D / splits must be whole) over a thread-block cluster.
+// mode 2: the decode shape for SOME sequences of a step that also holds prompt portions: `work` lists the
+// sequences that bring exactly one token (num_work = listed sequences * ceil(group / 16)).
 MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* out, const int* seq_starts,
                                        const int* seq_pos0, const int* block_table, const int* work, int num_work,
                                        int max_blocks, int num_pages, int page_size, int num_heads, int num_kv_heads,
@@ -1095,14 +1100,17 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
         return fail(MLB_UNSUPPORTED_SIZE, "paged_attention_mma: page_size %d must be a multiple of 16", page_size);
     if (num_pages <= 0 || max_blocks <= 0 || window < 0 || num_work < 0)
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: bad cache geometry");
-    if (mode == 1 && !(splits == 1 || splits == 2 || splits == 4 || splits == 8 || splits == 16))
+    if (mode < 0 || mode > 2) return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: unknown mode %d", mode);
+    if (mode == 2 && !work) return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: mode 2 needs the list of sequences");
+    if (mode >= 1 && !(splits == 1 || splits == 2 || splits == 4 || splits == 8 || splits == 16))
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: %d splits, expected 1, 2, 4, 8 or 16", splits);
-    if (mode == 1 && D % splits != 0)
+    if (mode >= 1 && D % splits != 0)
         return fail(MLB_UNSUPPORTED_SIZE, "paged_attention_mma: %d splits do not divide the head size %d", splits, D);
     if (num_work == 0) return MLB_OK;
     FaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, seq_starts, seq_pos0,
                block_table, work, max_blocks, num_pages, page_size, num_heads, num_kv_heads,
-               num_heads / num_kv_heads, window, scale * LOG2E, (page_size & (page_size - 1)) == 0 ? __builtin_ctz((unsigned)page_size) : -1, error_flag};
+               num_heads / num_kv_heads, window, scale * LOG2E, (page_size & (page_size - 1)) == 0 ? __builtin_ctz((unsigned)page_size) : -1, error_flag,
+               mode == 2 ? 1 : 0};
     if (mode == 0) {
         static bool prefill_configured_on[MAX_DEVICES] = {false};
         bool& prefill_configured = prefill_configured_on[device_index()];

@@ -75,6 +75,7 @@ class DecodeGraph:
             state_slots=d("slots"), logit_rows=d("logit_rows"), error_flag=engine.error_flag,
             seq_starts_host=list(range(A + 1)), seq_pos0_host=[], state_slots_host=[], max_new_tokens=1, max_seq_len=1)
         self.views = engine.cache_views(self.ctx)
+        self._planners = list({b.mixer.plan_group(): b.mixer for b in engine.model.blocks}.values())    # one mixer per shared plan
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.requests: List[Hashable] = []
         self._table_state: Dict[str, List[tuple]] = {}
@@ -170,13 +171,13 @@ class DecodeGraph:
 
     def stale(self, max_seq_len: int) -> bool:
         """The captured step was cut for another context length than the one it is about to serve."""
-        return self.graph is not None and any(b.mixer.plan_stale(self.ctx, max_seq_len) for b in self.engine.model.blocks)
+        return self.graph is not None and any(m.plan_stale(self.ctx, max_seq_len) for m in self._planners)
 
     def invalidate(self) -> None:
         """Forget the captured step and the launch plans frozen into it; the next capture plans anew."""
         self.graph = None
-        for block in self.engine.model.blocks:
-            block.mixer.forget_plans(self.ctx)
+        for mixer in self._planners:
+            mixer.forget_plans(self.ctx)
 
     def fits(self, requests: Sequence[Hashable]) -> bool:
         cache = self.engine.cache

@@ -9,6 +9,7 @@ device -> host copy per step brings the selected tokens (and the kernels' error 
 """
 from __future__ import annotations
 
+import time
 from typing import Dict, List, Optional, Sequence, Union
 
 import torch
@@ -40,6 +41,7 @@ class LLM:
         self.graph_steps = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self.wait_s = 0.0            # host time spent blocked in the step's one device -> host read: the GPU was busy for all of it
 
     # ------------------------------------------------------------------ request interface
     def submit(self, prompt: Sequence[int], config: Optional[GenerationConfig] = None) -> int:
@@ -75,7 +77,9 @@ class LLM:
         if R:
             self.sampler.sample_into(logits, [r.config for r in wanting], [len(r.generated) for r in wanting], packed[:R])
         packed[R:].copy_(self.engine.error_flag)
+        t0 = time.perf_counter()
         host = packed.tolist()                                   # the step's one device -> host copy
+        self.wait_s += time.perf_counter() - t0
         self.h2d_bytes += 4 * plan.num_tokens
         self.d2h_bytes += 4 * (R + 1)
         if host[R]:
@@ -116,7 +120,9 @@ class LLM:
         self.graph_steps += 1
         self.engine.steps_run += 1
         self.engine.tokens_run += len(ids)
+        t0 = time.perf_counter()
         tokens = graph.read_tokens()
+        self.wait_s += time.perf_counter() - t0
         finished = self.scheduler.update(plan, tokens)
         if finished:
             self._graph = None

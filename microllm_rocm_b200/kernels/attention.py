@@ -6,9 +6,10 @@ multiple of 16; the plain kernel otherwise.  A step whose sequences all bring on
 the decode shape of `attention_mma.cu` (keys split over a thread-block cluster that merges
 through distributed shared memory).  In any other step every sequence that brings at least
 `TC_MIN_NEW_TOKENS` tokens goes to the tcgen05 kernel (`attention_tc.cu`: 128 query rows per
-CTA, scores and output in tensor memory; head sizes 64 and 128), the others (decoded tokens
-and short portions beside them) to the prefill shape of `attention_mma.cu` with its 16-row
-tiles.  The two launches write disjoint rows of the output.
+CTA, scores and output in tensor memory; head sizes 64 and 128), every sequence that brings
+exactly one token (a decoded token beside prompt portions) to the decode shape again, through a
+list of those sequences, and the short portions that remain to the prefill shape of
+`attention_mma.cu` with its 16-row tiles.  The launches write disjoint rows of the output.
 """
 from __future__ import annotations
 
@@ -103,7 +104,8 @@ def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
         return plan
     starts, A = ctx.seq_starts_host, ctx.num_seqs
     decode = ctx.max_new_tokens == 1
-    work, tc_work = [], []
+    work, tc_work, listed = [], [], []
+    tiles_per_token = -(-group // 16)
     for a in range(A):
         n_new = starts[a + 1] - starts[a]
         if use_tc and not decode and n_new >= TC_MIN_NEW_TOKENS:
@@ -112,6 +114,9 @@ def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
                 last_pos = pos0 + min(n_new, (tile + 1) * TC_ROWS_PER_TILE) - 1
                 tc_work.append((last_pos // TC_KEYS_PER_TILE, a, tile))
             continue
+        if not decode and n_new == 1:
+            listed.append(a)          # a decoded token beside prompt portions: the decode shape, with its key split
+            continue
         tiles = -(-n_new * group // 16)
         work += [(a, first) for first in range(0, tiles, 1 if decode else 4)]
     if not decode:
@@ -119,10 +124,17 @@ def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
         work.sort(key=lambda item: -item[1])
         tc_work.sort(key=lambda item: -item[0])
     device = ctx.positions.device
+    sms = sm_count(device)
     work_dev = torch.tensor(work, dtype=torch.int32).reshape(-1).to(device, non_blocking=True)
     tc_dev = torch.tensor([(a, t) for _, a, t in tc_work], dtype=torch.int32).reshape(-1).to(device, non_blocking=True)
-    splits = decode_splits(len(work) * num_kv_heads, ctx.max_seq_len, sm_count(device)) if decode else 1
-    plan = (work_dev, len(work), 1 if decode else 0, splits, tc_dev, len(tc_work))
+    splits = decode_splits(len(work) * num_kv_heads, ctx.max_seq_len, sms) if decode else 1
+    listed_dev, listed_splits = None, 1
+    if listed:
+        listed_dev = torch.tensor(listed, dtype=torch.int32).to(device, non_blocking=True)
+        longest = max(ctx.seq_pos0_host[a] for a in listed) + 1
+        listed_splits = decode_splits(len(listed) * tiles_per_token * num_kv_heads, longest, sms)
+    plan = (work_dev, len(work), 1 if decode else 0, splits, tc_dev, len(tc_work), listed_dev, len(listed) * tiles_per_token,
+            listed_splits)
     ctx.extras[key] = plan
     return plan
 
@@ -137,7 +149,8 @@ def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx
     if pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("paged_attention: the tensor-core kernel wants bf16 queries, pages and output")
     use_tc = tc_supported(head_dim, page_size, scale) and q.is_contiguous() and out.is_contiguous()
-    work, num_work, mode, splits, tc_work, num_tc = _plan(ctx, num_heads // num_kv_heads, num_kv_heads, use_tc)
+    work, num_work, mode, splits, tc_work, num_tc, listed, num_listed, listed_splits = _plan(
+        ctx, num_heads // num_kv_heads, num_kv_heads, use_tc)
     if num_tc:
         T = ops.lib("attention_tc.cu", {"HEAD_DIM": head_dim})
         build.check(T, T.mlb_paged_attention_tc(
@@ -145,9 +158,17 @@ def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx
             ctx.seq_pos0.data_ptr(), block_table.data_ptr(), tc_work.data_ptr(), num_tc, block_table.shape[1],
             pages.shape[0], page_size, num_heads, num_kv_heads, int(window or 0), float(scale), ops._ptr(ctx.error_flag),
             ops._stream()))
-    if not num_work:
+    if not num_work and not num_listed:
         return
     L = ops.lib("attention_mma.cu", {"HEAD_DIM": head_dim})
+    if num_listed:
+        # decoded tokens beside prompt portions: the decode shape for the listed sequences (mode 2)
+        build.check(L, L.mlb_paged_attention_mma(
+            q.data_ptr(), pages.data_ptr(), out.data_ptr(), ctx.seq_starts.data_ptr(), ctx.seq_pos0.data_ptr(), block_table.data_ptr(),
+            listed.data_ptr(), num_listed, block_table.shape[1], pages.shape[0], page_size, num_heads, num_kv_heads,
+            int(window or 0), float(scale), 2, listed_splits, ops._ptr(ctx.error_flag), ops._stream()))
+    if not num_work:
+        return
     build.check(L, L.mlb_paged_attention_mma(
         q.data_ptr(), pages.data_ptr(), out.data_ptr(), ctx.seq_starts.data_ptr(), ctx.seq_pos0.data_ptr(), block_table.data_ptr(), work.data_ptr(), num_work,
         block_table.shape[1], pages.shape[0], page_size, num_heads, num_kv_heads, int(window or 0), float(scale),

@@ -96,6 +96,9 @@ class Attention(Mixer):
     def forget_plans(self, ctx: StepContext) -> None:
         attention_kernels.forget_plans(ctx)
 
+    def plan_group(self):
+        return ("attention", self.rt.device)          # the kernels' plans are kept per (group size, kv heads), for all layers
+
     # --- compute ------------------------------------------------------------------------
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVView) -> torch.Tensor:
         T = x.shape[0]

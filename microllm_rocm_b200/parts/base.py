@@ -224,6 +224,11 @@ class Mixer(Part):
         """Drop this mixer's plans from `ctx`; the next forward plans anew."""
         return None
 
+    def plan_group(self):
+        """Mixers with equal plan_group share their plans in a context (the layers of a model, usually): asking one
+        of them whether the plans are stale answers for all.  Default: every mixer plans for itself."""
+        return id(self)
+
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:

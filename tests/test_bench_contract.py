@@ -1,5 +1,6 @@
-"""What bench.py promises without a GPU: more than one GPU is refused with one line and exit code 2, the
-reference arm answers with its `unavailable` line and exit code 0."""
+"""What bench.py promises without a GPU: more than one GPU is refused with one line and exit code 2, and the
+reference arm answers with exit code 0 and ONE JSON line marked `"impl": "reference"` -- either a measurement
+(`value`) or the reason why there is none (`unavailable`)."""
 import json
 import os
 import subprocess
@@ -18,8 +19,12 @@ def test_more_than_one_gpu_is_refused():
     assert len(proc.stdout.strip().splitlines()) == 1 and "one GPU" in proc.stdout
 
 
-def test_reference_arm_is_unavailable():
+def test_reference_arm_answers_with_a_measurement_or_a_reason():
     proc = run("--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1")
     assert proc.returncode == 0
     line = json.loads(proc.stdout.strip().splitlines()[-1])
-    assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and line["unavailable"]
+    assert line["impl"] == "reference"
+    if "unavailable" in line:
+        assert isinstance(line["unavailable"], str) and len(line["unavailable"].splitlines()) == 1 and line["unavailable"]
+    else:
+        assert line["value"] > 0 and line["metric"] and line["config"]

@@ -209,6 +209,40 @@ def test_decode_steps_at_long_contexts_against_the_formula(batch, context, nh, n
     assert worst < BF16_ROW_TOL, worst
 
 
+@gpu
+@pytest.mark.parametrize("nh,nkv", [(12, 2), (40, 8), (18, 1)])
+def test_decoded_tokens_beside_a_prompt_portion_use_the_key_split(nh, nkv):
+    """A step that mixes a 300-token prompt portion with single tokens of sequences that already hold thousands of
+    keys: the single tokens go through the decode shape (their keys split over a cluster), found through a list of
+    their sequences, the portion through the tensor-memory kernel; each writes its own rows."""
+    d, page = 128, 64
+    lens = [3000, 2500, 41, 1717, 4000, 1]
+    news = [1, 300, 1, 1, 1, 1]
+    case = PagedCase(lens, nkv, d, page, seed=nh * 31 + nkv)
+    gen = case.gen
+    qs = [(torch.randn((n, nh, d), generator=gen, device=DEV) * PEAK).bfloat16() for n in news]
+    direction = torch.randn(d, generator=gen, device=DEV)
+    direction /= direction.norm()
+    fars = [(s * 977 + 5) % n for s, n in enumerate(lens)]
+    for s in (0, 3, 4):
+        case.plant(s, fars[s], direction, PLANT)
+        qs[s][:, :nh // 2] = (direction * PLANT).bfloat16()
+    out, starts, pos0, plans = launch(case, qs, news, nh, nkv, d, None)
+    assert plans and plans[0][7] == 5 * -(-(nh // nkv) // 16) and plans[0][8] > 1      # five listed sequences, keys split
+    assert torch.isfinite(out).all()
+    worst = 0.0
+    for s, n in enumerate(lens):
+        k, v = case.dense(s)
+        rows = torch.arange(news[s], device=DEV)
+        want = reference_rows(qs[s].float(), rows + pos0[s], k, v, None)
+        got = out[starts[s]:starts[s + 1]].reshape(news[s], nh, d)
+        worst = max(worst, worst_relative_error(got, want))
+        if s in (0, 3, 4):
+            assert (got[0, 0] - v[fars[s], 0]).abs().max() < 0.05, s
+    print(f"decoded tokens beside a portion, heads {nh}/{nkv}: worst relative row error {worst:.4f}")
+    assert worst < BF16_ROW_TOL, worst
+
+
 # ------------------------------------------------------------------------------ two layers of the benchmark shape
 @gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
