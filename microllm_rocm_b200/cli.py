@@ -16,7 +16,8 @@ that describes this engine: --use-cache true (there is no uncached path), --batc
 tokenizer flags (--text, --vocab, --merges, --tokenizer-family, --chat-user) are refused by name.  The reference's command line is
 always greedy and has no random-weights mode; added here: --model DIR (config.json and
 model.safetensors in one folder), --dtype fp32|bf16, --temperature, --sampling-top-k, --seed,
---stop-tokens, --page-size, --num-pages, --max-tokens-per-step, --max-seqs, and
+--stop-tokens, --stop-on-eos true|false (the configuration's eos_token_id ends a generation), --page-size,
+--num-pages, --max-tokens-per-step, --max-seqs, and
 --random-config NAME --random-seed S --write-model DIR to write a random model folder.
 Tokenizers are out of scope: prompts are token ids.
 """
@@ -39,6 +40,7 @@ DEFAULTS: Dict[str, object] = {
     "continuous-prompt-offsets": "", "continuous-arrival-steps": "",
     "temperature": 0.0, "sampling-top-k": 0, "seed": 1, "stop-tokens": "", "page-size": 16, "num-pages": 0,
     "max-tokens-per-step": 2048, "max-seqs": 64, "random-config": "", "random-seed": 0, "write-model": "",
+    "stop-on-eos": "false",
     # the reference's switches between code paths: only the value that describes this engine is accepted
     "use-cache": "true", "prefill-logits": "last", "batch-argmax-mode": "device", "decode-mode": "generation",
     "continuous-prefill-batch": "true", "continuous-diagnostics": "false",
@@ -110,6 +112,8 @@ def int_list(text: str, what: str) -> List[int]:
 def validate(o: Dict[str, object]) -> None:
     if o["prefill-logits"] not in ("last", "full"):
         raise UsageError("--prefill-logits must be last or full")
+    if o["stop-on-eos"] not in BOOL:
+        raise UsageError("--stop-on-eos must be true or false")
     for key, (legal, ours, why) in ONE_WAY.items():
         if o[key] not in legal:
             raise UsageError(f"--{key} must be {' or '.join(legal)}")
@@ -172,13 +176,17 @@ def main(argv: Optional[List[str]] = None) -> int:
         print(json.dumps({"schema_version": 1, "status": "error", "error": str(e)}))
         return 2
     if o["random-config"] and o["write-model"]:
-        from .config import get_architecture, preset
+        from .config import find_preset, parameter_count
         from .weights import write_random_model
-        cfg = preset(o["random-config"])
-        write_random_model(get_architecture("Qwen2ForCausalLM"), cfg, o["random-seed"], o["write-model"],
+        try:
+            arch, cfg = find_preset(o["random-config"])
+        except KeyError as e:
+            print(json.dumps({"schema_version": 1, "status": "error", "error": str(e.args[0])}))
+            return 2
+        write_random_model(arch, cfg, o["random-seed"], o["write-model"],
                            {"fp32": "float32", "bf16": "bfloat16"}.get(o["dtype"], o["dtype"] or None))
-        print(json.dumps({"schema_version": 1, "status": "pass", "wrote": o["write-model"],
-                          "parameter_count": cfg.parameter_count()}))
+        print(json.dumps({"schema_version": 1, "status": "pass", "wrote": o["write-model"], "architecture": arch.name,
+                          "parameter_count": parameter_count(arch, cfg)}))
         return 0
     return run(o)
 
@@ -222,13 +230,23 @@ def run(o) -> int:
     props = torch.cuda.get_device_properties(engine.device)
     out = {"schema_version": 1, "status": "pass", "device": str(engine.device), "device_name": props.name,
            "architecture": f"sm_{props.major}{props.minor}", "device_total_bytes": props.total_memory,
-           "compute_dtype": dtype, "workload": o["workload"], "parameter_count": cfg.parameter_count(),
+           "compute_dtype": dtype, "workload": o["workload"], "parameter_count": engine.parameter_count,
            "loaded_tensors": len(engine.model.expected_tensors()), "token_count": len(ids), "batch": batch,
            "cache_prefill_mode": o["cache-prefill-mode"], "kv_cache_dtype": dtype, "page_size": page,
            "num_pages": num_pages, "warmup": o["warmup"], "steps": o["steps"], "load_ms": load_ms}
+    stop_tokens = int_list(o["stop-tokens"], "--stop-tokens")
+    if BOOL[o["stop-on-eos"]]:
+        # The reference parses eos_token_id and never uses it (src/model/huggingface.cpp:178-179); here it becomes a
+        # stop token on request.  A configuration may name one id or a list of them.
+        eos = getattr(cfg, "eos_token_id", None)
+        eos_ids = [] if eos is None else (list(eos) if isinstance(eos, (list, tuple)) else [eos])
+        if not eos_ids:
+            print(json.dumps({"schema_version": 1, "status": "error", "error": "--stop-on-eos true: config.json names no eos_token_id"}))
+            return 2
+        stop_tokens = list(dict.fromkeys(stop_tokens + [int(t) for t in eos_ids]))
+        out["stop_on_eos"] = eos_ids
     sampling = GenerationConfig(max_new_tokens=max(new_tokens, 0), temperature=o["temperature"],
-                                top_k=o["sampling-top-k"], seed=o["seed"],
-                                stop_tokens=tuple(int_list(o["stop-tokens"], "--stop-tokens")))
+                                top_k=o["sampling-top-k"], seed=o["seed"], stop_tokens=tuple(stop_tokens))
 
     def timed(fn):
         torch.cuda.synchronize()

@@ -8,7 +8,7 @@ from typing import Optional
 import torch
 
 from ..cache.manager import CacheManager
-from ..config.registry import architecture_of, get_architecture
+from ..config.registry import architecture_for, architecture_of, get_architecture
 from ..kernels import build as kernel_build
 from ..kernels import ops
 from ..parts.base import Runtime
@@ -76,21 +76,23 @@ def load_engine(folder: str, dtype="bfloat16", page_size: int = DEFAULT_PAGE_SIZ
     rt = Runtime(dev, resolve_dtype(dtype))
     model = build_model(arch.build_spec(config), rt)
     prepare_kernels(model)
-    load_weights(model, weights_path or folder, strict=strict)
+    report = load_weights(model, weights_path or folder, strict=strict)
     if num_pages is None:
         num_pages = pages_for_tokens(max_tokens if max_tokens is not None else config.max_position_embeddings, page_size)
     engine = make_engine(model, page_size, num_pages, max_requests)
     engine.config = config
+    engine.load_report = report
     return engine
 
 
 def random_engine(config, seed: int = 0, dtype="bfloat16", page_size: int = DEFAULT_PAGE_SIZE,
                   num_pages: Optional[int] = None, max_tokens: Optional[int] = None, max_requests: int = 64,
-                  device: Optional[str] = None, architecture: str = "Qwen2ForCausalLM",
+                  device: Optional[str] = None, architecture: Optional[str] = None,
                   storage_dtype: Optional[torch.dtype] = None, draw_on_device: bool = False) -> Engine:
-    """An engine over random weights drawn from `seed`, without a model folder."""
+    """An engine over random weights drawn from `seed`, without a model folder.  The architecture is the one
+    the configuration's class belongs to, unless named."""
     dev = require_gpu(device)
-    arch = get_architecture(architecture)
+    arch = get_architecture(architecture) if architecture else architecture_for(config)
     rt = Runtime(dev, resolve_dtype(dtype))
     model = build_model(arch.build_spec(config), rt)
     prepare_kernels(model)

@@ -59,6 +59,17 @@ class Engine:
         self._pinned_events: List[Optional[torch.cuda.Event]] = [None] * 4
         self._pinned_next = 0
 
+    @property
+    def parameter_count(self) -> int:
+        """Elements of every tensor the model declares (a tied head counts once)."""
+        total = 0
+        for spec in self.model.expected_tensors().values():
+            n = 1
+            for s in spec.shape:
+                n *= int(s)
+            total += n
+        return total
+
     # ------------------------------------------------------------------ batch assembly
     def _pinned_buffer(self, n: int):
         """A pinned staging buffer that no copy in flight still reads."""

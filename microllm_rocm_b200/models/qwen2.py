@@ -9,7 +9,7 @@ This file only describes; the parts it names live in `parts/` and know nothing o
 """
 from __future__ import annotations
 
-from ..config.qwen2 import Qwen2Config, ARCHITECTURE
+from ..config.qwen2 import ARCHITECTURE, PRESETS, Qwen2Config
 from ..config.registry import Architecture, register_architecture
 from ..config.spec import LayerSpec, ModelSpec, PartSpec, RunSpec
 
@@ -52,5 +52,5 @@ def build_spec(cfg: Qwen2Config) -> ModelSpec:
     return spec
 
 
-register_architecture(Architecture(name=ARCHITECTURE, config_class=Qwen2Config, build_spec=build_spec),
-                      replace=True)
+register_architecture(Architecture(name=ARCHITECTURE, config_class=Qwen2Config, build_spec=build_spec,
+                                   model_types=("qwen2",), presets=PRESETS), replace=True)

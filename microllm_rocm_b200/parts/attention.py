@@ -64,10 +64,24 @@ class Attention(Mixer):
             specs["o_proj.bias"] = WeightSpec((self.hidden,), role="vector")
         return specs
 
-    def bind(self, tensors):
-        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]], 0).contiguous()
+    def fused_tensors(self):
+        q, kv = self.nh * self.d, self.nkv * self.d
+        fused = {"qkv_proj.weight": (WeightSpec((q + 2 * kv, self.hidden)),
+                                     [("q_proj.weight", 0), ("k_proj.weight", q), ("v_proj.weight", q + kv)])}
         if self.qkv_bias:
-            self.b_qkv = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]], 0).contiguous()
+            fused["qkv_proj.bias"] = (WeightSpec((q + 2 * kv,), role="vector"),
+                                      [("q_proj.bias", 0), ("k_proj.bias", q), ("v_proj.bias", q + kv)])
+        return fused
+
+    def bind(self, tensors):
+        # the loader hands over the fused tensors; a caller with the checkpoint's pieces gets them joined here
+        if "qkv_proj.weight" in tensors:
+            self.w_qkv = tensors["qkv_proj.weight"]
+            self.b_qkv = tensors.get("qkv_proj.bias") if self.qkv_bias else None
+        else:
+            self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]], 0).contiguous()
+            if self.qkv_bias:
+                self.b_qkv = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]], 0).contiguous()
         self.w_o = tensors["o_proj.weight"]
         self.b_o = tensors.get("o_proj.bias")
 

@@ -152,6 +152,14 @@ class Part:
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         pass
 
+    def fused_tensors(self) -> Dict[str, Tuple[WeightSpec, List[Tuple[str, int]]]]:
+        """Tensors this part keeps FUSED on the device although the checkpoint stores their pieces apart:
+        local name of the fused tensor -> (its spec, [(local name of a piece, first row it occupies), ...]).
+        The loader then allocates the fused tensor once and streams each piece straight into its rows, and
+        `bind` receives the fused tensor under its local name instead of the pieces.  Default: nothing is fused
+        (a part may still join pieces in `bind`, at the price of holding them twice for a moment)."""
+        return {}
+
     def kernel_sources(self) -> List[Tuple[str, dict]]:
         """(source file, defines) of the kernel objects this part will ask for beyond those every model needs,
         so that they are compiled together, in parallel, before the first step instead of one by one inside it."""

@@ -127,9 +127,41 @@ class Model:
         params = self.spec.head.params
         return [params["name"]] if params.get("tied_to") is not None and "name" in params else []
 
-    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        """`tensors`: full name -> device tensor, already in the dtype policy of the runtime."""
+    def placements(self):
+        """Where each checkpoint tensor goes on the device.  Returns (destinations, pieces):
+        destinations: full name of a device tensor -> its WeightSpec (a fused tensor, or the checkpoint tensor itself);
+        pieces: full checkpoint name -> (full destination name, first row)."""
+        destinations: Dict[str, WeightSpec] = {}
+        pieces: Dict[str, Tuple[str, int]] = {}
         for prefix, part in self._parts:
+            fused = part.fused_tensors()
+            inside = {}
+            for dest, (spec, parts_of) in fused.items():
+                destinations[prefix + dest] = spec
+                for local, row in parts_of:
+                    inside[local] = (prefix + dest, row)
+            for local, ws in part.weight_specs().items():
+                if local in inside:
+                    pieces[prefix + local] = inside[local]
+                else:
+                    destinations.setdefault(prefix + local, ws)
+                    pieces[prefix + local] = (prefix + local, 0)
+        return destinations, pieces
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """`tensors`: full name -> device tensor, already in the dtype policy of the runtime; either under the
+        checkpoint's names or under the destination names of `placements()`."""
+        for prefix, part in self._parts:
+            fused = part.fused_tensors()
+            if fused and all(prefix + dest in tensors for dest in fused):
+                covered = {local for _, parts_of in fused.values() for local, _ in parts_of}
+                local = {dest: tensors[prefix + dest] for dest in fused}
+                local.update({name: tensors[prefix + name] for name in part.weight_specs() if name not in covered})
+                tied = getattr(part, "tied_to", None)
+                if tied is not None:
+                    local[tied] = tensors[tied]
+                part.bind(local)
+                continue
             local = {name: tensors[prefix + name] for name in part.weight_specs()}
             tied = getattr(part, "tied_to", None)
             if tied is not None:

@@ -29,8 +29,15 @@ class SwiGLU(FeedForward):
     def kernel_sources(self):
         return [] if self.rt.is_fp32 else gemm_bf16.sources(engine_only=True)
 
+    def fused_tensors(self):
+        return {"gate_up_proj.weight": (WeightSpec((2 * self.inter, self.hidden)),
+                                        [("gate_proj.weight", 0), ("up_proj.weight", self.inter)])}
+
     def bind(self, tensors):
-        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], 0).contiguous()
+        if "gate_up_proj.weight" in tensors:             # from the loader: already fused, gate rows then up rows
+            self.w_gate_up = tensors["gate_up_proj.weight"]
+        else:
+            self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], 0).contiguous()
         self.w_down = tensors["down_proj.weight"]
 
     def replay_key(self):

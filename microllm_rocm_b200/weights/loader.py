@@ -14,8 +14,9 @@ the serving path; the reference widens everything to fp32, model.cpp:1877-1905);
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
-from typing import Dict, List, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import torch
 
@@ -34,6 +35,8 @@ class LoadReport:
     wrong_shape: List[Tuple[str, Tuple[int, ...], Tuple[int, ...]]] = field(default_factory=list)  # name, want, got
     wrong_dtype: List[Tuple[str, str]] = field(default_factory=list)
     ignored: List[str] = field(default_factory=list)
+    load_ms: float = 0.0              # from the first byte staged to the last copy finished
+    bytes_read: int = 0               # payload bytes taken from the file(s)
 
     @property
     def ok(self) -> bool:
@@ -116,9 +119,75 @@ def load_weights(model, folder_or_file: str, strict: bool = True) -> LoadReport:
     if not report.ok:
         raise WeightLoadError(report, folder_or_file)
     rt: Runtime = model.rt
-    tensors: Dict[str, torch.Tensor] = {}
-    for name, spec in expected.items():
+    started = time.perf_counter()
+    destinations, pieces = model.placements()
+    tensors: Dict[str, torch.Tensor] = {
+        name: torch.empty(spec.shape, dtype=target_dtype(spec.role, rt), device=rt.device) for name, spec in destinations.items()}
+    stream = _Stager(rt.device) if rt.device.type == "cuda" else None
+    for name in expected:
+        dest, row = pieces[name]
         src = where[name].tensor(name)
-        tensors[name] = src.to(device=rt.device, dtype=target_dtype(spec.role, rt), non_blocking=False).contiguous()
+        target = tensors[dest]
+        rows = src.shape[0] if src.dim() else 1
+        into = target[row:row + rows] if target.dim() else target
+        if tuple(into.shape) != tuple(src.shape):
+            raise ValueError(f"tensor {name!r} of shape {list(src.shape)} does not fit rows {row}.. of {dest!r} {list(target.shape)}")
+        if stream is not None:
+            stream.copy(src, into)
+        else:
+            into.copy_(src)
+        report.bytes_read += src.numel() * src.element_size()
+    if stream is not None:
+        stream.finish()
+    report.load_ms = (time.perf_counter() - started) * 1e3
     model.bind(tensors)
     return report
+
+
+class _Stager:
+    """File -> device in bounded pieces: mapped file -> pinned host buffer (a ring of them, so that the next piece
+    is staged while the last one travels) -> asynchronous copy, straight into the destination's rows when the
+    file holds the destination's dtype, through a device buffer and a cast there when it does not.  The reference
+    streams in the same manner (bounded staging, conversion on the device: src/model/model.cpp:1786-1908)."""
+
+    def __init__(self, device: torch.device, piece_bytes: int = 32 << 20, buffers: int = 3):
+        self.device, self.piece_bytes = device, piece_bytes
+        self.pinned = [torch.empty(piece_bytes, dtype=torch.uint8, pin_memory=True) for _ in range(buffers)]
+        self.events: List[Optional[torch.cuda.Event]] = [None] * buffers
+        self.cast_buffer: Optional[torch.Tensor] = None
+        self.next = 0
+
+    def copy(self, src: torch.Tensor, into: torch.Tensor) -> None:
+        """src: CPU tensor (a view of the mapped file); into: contiguous device tensor of the same shape."""
+        if not into.is_contiguous():
+            raise ValueError("the destination rows must be contiguous")
+        n = src.numel()
+        if n == 0:
+            return
+        flat_src = src.reshape(-1)
+        flat_dst = into.view(-1) if into.dim() else into.reshape(1)
+        same = src.dtype == into.dtype
+        item = src.element_size()
+        per_piece = max(1, self.piece_bytes // item)
+        if not same and (self.cast_buffer is None or self.cast_buffer.numel() < self.piece_bytes):
+            self.cast_buffer = torch.empty(self.piece_bytes, dtype=torch.uint8, device=self.device)
+        for begin in range(0, n, per_piece):
+            count = min(per_piece, n - begin)
+            i = self.next
+            self.next = (i + 1) % len(self.pinned)
+            if self.events[i] is not None:
+                self.events[i].synchronize()              # the copy that last read this buffer has run
+            host = self.pinned[i][:count * item].view(src.dtype)
+            host.copy_(flat_src[begin:begin + count])     # page cache -> pinned memory
+            if same:
+                flat_dst[begin:begin + count].copy_(host, non_blocking=True)
+            else:
+                staged = self.cast_buffer[:count * item].view(src.dtype)
+                staged.copy_(host, non_blocking=True)
+                flat_dst[begin:begin + count].copy_(staged)      # the cast, on the device, in stream order
+            event = self.events[i] or torch.cuda.Event()
+            event.record()
+            self.events[i] = event
+
+    def finish(self) -> None:
+        torch.cuda.synchronize(self.device)

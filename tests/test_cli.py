@@ -38,6 +38,7 @@ def test_pairs_names_and_types():
     (BASE + ["--cache-logits-output", "x.bin", "--new-tokens", "1"], "at least two new tokens"),
     (["--model", "folder", "--workload", "continuous"], "continuous workload requires"),
     (["--model", "folder"], "--tokens is required"),
+    (BASE + ["--stop-on-eos", "maybe"], "--stop-on-eos must be true or false"),
 ])
 def test_rules_of_the_reference(argv, message):
     with pytest.raises(cli.UsageError, match=message):

@@ -152,6 +152,28 @@ def test_command_line(folders, tmp_path):
     assert info["admissions"] == 3
 
 
+def test_command_line_stops_on_the_configuration_eos(folders, tmp_path):
+    """--stop-on-eos true makes config.json's eos_token_id a stop token: the generation ends with it."""
+    import shutil
+    key = "a"
+    prompt = random_tokens(9, tiny_config(key).vocab_size, 2)
+    want = plain_generate(folders[key], prompt, 6)
+    folder = tmp_path / "with_eos"
+    shutil.copytree(folders[key], folder)
+    raw = json.load(open(folder / "config.json"))
+    raw["eos_token_id"] = want[2]                       # the third token the model will generate
+    json.dump(raw, open(folder / "config.json", "w"))
+    base = [sys.executable, os.path.join(ROOT, "bin", "microllm_hf_infer"), "--model", str(folder), "--tokens",
+            ",".join(map(str, prompt)), "--workload", "decode", "--new-tokens", "6"]
+    proc = subprocess.run(base + ["--stop-on-eos", "true"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    info = json.loads(proc.stdout.strip().splitlines()[-1])
+    cut = want[:want.index(want[2]) + 1]
+    assert info["generated_tokens"] == cut and info["stop_on_eos"] == [want[2]]
+    proc = subprocess.run(base, capture_output=True, text=True, timeout=600)                    # without the flag eos is just a token
+    assert json.loads(proc.stdout.strip().splitlines()[-1])["generated_tokens"] == want
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_captured_decode_steps_equal_launched_ones(folders, dtype):
     """Steady decoding replays a captured step whose inputs live on the device; it must select

@@ -167,3 +167,50 @@ def test_sharded_folder_through_index(tmp_path):
     json.dump(index, open(os.path.join(folder, "model.safetensors.index.json"), "w"))
     with pytest.raises(SafetensorsError, match="leaves the model folder"):
         open_model_files(folder)
+
+
+@pytest.mark.gpu
+def test_a_benchmark_size_folder_streams_onto_the_device_bit_for_bit(tmp_path):
+    """The Qwen2.5-1.5B shape written as a bf16 model folder (3.1 GB) and loaded back through the streaming
+    loader: pieces of the mapped file go through pinned staging buffers into the rows of the FUSED device
+    tensors (q, k, v under one another; gate over up) without a second copy on the device.  Tensors are
+    compared bit for bit with the file as a minimal reader sees it, and the time is printed."""
+    import time
+    from microllm_rocm_b200.config import find_preset
+    from microllm_rocm_b200.engine.loading import load_engine
+    from microllm_rocm_b200.weights import safetensors as st
+    from microllm_rocm_b200.parts.base import Runtime
+    from microllm_rocm_b200.parts.build import build_model
+    from microllm_rocm_b200.weights.random_init import random_tensors
+    arch, cfg = find_preset("qwen2.5-1.5b")
+    folder = str(tmp_path / "model")
+    import os
+    os.makedirs(folder)
+    cfg.save(folder)
+    # drawn on the device (a CPU draw of 1.5 G values takes a minute), written in the checkpoint's naming
+    declared = build_model(arch.build_spec(cfg), Runtime(torch.device("cpu"), torch.float32)).expected_tensors()
+    t0 = time.perf_counter()
+    st.save_file(random_tensors(declared, 3, torch.device("cuda"), torch.bfloat16), os.path.join(folder, "model.safetensors"))
+    wrote = time.perf_counter() - t0
+    torch.cuda.empty_cache()
+    before = torch.cuda.memory_allocated()
+    engine = load_engine(folder, dtype="bfloat16", page_size=64, max_tokens=256, max_requests=2)
+    report = engine.load_report
+    size = os.path.getsize(os.path.join(folder, "model.safetensors"))
+    print(f"wrote {size / 1e9:.2f} GB in {wrote:.1f} s; loaded {report.bytes_read / 1e9:.2f} GB in {report.load_ms:.0f} ms "
+          f"({report.bytes_read / 1e6 / report.load_ms:.2f} GB/s)")
+    assert report.bytes_read == sum(t.end - t.begin for t in st.SafetensorsFile(os.path.join(folder, "model.safetensors")).infos.values())
+    # device memory holds the weights once (plus the small cache of this engine and staging)
+    assert torch.cuda.memory_allocated() - before < report.bytes_read * 1.05 + (256 << 20)
+    f = st.SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    mixer, mlp = engine.model.blocks[17].mixer, engine.model.blocks[17].feed_forward
+    q, kv = cfg.num_attention_heads * cfg.head_size, cfg.num_key_value_heads * cfg.head_size
+    p = "model.layers.17."
+    assert torch.equal(mixer.w_qkv[:q].cpu(), f.tensor(p + "self_attn.q_proj.weight"))
+    assert torch.equal(mixer.w_qkv[q:q + kv].cpu(), f.tensor(p + "self_attn.k_proj.weight"))
+    assert torch.equal(mixer.w_qkv[q + kv:].cpu(), f.tensor(p + "self_attn.v_proj.weight"))
+    assert torch.equal(mixer.b_qkv[q:q + kv].cpu(), f.tensor(p + "self_attn.k_proj.bias").float())
+    assert torch.equal(mlp.w_gate_up[cfg.intermediate_size:].cpu(), f.tensor(p + "mlp.up_proj.weight"))
+    assert torch.equal(mlp.w_down.cpu(), f.tensor(p + "mlp.down_proj.weight"))
+    assert torch.equal(engine.model.embedding.table[100000:100003].cpu(), f.tensor("model.embed_tokens.weight")[100000:100003])
+    assert engine.model.head.weight.data_ptr() == engine.model.embedding.table.data_ptr()         # tied: one table
