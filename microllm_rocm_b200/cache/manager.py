@@ -51,9 +51,13 @@ class CacheGroup:
 
 class CacheManager:
     def __init__(self, entries: Dict[str, object], page_size: int, num_pages: int, max_requests: int,
-                 device: Optional[torch.device] = None, kv_dtype: torch.dtype = torch.float32):
+                 device: Optional[torch.device] = None, kv_dtype: torch.dtype = torch.float32,
+                 max_step_tokens: Optional[int] = None):
         """entries: cache name -> PagedKVNeed | FixedStateNeed (from parts.Model.cache_entries).
-        num_pages: pages per group.  device None: books only, no storage (for host tests)."""
+        num_pages: pages of a group that keeps all keys.  device None: books only, no storage (for host tests).
+        max_step_tokens: the most tokens one request brings in a step, when the caller promises one: a group
+        with a window of W keys then never holds more than W - 1 + max_step_tokens tokens of a request, and its
+        pool (and storage) is sized for max_requests such spans instead of for num_pages."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size, self.num_pages, self.max_requests = int(page_size), int(num_pages), int(max_requests)
@@ -68,12 +72,12 @@ class CacheManager:
             if isinstance(need, PagedKVNeed):
                 key = group_key(need)
                 if key not in self.groups:
-                    self.groups[key] = CacheGroup(key, need.window, num_pages)
+                    self.groups[key] = CacheGroup(key, need.window, self.pages_for_group(need.window, max_step_tokens))
                 self.entry_group[name] = key
                 if device is not None:
                     self.kv_storage[name] = torch.zeros(
-                        (num_pages, 2, need.num_kv_heads, page_size, need.head_dim), dtype=need.dtype or kv_dtype,
-                        device=device)
+                        (self.groups[key].pool.num_pages, 2, need.num_kv_heads, page_size, need.head_dim),
+                        dtype=need.dtype or kv_dtype, device=device)
             elif isinstance(need, FixedStateNeed):
                 self.state_needs[name] = need
                 if device is not None:
@@ -84,6 +88,15 @@ class CacheManager:
         self.requests: Dict[Hashable, _Request] = {}
         self.pages_released_by_window = 0
         self.tables_version = 0          # grows whenever any block table changes: lets a reader skip a comparison
+
+    def pages_for_group(self, window: Optional[int], max_step_tokens: Optional[int]) -> int:
+        """Pages of a group's pool: num_pages for all keys; for a window, what max_requests requests can hold at
+        most while each keeps W - 1 old keys and brings up to max_step_tokens new ones (one more block for a span
+        that does not start on a block's edge) -- never more than num_pages."""
+        if window is None or not max_step_tokens:
+            return self.num_pages
+        span_blocks = self.blocks_for(int(window) - 1 + int(max_step_tokens)) + 1
+        return max(1, min(self.num_pages, self.max_requests * span_blocks))
 
     # ----- requests -------------------------------------------------------------------------
     def add(self, request: Hashable) -> bool:

@@ -12,8 +12,12 @@ full|token, --bf16-ffn/--bf16-attention, --kv-cache-dtype, --cache-capacity,
 and this engine does not are read and checked as the reference checks them, and accepted with the one value
 that describes this engine: --use-cache true (there is no uncached path), --batch-argmax-mode device, --decode-mode generation, --continuous-prefill-batch true,
 --continuous-diagnostics false; any other legal value is refused with a sentence that says so, and
---continuous-cache-buckets (a paged cache has no buckets), --kv-cache-fp32-layers, --trace-output and the
+--continuous-cache-buckets (a paged cache has no buckets), --kv-cache-fp32-layers and the
 tokenizer flags (--text, --vocab, --merges, --tokenizer-family, --chat-user) are refused by name.  The reference's command line is
+--trace-output FILE (with --trace-max-elements N, prefill workload only, as hf_infer.cpp:268-273) writes one JSON line per
+intermediate tensor of the prompt's step in the reference's record layout (src/profiling/trace.cpp:156-195): the embedding,
+the residual stream and the pending delta after every layer, the final norm and the logits, each with its statistics and
+its first N values.  The reference's command line is
 always greedy and has no random-weights mode; added here: --model DIR (config.json and
 model.safetensors in one folder), --dtype fp32|bf16, --temperature, --sampling-top-k, --seed,
 --stop-tokens, --stop-on-eos true|false (the configuration's eos_token_id ends a generation), --page-size,
@@ -40,7 +44,7 @@ DEFAULTS: Dict[str, object] = {
     "continuous-prompt-offsets": "", "continuous-arrival-steps": "",
     "temperature": 0.0, "sampling-top-k": 0, "seed": 1, "stop-tokens": "", "page-size": 16, "num-pages": 0,
     "max-tokens-per-step": 2048, "max-seqs": 64, "random-config": "", "random-seed": 0, "write-model": "",
-    "stop-on-eos": "false",
+    "stop-on-eos": "false", "trace-output": "", "trace-max-elements": 4096,
     # the reference's switches between code paths: only the value that describes this engine is accepted
     "use-cache": "true", "prefill-logits": "last", "batch-argmax-mode": "device", "decode-mode": "generation",
     "continuous-prefill-batch": "true", "continuous-diagnostics": "false",
@@ -57,8 +61,6 @@ ONE_WAY = {
 NOT_HERE = {
     "continuous-cache-buckets": "a paged cache has no capacity buckets",
     "kv-cache-fp32-layers": "the cache has the compute dtype in every layer",
-    "trace-output": "tensor traces are not built; bin/trace_run replays token traces and writes logits",
-    "trace-max-elements": "tensor traces are not built",
     "bf16-algorithm-index": "the library chooses its own algorithm",
     "text": "tokenizers are not part of this engine: give --tokens",
     "vocab": "tokenizers are not part of this engine: give --tokens",
@@ -70,6 +72,42 @@ NOT_HERE = {
 
 class UsageError(ValueError):
     pass
+
+
+class TensorTrace:
+    """Collects (name, tensor) from a step and writes them as JSON lines in the reference's record layout
+    (src/profiling/trace.cpp:126-195: sequence, kind, name, shape, dtype, statistics over the finite values,
+    the first `max_elements` values)."""
+
+    def __init__(self, path: str, max_elements: int, run_id: str):
+        self.path, self.max_elements, self.run_id = path, int(max_elements), run_id
+        self.records = []
+
+    def __call__(self, name, tensor) -> None:
+        import torch
+        values = tensor.detach().to(torch.float64).reshape(-1).cpu()
+        finite = values[torch.isfinite(values)]
+        stats = {"numel": int(values.numel()), "finite_count": int(finite.numel()), "minimum": 0.0, "maximum": 0.0,
+                 "mean": 0.0, "l2_norm": 0.0}
+        if finite.numel():
+            stats.update(minimum=float(finite.min()), maximum=float(finite.max()), mean=float(finite.mean()),
+                         l2_norm=float(finite.square().sum().sqrt()))
+        head = values[:self.max_elements].tolist()
+        shown = [("nan" if v != v else "inf" if v == float("inf") else "-inf" if v == float("-inf") else v) for v in head]
+        self.records.append({"schema_version": 1, "framework": "microllm_rocm_b200", "run_id": self.run_id,
+                             "phase": "inference-values", "sequence": len(self.records), "iteration": 0,
+                             "kind": "model" if name in ("embedding", "final_norm", "logits") else "layer", "name": name,
+                             "shape": list(tensor.shape), "dtype": str(tensor.dtype).replace("torch.", ""),
+                             "device": str(tensor.device), "wall_ms": 0.0, "statistics": stats,
+                             "values_truncated": values.numel() > len(head), "values": shown})
+
+    def write(self) -> int:
+        folder = os.path.dirname(os.path.abspath(self.path))
+        os.makedirs(folder, exist_ok=True)
+        with open(self.path, "w", encoding="utf-8") as f:
+            for r in self.records:
+                f.write(json.dumps(r) + "\n")
+        return len(self.records)
 
 
 def parse(argv: List[str]) -> Dict[str, object]:
@@ -114,6 +152,10 @@ def validate(o: Dict[str, object]) -> None:
         raise UsageError("--prefill-logits must be last or full")
     if o["stop-on-eos"] not in BOOL:
         raise UsageError("--stop-on-eos must be true or false")
+    if o["trace-max-elements"] <= 0:
+        raise UsageError("--trace-max-elements must be positive")
+    if o["trace-output"] and (o["workload"] != "prefill" or o["prefill-warmup"] != 0 or o["prefill-steps"] != 1):
+        raise UsageError("--trace-output requires prefill workload, zero prefill warmup, and one prefill step")
     for key, (legal, ours, why) in ONE_WAY.items():
         if o[key] not in legal:
             raise UsageError(f"--{key} must be {' or '.join(legal)}")
@@ -256,6 +298,7 @@ def run(o) -> int:
         return r, (time.perf_counter() - a) * 1e3
 
     full_logits = o["prefill-logits"] == "full"
+    tracer = TensorTrace(o["trace-output"], o["trace-max-elements"], dtype) if o["trace-output"] else None
 
     def prefill_once():
         cache = engine.cache
@@ -274,7 +317,7 @@ def run(o) -> int:
                     logits = torch.cat(pieces)                # the first request's rows, one per position
             else:
                 want = list(range(len(ids))) if full_logits else [len(ids) - 1]
-                logits = engine.step([StepEntry(r, ids, want) for r in rows])
+                logits = engine.step([StepEntry(r, ids, want) for r in rows], tensor_sink=tracer)
             engine.check_device_errors()
             return logits
         finally:
@@ -298,6 +341,8 @@ def run(o) -> int:
                     "forward_ms": total / o["prefill-steps"],
                     "prefill_tokens_per_second": batch * len(ids) * o["prefill-steps"] / (total / 1e3),
                     "top_logits": [{"token": int(i), "logit": float(v)} for v, i in zip(top.values, top.indices)]})
+        if tracer is not None:
+            out["trace_record_count"] = tracer.write()
 
     if o["workload"] in ("decode", "both") and new_tokens > 0:
         llm = LLM(engine, max_tokens_per_step=o["max-tokens-per-step"], max_seqs=max(batch, o["max-seqs"]))

@@ -30,7 +30,8 @@ class LLM:
             self.engine = model
         else:
             self.engine = load_engine(model, dtype=dtype, page_size=page_size, num_pages=num_pages,
-                                      max_tokens=max_tokens, max_requests=max_seqs, device=device)
+                                      max_tokens=max_tokens, max_requests=max_seqs, device=device,
+                                      max_step_tokens=max_tokens_per_step)
         spec = self.engine.model.spec
         self.scheduler = Scheduler(self.engine.cache, spec.vocab_size, spec.max_position,
                                    max_tokens_per_step=max_tokens_per_step,

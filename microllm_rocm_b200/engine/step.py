@@ -55,6 +55,7 @@ class Engine:
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self.tokens_run = 0
+        self.max_step_tokens: Optional[int] = None      # set when the cache's window groups were sized on this promise
         self._pinned: List[Optional[torch.Tensor]] = [None] * 4     # ring of staging buffers
         self._pinned_events: List[Optional[torch.cuda.Event]] = [None] * 4
         self._pinned_next = 0
@@ -97,6 +98,9 @@ class Engine:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.request!r} brings no tokens")
+            if self.max_step_tokens and n > self.max_step_tokens:
+                raise StepError(f"request {e.request!r} brings {n} tokens in one step; the cache was sized for at most "
+                                f"{self.max_step_tokens}")
             p = cache.length(e.request)
             if p + n > spec.max_position:
                 raise StepError(f"request {e.request!r} would hold {p + n} tokens, beyond max_position "
@@ -168,11 +172,14 @@ class Engine:
             max_new_tokens=max(counts), max_seq_len=max(p + n for p, n in zip(pos0, counts)))
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], tensor_sink=None) -> torch.Tensor:
         """Run the given tokens; returns fp32 logits [wanted, vocab] on the device, in the order
-        of the entries and of each entry's `want`.  Lengths advance only if the step ran."""
+        of the entries and of each entry's `want`.  Lengths advance only if the step ran.
+        `tensor_sink(name, tensor)`: receives the step's intermediate tensors (a tensor trace; see
+        StepContext.tensor_sink)."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         ctx = self.build_context(entries)
+        ctx.tensor_sink = tensor_sink
         views = self.cache_views(ctx)
         logits = self.model.forward(ctx, views)
         for e, p in zip(entries, ctx.seq_pos0_host):

@@ -116,6 +116,10 @@ class StepContext:
     # results computed from the step's device state (a table of this step's angles, say): valid for ONE forward;
     # the model empties it before every forward, also when the context itself lives on (a captured decode step)
     step_values: Dict[Any, Any] = field(default_factory=dict)
+    # When set, the model hands it (name, tensor) after the embedding, after every run of the execution list
+    # (residual stream and the delta not yet added to it), after the final norm and for the logits: a per-step
+    # tensor trace.  Such a step runs every layer call by call.
+    tensor_sink: Optional[Callable[[str, torch.Tensor], None]] = None
 
     @property
     def decode_only(self) -> bool:

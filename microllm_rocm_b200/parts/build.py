@@ -179,7 +179,10 @@ class Model:
         residual = self.embedding.forward(ctx.token_ids)
         self.position.on_embedding(residual, ctx)
         delta = None
-        keys = self._layer_replay_keys() if self.replay_layers else None
+        sink = ctx.tensor_sink
+        if sink is not None:
+            sink("embedding", residual)
+        keys = self._layer_replay_keys() if self.replay_layers and sink is None else None
         recordings = {}                      # structure of a run -> (recording, the recorded run's own pointers) | None
         for i, run in enumerate(self.spec.order):
             name, owns = self.run_cache[i]
@@ -193,6 +196,9 @@ class Model:
             if key is None:
                 # the first run of a step plans launches and makes the step's tables: it always runs call by call
                 residual, delta = block.forward(residual, delta, ctx, view)
+                if sink is not None:
+                    sink(f"run{i}.layer{run.layer}.residual", residual)
+                    sink(f"run{i}.layer{run.layer}.delta", delta)
                 continue
             pointers = self._run_pointers(block, view)
             if key not in recordings:
@@ -223,7 +229,11 @@ class Model:
             ops.add_inplace(residual, delta)
         rows = torch.empty((R, self.spec.hidden_size), dtype=self.rt.dtype, device=residual.device)
         self.final_norm.forward(residual, rows, rows=ctx.logit_rows)
-        return self.head.forward(rows, ctx.error_flag)
+        logits = self.head.forward(rows, ctx.error_flag)
+        if sink is not None:
+            sink("final_norm", rows)
+            sink("logits", logits)
+        return logits
 
 
 def _view_tensors(view) -> List[Optional[torch.Tensor]]:

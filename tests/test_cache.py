@@ -129,3 +129,35 @@ def test_random_orders_never_lose_or_duplicate_a_page(seed):
         c.release(q)
     c.check()
     assert all(g.pool.used_count == 0 for g in c.groups.values()) and c.slots.used_count == 0
+
+
+def test_a_window_group_needs_pages_for_its_window_only():
+    """With a promise on how many tokens a request brings per step, the pool of a windowed group is sized for
+    the spans that can be live (window - 1 + step tokens per request), not for whole sequences; a request that
+    runs far beyond the window never fails to get its pages, and the books stay right."""
+    from microllm_rocm_b200.cache.manager import CacheManager
+    from microllm_rocm_b200.parts.base import PagedKVNeed
+    entries = {"full": PagedKVNeed(2, 32, None), "win": PagedKVNeed(2, 32, 40)}
+    cache = CacheManager(entries, page_size=16, num_pages=200, max_requests=3, max_step_tokens=24)
+    assert cache.groups["full"].pool.num_pages == 200
+    assert cache.groups["window40"].pool.num_pages == 3 * (-(-(39 + 24) // 16) + 1) == 15
+    rng = random.Random(5)
+    lengths = {}
+    for rid in ("a", "b", "c"):
+        assert cache.add(rid)
+        lengths[rid] = 0
+    for _ in range(300):
+        rid = rng.choice(list(lengths))
+        n = rng.randint(1, 24)
+        if lengths[rid] + n > 1000:
+            continue
+        assert cache.reserve(rid, lengths[rid] + n), (rid, lengths[rid], n)
+        lengths[rid] += n
+        cache.commit(rid, lengths[rid])
+        cache.check()
+    assert max(lengths.values()) > 500
+    assert cache.groups["window40"].pool.peak_used <= 15
+    for rid in lengths:
+        cache.release(rid)
+    cache.check()
+    assert cache.groups["window40"].pool.used_count == 0 and cache.groups["full"].pool.used_count == 0

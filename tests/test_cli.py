@@ -39,6 +39,9 @@ def test_pairs_names_and_types():
     (["--model", "folder", "--workload", "continuous"], "continuous workload requires"),
     (["--model", "folder"], "--tokens is required"),
     (BASE + ["--stop-on-eos", "maybe"], "--stop-on-eos must be true or false"),
+    (BASE + ["--trace-output", "t.jsonl"], "--trace-output requires prefill workload"),
+    (BASE + ["--trace-output", "t.jsonl", "--workload", "prefill", "--prefill-steps", "2"], "--trace-output requires prefill workload"),
+    (BASE + ["--trace-max-elements", "0"], "--trace-max-elements must be positive"),
 ])
 def test_rules_of_the_reference(argv, message):
     with pytest.raises(cli.UsageError, match=message):
@@ -57,6 +60,6 @@ def test_switches_between_paths_this_engine_does_not_have():
             check(BASE + [flag, value])
     with pytest.raises(cli.UsageError, match="--decode-mode must be generation or steady"):
         check(BASE + ["--decode-mode", "fast"])
-    for flag in ("--text", "--vocab", "--merges", "--continuous-cache-buckets", "--trace-output", "--kv-cache-fp32-layers"):
+    for flag in ("--text", "--vocab", "--merges", "--continuous-cache-buckets", "--kv-cache-fp32-layers"):
         with pytest.raises(cli.UsageError, match="does not have"):
             cli.parse(["--model", "folder", flag, "x"])

@@ -152,6 +152,32 @@ def test_command_line(folders, tmp_path):
     assert info["admissions"] == 3
 
 
+def test_command_line_writes_a_tensor_trace_of_the_prompt_step(folders, tmp_path):
+    """--trace-output: one record per intermediate tensor of the prompt's step, in the reference's layout; the
+    residual stream after the last layer plus its pending delta, normed, is what the logits come from, so the
+    records can be checked against the plain implementation's own intermediate values."""
+    key = "a"
+    prompt = random_tokens(9, tiny_config(key).vocab_size, 2)
+    trace = tmp_path / "trace.jsonl"
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "microllm_hf_infer"), "--model", folders[key], "--tokens",
+           ",".join(map(str, prompt)), "--workload", "prefill", "--trace-output", str(trace), "--trace-max-elements", "7"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    info = json.loads(proc.stdout.strip().splitlines()[-1])
+    records = [json.loads(line) for line in open(trace)]
+    layers = tiny_config(key).num_hidden_layers
+    assert info["trace_record_count"] == len(records) == 1 + 2 * layers + 2
+    assert [r["name"] for r in records][:2] == ["embedding", "run0.layer0.residual"] and records[-1]["name"] == "logits"
+    assert all(r["schema_version"] == 1 and len(r["values"]) <= 7 and r["statistics"]["finite_count"] == r["statistics"]["numel"] for r in records)
+    weights = plain.read_safetensors(os.path.join(folders[key], "model.safetensors"))
+    emb = plain.embedding(weights["model.embed_tokens.weight"], prompt)
+    assert records[0]["shape"] == list(emb.shape)
+    assert torch.allclose(torch.tensor(records[0]["values"], dtype=torch.float64), emb.reshape(-1)[:7].double(), atol=1e-6)
+    assert abs(records[0]["statistics"]["l2_norm"] - float(emb.double().norm())) < 1e-4
+    logits = plain_logits(folders[key], prompt)[-1]
+    assert torch.allclose(torch.tensor(records[-1]["values"], dtype=torch.float64), logits[:7].double(), atol=2e-5)
+
+
 def test_command_line_stops_on_the_configuration_eos(folders, tmp_path):
     """--stop-on-eos true makes config.json's eos_token_id a stop token: the generation ends with it."""
     import shutil
