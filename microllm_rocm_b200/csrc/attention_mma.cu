@@ -27,6 +27,9 @@
 #include "common.cuh"
 
 #include <cooperative_groups.h>
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
 
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=<multiple of 32, at most 256>"
@@ -903,6 +906,93 @@ __device__ __forceinline__ void consume_keys_t(const FaParams& p, const __nv_bfl
     }
 }
 
+// What follows the key loop of the keys-on-M decode kernels: the warps of a CTA merge their shares in shared
+// memory, then the CTAs of the cluster merge theirs through distributed shared memory, CTA `rank` finishing the
+// slice [rank, rank + 1) * D / splits of every head.  Every thread of the CTA calls it (it holds CTA- and
+// cluster-wide barriers); `active` is false for threads of a warp that walked no keys (a copy-issuing warp).
+template <int DW>
+__device__ __forceinline__ void merge_and_store_t(const FaParams& p, const TileGeometry& geo, RowStateT& st, float* frag,
+                                                  float* warp_m, float* warp_l, float* cta_o, float* cta_m, float* cta_l,
+                                                  int heads, int splits, int rank, bool active) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    if (active) {
+        // a head's sum over this warp's keys: the lanes of equal t hold its shares
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 4);
+            st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 8);
+            st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 16);
+        }
+        // every warp publishes its fragments, then each thread merges a share of them
+#pragma unroll
+        for (int k = 0; k < NPAIR * 8; ++k)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) frag[(warp * FRAGS_T + k * 4 + e) * 32 + lane] = st.o[k][e];
+        if (g == 0) {
+            warp_m[warp * 8 + 2 * t] = st.m[0]; warp_m[warp * 8 + 2 * t + 1] = st.m[1];
+            warp_l[warp * 8 + 2 * t] = st.l[0]; warp_l[warp * 8 + 2 * t + 1] = st.l[1];
+        }
+    }
+    __syncthreads();
+    if (active) {
+        float scale_w[2][DW];                    // of heads 2t and 2t+1
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int h = 2 * t + i;
+            float m_all = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < DW; ++w) m_all = fmaxf(m_all, warp_m[w * 8 + h]);
+            float l_all = 0.0f;
+#pragma unroll
+            for (int w = 0; w < DW; ++w) {
+                const float mw = warp_m[w * 8 + h];
+                scale_w[i][w] = (mw == -INFINITY) ? 0.0f : exp2f(mw - m_all);
+                l_all += warp_l[w * 8 + h] * scale_w[i][w];
+            }
+            if (warp == 0 && g == 0) { cta_m[h] = m_all; cta_l[h] = l_all; }
+        }
+#pragma unroll
+        for (int k = 0; k < FRAGS_T / DW; ++k) {
+            const int idx = warp + k * DW;              // this thread merges fragment idx of all warps
+            const int kk = idx >> 2, e = idx & 3, i = e & 1, h = 2 * t + i;
+            const int dim = (2 * (kk >> 3) + (e >> 1)) * 64 + 8 * g + (kk & 7);
+            if (dim >= D || h >= heads) continue;
+            float val = 0.0f;
+#pragma unroll
+            for (int w = 0; w < DW; ++w) val += frag[(w * FRAGS_T + idx) * 32 + lane] * scale_w[i][w];
+            cta_o[h * D + dim] = val;
+        }
+    }
+    // across the cluster: CTA `rank` finishes the slice [rank, rank + 1) * D / splits of every head
+    cluster.sync();
+    const int slice = D / splits;
+    for (int i = active ? (int)threadIdx.x : heads * slice; i < heads * slice; i += DW * 32) {
+        const int r = i / slice, dim = rank * slice + i % slice;
+        float m_all = -INFINITY;
+        float ms[MAX_SPLITS];
+#pragma unroll
+        for (int s2 = 0; s2 < MAX_SPLITS; ++s2) {
+            ms[s2] = -INFINITY;
+            if (s2 < splits) ms[s2] = *cluster.map_shared_rank(cta_m + r, s2);
+            m_all = fmaxf(m_all, ms[s2]);
+        }
+        float acc = 0.0f, l_all = 0.0f;
+#pragma unroll
+        for (int s2 = 0; s2 < MAX_SPLITS; ++s2) {
+            if (s2 < splits && ms[s2] != -INFINITY) {
+                const float w = exp2f(ms[s2] - m_all);
+                acc += w * *cluster.map_shared_rank(cta_o + r * D + dim, s2);
+                l_all += w * *cluster.map_shared_rank(cta_l + r, s2);
+            }
+        }
+        const int head = geo.kvh * p.group + r;
+        p.out[((size_t)geo.token0 * p.num_heads + head) * D + dim] = __float2bfloat16_rn(l_all > 0.0f ? acc / l_all : 0.0f);
+    }
+    cluster.sync();                          // nobody leaves while its shared memory may still be read
+}
+
 // shared memory (dynamic): queries | per-warp fragments [DW][FRAGS_T][32] | warp max/sum per head |
 // this CTA's merged heads [8][D] with their max and sum | block table
 constexpr size_t decode_t_smem(int dw) {
@@ -1003,79 +1093,267 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_t_kernel(F
             }
         }
     }
-    // a head's sum over this warp's keys: the lanes of equal t hold its shares
+    merge_and_store_t<DW>(p, geo, st, frag, warp_m, warp_l, cta_o, cta_m, cta_l, heads, splits, rank, true);
+}
+
+
+// ---------------------------------------------------------------------------------- decode, keys through a ring
+// The keys-on-M decode kernel again, for steps that read much more than a few megabytes of keys (many
+// sequences, long contexts).  There the kernel above is bound by what its warps can keep in flight: two key
+// tiles of registers per warp, the second one's loads only issued while the first is being used.  Here a fifth
+// warp issues the copies: TMA (cp.async.bulk.tensor, 128-byte swizzle) brings the K and V of 64 keys per stage
+// into a ring of RING_STAGES stages of shared memory, as far ahead of the four working warps as the ring is
+// deep and without a register of theirs.  A working warp takes its 16 keys of a stage out of the ring with
+// 16-byte loads in exactly the fragment layout the kernel above loads from global memory (the swizzle makes
+// them conflict-free), hands the stage back at once, and runs the same consume_keys_t.  The merge over warps and
+// over the cluster is the same function.  Heads of 128 elements.
+constexpr int RING_STAGES = 3;
+constexpr int RING_TILE_BYTES = 16 * D * 2;                 // the K (or V) of one 16-key tile
+constexpr int RING_STAGE_BYTES = 4 * 2 * RING_TILE_BYTES;   // four tiles, K and V: 32 KB at D = 128
+constexpr int RING_SPIN_LIMIT = 1 << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
+    return ok != 0;
+}
+// false when the bound was hit: the caller stops waiting, the flag tells the host
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code) {
+    for (int i = 0; i < RING_SPIN_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    if (error_flag) atomicExch(error_flag, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+
+// 16 bytes of a [16 rows x 64 elements] box as TMA's 128-byte swizzle laid it out: 16-byte chunk `chunk` of row
+// `row` sits at chunk ^ (row % 8)
+__device__ __forceinline__ uint4 ring_load16(const unsigned char* box, int row, int chunk) {
+    return *reinterpret_cast<const uint4*>(box + row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+// this warp's 16 keys of a stage, from the ring into the registers consume_keys_t wants (see load_keys)
+__device__ __forceinline__ void ring_take_keys(const unsigned char* tile, int base, int last_pos, KeyTile& kv) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    kv.base = base;
+    const unsigned char* kbox = tile;                             // [span (D / 64)][16 rows][128 bytes]
+    const unsigned char* vbox = tile + RING_TILE_BYTES;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 4);
-        st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 8);
-        st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 16);
+    for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+        for (int c = 0; c < KCHUNKS; ++c) kv.k[nb][c] = ring_load16(kbox + (c >> 1) * (16 * 128), nb * 8 + g, (c & 1) * 4 + t);
+#pragma unroll
+    for (int vb = 0; vb < VBLOCKS; ++vb)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int key = 2 * t + (r & 1) + 8 * (r >> 1);       // this thread's keys: 2t, 2t+1, 2t+8, 2t+9
+            // slots behind the sequence's last key were never written: zero, so that zero probability times them stays zero
+            kv.v[vb][r] = base + key <= last_pos ? ring_load16(vbox + vb * (16 * 128), key, g) : make_uint4(0, 0, 0, 0);
+        }
+}
+
+constexpr size_t decode_ring_smem() {
+    // ring (1024-byte aligned; the per-warp fragments of the merge reuse it) | queries | warp max/sum | merged heads | table
+    return 1024 + (size_t)RING_STAGES * RING_STAGE_BYTES + 16 * Q_STRIDE * sizeof(__nv_bfloat16) + 2 * 4 * 8 * sizeof(float) +
+           (size_t)8 * D * sizeof(float) + 16 * sizeof(float) + TABLE_SPAN * sizeof(int);
+}
+
+__global__ void __launch_bounds__(160, 2) fa_decode_ring_kernel(const __grid_constant__ CUtensorMap map_kv, FaParams p) {
+    pdl_launch_dependents();
+    constexpr int DW = 4;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long full_bar[RING_STAGES], empty_bar[RING_STAGES];
+    unsigned char* ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    float* frag = reinterpret_cast<float*>(ring);                  // [DW][FRAGS_T][32], once the ring is drained
+    static_assert((size_t)DW * FRAGS_T * 32 * sizeof(float) <= (size_t)RING_STAGES * RING_STAGE_BYTES, "the merge's fragments must fit the ring");
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(ring + RING_STAGES * RING_STAGE_BYTES);
+    float* warp_m = reinterpret_cast<float*>(q_s + 16 * Q_STRIDE);     // [DW][8]
+    float* warp_l = warp_m + DW * 8;
+    float* cta_o = warp_l + DW * 8;                // [8][D]
+    float* cta_m = cta_o + 8 * D;
+    float* cta_l = cta_m + 8;
+    int* table_s = reinterpret_cast<int*>(cta_l + 8);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    TileGeometry geo;
+    geo.seq = p.listed ? __ldg(p.work + blockIdx.x) : (int)blockIdx.x;
+    geo.kvh = blockIdx.y;
+    geo.token0 = p.listed ? __ldg(p.seq_starts + geo.seq) : geo.seq;
+    geo.n_new = 1;
+    geo.row0 = 0;
+    const int heads = p.group;                     // <= 8
+    const int pos0_load = __ldg(p.seq_pos0 + geo.seq);
+    PageTable pt;
+    fill_page_table(pt, table_s, p.block_table + (size_t)geo.seq * p.max_blocks, p.max_blocks, 0, p.max_blocks - 1,
+                    threadIdx.x, 160);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < RING_STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), DW);           // one arrival per working warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    // every warp publishes its fragments, then each thread merges a share of them
+    geo.pos0 = pos0_load;
+    const int last_pos = geo.pos0;
+    const int lo = (p.window > 0 && last_pos - p.window + 1 > 0) ? last_pos - p.window + 1 : 0;
+    int tile_begin = lo / 16, tile_end = last_pos / 16 + 1;
+    const int splits = (int)gridDim.z, rank = (int)blockIdx.z;
+    if (splits > 1) {                        // this CTA's even share of the sequence's key tiles
+        const int per_split = (tile_end - tile_begin + splits - 1) / splits;
+        tile_begin += rank * per_split;
+        tile_end = min(tile_end, tile_begin + per_split);
+    }
+    const int num_stages = tile_end > tile_begin ? (tile_end - tile_begin + 3) / 4 : 0;      // 64 keys each
+    __syncthreads();                         // the block table and the barriers are in shared memory
+
+    RowStateT st;
+    st.m[0] = st.m[1] = -INFINITY;
+    st.l[0] = st.l[1] = 0.0f;
 #pragma unroll
     for (int k = 0; k < NPAIR * 8; ++k)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) frag[(warp * FRAGS_T + k * 4 + e) * 32 + lane] = st.o[k][e];
-    if (g == 0) {
-        warp_m[warp * 8 + 2 * t] = st.m[0]; warp_m[warp * 8 + 2 * t + 1] = st.m[1];
-        warp_l[warp * 8 + 2 * t] = st.l[0]; warp_l[warp * 8 + 2 * t + 1] = st.l[1];
-    }
-    __syncthreads();
-    float scale_w[2][DW];                    // of heads 2t and 2t+1
+        for (int e = 0; e < 4; ++e) st.o[k][e] = 0.0f;
+
+    if (warp == DW) {
+        // ---------------------------------------------------------------- the copying warp
+        if (lane == 0) {
+            bool waited = false, ok = true;
+            int issued = 0;
+            for (int i = 0; i < num_stages && ok; ++i) {
+                const int s = i % RING_STAGES;
+                if (i >= RING_STAGES && !mbar_wait(smem_u32(&empty_bar[s]), ((i / RING_STAGES) - 1) & 1, p.error_flag, 61)) { ok = false; break; }
+                const int kt0 = tile_begin + 4 * i, n_tiles = min(4, tile_end - kt0);
+                // the tile that holds the new token's key was written by the kernel in front: everything before it
+                // travels while that kernel still runs
+                if (!waited && kt0 + n_tiles > last_pos / 16) { pdl_wait(); waited = true; }
+                uint32_t bytes = 0;
+                int page_of_tile[4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int h = 2 * t + i;
-        float m_all = -INFINITY;
+                for (int j = 0; j < 4; ++j) {
+                    page_of_tile[j] = -1;
+                    if (j < n_tiles) {
+                        const int base = (kt0 + j) * 16;
+                        const int page = pt.page_of(p.page_shift >= 0 ? base >> p.page_shift : base / p.page_size);
+                        if (page >= 0 && page < p.num_pages) { page_of_tile[j] = page; bytes += 2 * RING_TILE_BYTES; }
+                    }
+                }
+                const uint32_t bar = smem_u32(&full_bar[s]);
+                if (bytes == 0) { mbar_arrive(bar); issued = i + 1; continue; }        // nothing to copy: the stage is "full" at once
+                mbar_expect_tx(bar, bytes);
 #pragma unroll
-        for (int w = 0; w < DW; ++w) m_all = fmaxf(m_all, warp_m[w * 8 + h]);
-        float l_all = 0.0f;
+                for (int j = 0; j < 4; ++j) {
+                    if (page_of_tile[j] < 0) continue;
+                    const int base = (kt0 + j) * 16;
+                    const int slot = p.page_shift >= 0 ? base & (p.page_size - 1) : base % p.page_size;
+                    const int row_k = ((page_of_tile[j] * 2) * p.num_kv_heads + geo.kvh) * p.page_size + slot;
+                    const int row_v = row_k + p.num_kv_heads * p.page_size;
+                    const uint32_t dst = smem_u32(ring) + s * RING_STAGE_BYTES + j * 2 * RING_TILE_BYTES;
 #pragma unroll
-        for (int w = 0; w < DW; ++w) {
-            const float mw = warp_m[w * 8 + h];
-            scale_w[i][w] = (mw == -INFINITY) ? 0.0f : exp2f(mw - m_all);
-            l_all += warp_l[w * 8 + h] * scale_w[i][w];
-        }
-        if (warp == 0 && g == 0) { cta_m[h] = m_all; cta_l[h] = l_all; }
-    }
-#pragma unroll
-    for (int k = 0; k < FRAGS_T / DW; ++k) {
-        const int idx = warp + k * DW;              // this thread merges fragment idx of all warps
-        const int kk = idx >> 2, e = idx & 3, i = e & 1, h = 2 * t + i;
-        const int dim = (2 * (kk >> 3) + (e >> 1)) * 64 + 8 * g + (kk & 7);
-        if (dim >= D || h >= heads) continue;
-        float val = 0.0f;
-#pragma unroll
-        for (int w = 0; w < DW; ++w) val += frag[(w * FRAGS_T + idx) * 32 + lane] * scale_w[i][w];
-        cta_o[h * D + dim] = val;
-    }
-    // across the cluster: CTA `rank` finishes the slice [rank, rank + 1) * D / splits of every head
-    cluster.sync();
-    const int slice = D / splits;
-    for (int i = threadIdx.x; i < heads * slice; i += DW * 32) {
-        const int r = i / slice, dim = rank * slice + i % slice;
-        float m_all = -INFINITY;
-        float ms[MAX_SPLITS];
-#pragma unroll
-        for (int s2 = 0; s2 < MAX_SPLITS; ++s2) {
-            ms[s2] = -INFINITY;
-            if (s2 < splits) ms[s2] = *cluster.map_shared_rank(cta_m + r, s2);
-            m_all = fmaxf(m_all, ms[s2]);
-        }
-        float acc = 0.0f, l_all = 0.0f;
-#pragma unroll
-        for (int s2 = 0; s2 < MAX_SPLITS; ++s2) {
-            if (s2 < splits && ms[s2] != -INFINITY) {
-                const float w = exp2f(ms[s2] - m_all);
-                acc += w * *cluster.map_shared_rank(cta_o + r * D + dim, s2);
-                l_all += w * *cluster.map_shared_rank(cta_l + r, s2);
+                    for (int span = 0; span < D / 64; ++span) {
+                        tma_load_2d(dst + span * (16 * 128), &map_kv, span * 64, row_k, bar);
+                        tma_load_2d(dst + RING_TILE_BYTES + span * (16 * 128), &map_kv, span * 64, row_v, bar);
+                    }
+                }
+                issued = i + 1;
+            }
+            if (!ok) {
+                // given up: let the copies already issued land before the shared memory is handed back
+                for (int i = max(0, issued - RING_STAGES); i < issued; ++i)
+                    mbar_wait(smem_u32(&full_bar[i % RING_STAGES]), (i / RING_STAGES) & 1, nullptr, 0);
             }
         }
-        const int head = geo.kvh * p.group + r;
-        p.out[((size_t)geo.token0 * p.num_heads + head) * D + dim] = __float2bfloat16_rn(l_all > 0.0f ? acc / l_all : 0.0f);
+    } else {
+        // ---------------------------------------------------------------- the working warps
+        pdl_wait();
+        {
+            constexpr int VEC_PER_ROW = D / 8;
+            for (int i = threadIdx.x; i < 8 * VEC_PER_ROW; i += DW * 32) {
+                const int r = i / VEC_PER_ROW, c = (i % VEC_PER_ROW) * 8;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (r < heads) v = load16(p.q + ((size_t)geo.token0 * p.num_heads + geo.kvh * p.group + r) * D + c);
+                *reinterpret_cast<uint4*>(q_s + r * Q_STRIDE + c) = v;
+            }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");          // the queries are in shared memory (the four working warps only)
+        bool ok = true;
+        for (int i = 0; i < num_stages && ok; ++i) {
+            const int s = i % RING_STAGES;
+            const int kt = tile_begin + 4 * i + warp;
+            ok = mbar_wait(smem_u32(&full_bar[s]), (i / RING_STAGES) & 1, p.error_flag, 62);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            KeyTile tile;
+            tile.base = -1;
+            if (kt < tile_end) {
+                const int base = kt * 16;
+                const int page = pt.page_of(p.page_shift >= 0 ? base >> p.page_shift : base / p.page_size);
+                if (page >= 0 && page < p.num_pages) ring_take_keys(ring + s * RING_STAGE_BYTES + warp * 2 * RING_TILE_BYTES, base, last_pos, tile);
+                else if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 3);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));      // the stage may be refilled while this tile is used
+            consume_keys_t(p, q_s, tile, last_pos, lo, st);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");          // every warp has taken its last tile: the ring may become the merge's scratch
     }
-    cluster.sync();                          // nobody leaves while its shared memory may still be read
+    merge_and_store_t<DW>(p, geo, st, frag, warp_m, warp_l, cta_o, cta_m, cta_l, heads, splits, rank, warp < DW);
 }
 
 }  // namespace
+
+
+// ---- the tensor map of the paged cache for the ring kernel: rows = (page, K|V, kv head, slot), D columns; a box is
+// one 16-key tile by 64 elements, 128-byte swizzled.  Encoded once per cache (its address and size) and kept.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int cache_tensor_map(CUtensorMap* map, const void* pages, long long rows) {
+    static std::mutex mutex;
+    static std::unordered_map<unsigned long long, CUtensorMap> known;
+    const unsigned long long key = (unsigned long long)(uintptr_t)pages * 1000003ull ^ (unsigned long long)rows;
+    {
+        std::lock_guard<std::mutex> lock(mutex);
+        auto found = known.find(key);
+        if (found != known.end()) { *map = found->second; return MLB_OK; }
+    }
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+    }
+    if (!fn) return fail(MLB_CUDA_ERROR, "paged_attention_mma: cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64u, 16u};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MLB_CUDA_ERROR, "paged_attention_mma: cuTensorMapEncodeTiled failed with %d", (int)r);
+    std::lock_guard<std::mutex> lock(mutex);
+    if (known.size() > 4096) known.clear();
+    known.emplace(key, *map);
+    return MLB_OK;
+}
 
 // up to this many CTAs the decode shape runs eight warps per CTA (measured: one sequence of two kv heads gains,
 // eight sequences lose)
@@ -1089,6 +1367,9 @@ MLB_EXPORT int mlb_fa_max_splits() { return MAX_SPLITS; }
 // the keys are cut `splits` ways (1, 2, 4, 8 or 16; D / splits must be whole) over a thread-block cluster.
 // mode 2: the decode shape for SOME sequences of a step that also holds prompt portions: `work` lists the
 // sequences that bring exactly one token (num_work = listed sequences * ceil(group / 16)).
+// Heads of 128 with groups of at most 8 heads and clusters of at most 8: adding 4 to the mode asks for the kernel that
+// brings the keys through a shared-memory ring (the caller knows the context lengths and decides when it pays),
+// adding 8 forbids it; with neither, a grid of at least one CTA per multiprocessor takes it.
 MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* out, const int* seq_starts,
                                        const int* seq_pos0, const int* block_table, const int* work, int num_work,
                                        int max_blocks, int num_pages, int page_size, int num_heads, int num_kv_heads,
@@ -1100,6 +1381,8 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
         return fail(MLB_UNSUPPORTED_SIZE, "paged_attention_mma: page_size %d must be a multiple of 16", page_size);
     if (num_pages <= 0 || max_blocks <= 0 || window < 0 || num_work < 0)
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: bad cache geometry");
+    const bool force_ring = (mode & 4) != 0, forbid_ring = (mode & 8) != 0;
+    mode &= 3;
     if (mode < 0 || mode > 2) return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: unknown mode %d", mode);
     if (mode == 2 && !work) return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: mode 2 needs the list of sequences");
     if (mode >= 1 && !(splits == 1 || splits == 2 || splits == 4 || splits == 8 || splits == 16))
@@ -1174,6 +1457,27 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
             cudaGetLastError();
         }
         if (clusters16 < 1) return fail(MLB_UNSUPPORTED_SIZE, "fa_decode: clusters of %d CTAs cannot be resident on this device", splits);
+    }
+    const long long grid_ctas = (long long)num_work * num_kv_heads * splits;
+    if (keys_on_m && D == 128 && !forbid_ring && splits <= 8 && (force_ring || (!wide && grid_ctas >= sm_count()))) {
+        const long long rows = (long long)num_pages * 2 * num_kv_heads * page_size;
+        if (rows >= (1ll << 31)) return fail(MLB_UNSUPPORTED_SIZE, "paged_attention_mma: the cache has too many rows (%lld)", rows);
+        if (((uintptr_t)pages & 15) != 0) return fail(MLB_UNSUPPORTED_SIZE, "paged_attention_mma: the cache must be 16-byte aligned");
+        CUtensorMap map_kv;
+        int status = cache_tensor_map(&map_kv, pages, rows);
+        if (status != MLB_OK) return status;
+        static bool ring_configured_on[MAX_DEVICES] = {false};
+        bool& ring_configured = ring_configured_on[device_index()];
+        if (!ring_configured) {
+            cudaError_t e = cudaFuncSetAttribute(fa_decode_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_ring_smem());
+            if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "fa_decode_ring: cannot reserve %d bytes of shared memory: %s",
+                                              (int)decode_ring_smem(), cudaGetErrorString(e));
+            ring_configured = true;
+        }
+        config.blockDim = dim3(160);
+        config.dynamicSmemBytes = decode_ring_smem();
+        cudaLaunchKernelEx(&config, fa_decode_ring_kernel, map_kv, p);
+        return check_launch("fa_decode_ring");
     }
     if (keys_on_m) {
         if (wide) cudaLaunchKernelEx(&config, fa_decode_t_kernel<8>, p);

@@ -27,6 +27,11 @@ MIN_KEY_TILES_PER_SPLIT = 4         # one 16-key tile per warp at least
 DECODE_SPLITS = (16, 8, 4, 2)       # cluster sizes tried, largest first
 WIDE_CLUSTER_CTAS = 48              # measured: one sequence of two kv heads gains 3 % from clusters of 16, eight sequences lose 10 %
 
+# Which decode kernel takes heads of 128: None = by the step's shape (`decode_ring_pays`); True / False = always /
+# never.  Tests set it to run both kernels on the same inputs.
+DECODE_RING = None
+RING_MIN_KEYS_PER_CTA = 1024        # measured: 16 stages of 64 keys per CTA and the ring wins by 7-8 %, 8 stages and it loses 12 %
+
 TC_HEAD_DIMS = (64, 128)
 TC_KEYS_PER_TILE = 128
 TC_ROWS_PER_TILE = 128
@@ -80,13 +85,21 @@ def decode_splits(items: int, max_seq_len: int, sms: int = DEFAULT_SM_COUNT) -> 
     return 1
 
 
+def decode_ring_pays(items: int, splits: int, max_seq_len: int, sms: int = DEFAULT_SM_COUNT) -> bool:
+    """Whether a decode step should bring its keys through the shared-memory ring (TMA, a copying warp) instead of
+    straight into registers: when every multiprocessor has a CTA and each CTA streams a thousand keys or more.
+    Below that the ring's set-up and its extra hand-offs cost more than the deeper prefetch brings."""
+    return items * splits >= sms and max_seq_len // max(1, splits) >= RING_MIN_KEYS_PER_CTA and splits <= 8
+
+
 def decode_plan_stale(ctx, max_seq_len: int, sms: int = DEFAULT_SM_COUNT) -> bool:
     """Whether a decode step planned for `ctx` (its plans are kept in ctx.extras, and frozen into a captured
     graph) would be cut differently at this context length: a step captured at a short context has one CTA
     per (sequence, kv head) and must not serve a context of thousands that way."""
     for key, plan in ctx.extras.items():
         if isinstance(key, tuple) and key and key[0] == "attention_mma" and plan[2] == 1:
-            if decode_splits(plan[1] * key[2], max_seq_len, sms) != plan[3]:
+            splits = decode_splits(plan[1] * key[2], max_seq_len, sms)
+            if splits != plan[3] or (len(plan) > 9 and decode_ring_pays(plan[1] * key[2], splits, max_seq_len, sms) != plan[9]):
                 return True
     return False
 
@@ -128,13 +141,15 @@ def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
     work_dev = torch.tensor(work, dtype=torch.int32).reshape(-1).to(device, non_blocking=True)
     tc_dev = torch.tensor([(a, t) for _, a, t in tc_work], dtype=torch.int32).reshape(-1).to(device, non_blocking=True)
     splits = decode_splits(len(work) * num_kv_heads, ctx.max_seq_len, sms) if decode else 1
+    ring = decode and decode_ring_pays(len(work) * num_kv_heads, splits, ctx.max_seq_len, sms)
     listed_dev, listed_splits = None, 1
     if listed:
         listed_dev = torch.tensor(listed, dtype=torch.int32).to(device, non_blocking=True)
         longest = max(ctx.seq_pos0_host[a] for a in listed) + 1
         listed_splits = decode_splits(len(listed) * tiles_per_token * num_kv_heads, longest, sms)
+        ring = decode_ring_pays(len(listed) * tiles_per_token * num_kv_heads, listed_splits, longest, sms)
     plan = (work_dev, len(work), 1 if decode else 0, splits, tc_dev, len(tc_work), listed_dev, len(listed) * tiles_per_token,
-            listed_splits)
+            listed_splits, ring)
     ctx.extras[key] = plan
     return plan
 
@@ -149,8 +164,9 @@ def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx
     if pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("paged_attention: the tensor-core kernel wants bf16 queries, pages and output")
     use_tc = tc_supported(head_dim, page_size, scale) and q.is_contiguous() and out.is_contiguous()
-    work, num_work, mode, splits, tc_work, num_tc, listed, num_listed, listed_splits = _plan(
+    work, num_work, mode, splits, tc_work, num_tc, listed, num_listed, listed_splits, ring = _plan(
         ctx, num_heads // num_kv_heads, num_kv_heads, use_tc)
+    ring_bits = 4 if (ring if DECODE_RING is None else DECODE_RING) else 8
     if num_tc:
         T = ops.lib("attention_tc.cu", {"HEAD_DIM": head_dim})
         build.check(T, T.mlb_paged_attention_tc(
@@ -166,10 +182,10 @@ def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx
         build.check(L, L.mlb_paged_attention_mma(
             q.data_ptr(), pages.data_ptr(), out.data_ptr(), ctx.seq_starts.data_ptr(), ctx.seq_pos0.data_ptr(), block_table.data_ptr(),
             listed.data_ptr(), num_listed, block_table.shape[1], pages.shape[0], page_size, num_heads, num_kv_heads,
-            int(window or 0), float(scale), 2, listed_splits, ops._ptr(ctx.error_flag), ops._stream()))
+            int(window or 0), float(scale), 2 + ring_bits, listed_splits, ops._ptr(ctx.error_flag), ops._stream()))
     if not num_work:
         return
     build.check(L, L.mlb_paged_attention_mma(
         q.data_ptr(), pages.data_ptr(), out.data_ptr(), ctx.seq_starts.data_ptr(), ctx.seq_pos0.data_ptr(), block_table.data_ptr(), work.data_ptr(), num_work,
         block_table.shape[1], pages.shape[0], page_size, num_heads, num_kv_heads, int(window or 0), float(scale),
-        mode, splits, ops._ptr(ctx.error_flag), ops._stream()))
+        mode + (ring_bits if mode else 0), splits, ops._ptr(ctx.error_flag), ops._stream()))

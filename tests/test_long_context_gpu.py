@@ -173,11 +173,14 @@ def test_long_prompt_portions_against_the_formula(context, new, window):
     (1, 2073, 12, 2, 64, 16), (8, 2073, 12, 2, 64, 8), (64, 2073, 12, 2, 64, 2),
     (1, 8192, 12, 2, 64, 16), (8, 4096, 12, 2, 64, 8), (64, 4096, 12, 2, 64, 2), (8, 8192, 12, 2, 64, 8),
     (8, 8192, 40, 8, 64, 4), (2, 16500, 12, 2, 16, 8)])
-def test_decode_steps_at_long_contexts_against_the_formula(batch, context, nh, nkv, page, splits):
+@pytest.mark.parametrize("ring", [False, True])
+def test_decode_steps_at_long_contexts_against_the_formula(batch, context, nh, nkv, page, splits, ring):
     """One decode step per case; the sequences of a batch differ in length (the longest has `context` tokens,
     the shortest a few hundred fewer, one of them only 40), so the CTAs of a cluster get uneven shares.  The last
     case has more than 1,024 blocks per sequence (16,500 tokens in 16-token pages): the block table no longer fits
-    the kernel's shared-memory copy and is read from global memory."""
+    the kernel's shared-memory copy and is read from global memory.  Every case runs through both decode kernels:
+    keys straight into registers, and keys through the ring of shared memory that TMA fills."""
+    from microllm_rocm_b200.kernels import attention
     d = 128
     lens = [max(41, context - 37 * i) for i in range(batch)]
     if batch > 1:
@@ -193,7 +196,11 @@ def test_decode_steps_at_long_contexts_against_the_formula(batch, context, nh, n
         fars.append(far)
         case.plant(s, far, direction, PLANT)
     q[:, :nh // 2] = (direction * PLANT).bfloat16()
-    out, _, _, plans = launch(case, [q[s:s + 1] for s in range(batch)], [1] * batch, nh, nkv, d, None)
+    attention.DECODE_RING = ring
+    try:
+        out, _, _, plans = launch(case, [q[s:s + 1] for s in range(batch)], [1] * batch, nh, nkv, d, None)
+    finally:
+        attention.DECODE_RING = None
     assert plans and plans[0][3] == splits, f"planned clusters of {plans[0][3]}, the case is meant for {splits}"
     out = out.reshape(batch, nh, d)
     assert torch.isfinite(out).all()
@@ -205,13 +212,14 @@ def test_decode_steps_at_long_contexts_against_the_formula(batch, context, nh, n
         group = nh // nkv
         for h in (0, nh // 2 - 1):
             assert (out[s, h] - v[fars[s], h // group]).abs().max() < 0.05, (s, h)
-    print(f"decode batch {batch} context {context} heads {nh}/{nkv} clusters of {splits}: worst relative row error {worst:.4f}")
+    print(f"decode batch {batch} context {context} heads {nh}/{nkv} clusters of {splits} ring {ring}: worst relative row error {worst:.4f}")
     assert worst < BF16_ROW_TOL, worst
 
 
 @gpu
+@pytest.mark.parametrize("ring", [False, True])
 @pytest.mark.parametrize("nh,nkv", [(12, 2), (40, 8), (18, 1)])
-def test_decoded_tokens_beside_a_prompt_portion_use_the_key_split(nh, nkv):
+def test_decoded_tokens_beside_a_prompt_portion_use_the_key_split(nh, nkv, ring):
     """A step that mixes a 300-token prompt portion with single tokens of sequences that already hold thousands of
     keys: the single tokens go through the decode shape (their keys split over a cluster), found through a list of
     their sequences, the portion through the tensor-memory kernel; each writes its own rows."""
@@ -227,7 +235,12 @@ def test_decoded_tokens_beside_a_prompt_portion_use_the_key_split(nh, nkv):
     for s in (0, 3, 4):
         case.plant(s, fars[s], direction, PLANT)
         qs[s][:, :nh // 2] = (direction * PLANT).bfloat16()
-    out, starts, pos0, plans = launch(case, qs, news, nh, nkv, d, None)
+    from microllm_rocm_b200.kernels import attention
+    attention.DECODE_RING = ring
+    try:
+        out, starts, pos0, plans = launch(case, qs, news, nh, nkv, d, None)
+    finally:
+        attention.DECODE_RING = None
     assert plans and plans[0][7] == 5 * -(-(nh // nkv) // 16) and plans[0][8] > 1      # five listed sequences, keys split
     assert torch.isfinite(out).all()
     worst = 0.0

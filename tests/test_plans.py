@@ -57,6 +57,14 @@ def test_decode_key_split_grows_with_the_context_and_fits_one_wave():
     assert attention.decode_splits(2, 32768) == 16 and attention.decode_splits(128, 2048) == 2
 
 
+def test_the_key_ring_is_for_long_streams_on_a_full_gpu():
+    from microllm_rocm_b200.kernels import attention
+    assert attention.decode_ring_pays(128, 2, 2073)             # batch 64, two kv heads, clusters of 2: 1,036 keys per CTA
+    assert not attention.decode_ring_pays(64, 4, 2073)          # batch 32: 518 keys per CTA
+    assert not attention.decode_ring_pays(16, 8, 2073)          # batch 8: fewer CTAs than multiprocessors
+    assert attention.decode_ring_pays(64, 4, 8192) and not attention.decode_ring_pays(2, 16, 32768)
+
+
 class _Ctx:
     def __init__(self, extras):
         self.extras = extras
