@@ -828,6 +828,16 @@ struct RowStateT {
     float o[NPAIR * 8][4];    // [pair*8 + j]: e < 2: element vb0*64 + 8g + j, e >= 2: element vb1*64 + 8g + j; head 2t + (e & 1)
 };
 
+// INTERLEAVED: which 8 head elements of a 32-element chunk pair a thread takes.  Plain: chunk c, elements
+// c*32 + t*8.  Interleaved (keys read from the swizzled ring): of every 64 elements the thread takes the 16-byte
+// pieces 2t and 2t+1 in turn, so that the four threads of a quad touch every second piece and the two key rows
+// of a quarter warp fall into different banks.  K and Q only have to agree.
+template <bool INTERLEAVED>
+__device__ __forceinline__ int k_column(int c, int t) {
+    return INTERLEAVED ? (c >> 1) * 64 + ((t << 1) | (c & 1)) * 8 : c * 32 + t * 8;
+}
+
+template <bool INTERLEAVED = false>
 __device__ __forceinline__ void consume_keys_t(const FaParams& p, const __nv_bfloat16* q_s, const KeyTile& kv, int last_pos,
                                                int lo, RowStateT& st) {
     if (kv.base < 0) return;
@@ -835,7 +845,7 @@ __device__ __forceinline__ void consume_keys_t(const FaParams& p, const __nv_bfl
     float s0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s1[4] = {0.0f, 0.0f, 0.0f, 0.0f};     // two chains
 #pragma unroll
     for (int c = 0; c < KCHUNKS; ++c) {
-        const uint4 q = *reinterpret_cast<const uint4*>(q_s + g * Q_STRIDE + c * 32 + t * 8);       // head g
+        const uint4 q = *reinterpret_cast<const uint4*>(q_s + g * Q_STRIDE + k_column<INTERLEAVED>(c, t));       // head g
         mma_bf16(s0, kv.k[0][c].x, kv.k[1][c].x, kv.k[0][c].y, kv.k[1][c].y, q.x, q.y);
         mma_bf16(s1, kv.k[0][c].z, kv.k[1][c].z, kv.k[0][c].w, kv.k[1][c].w, q.z, q.w);
     }
@@ -1155,7 +1165,7 @@ __device__ __forceinline__ void ring_take_keys(const unsigned char* tile, int ba
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
-        for (int c = 0; c < KCHUNKS; ++c) kv.k[nb][c] = ring_load16(kbox + (c >> 1) * (16 * 128), nb * 8 + g, (c & 1) * 4 + t);
+        for (int c = 0; c < KCHUNKS; ++c) kv.k[nb][c] = ring_load16(kbox + (c >> 1) * (16 * 128), nb * 8 + g, (t << 1) | (c & 1));     // k_column<true>
 #pragma unroll
     for (int vb = 0; vb < VBLOCKS; ++vb)
 #pragma unroll
@@ -1307,7 +1317,7 @@ __global__ void __launch_bounds__(160, 2) fa_decode_ring_kernel(const __grid_con
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));      // the stage may be refilled while this tile is used
-            consume_keys_t(p, q_s, tile, last_pos, lo, st);
+            consume_keys_t<true>(p, q_s, tile, last_pos, lo, st);
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");          // every warp has taken its last tile: the ring may become the merge's scratch
     }
