@@ -2,11 +2,19 @@
 model folder (config.json + model.safetensors).
 
 Distributions: every matrix, table and bias N(0, 0.02); norm weights 1 + N(0, 0.1); each
-part states its own in `WeightSpec.init`.  Each tensor has its own generator seeded from
-(seed, tensor name), so a tensor's values do not depend on which other tensors exist or on
-the order they are drawn in.  (The reference initialises with std::mt19937_64 and
+part states its own in `WeightSpec.init`.  (The reference initialises with std::mt19937_64 and
 std::normal_distribution in construction order, src/model/model.cpp:232-237,285-295 --
 not reproducible outside one standard library; its biases start at 0 and norms at 1.)
+
+The generator is counter-based and uses integer arithmetic only, so that the CPU, the GPU and any
+other program that restates these few lines produce the same bits, and a large model can be filled
+on the device: element i of a tensor takes the three 64-bit words
+    SplitMix64 finaliser(key + GOLDEN * (3 i + j + 1)),  j = 0, 1, 2,    key = f(seed, crc32(name)),
+cuts them into twelve 16-bit fields, and the standard normal value is (2 * sum - 12 * 65535) / 2^17:
+the sum of twelve uniforms (Irwin-Hall; variance 1 - 2^-32, support +-6), exact in fp32.  One fp32
+multiplication by the standard deviation (and one addition of 1 for norm weights) follows; a bf16 model
+is the round-to-nearest-even of these fp32 values.  A tensor's values depend on (seed, its name, the
+element's index) alone: not on which other tensors exist, nor on the order or the device they are drawn on.
 """
 from __future__ import annotations
 
@@ -23,24 +31,69 @@ from .loader import target_dtype
 from .safetensors import save_file
 
 
-def _tensor_seed(seed: int, name: str) -> int:
-    return (int(seed) * 1000003 + zlib.crc32(name.encode("utf-8"))) % (2 ** 63 - 1)
+_GOLDEN = 0x9E3779B97F4A7C15
+_MUL1 = 0xBF58476D1CE4E5B9
+_MUL2 = 0x94D049BB133111EB
+_CHUNK = 1 << 24                  # elements drawn at a time (bounds the integer temporaries to ~1 GB)
+
+
+def _signed(v: int) -> int:
+    """The int64 with the bit pattern of the unsigned 64-bit v (torch has no uint64 arithmetic;
+    two's-complement multiplication and addition wrap the same way)."""
+    v &= (1 << 64) - 1
+    return v - (1 << 64) if v >= (1 << 63) else v
+
+
+def _shift_right(z: torch.Tensor, bits: int) -> torch.Tensor:
+    return (z >> bits) & ((1 << (64 - bits)) - 1)              # logical, not arithmetic
+
+
+def _finalise(z: torch.Tensor) -> torch.Tensor:
+    """SplitMix64's output function on int64 tensors."""
+    z = (z ^ _shift_right(z, 30)) * _signed(_MUL1)
+    z = (z ^ _shift_right(z, 27)) * _signed(_MUL2)
+    return z ^ _shift_right(z, 31)
+
+
+def tensor_key(seed: int, name: str) -> int:
+    """64-bit stream key of a tensor: the seed and the name's CRC-32 through the same finaliser."""
+    z = (int(seed) * _GOLDEN + zlib.crc32(name.encode("utf-8")) * _MUL2 + _MUL1) & ((1 << 64) - 1)
+    z = ((z ^ (z >> 30)) * _MUL1) & ((1 << 64) - 1)
+    z = ((z ^ (z >> 27)) * _MUL2) & ((1 << 64) - 1)
+    return z ^ (z >> 31)
+
+
+def standard_normal(key: int, begin: int, count: int, device: torch.device) -> torch.Tensor:
+    """Elements begin .. begin+count of the stream `key`, fp32, the same bits on every device."""
+    index = torch.arange(begin, begin + count, dtype=torch.int64, device=device)
+    total = torch.zeros(count, dtype=torch.int64, device=device)
+    for j in range(3):
+        word = _finalise((index * 3 + (j + 1)) * _signed(_GOLDEN) + _signed(key))
+        total += word & 0xFFFF
+        for field in (1, 2, 3):
+            total += _shift_right(word, 16 * field) & 0xFFFF
+    return (total * 2 - 12 * 65535).to(torch.float32) * (1.0 / 131072.0)
 
 
 def draw(spec: WeightSpec, seed: int, name: str, device: torch.device) -> torch.Tensor:
-    """fp32 values of one tensor.  CPU and CUDA generators differ: a model folder is always
-    written from CPU draws; in-memory models for benchmarks may draw on the device."""
-    gen = torch.Generator(device=device)
-    gen.manual_seed(_tensor_seed(seed, name))
+    """fp32 values of one tensor, computed on `device`; the bits do not depend on the device."""
     kind, std = spec.init
     if spec.role == "int_table":
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
-    x = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device) * std
-    if kind == "one_plus_normal":
-        x += 1.0
-    elif kind != "normal":
+    if kind not in ("normal", "one_plus_normal"):
         raise ValueError(f"unknown init {kind!r} for {name}")
-    return x
+    n = 1
+    for s in spec.shape:
+        n *= int(s)
+    key = tensor_key(seed, name)
+    out = torch.empty(n, dtype=torch.float32, device=device)
+    for begin in range(0, n, _CHUNK):
+        count = min(_CHUNK, n - begin)
+        x = standard_normal(key, begin, count, device) * float(std)
+        if kind == "one_plus_normal":
+            x += 1.0
+        out[begin:begin + count] = x
+    return out.reshape(tuple(spec.shape))
 
 
 def random_tensors(expected: Dict[str, WeightSpec], seed: int, device: torch.device,
@@ -55,9 +108,9 @@ def random_tensors(expected: Dict[str, WeightSpec], seed: int, device: torch.dev
 
 
 def init_random(model, seed: int, storage_dtype: torch.dtype = None, draw_on_device: bool = False) -> None:
-    """Bind random weights to `model` in memory.  Values are those a folder written by
-    `write_random_model` with the same seed and storage dtype would hold when
-    draw_on_device is False."""
+    """Bind random weights to `model` in memory: the values a folder written by `write_random_model`
+    with the same seed and storage dtype holds.  draw_on_device only says where the arithmetic runs
+    (a large model is filled in seconds on the GPU)."""
     rt: Runtime = model.rt
     storage_dtype = storage_dtype or rt.dtype
     where = rt.device if draw_on_device else torch.device("cpu")

@@ -152,6 +152,58 @@ def test_random_mode_is_seeded_and_has_the_stated_distributions(tmp_path):
     assert len(fa.names()) == 3 * 12 + 3
 
 
+def test_random_values_are_the_documented_counter_function_of_seed_name_and_index():
+    """An independent restatement with Python integers: SplitMix64's finaliser over key + GOLDEN * (3 i + j + 1),
+    twelve 16-bit fields, (2 * sum - 12 * 65535) / 2^17, times the standard deviation."""
+    import zlib
+    from microllm_rocm_b200.parts.base import WeightSpec
+    from microllm_rocm_b200.weights.random_init import draw
+    M = (1 << 64) - 1
+
+    def finalise(z):
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M
+        return z ^ (z >> 31)
+
+    def value(seed, name, i):
+        key = finalise((seed * 0x9E3779B97F4A7C15 + zlib.crc32(name.encode()) * 0x94D049BB133111EB + 0xBF58476D1CE4E5B9) & M)
+        total = 0
+        for j in range(3):
+            word = finalise((key + 0x9E3779B97F4A7C15 * (3 * i + j + 1)) & M)
+            total += sum((word >> (16 * f)) & 0xFFFF for f in range(4))
+        return (2 * total - 12 * 65535) / 131072.0
+
+    name = "model.layers.1.mlp.down_proj.weight"
+    got = draw(WeightSpec((7, 13), "matrix", ("normal", 0.02)), 9, name, torch.device("cpu")).reshape(-1)
+    want = torch.tensor([value(9, name, i) for i in range(91)], dtype=torch.float32) * 0.02
+    assert torch.equal(got, want)
+    ones = draw(WeightSpec((5,), "vector", ("one_plus_normal", 0.1)), 9, "model.norm.weight", torch.device("cpu"))
+    assert torch.equal(ones, torch.tensor([value(9, "model.norm.weight", i) for i in range(5)], dtype=torch.float32) * 0.1 + 1.0)
+    # neither the tensor's extent nor a chunk boundary changes an element's value
+    longer = draw(WeightSpec((40, 13), "matrix", ("normal", 0.02)), 9, name, torch.device("cpu")).reshape(-1)
+    assert torch.equal(longer[:91], got)
+    big = draw(WeightSpec((1 << 16,), "matrix", ("normal", 1.0)), 1, "t", torch.device("cpu"))
+    assert abs(float(big.mean())) < 0.02 and abs(float(big.std()) - 1.0) < 0.02 and float(big.abs().max()) > 3.5
+
+
+@pytest.mark.gpu
+def test_a_model_drawn_on_the_device_holds_the_bits_of_the_written_folder(tmp_path):
+    from microllm_rocm_b200.parts.base import WeightSpec
+    from microllm_rocm_b200.weights import random_init
+    folder = write_random_model(ARCH, tiny_config("b"), 5, str(tmp_path / "m"), "bfloat16")
+    f = SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    declared = build_model(ARCH.build_spec(tiny_config("b")), Runtime(torch.device("cpu"), torch.float32)).expected_tensors()
+    on_device = random_init.random_tensors(declared, 5, torch.device("cuda"), torch.bfloat16)
+    assert set(on_device) == set(f.names())
+    for name in f.names():
+        assert torch.equal(on_device[name].cpu(), f.tensor(name)), name
+    # across a chunk boundary of the generator too
+    spec = WeightSpec((random_init._CHUNK + 1000,), "matrix", ("normal", 0.02))
+    a = random_init.draw(spec, 2, "x", torch.device("cuda")).cpu()
+    b = random_init.draw(spec, 2, "x", torch.device("cpu"))
+    assert torch.equal(a, b)
+
+
 def test_sharded_folder_through_index(tmp_path):
     folder = write_random_model(ARCH, tiny_config("a"), 0, str(tmp_path / "m"), "float32")
     f = SafetensorsFile(os.path.join(folder, "model.safetensors"))
