@@ -428,7 +428,10 @@ def run_ours(args):
     # ---- decode, end to end through the Python entry point -----------------------------------
     llm = LLM(engine, max_tokens_per_step=max(2048, args.batch), max_seqs=max_batch)
     host_prompts = prompts(args.batch)
-    ids = [llm.submit(p, GenerationConfig(max_new_tokens=args.steps + args.warmup + args.batch + 8, temperature=0.0)) for p in host_prompts]
+    # requests whose prompt is through decode while the others' prompts still run: allow for those tokens, so that
+    # no request ends (and the batch shrinks) inside the timed steps
+    early = args.batch * -(-prompt_len // llm.scheduler.max_tokens_per_step)
+    ids = [llm.submit(p, GenerationConfig(max_new_tokens=args.steps + args.warmup + early + 8, temperature=0.0)) for p in host_prompts]
     while any(llm.poll(i).computed < prompt_len for i in ids):          # prompts in, first token out
         llm.step()
     for _ in range(args.warmup):
@@ -436,10 +439,13 @@ def run_ours(args):
     h2d0, d2h0 = llm.h2d_bytes, llm.d2h_bytes
     torch.cuda.synchronize()
     t0 = time.perf_counter()
+    ended = 0
     for _ in range(args.steps):
-        llm.step()
+        ended += len(llm.step())
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    if ended:
+        raise RuntimeError(f"{ended} request(s) ended inside the timed end-to-end steps: the batch was not {args.batch} throughout")
     for i in ids:
         llm.cancel(i)
     e2e = {"value": args.batch * args.steps / e2e_s, "unit": "tokens/s",

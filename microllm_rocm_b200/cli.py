@@ -13,7 +13,7 @@ and this engine does not are read and checked as the reference checks them, and 
 that describes this engine: --use-cache true (there is no uncached path), --batch-argmax-mode device, --decode-mode generation, --continuous-prefill-batch true,
 --continuous-diagnostics false; any other legal value is refused with a sentence that says so, and
 --continuous-cache-buckets (a paged cache has no buckets), --kv-cache-fp32-layers and the
-tokenizer flags (--text, --vocab, --merges, --tokenizer-family, --chat-user) are refused by name.  The reference's command line is
+tokenizer flags (--text, --vocab, --merges, --tokenizer-family, --chat-user) are refused by name.
 --trace-output FILE (with --trace-max-elements N, prefill workload only, as hf_infer.cpp:268-273) writes one JSON line per
 intermediate tensor of the prompt's step in the reference's record layout (src/profiling/trace.cpp:156-195): the embedding,
 the residual stream and the pending delta after every layer, the final norm and the logits, each with its statistics and
@@ -211,6 +211,12 @@ def compute_dtype(o) -> str:
 
 def main(argv: Optional[List[str]] = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
+    if argv in (["--help"], ["-h"]):             # the reference has no such flag; its options are `--name value` pairs
+        print(__doc__.strip())
+        print("\nOptions and their defaults:")
+        for name, value in DEFAULTS.items():
+            print(f"  --{name} {value!r}")
+        return 0
     try:
         o = parse(argv)
         validate(o)

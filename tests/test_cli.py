@@ -63,3 +63,11 @@ def test_switches_between_paths_this_engine_does_not_have():
     for flag in ("--text", "--vocab", "--merges", "--continuous-cache-buckets", "--kv-cache-fp32-layers"):
         with pytest.raises(cli.UsageError, match="does not have"):
             cli.parse(["--model", "folder", flag, "x"])
+
+
+def test_help_lists_every_option(capsys):
+    from microllm_rocm_b200 import cli
+    assert cli.main(["--help"]) == 0
+    text = capsys.readouterr().out
+    for name in cli.DEFAULTS:
+        assert f"--{name} " in text
