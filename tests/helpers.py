@@ -42,8 +42,10 @@ SEEDS = {"a": 0, "b": 1, "c": 2, "d": 3}
 
 # fp32: engine and plain differ only by summation order.  bf16: both round to bf16 at the
 # same places, so what remains is summation order times bf16 steps of the intermediate values.
-FP32_ATOL = 2e-5
-BF16_REL = 0.03          # of the largest |logit| of the compared rows
+# Measured over every schedule of the engine tests (printed by compare_with_plain): fp32 worst |error| 8.3e-7,
+# bf16 worst 0.0054 of the largest |logit|.  The limits are a few times that.
+FP32_ATOL = 4e-6
+BF16_REL = 0.015         # of the largest |logit| of the compared rows
 
 
 def tiny_config(key: str) -> Qwen2Config:
@@ -187,7 +189,7 @@ def collect(engine, steps: List[dict]) -> Dict[Tuple[str, int], torch.Tensor]:
 def compare_with_plain(got: Dict[Tuple[str, int], torch.Tensor], folder: str, requests: Dict[str, List[int]],
                        precision: str) -> float:
     """Every (request, position) against the plain implementation; returns the worst error."""
-    worst = 0.0
+    worst, worst_ratio = 0.0, 0.0
     for rid, toks in requests.items():
         ref = plain_logits(folder, toks, precision)
         rows = torch.stack([got[(rid, p)] for p in range(len(toks))])
@@ -203,4 +205,6 @@ def compare_with_plain(got: Dict[Tuple[str, int], torch.Tensor], folder: str, re
             raise AssertionError(f"request {rid}: first wrong position {pos} of {len(toks)} "
                                  f"(max err there {float(err[pos].max()):.3e}, tolerance {tol_desc})")
         worst = max(worst, float(err.max()))
+        worst_ratio = max(worst_ratio, float(err.max() / ref.abs().max()))
+    print(f"[parity] {precision}: worst |error| {worst:.3e} = {worst_ratio:.5f} of the largest |logit|")
     return worst

@@ -201,6 +201,49 @@ def register_toy():
                     state[self.h] = counts[-1]
             return out
 
+    @register_mixer("toy_planned_scale", replace=True)
+    class PlannedScale(Mixer):
+        """W x scaled by a factor that depends on the token's position, looked up in a device table that the mixer
+        PLANS on the host for the longest sequence of the step and keeps in ctx.extras.  A captured decode step
+        freezes the table it was captured with: beyond the table's end the lookup is clamped and the result
+        wrong, unless whoever holds the context asks plan_stale() and lets the mixer plan anew."""
+        graph_safe = True                 # device-resident inputs only: positions and the planned table
+        PLAN_KEY = ("toy_planned_scale", "table")
+        GRANULE = 16
+        plans_made = 0
+
+        def __init__(self, params, rt, position=None):
+            self.prefix, self.h, self.rt = params.get("prefix", ""), int(params["hidden_size"]), rt
+
+        def weight_specs(self):
+            return {"mix.weight": WeightSpec((self.h, self.h))}
+
+        def bind(self, tensors):
+            self.w = tensors["mix.weight"]
+
+        @classmethod
+        def capacity_for(cls, max_seq_len):
+            return -(-max(1, max_seq_len) // cls.GRANULE) * cls.GRANULE
+
+        def plan_group(self):
+            return self.PLAN_KEY
+
+        def plan_stale(self, ctx, max_seq_len):
+            table = ctx.extras.get(self.PLAN_KEY)
+            return table is not None and table.shape[0] != self.capacity_for(max_seq_len)
+
+        def forget_plans(self, ctx):
+            ctx.extras.pop(self.PLAN_KEY, None)
+
+        def forward(self, x, ctx, cache):
+            table = ctx.extras.get(self.PLAN_KEY)
+            if table is None or (not ctx.decode_only and table.shape[0] < self.capacity_for(ctx.max_seq_len)):
+                capacity = self.capacity_for(ctx.max_seq_len)
+                table = ctx.extras[self.PLAN_KEY] = 1.0 + 0.25 * (torch.arange(capacity, device=x.device) // 8).float()
+                type(self).plans_made += 1
+            scale = table[torch.clamp(ctx.positions.long(), max=table.shape[0] - 1)]
+            return (x.float() @ self.w.float().t()) * scale[:, None]
+
     @dataclasses.dataclass(frozen=True)
     class ToyConfig:
         vocab_size: int
@@ -230,7 +273,9 @@ def register_toy():
         for l, kind in enumerate(cfg.kinds):
             mixer = (PartSpec("attention", dict(prefix="attn.", hidden_size=h, num_heads=cfg.num_heads, num_kv_heads=1,
                                                 head_dim=h // cfg.num_heads, qkv_bias=False, window=None))
-                     if kind == "attention" else PartSpec("toy_running_mean", dict(prefix="toy.", hidden_size=h)))
+                     if kind == "attention" else
+                     PartSpec("toy_planned_scale", dict(prefix="toy.", hidden_size=h)) if kind == "planned" else
+                     PartSpec("toy_running_mean", dict(prefix="toy.", hidden_size=h)))
             layers.append(LayerSpec(prefix=f"layers.{l}.", block=PartSpec("pre_norm_residual"), mixer_norm=norm("n1."),
                                     mixer=mixer, ffn_norm=norm("n2."),
                                     feed_forward=PartSpec("swiglu", dict(prefix="ff.", hidden_size=h,
@@ -260,6 +305,9 @@ def plain_toy_forward(w, cfg, toks):
             k = plain.rope_split_half(plain.linear(h, w[p + "attn.k_proj.weight"]).view(T, 1, D), pos, 10000.0)
             v = plain.linear(h, w[p + "attn.v_proj.weight"]).view(T, 1, D)
             x = x + plain.linear(plain.causal_gqa_attention(q, k, v, None).reshape(T, H), w[p + "attn.o_proj.weight"])
+        elif kind == "planned":
+            scale = 1.0 + 0.25 * (torch.arange(T) // 8).float()
+            x = x + plain.linear(h, w[p + "toy.mix.weight"]) * scale[:, None]
         else:
             mean = torch.cumsum(h, 0) / torch.arange(1, T + 1, dtype=torch.float32)[:, None]
             x = x + plain.linear(mean, w[p + "toy.mix.weight"])
@@ -291,6 +339,41 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     mixed = collect(load_engine(folder, dtype="float32", page_size=16, max_tokens=peak, max_requests=3), steps)
     for key, row in whole.items():
         assert torch.allclose(mixed[key], row, atol=3e-5), key
+
+
+def test_a_toy_mixer_freezes_a_plan_into_a_captured_decode_step_and_plans_anew(tmp_path):
+    """A mixer defined here keeps a host-made launch plan (a table sized for the longest sequence) in the step
+    context; steady decoding captures the step, plan included.  The engine asks the mixer's own hooks whether the
+    plan still suits the context and lets it plan anew: generation through captured steps equals generation
+    step by step and the plain forward, across three sizes of the table.  Nothing under the package names this mixer."""
+    from microllm_rocm_b200.engine.llm import LLM
+    from microllm_rocm_b200.parts.base import MIXERS
+    from microllm_rocm_b200.sampling import GenerationConfig
+    from microllm_rocm_b200.weights import write_random_model
+    arch, ToyConfig = register_toy()
+    cfg = ToyConfig(vocab_size=90, hidden_size=32, intermediate_size=56, kinds=("planned", "attention", "planned"))
+    folder = write_random_model(arch, cfg, 6, str(tmp_path / "planned"), "float32")
+    planned = MIXERS["toy_planned_scale"]
+    prompt = random_tokens(10, cfg.vocab_size, 3)
+    greedy = GenerationConfig(max_new_tokens=30, temperature=0.0)
+
+    stepwise = LLM(folder, dtype="float32", max_tokens=256, max_seqs=2, cuda_graphs=False)
+    want = stepwise.generate([prompt], greedy)[0]
+
+    llm = LLM(folder, dtype="float32", max_tokens=256, max_seqs=2, cuda_graphs=True)
+    assert llm.graphs is not None, "the toy mixer says it is graph safe"
+    planned.plans_made = 0
+    got = llm.generate([prompt], greedy)[0]
+    assert got == want
+    # lengths 11..40 pass the table sizes 16, 32 and 48: planned for the prompt, then once per size
+    assert planned.plans_made >= 3 and llm.graphs.captures >= 3, (planned.plans_made, llm.graphs.captures)
+    assert llm.graph_steps >= 25
+
+    w = plain.read_safetensors(os.path.join(folder, "model.safetensors"))
+    logits = plain_toy_forward(w, cfg, prompt + got)
+    for i, token in enumerate(got):
+        row = logits[len(prompt) + i - 1]
+        assert int(row.argmax()) == token or float(row.max() - row[token]) < 1e-4, i
 
 
 # --------------------------------------------------------------------------------- more toy parts: routing, positions, a norm
