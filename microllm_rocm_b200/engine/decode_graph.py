@@ -34,8 +34,12 @@ def _round_up_pow2(n: int) -> int:
 
 
 class DecodeGraph:
-    def __init__(self, engine: Engine, batch: int, table_widths: Dict[str, int]):
-        self.engine, self.batch = engine, batch
+    def __init__(self, engine: Engine, batch: int, table_widths: Dict[str, int], host_io: bool = False):
+        # host_io: the captured step begins with the copy of the requests' input tokens out of pinned host memory
+        # and ends with the copy of the selected tokens (and the error flag) into pinned host memory, so that a
+        # step costs the host ONE launch between writing the tokens and waiting for the answers.  Without it the
+        # tokens stay where the sampler left them and the caller copies what it wants (a device-only loop).
+        self.engine, self.batch, self.host_io = engine, batch, bool(host_io)
         self.widths = dict(table_widths)
         dev = engine.device
         A = batch
@@ -162,10 +166,13 @@ class DecodeGraph:
         self._wait_upload()
         if self._token_views is None:
             a, b = self._s["tokens"]
-            ops.copy_async(self.dev[a:b], self.host[a:b])         # checked once; from now on by raw pointers
+            if not self.host_io:
+                ops.copy_async(self.dev[a:b], self.host[a:b])     # checked once; from now on by raw pointers
             self._token_views = (self.host.numpy()[a:b], self.host[a:b].data_ptr(), self.dev[a:b].data_ptr(), 4 * (b - a))
         array, pinned, device, nbytes = self._token_views
         array[:] = tokens
+        if self.host_io:
+            return                                        # the replay's first node copies them
         ops.copy_raw(device, pinned, nbytes, True)
         self._mark_upload()
 
@@ -185,10 +192,15 @@ class DecodeGraph:
 
     # ------------------------------------------------------------------ capture and replay
     def _body(self) -> None:
+        if self.host_io:
+            a, b = self._s["tokens"]
+            ops.copy_raw(self.dev[a:b].data_ptr(), self.host[a:b].data_ptr(), 4 * (b - a), True)
         logits = self.engine.model.forward(self.ctx, self.views)
         ops.sample_rows(logits, self.temperature, self.top_k, self.seed, self.draw, self.ctx.token_ids)
         ops.decode_advance(self.ctx.positions, self.ctx.seq_pos0, self.ctx.seq_lens, self.draw, self.ctx.token_ids,
                            self.engine.error_flag, self.out_dev)
+        if self.host_io:
+            ops.copy_raw(self.out_host.data_ptr(), self.out_dev.data_ptr(), 4 * (self.batch + 1), False)
 
     def capture(self) -> None:
         """Run the step once eagerly (plans launches, warms libraries), then record it.  The
@@ -213,7 +225,8 @@ class DecodeGraph:
     def read_tokens(self) -> List[int]:
         """The tokens the last replay selected (one device -> host copy, synchronising)."""
         A = self.batch
-        ops.copy_raw(self.out_host.data_ptr(), self.out_dev.data_ptr(), 4 * (A + 1), False)
+        if not self.host_io:
+            ops.copy_raw(self.out_host.data_ptr(), self.out_dev.data_ptr(), 4 * (A + 1), False)
         ops.stream_synchronize()
         self._upload_pending = False                      # everything queued before has run
         host = self.out_host.tolist()
@@ -227,8 +240,8 @@ class DecodeGraphPool:
     """Captured decode steps by batch size and table width; built on first use.  At most `max_graphs` are
     kept (each owns its activations and a captured graph): the one used longest ago goes first."""
 
-    def __init__(self, engine: Engine, max_graphs: int = 32):
-        self.engine = engine
+    def __init__(self, engine: Engine, max_graphs: int = 32, host_io: bool = False):
+        self.engine, self.host_io = engine, bool(host_io)
         self.max_graphs = max(1, int(max_graphs))
         self.graphs: Dict[tuple, DecodeGraph] = {}          # insertion order = order of last use
         self.captures = 0
@@ -245,7 +258,7 @@ class DecodeGraphPool:
         if graph is None:
             while len(self.graphs) >= self.max_graphs:
                 del self.graphs[next(iter(self.graphs))]
-            graph = DecodeGraph(self.engine, len(requests), widths)
+            graph = DecodeGraph(self.engine, len(requests), widths, host_io=self.host_io)
         self.graphs[key] = graph                             # (re)inserted last: most recently used
         return graph
 

@@ -37,18 +37,25 @@ class LLM:
                                    max_tokens_per_step=max_tokens_per_step,
                                    max_seqs=min(max_seqs, self.engine.cache.max_requests))
         self.sampler = Sampler(self.engine.device)
-        self.graphs = DecodeGraphPool(self.engine) if cuda_graphs and graph_capable(self.engine) else None
+        self.graphs = DecodeGraphPool(self.engine, host_io=True) if cuda_graphs and graph_capable(self.engine) else None
         self._graph: Optional[DecodeGraph] = None       # the captured step whose device state is current
         self.graph_steps = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.wait_s = 0.0            # host time spent blocked in the step's one device -> host read: the GPU was busy for all of it
+        # Steady decoding: while the GPU runs a captured step the host already prepares the next one (pages, tables,
+        # the check of the captured plan), so that between reading a step's tokens and launching the next step
+        # only the scheduler's update and the token upload remain.  The prepared plan is used only if nothing
+        # happened in between that the scheduler would have decided differently.
+        self._prepared: Optional[StepPlan] = None
+        self.prepared_steps = 0
 
     # ------------------------------------------------------------------ request interface
     def submit(self, prompt: Sequence[int], config: Optional[GenerationConfig] = None) -> int:
         return self.scheduler.submit(prompt, config)
 
     def cancel(self, request_id: int) -> bool:
+        self._prepared = None
         return self.scheduler.cancel(request_id)
 
     def poll(self, request_id: int) -> Request:
@@ -60,6 +67,10 @@ class LLM:
     def step(self) -> List[Request]:
         """One scheduler decision, one model step, one token selection.  Returns the requests
         that finished in it."""
+        prepared, self._prepared = self._prepared, None
+        if (prepared is not None and not self.scheduler.waiting and len(prepared.entries) == len(self.scheduler.running)
+                and all(e.request.computed == e.begin and not e.request.finished for e in prepared.entries)):
+            return self._graph_step(prepared, prepared=True)
         plan = self.scheduler.schedule()
         if not plan.entries:
             if self.scheduler.has_work() and not plan.preempted:
@@ -88,35 +99,59 @@ class LLM:
             raise StepError(device_error_text(host[R]))
         return self.scheduler.update(plan, host[:R])
 
-    def _graph_step(self, plan: StepPlan) -> List[Request]:
+    def _prepare_next(self, plan: StepPlan, graph: DecodeGraph) -> None:
+        """While the GPU runs `plan` as a captured step: what the same requests' next step needs from the host.
+        Leaves a plan in self._prepared only if that step can be this graph's next replay as it stands."""
+        if self.scheduler.waiting or len(plan.entries) != len(self.scheduler.running) or len(plan.entries) > self.scheduler.max_seqs:
+            return
+        cache = self.engine.cache
+        for e in plan.entries:
+            if len(e.request.generated) + 2 > e.request.config.max_new_tokens:
+                return                                   # ends by length with this step's token: the batch changes
+            if not cache.reserve(e.request.id, e.begin + 2):
+                return                                   # out of pages: the scheduler decides who gives way
+        ids = graph.requests
+        if graph.stale(max(e.begin for e in plan.entries) + 2) or not graph.fits(ids):
+            return
+        graph.refresh_tables()                           # queued behind the running step; the next replay finds them
+        self._prepared = StepPlan([type(e)(e.request, e.begin + 1, 1, True) for e in plan.entries])
+
+    def _graph_step(self, plan: StepPlan, prepared: bool = False) -> List[Request]:
         """A step in which every request brings its one last-selected token: replay the captured
         decode step instead of launching it kernel by kernel."""
         ids = [e.request.id for e in plan.entries]
         graph = self._graph
         longest = max(e.begin for e in plan.entries) + 1
-        if graph is not None and graph.stale(longest):
-            graph = None                                 # the context outgrew the way the captured step cuts the keys
-        if graph is None or graph.requests != ids or not graph.fits(ids):
-            remaining = max(e.request.config.max_new_tokens - len(e.request.generated) for e in plan.entries)
-            graph = self.graphs.get(ids, headroom_tokens=remaining)
-            if graph.stale(longest):
-                graph.invalidate()                       # captured for another context length: plan and capture anew
-            state = ([e.request.token(e.begin) for e in plan.entries], [e.begin for e in plan.entries],
-                     [e.request.config for e in plan.entries], [len(e.request.generated) for e in plan.entries])
-            graph.load(ids, *state)
-            if graph.graph is None:
-                self.graphs.ensure_captured(graph)
-                graph.load(ids, *state)                  # the eager run before capture moved the state
-            self._graph = graph
-            self.h2d_bytes += 4 * graph.total
-        else:
-            graph.refresh_tables()
+        if prepared and graph is not None and graph.requests == ids:
+            # pages, tables and the captured plan were seen to while the last step ran
             graph.upload_tokens([e.request.token(e.begin) for e in plan.entries])
             self.h2d_bytes += 4 * len(ids)
+            self.prepared_steps += 1
+        else:
+            if graph is not None and graph.stale(longest):
+                graph = None                             # the context outgrew the way the captured step cuts the keys
+            if graph is None or graph.requests != ids or not graph.fits(ids):
+                remaining = max(e.request.config.max_new_tokens - len(e.request.generated) for e in plan.entries)
+                graph = self.graphs.get(ids, headroom_tokens=remaining)
+                if graph.stale(longest):
+                    graph.invalidate()                   # captured for another context length: plan and capture anew
+                state = ([e.request.token(e.begin) for e in plan.entries], [e.begin for e in plan.entries],
+                         [e.request.config for e in plan.entries], [len(e.request.generated) for e in plan.entries])
+                graph.load(ids, *state)
+                if graph.graph is None:
+                    self.graphs.ensure_captured(graph)
+                    graph.load(ids, *state)              # the eager run before capture moved the state
+                self._graph = graph
+                self.h2d_bytes += 4 * graph.total
+            else:
+                graph.refresh_tables()
+                graph.upload_tokens([e.request.token(e.begin) for e in plan.entries])
+                self.h2d_bytes += 4 * len(ids)
         graph.replay()
         # what does not need the step's tokens happens while the GPU runs
         for e in plan.entries:
             self.engine.cache.commit(e.request.id, e.begin + 1)
+        self._prepare_next(plan, graph)
         self.d2h_bytes += 4 * (len(ids) + 1)
         self.graph_steps += 1
         self.engine.steps_run += 1
@@ -127,6 +162,7 @@ class LLM:
         finished = self.scheduler.update(plan, tokens)
         if finished:
             self._graph = None
+            self._prepared = None
         return finished
 
     # ------------------------------------------------------------------ whole generations

@@ -215,6 +215,7 @@ def test_captured_decode_steps_equal_launched_ones(folders, dtype):
     graphed = llm_for(folders[key], dtype, max_tokens=1024)
     got = graphed.generate(prompts, cfgs)
     assert graphed.graph_steps > 50 and plain_path.graph_steps == 0
+    assert graphed.prepared_steps > 40               # most steady steps found pages, tables and plan seen to beforehand
     if dtype == "float32":
         assert got == want
     else:
@@ -337,6 +338,36 @@ def test_the_driver_entry_point_generates_and_compares():
     in fp32 and bf16 and agree with the plain implementation."""
     import __graft_entry__ as entry
     entry.smoke()
+
+
+def test_steps_prepared_ahead_give_way_to_cancels_arrivals_and_ends(folders):
+    """While a captured decode step runs, the host prepares the same requests' next step.  A cancel, a new
+    request or a request that ends must make it fall back to the scheduler's decision: every surviving request
+    gets exactly the tokens it gets alone, the pool ends empty."""
+    from microllm_rocm_b200 import GenerationConfig
+    key = "b"
+    vocab = tiny_config(key).vocab_size
+    prompts = [random_tokens(n, vocab, 3 * n + 1) for n in [9, 40, 22, 17]]
+    cfgs = [GenerationConfig(max_new_tokens=n, temperature=0.0) for n in [60, 25, 80, 30]]
+    alone = llm_for(folders[key], "float32", max_tokens=2048, cuda_graphs=False)
+    want = [alone.generate([p], c)[0] for p, c in zip(prompts, cfgs)]
+    llm = llm_for(folders[key], "float32", max_tokens=2048)
+    ids = [llm.submit(p, c) for p, c in zip(prompts[:3], cfgs[:3])]
+    for _ in range(12):
+        llm.step()
+    assert llm.prepared_steps >= 8
+    assert llm.cancel(ids[1])                              # one of the three leaves in the middle of steady decoding
+    for _ in range(6):
+        llm.step()
+    ids.append(llm.submit(prompts[3], cfgs[3]))            # a new one arrives: a prompt step between captured ones
+    while llm.has_work():
+        llm.step()
+    for i in (0, 2, 3):
+        assert list(llm.poll(ids[i]).generated) == want[i], i
+    got = list(llm.poll(ids[1]).generated)
+    assert got == want[1][:len(got)] and len(got) < len(want[1])
+    assert llm.metrics()["cache"]["live_requests"] == 0
+    llm.engine.cache.check()
 
 
 @pytest.mark.parametrize("key,pool,budget,seed,preempts", [("b", 320, 2048, 0, True), ("b", 400, 64, 7, False),
