@@ -30,6 +30,7 @@ from ..parts.base import FixedStateNeed, PagedKVNeed, PagedKVView, StateView
 from .pages import PageError, PagePool, SlotPool
 
 RELEASED = -1      # block-table entry of a block that was given back (or never existed)
+GUARD_VALUE = -24576.0     # exact in bf16 and fp32; what a guard page holds
 
 
 def group_key(need: PagedKVNeed) -> str:
@@ -52,12 +53,15 @@ class CacheGroup:
 class CacheManager:
     def __init__(self, entries: Dict[str, object], page_size: int, num_pages: int, max_requests: int,
                  device: Optional[torch.device] = None, kv_dtype: torch.dtype = torch.float32,
-                 max_step_tokens: Optional[int] = None):
+                 max_step_tokens: Optional[int] = None, guard_pages: bool = False):
         """entries: cache name -> PagedKVNeed | FixedStateNeed (from parts.Model.cache_entries).
         num_pages: pages of a group that keeps all keys.  device None: books only, no storage (for host tests).
         max_step_tokens: the most tokens one request brings in a step, when the caller promises one: a group
         with a window of W keys then never holds more than W - 1 + max_step_tokens tokens of a request, and its
-        pool (and storage) is sized for max_requests such spans instead of for num_pages."""
+        pool (and storage) is sized for max_requests such spans instead of for num_pages.
+        guard_pages: a debugging aid.  Every paged entry's storage gets one more page in front and one behind,
+        filled with a fixed pattern that no kernel may touch; check_guards() reads them back.  A store that runs off
+        either end of the pool (a page index of -1 or num_pages that slipped through a kernel's checks) shows there."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size, self.num_pages, self.max_requests = int(page_size), int(num_pages), int(max_requests)
@@ -67,6 +71,7 @@ class CacheManager:
         self.kv_storage: Dict[str, torch.Tensor] = {}
         self.state_storage: Dict[str, torch.Tensor] = {}
         self.state_needs: Dict[str, FixedStateNeed] = {}
+        self.guarded: Dict[str, torch.Tensor] = {}       # entry -> the whole allocation, guards included
         for name, need in entries.items():
             need = getattr(need, "need", need)
             if isinstance(need, PagedKVNeed):
@@ -75,9 +80,15 @@ class CacheManager:
                     self.groups[key] = CacheGroup(key, need.window, self.pages_for_group(need.window, max_step_tokens))
                 self.entry_group[name] = key
                 if device is not None:
-                    self.kv_storage[name] = torch.zeros(
-                        (self.groups[key].pool.num_pages, 2, need.num_kv_heads, page_size, need.head_dim),
-                        dtype=need.dtype or kv_dtype, device=device)
+                    pages = self.groups[key].pool.num_pages
+                    whole = torch.zeros((pages + (2 if guard_pages else 0), 2, need.num_kv_heads, page_size, need.head_dim),
+                                        dtype=need.dtype or kv_dtype, device=device)
+                    if guard_pages:
+                        whole[0].fill_(GUARD_VALUE)
+                        whole[-1].fill_(GUARD_VALUE)
+                        self.guarded[name] = whole
+                        whole = whole[1:-1]                 # contiguous: the pool begins one page into the allocation
+                    self.kv_storage[name] = whole
             elif isinstance(need, FixedStateNeed):
                 self.state_needs[name] = need
                 if device is not None:
@@ -206,6 +217,14 @@ class CacheManager:
 
     def kv_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.kv_storage.values())
+
+    def check_guards(self) -> None:
+        """With guard_pages: the page in front of and the page behind every pool still hold their pattern."""
+        for name, whole in self.guarded.items():
+            for where, page in (("in front of", whole[0]), ("behind", whole[-1])):
+                wrong = int((page != GUARD_VALUE).sum().item())
+                if wrong:
+                    raise PageError(f"cache entry {name!r}: {wrong} elements of the guard page {where} the pool were overwritten")
 
     def check(self) -> None:
         """No page lost, none held twice, books and pools agree."""

@@ -53,9 +53,10 @@ def prepare_kernels(model=None) -> None:
     kernel_build.compile_many(sources)
 
 
-def make_engine(model, page_size: int, num_pages: int, max_requests: int, max_step_tokens: Optional[int] = None) -> Engine:
+def make_engine(model, page_size: int, num_pages: int, max_requests: int, max_step_tokens: Optional[int] = None,
+                guard_pages: bool = False) -> Engine:
     cache = CacheManager(model.cache_entries, page_size, num_pages, max_requests, device=model.rt.device,
-                         kv_dtype=model.rt.dtype, max_step_tokens=max_step_tokens)
+                         kv_dtype=model.rt.dtype, max_step_tokens=max_step_tokens, guard_pages=guard_pages)
     engine = Engine(model, cache)
     engine.max_step_tokens = max_step_tokens      # the promise the window groups' pools were sized on
     return engine
@@ -68,11 +69,12 @@ def pages_for_tokens(max_tokens: int, page_size: int) -> int:
 def load_engine(folder: str, dtype="bfloat16", page_size: int = DEFAULT_PAGE_SIZE, num_pages: Optional[int] = None,
                 max_tokens: Optional[int] = None, max_requests: int = 64, device: Optional[str] = None,
                 strict: bool = True, config_path: Optional[str] = None, weights_path: Optional[str] = None,
-                max_step_tokens: Optional[int] = None) -> Engine:
+                max_step_tokens: Optional[int] = None, guard_pages: bool = False) -> Engine:
     """Read config.json, choose the architecture by its name, load model.safetensors, and set
     up a cache of `num_pages` pages per layer group (or enough for `max_tokens` tokens).  `max_step_tokens`:
     a promise that no request brings more tokens than this in one step, which lets groups of windowed layers
-    have smaller pools (see CacheManager)."""
+    have smaller pools (see CacheManager).  `guard_pages`: a page of a fixed pattern in front of and behind every
+    pool, checked by `engine.cache.check_guards()` (debugging aid)."""
     dev = require_gpu(device)
     with open(config_path or os.path.join(folder, "config.json"), "r", encoding="utf-8") as f:
         raw = json.load(f)
@@ -84,7 +86,7 @@ def load_engine(folder: str, dtype="bfloat16", page_size: int = DEFAULT_PAGE_SIZ
     report = load_weights(model, weights_path or folder, strict=strict)
     if num_pages is None:
         num_pages = pages_for_tokens(max_tokens if max_tokens is not None else config.max_position_embeddings, page_size)
-    engine = make_engine(model, page_size, num_pages, max_requests, max_step_tokens)
+    engine = make_engine(model, page_size, num_pages, max_requests, max_step_tokens, guard_pages)
     engine.config = config
     engine.load_report = report
     return engine

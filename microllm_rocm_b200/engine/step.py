@@ -204,3 +204,4 @@ class Engine:
         if code:
             self.error_flag.zero_()
             raise StepError(device_error_text(code))
+        self.cache.check_guards()              # nothing to read unless the cache was made with guard pages

@@ -32,6 +32,8 @@ def parse_args(argv):
     p.add_argument("--max-tokens", type=int, required=True,
                    help="most tokens live requests hold at any time (each rounded up to 64)")
     p.add_argument("--page-size", type=int, default=TRACE_PAGE_SIZE)
+    p.add_argument("--guard-pages", action="store_true",
+                   help="debugging aid: a page of a fixed pattern in front of and behind every cache pool, read back after every step")
     return p.parse_args(argv)
 
 
@@ -47,7 +49,7 @@ def run(argv: List[str], stdin=None, stdout=None) -> int:
     from .loading import load_engine, pages_for_tokens
     num_pages = pages_for_tokens(args.max_tokens, args.page_size)
     engine = load_engine(args.model, dtype=args.dtype, page_size=args.page_size, num_pages=num_pages,
-                         max_requests=MAX_LIVE_REQUESTS)
+                         max_requests=MAX_LIVE_REQUESTS, guard_pages=args.guard_pages)
     print(f"[trace_run] ready: {num_pages} pages of {args.page_size} tokens per layer group",
           file=sys.stderr, flush=True)
     def to_file(step, logits):

@@ -161,3 +161,34 @@ def test_a_window_group_needs_pages_for_its_window_only():
         cache.release(rid)
     cache.check()
     assert cache.groups["window40"].pool.used_count == 0 and cache.groups["full"].pool.used_count == 0
+
+
+def test_guard_pages_show_a_store_outside_the_pool():
+    """With guard_pages every paged entry has a page of a fixed pattern in front of and behind its pool.  The
+    pool's own pages are where they would be without guards (the entry's tensor starts one page in); a value
+    written just outside either end is found by check_guards()."""
+    import torch
+    from microllm_rocm_b200.cache.manager import GUARD_VALUE
+    from microllm_rocm_b200.cache.pages import PageError
+    entries = {"run0": PagedKVNeed(2, 8), "run1": PagedKVNeed(1, 16, window=24), "run2": FixedStateNeed((4,))}
+    cache = CacheManager(entries, page_size=16, num_pages=6, max_requests=2, device=torch.device("cpu"),
+                         kv_dtype=torch.bfloat16, guard_pages=True)
+    for name in ("run0", "run1"):
+        pool, whole = cache.kv_storage[name], cache.guarded[name]
+        assert pool.is_contiguous() and pool.shape[0] == whole.shape[0] - 2
+        assert pool.data_ptr() == whole.data_ptr() + whole[0].numel() * whole.element_size()
+        assert float(whole[0].float().min()) == GUARD_VALUE == float(whole[-1].float().max())
+        assert float(pool.float().abs().max()) == 0.0
+    cache.check_guards()
+    cache.kv_storage["run0"].fill_(1.0)                   # every legal store
+    cache.check_guards()
+    cache.guarded["run1"][-1, 0, 0, 0, 3] = 0.5            # one element past the last page
+    with pytest.raises(PageError, match="run1.*behind"):
+        cache.check_guards()
+    cache.guarded["run1"][-1].fill_(GUARD_VALUE)
+    cache.guarded["run0"][0, 1, 1, 15, 7] = 2.0            # the last element before the first page
+    with pytest.raises(PageError, match="run0.*in front"):
+        cache.check_guards()
+    plain_cache = CacheManager(entries, page_size=16, num_pages=6, max_requests=2, device=torch.device("cpu"))
+    assert not plain_cache.guarded
+    plain_cache.check_guards()                            # nothing to check, nothing raised

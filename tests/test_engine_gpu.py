@@ -30,9 +30,9 @@ def requests_for(key):
     return {f"r{i}": random_tokens(n, vocab, 100 * i + n) for i, n in enumerate(LENGTHS[key])}
 
 
-def engine_for(folder, dtype, max_tokens=1024, page_size=16):
+def engine_for(folder, dtype, max_tokens=1024, page_size=16, guard_pages=False):
     from microllm_rocm_b200.engine.loading import load_engine
-    return load_engine(folder, dtype=dtype, page_size=page_size, max_tokens=max_tokens, max_requests=8)
+    return load_engine(folder, dtype=dtype, page_size=page_size, max_tokens=max_tokens, max_requests=8, guard_pages=guard_pages)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -52,8 +52,12 @@ def test_mixed_batches_with_reused_pages(folders, key, dtype):
     lengths = [60, 33, 150, 90, 47, 128, 75, 20, 101, 64]
     reqs = {f"m{i}": random_tokens(n, vocab, 7 * i + n) for i, n in enumerate(lengths)}
     steps, peak = steps_mixed(reqs, max_live=4, seed=3)
-    engine = engine_for(folders[key], dtype, max_tokens=peak)
+    # a page of a fixed pattern in front of and behind every pool, read back after every step: with a pool this
+    # tight the first and the last page are in use all the time, and nothing may be stored beside them
+    engine = engine_for(folders[key], dtype, max_tokens=peak, guard_pages=True)
+    assert len(engine.cache.guarded) == tiny_config(key).num_hidden_layers
     got = collect(engine, steps)
+    engine.cache.check_guards()
     compare_with_plain(got, folders[key], reqs, PRECISION[dtype])
     stats = engine.cache.stats()
     for group in engine.cache.groups:
@@ -100,8 +104,9 @@ def test_head_size_128_with_six_heads_per_kv_head(tmp_path_factory, page_size):
     compare_with_plain(got, folder, reqs, "bfloat16")
     steps, peak = steps_mixed(reqs, max_live=3, seed=9, decode_tail=5)
     live = sum(-(-len(t) // page_size) * page_size for t in reqs.values())       # all three may be live at once
-    engine = engine_for(folder, "bfloat16", max_tokens=live, page_size=page_size)
+    engine = engine_for(folder, "bfloat16", max_tokens=live, page_size=page_size, guard_pages=True)
     compare_with_plain(collect(engine, steps), folder, reqs, "bfloat16")
+    engine.cache.check_guards()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
