@@ -80,7 +80,7 @@ class CacheManager:
                     self.groups[key] = CacheGroup(key, need.window, self.pages_for_group(need.window, max_step_tokens))
                 self.entry_group[name] = key
                 if device is not None:
-                    pages = self.groups[key].pool.num_pages
+                    pages = self.groups[key].pool.num_pages + 1        # the pool's pages, then the spare page (see pad_page)
                     whole = torch.zeros((pages + (2 if guard_pages else 0), 2, need.num_kv_heads, page_size, need.head_dim),
                                         dtype=need.dtype or kv_dtype, device=device)
                     if guard_pages:
@@ -92,10 +92,15 @@ class CacheManager:
             elif isinstance(need, FixedStateNeed):
                 self.state_needs[name] = need
                 if device is not None:
-                    self.state_storage[name] = torch.zeros((max_requests, *need.shape), dtype=need.dtype, device=device)
+                    self.state_storage[name] = torch.zeros((max_requests + 1, *need.shape), dtype=need.dtype, device=device)
             else:
                 raise TypeError(f"cache entry {name!r} has an unknown need {need!r}")
         self.slots = SlotPool(max_requests)
+        # One page behind every pool and one state slot behind the requests' slots belong to nobody: rows that
+        # only fill a batch of fixed size up (a captured decode step run for fewer requests than it was
+        # captured for) store their key and keep their state there.  What they hold is never read for a request.
+        self.pad_page: Dict[str, int] = {k: g.pool.num_pages for k, g in self.groups.items()}
+        self.pad_slot = max_requests
         self.requests: Dict[Hashable, _Request] = {}
         self.pages_released_by_window = 0
         self.tables_version = 0          # grows whenever any block table changes: lets a reader skip a comparison

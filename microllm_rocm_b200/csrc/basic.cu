@@ -293,27 +293,30 @@ MLB_EXPORT int mlb_cast_f32_bf16(const float* in, void* out, long long n, cudaSt
 __global__ void decode_advance_kernel(int* __restrict__ positions, int* __restrict__ seq_pos0,
                                       int* __restrict__ seq_lens, long long* __restrict__ draw, int n,
                                       const int* __restrict__ tokens, const int* __restrict__ error_flag,
-                                      int* __restrict__ result) {
+                                      int* __restrict__ result, const int* __restrict__ grows) {
     pdl_prologue();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i == 0 && result) result[n] = error_flag ? *error_flag : 0;
     if (i >= n) return;
-    positions[i] += 1;
-    seq_pos0[i] += 1;
-    seq_lens[i] += 1;
-    draw[i] += 1;
+    const int by = grows ? grows[i] : 1;      // 0 for a row that only fills the batch up: it stays at its first position
+    positions[i] += by;
+    seq_pos0[i] += by;
+    seq_lens[i] += by;
+    draw[i] += by;
     if (result) result[i] = tokens[i];
 }
 
 // `result` (may be null): n + 1 ints that receive the step's selected tokens and then the error flag, so
-// that one device -> host copy brings everything the host wants to see of a step.
+// that one device -> host copy brings everything the host wants to see of a step.  `grows` (may be null: every
+// row grows): 1 or 0 per row.
 MLB_EXPORT int mlb_decode_advance(int* positions, int* seq_pos0, int* seq_lens, long long* draw, int n,
-                                  const int* tokens, const int* error_flag, int* result, cudaStream_t stream) {
+                                  const int* tokens, const int* error_flag, int* result, const int* grows,
+                                  cudaStream_t stream) {
     if (n < 0) return fail(MLB_INVALID_ARGUMENT, "decode_advance: negative size");
     if (result && !tokens) return fail(MLB_INVALID_ARGUMENT, "decode_advance: a result buffer needs the tokens");
     if (n == 0) return MLB_OK;
     launch_kernel(decode_advance_kernel, (n + 127) / 128, 128, 0, stream, positions, seq_pos0, seq_lens, draw, n, tokens,
-                  error_flag, result);
+                  error_flag, result, grows);
     return check_launch("decode_advance");
 }
 

@@ -19,6 +19,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
+from ..cache.manager import RELEASED
 from ..kernels import ops
 from ..parts.base import StepContext
 from ..sampling.config import GenerationConfig
@@ -53,7 +54,7 @@ class DecodeGraph:
             return view
 
         self._s = {name: take(A) for name in ("tokens", "positions", "token_seq", "seq_pos0", "seq_lens", "slots",
-                                              "logit_rows", "temperature", "top_k")}
+                                              "logit_rows", "temperature", "top_k", "grows")}
         self._s["seq_starts"] = take(A + 1)
         self._s["seed"] = take(2 * A, align=2)
         self._s["draw"] = take(2 * A, align=2)
@@ -70,6 +71,8 @@ class DecodeGraph:
         d = lambda name: self.dev[self._s[name][0]:self._s[name][1]]
         self.temperature = d("temperature").view(torch.float32)
         self.top_k = d("top_k")
+        self.grows = d("grows")
+        self.active = 0                # rows that belong to requests; the others only fill the captured batch up
         self.seed = d("seed").view(torch.int64)
         self.draw = d("draw").view(torch.int64)
         self.ctx = StepContext(
@@ -92,25 +95,32 @@ class DecodeGraph:
 
     def load(self, requests: Sequence[Hashable], tokens: Sequence[int], lengths: Sequence[int],
              configs: Sequence[GenerationConfig], draws: Sequence[int]) -> None:
-        """Set the device state: request i feeds `tokens[i]` at position `lengths[i]`."""
+        """Set the device state: request i feeds `tokens[i]` at position `lengths[i]`.  Fewer requests than the
+        captured batch: the remaining rows feed token 0 at position 0 of a sequence of their own that lives in the
+        cache's spare page and slot and never grows; what they select is not read."""
         A = self.batch
-        if len(requests) != A:
-            raise StepError("a decode graph serves exactly the batch size it was built for")
+        n = len(requests)
+        if not 0 < n <= A:
+            raise StepError("a decode graph serves at most the batch size it was built for")
         self._wait_upload()
         cache = self.engine.cache
         self.requests = list(requests)
-        self._h("tokens")[:] = tokens
-        self._h("positions")[:] = lengths
+        self.active = n
+        pad = A - n
+        self._h("tokens")[:] = list(tokens) + [0] * pad
+        self._h("positions")[:] = list(lengths) + [0] * pad
         self._h("token_seq")[:] = np.arange(A)
-        self._h("seq_pos0")[:] = lengths
-        self._h("seq_lens")[:] = np.asarray(lengths) + 1
-        self._h("slots")[:] = [cache.slot(q) for q in requests]
+        self._h("seq_pos0")[:] = list(lengths) + [0] * pad
+        self._h("seq_lens")[:] = [x + 1 for x in lengths] + [1] * pad
+        self._h("slots")[:] = [cache.slot(q) for q in requests] + [cache.pad_slot] * pad
         self._h("logit_rows")[:] = np.arange(A)
         self._h("seq_starts")[:] = np.arange(A + 1)
-        self._h("temperature").view(np.float32)[:] = [0.0 if c.greedy else c.temperature for c in configs]
-        self._h("top_k")[:] = [c.top_k for c in configs]
-        self._h("seed").view(np.int64)[:] = [c.seed for c in configs]
-        self._h("draw").view(np.int64)[:] = list(draws)
+        self._h("grows")[:] = [1] * n + [0] * pad
+        self._h("temperature").view(np.float32)[:] = [0.0 if c.greedy else c.temperature for c in configs] + [0.0] * pad
+        self._h("top_k")[:] = [c.top_k for c in configs] + [0] * pad
+        self._h("seed").view(np.int64)[:] = [c.seed for c in configs] + [0] * pad
+        self._h("draw").view(np.int64)[:] = list(draws) + [0] * pad
+        self._table_state = {}
         self._fill_tables()
         self._tables_version = cache.tables_version
         self.dev.copy_(self.host, non_blocking=True)
@@ -140,6 +150,8 @@ class DecodeGraph:
             changed = True
             self._table_state[g] = state
             rows = cache.block_table(g, self.requests, self.widths[g])
+            filler = [cache.pad_page[g]] + [RELEASED] * (self.widths[g] - 1)
+            rows += [filler] * (self.batch - len(rows))
             arr[a:b] = np.asarray(rows, dtype=np.int32).reshape(-1)
         return changed
 
@@ -170,7 +182,7 @@ class DecodeGraph:
                 ops.copy_async(self.dev[a:b], self.host[a:b])     # checked once; from now on by raw pointers
             self._token_views = (self.host.numpy()[a:b], self.host[a:b].data_ptr(), self.dev[a:b].data_ptr(), 4 * (b - a))
         array, pinned, device, nbytes = self._token_views
-        array[:] = tokens
+        array[:len(tokens)] = tokens
         if self.host_io:
             return                                        # the replay's first node copies them
         ops.copy_raw(device, pinned, nbytes, True)
@@ -198,7 +210,7 @@ class DecodeGraph:
         logits = self.engine.model.forward(self.ctx, self.views)
         ops.sample_rows(logits, self.temperature, self.top_k, self.seed, self.draw, self.ctx.token_ids)
         ops.decode_advance(self.ctx.positions, self.ctx.seq_pos0, self.ctx.seq_lens, self.draw, self.ctx.token_ids,
-                           self.engine.error_flag, self.out_dev)
+                           self.engine.error_flag, self.out_dev, self.grows)
         if self.host_io:
             ops.copy_raw(self.out_host.data_ptr(), self.out_dev.data_ptr(), 4 * (self.batch + 1), False)
 
@@ -233,12 +245,25 @@ class DecodeGraph:
         if host[A]:
             self.engine.error_flag.zero_()
             raise StepError(device_error_text(host[A]))
-        return host[:A]
+        return host[:self.active]
+
+
+# Batch sizes that steps are captured for.  A step of fewer requests runs in the next size up, the rows in
+# between filled with sequences of one token that live in the cache's spare page: when requests end one by one
+# (the tail of a burst), every few steps would otherwise want a capture of their own, which costs as much as
+# several steps.  Beyond the list: multiples of 64.
+BATCH_SIZES = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+def captured_batch(requests: int, most: int) -> int:
+    """The captured batch size that serves `requests` requests when the cache has `most` request slots."""
+    size = next((b for b in BATCH_SIZES if b >= requests), -(-requests // 64) * 64)
+    return max(requests, min(size, most))
 
 
 class DecodeGraphPool:
-    """Captured decode steps by batch size and table width; built on first use.  At most `max_graphs` are
-    kept (each owns its activations and a captured graph): the one used longest ago goes first."""
+    """Captured decode steps by batch size (one of BATCH_SIZES) and table width; built on first use.  At most
+    `max_graphs` are kept (each owns its activations and a captured graph): the one used longest ago goes first."""
 
     def __init__(self, engine: Engine, max_graphs: int = 32, host_io: bool = False):
         self.engine, self.host_io = engine, bool(host_io)
@@ -253,12 +278,13 @@ class DecodeGraphPool:
             need = max(cache.blocks_for(cache.length(q) + 1 + headroom_tokens) for q in requests)
             need = max(need, max(len(cache.requests[q].tables[g]) for q in requests))
             widths[g] = max(8, _round_up_pow2(need))
-        key = (len(requests), tuple(sorted(widths.items())))
+        batch = captured_batch(len(requests), cache.max_requests)
+        key = (batch, tuple(sorted(widths.items())))
         graph = self.graphs.pop(key, None)
         if graph is None:
             while len(self.graphs) >= self.max_graphs:
                 del self.graphs[next(iter(self.graphs))]
-            graph = DecodeGraph(self.engine, len(requests), widths, host_io=self.host_io)
+            graph = DecodeGraph(self.engine, batch, widths, host_io=self.host_io)
         self.graphs[key] = graph                             # (re)inserted last: most recently used
         return graph
 

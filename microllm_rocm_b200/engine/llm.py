@@ -125,7 +125,7 @@ class LLM:
         if prepared and graph is not None and graph.requests == ids:
             # pages, tables and the captured plan were seen to while the last step ran
             graph.upload_tokens([e.request.token(e.begin) for e in plan.entries])
-            self.h2d_bytes += 4 * len(ids)
+            self.h2d_bytes += 4 * graph.batch
             self.prepared_steps += 1
         else:
             if graph is not None and graph.stale(longest):
@@ -146,13 +146,13 @@ class LLM:
             else:
                 graph.refresh_tables()
                 graph.upload_tokens([e.request.token(e.begin) for e in plan.entries])
-                self.h2d_bytes += 4 * len(ids)
+                self.h2d_bytes += 4 * graph.batch
         graph.replay()
         # what does not need the step's tokens happens while the GPU runs
         for e in plan.entries:
             self.engine.cache.commit(e.request.id, e.begin + 1)
         self._prepare_next(plan, graph)
-        self.d2h_bytes += 4 * (len(ids) + 1)
+        self.d2h_bytes += 4 * (graph.batch + 1)
         self.graph_steps += 1
         self.engine.steps_run += 1
         self.engine.tokens_run += len(ids)

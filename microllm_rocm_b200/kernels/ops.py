@@ -63,7 +63,7 @@ _SIGNATURES = {
         "mlb_cast_f32_bf16": [c_void_p, c_void_p, c_longlong, c_void_p],
         "mlb_copy_async": [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
         "mlb_stream_synchronize": [c_void_p],
-        "mlb_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        "mlb_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     },
     "gemm_f32.cu": {
         "mlb_gemm_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -222,10 +222,11 @@ def cast_f32_bf16(x: torch.Tensor, out: torch.Tensor) -> None:
 
 def decode_advance(positions: torch.Tensor, seq_pos0: torch.Tensor, seq_lens: torch.Tensor, draw: torch.Tensor,
                    tokens: Optional[torch.Tensor] = None, error_flag: Optional[torch.Tensor] = None,
-                   result: Optional[torch.Tensor] = None) -> None:
+                   result: Optional[torch.Tensor] = None, grows: Optional[torch.Tensor] = None) -> None:
     """Every sequence of a captured decode step has grown by one token: advance its position,
     extents and draw counter on the device.  With `result` ([n + 1] int32) the step's selected
-    `tokens` and the error flag are gathered there, for one device -> host copy."""
+    `tokens` and the error flag are gathered there, for one device -> host copy.  `grows` ([n] int32 of
+    1 and 0): rows with 0 stay where they are (rows that only fill a captured batch up)."""
     n = positions.shape[0]
     _need(positions, "positions", torch.int32, 1); _need(seq_pos0, "seq_pos0", torch.int32, 1)
     _need(seq_lens, "seq_lens", torch.int32, 1); _need(draw, "draw", torch.int64, 1)
@@ -235,9 +236,13 @@ def decode_advance(positions: torch.Tensor, seq_pos0: torch.Tensor, seq_lens: to
         _need(result, "result", torch.int32, 1); _need(tokens, "tokens", torch.int32, 1)
         if result.shape[0] != n + 1 or tokens.shape[0] != n:
             raise KernelError("decode_advance: result holds one int per sequence and one more for the error flag")
+    if grows is not None:
+        _need(grows, "grows", torch.int32, 1)
+        if grows.shape[0] != n:
+            raise KernelError("decode_advance: one growth per sequence")
     L = lib("basic.cu")
     build.check(L, L.mlb_decode_advance(positions.data_ptr(), seq_pos0.data_ptr(), seq_lens.data_ptr(), draw.data_ptr(),
-                                        n, _ptr(tokens), _ptr(error_flag), _ptr(result), _stream()))
+                                        n, _ptr(tokens), _ptr(error_flag), _ptr(result), _ptr(grows), _stream()))
 
 
 def copy_async(dst: torch.Tensor, src: torch.Tensor) -> None:

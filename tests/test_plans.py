@@ -79,3 +79,11 @@ def test_a_frozen_decode_plan_is_recognised_as_stale():
     assert attention.decode_plan_stale(ctx, 2048)
     attention.forget_plans(ctx)
     assert key not in ctx.extras and len(ctx.extras) == 2 and not attention.decode_plan_stale(ctx, 2048)
+
+
+def test_captured_batch_sizes():
+    from microllm_rocm_b200.engine.decode_graph import BATCH_SIZES, captured_batch
+    assert [captured_batch(n, 256) for n in (1, 2, 3, 5, 8, 9, 13, 33, 64, 65, 200, 257, 300)] == \
+        [1, 2, 4, 8, 8, 12, 16, 48, 64, 96, 256, 257, 300]
+    assert captured_batch(5, 6) == 6 and captured_batch(6, 6) == 6 and captured_batch(3, 3) == 3      # never more rows than request slots... but never fewer than the requests
+    assert list(BATCH_SIZES) == sorted(BATCH_SIZES)
