@@ -4,12 +4,12 @@ fp32: always the plain kernel (fixed summation order, bit-stable across ways of 
 bf16: the tensor-core kernels when the head size is a multiple of 32 and the page size a
 multiple of 16; the plain kernel otherwise.  A step whose sequences all bring one token runs
 the decode shape of `attention_mma.cu` (keys split over a thread-block cluster that merges
-through distributed shared memory).  In any other step every sequence that brings at least
-`TC_MIN_NEW_TOKENS` tokens goes to the tcgen05 kernel (`attention_tc.cu`: 128 query rows per
-CTA, scores and output in tensor memory; head sizes 64 and 128), every sequence that brings
-exactly one token (a decoded token beside prompt portions) to the decode shape again, through a
-list of those sequences, and the short portions that remain to the prefill shape of
-`attention_mma.cu` with its 16-row tiles.  The launches write disjoint rows of the output.
+through distributed shared memory).  In any other step every sequence that brings two tokens or
+more goes to the tcgen05 kernel (`attention_tc.cu`: 128 query rows per CTA, scores and output in
+tensor memory; head sizes 64 and 128), every sequence that brings exactly one token (a decoded
+token beside prompt portions) to the decode shape again, through a list of those sequences.  Head
+sizes the tcgen05 kernel does not take go to the prefill shape of `attention_mma.cu` with its
+16-row tiles.  The launches write disjoint rows of the output.
 """
 from __future__ import annotations
 
@@ -35,7 +35,9 @@ RING_MIN_KEYS_PER_CTA = 1024        # measured: 16 stages of 64 keys per CTA and
 TC_HEAD_DIMS = (64, 128)
 TC_KEYS_PER_TILE = 128
 TC_ROWS_PER_TILE = 128
-TC_MIN_NEW_TOKENS = 48              # below this the 16-row tiles of the mma.sync kernel waste less
+# Measured with one sequence of 2 to 47 new tokens at contexts of 64 to 4,096 keys (heads 12/2 and 28/4 of 128): the
+# tcgen05 kernel takes 7.4 to 48 us where the mma.sync kernel's 16-row tiles take 8.4 to 230: it wins everywhere.
+TC_MIN_NEW_TOKENS = 2
 
 ops.register_signatures("attention_tc.cu", {
     "mlb_fa_tc_supported": [c_int, c_float],
