@@ -31,6 +31,11 @@ WIDE_CLUSTER_CTAS = 48              # measured: one sequence of two kv heads gai
 # never.  Tests set it to run both kernels on the same inputs.
 DECODE_RING = None
 RING_MIN_KEYS_PER_CTA = 1024        # measured: 16 stages of 64 keys per CTA and the ring wins by 7-8 %, 8 stages and it loses 12 %
+# Measured in whole decode steps at context 8,192 (8 layers of the 14B / 7B shapes): with 8 tokens the ring costs
+# 2.64 against 2.01 ms / 2.08 against 1.50 ms although the kernel alone is 8 % faster; with 16 tokens it wins, 2.03
+# against 2.42 / 1.35 against 1.52 ms.  Up to 8 tokens the kernels around the attention are the few-token products,
+# whose CTAs take 160 KB of shared memory: beside two ring CTAs (113 KB each) they cannot start early.
+RING_MIN_TOKENS = 9
 
 TC_HEAD_DIMS = (64, 128)
 TC_KEYS_PER_TILE = 128
@@ -87,11 +92,15 @@ def decode_splits(items: int, max_seq_len: int, sms: int = DEFAULT_SM_COUNT) -> 
     return 1
 
 
-def decode_ring_pays(items: int, splits: int, max_seq_len: int, sms: int = DEFAULT_SM_COUNT) -> bool:
+def decode_ring_pays(items: int, splits: int, max_seq_len: int, sms: int = DEFAULT_SM_COUNT,
+                     tokens: int = RING_MIN_TOKENS) -> bool:
     """Whether a decode step should bring its keys through the shared-memory ring (TMA, a copying warp) instead of
-    straight into registers: when every multiprocessor has a CTA and each CTA streams a thousand keys or more.
-    Below that the ring's set-up and its extra hand-offs cost more than the deeper prefetch brings."""
-    return items * splits >= sms and max_seq_len // max(1, splits) >= RING_MIN_KEYS_PER_CTA and splits <= 8
+    straight into registers: when every multiprocessor has a CTA, each CTA streams a thousand keys or more, and
+    the step holds more tokens than the few-token products take.  Below that the ring's set-up and its extra
+    hand-offs cost more than the deeper prefetch brings, or its shared memory keeps the next kernel from
+    starting early."""
+    return (items * splits >= sms and max_seq_len // max(1, splits) >= RING_MIN_KEYS_PER_CTA and splits <= 8
+            and tokens >= RING_MIN_TOKENS)
 
 
 def decode_plan_stale(ctx, max_seq_len: int, sms: int = DEFAULT_SM_COUNT) -> bool:
@@ -101,7 +110,7 @@ def decode_plan_stale(ctx, max_seq_len: int, sms: int = DEFAULT_SM_COUNT) -> boo
     for key, plan in ctx.extras.items():
         if isinstance(key, tuple) and key and key[0] == "attention_mma" and plan[2] == 1:
             splits = decode_splits(plan[1] * key[2], max_seq_len, sms)
-            if splits != plan[3] or (len(plan) > 9 and decode_ring_pays(plan[1] * key[2], splits, max_seq_len, sms) != plan[9]):
+            if splits != plan[3] or (len(plan) > 9 and decode_ring_pays(plan[1] * key[2], splits, max_seq_len, sms, ctx.num_tokens) != plan[9]):
                 return True
     return False
 
@@ -143,13 +152,13 @@ def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
     work_dev = torch.tensor(work, dtype=torch.int32).reshape(-1).to(device, non_blocking=True)
     tc_dev = torch.tensor([(a, t) for _, a, t in tc_work], dtype=torch.int32).reshape(-1).to(device, non_blocking=True)
     splits = decode_splits(len(work) * num_kv_heads, ctx.max_seq_len, sms) if decode else 1
-    ring = decode and decode_ring_pays(len(work) * num_kv_heads, splits, ctx.max_seq_len, sms)
+    ring = decode and decode_ring_pays(len(work) * num_kv_heads, splits, ctx.max_seq_len, sms, ctx.num_tokens)
     listed_dev, listed_splits = None, 1
     if listed:
         listed_dev = torch.tensor(listed, dtype=torch.int32).to(device, non_blocking=True)
         longest = max(ctx.seq_pos0_host[a] for a in listed) + 1
         listed_splits = decode_splits(len(listed) * tiles_per_token * num_kv_heads, longest, sms)
-        ring = decode_ring_pays(len(listed) * tiles_per_token * num_kv_heads, listed_splits, longest, sms)
+        ring = decode_ring_pays(len(listed) * tiles_per_token * num_kv_heads, listed_splits, longest, sms, ctx.num_tokens)
     plan = (work_dev, len(work), 1 if decode else 0, splits, tc_dev, len(tc_work), listed_dev, len(listed) * tiles_per_token,
             listed_splits, ring)
     ctx.extras[key] = plan
