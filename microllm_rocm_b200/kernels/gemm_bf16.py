@@ -114,9 +114,32 @@ GEMV_SILU_MAX_TOKENS = 8            # beyond one 8-token column block the fused 
 GEMV_FUSED_MAX_K = 6144             # the activations of 16 tokens over the whole K must fit shared memory
 
 
+# The mma.sync kernels stage the step's activations over their K range in shared memory (16 token rows).  Up to
+# this many elements of K per CTA (96 KB) two of their CTAs share an SM, so that the next kernel's CTAs become
+# resident, and fetch their first weights, while this kernel still runs; a wider product takes the SM for itself
+# and loses that.  Then the tcgen05 streaming kernel, whose TMA-filled ring keeps more of the weight stream in
+# flight than registers can, is the faster one at ANY token count.  Measured in whole decode steps of 1 and 8
+# tokens: every product of the 7B and 14B shapes (K = 3,584 / 5,120: 112 / 160 KB staged) gains on the streaming
+# kernel (8 layers: 1.36 -> 1.06 ms and 1.72 -> 1.45 ms), every product of the 1.5B shape (K = 1,536, and 2,987 per
+# CTA for the down projection) loses there (1.235 -> 1.374 ms for all of them, 28 layers).
+GEMV_MAX_STAGED_K = 3072
+
+
+def gemv_staged_k(n: int, k: int, sms: int = DEFAULT_SM_COUNT) -> int:
+    """Elements of K whose activations one CTA of the mma.sync kernels keeps in shared memory."""
+    if k <= GEMV_FUSED_MAX_K:
+        return k
+    plan = gemv_split_plan(n, k, sms)
+    return plan[1] if plan is not None else gemv_splits(n, k, sms)[1]
+
+
 def gemv_preferred(x: torch.Tensor, weight: torch.Tensor) -> bool:
-    """The weight-streaming kernels can take this product and are the faster way for it."""
-    return x.shape[0] <= GEMV_ROUTE_MAX_TOKENS and gemv_supported(x, weight)
+    """The mma.sync weight-streaming kernels can take this product and are the faster way for it."""
+    if not (x.shape[0] <= GEMV_ROUTE_MAX_TOKENS and gemv_supported(x, weight)):
+        return False
+    if gemv_staged_k(weight.shape[0], x.shape[1], sm_count(x.device)) <= GEMV_MAX_STAGED_K:
+        return True
+    return not stream_supported(x, weight)
 
 
 def gemv_fused_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -220,8 +243,10 @@ def stream_preferred(x: torch.Tensor, weight: torch.Tensor) -> bool:
     tokens; beyond that only the large ones, whose time is the weight stream (a small product is a few dependent
     round trips long, and there the partial results of its K split cost more than the library's way)."""
     m = x.shape[0]
-    if not (GEMV_ROUTE_MAX_TOKENS < m <= STREAM_MAX_TOKENS and stream_supported(x, weight)):
+    if not (m <= STREAM_MAX_TOKENS and stream_supported(x, weight)):
         return False
+    if m <= GEMV_ROUTE_MAX_TOKENS:
+        return not gemv_preferred(x, weight)
     return m <= STREAM_SMALL_PRODUCT_MAX_TOKENS or weight.numel() * weight.element_size() >= STREAM_SMALL_PRODUCT_BYTES
 
 

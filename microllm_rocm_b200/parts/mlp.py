@@ -54,7 +54,8 @@ class SwiGLU(FeedForward):
         # boundary -- the reference's policy for its bf16 feed-forward (src/ops/optimized.cpp:676-683).
         act = scratch(ctx, "swiglu.act", (x.shape[0], self.inter), self.rt.dtype, x.device)
         flag = ctx.error_flag if ctx is not None else None      # one flag covers the step: whoever reads it sees every kernel's
-        if x.dtype == torch.bfloat16 and x.shape[0] <= gemm_bf16.GEMV_SILU_MAX_TOKENS and gemm_bf16.gemv_fused_supported(x, self.w_gate_up):
+        if (x.dtype == torch.bfloat16 and x.shape[0] <= gemm_bf16.GEMV_SILU_MAX_TOKENS and gemm_bf16.gemv_preferred(x, self.w_gate_up)
+                and gemm_bf16.gemv_fused_supported(x, self.w_gate_up)):
             # a few tokens: one weight-streaming kernel, the activation is its epilogue
             gemm_bf16.gemv_silu_mul(x, self.w_gate_up, act)
         elif x.dtype == torch.bfloat16 and gemm_bf16.gemv_preferred(x, self.w_gate_up):
