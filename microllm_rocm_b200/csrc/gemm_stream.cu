@@ -278,7 +278,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const uint32_t buf = local & 1, use = local >> 1;
             const int tile = item % p.n_tiles, split = item / p.n_tiles;
             // ONE thread waits for the accumulator and tells the other 127: the four warps go on, or give up,
-            // together (they meet at barriers below).  Two flags in turn: the next item's verdict is written only
+            // together (they meet at barriers below).  Two flags in turn: the next item's answer is written only
             // after everybody has read this one's and passed the following barrier.
             if (warp == 2 && lane == 0) epilogue_ok_s[local & 1] = mbar_wait(smem_u32(&acc_full[buf]), use & 1, p.error_flag, 54) ? 1 : 0;
             epilogue_sync();
