@@ -227,33 +227,73 @@ FAMILIES = (("attention", ("fa_", "paged_attention")), ("products", ("gemv", "ge
             ("norm_rope_act", ("rmsnorm", "rope", "silu", "add_inplace", "embed")), ("sampling", ("argmax", "sample", "decode_advance")))
 
 
+def _kernel_records(session, replays: int = 3):
+    """(name, start us, end us) of every kernel of `replays` decode steps, from the device's kernel records (CUPTI
+    through the tensor framework's profiler), in order of start."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(replays):
+            session.step()
+        torch.cuda.synchronize()
+    records = []
+    for event in prof.events():
+        if event.device_type != torch.autograd.DeviceType.CUDA:
+            continue
+        name = event.name
+        if "memcpy" in name.lower() or "memset" in name.lower():
+            continue
+        records.append((name, float(event.time_range.start), float(event.time_range.end)))
+    records.sort(key=lambda r: r[1])
+    return records
+
+
+def _exposed(records):
+    """Kernels of a captured step start early and overlap: what a kernel adds to the step is the time from the
+    latest end of everything before it to its own end.  Yields (name, duration, exposed); the exposed times of a
+    step add up to its span."""
+    frontier = records[0][1] if records else 0.0
+    for name, start, end in records:
+        yield name, end - start, max(0.0, end - max(frontier, min(start, frontier)))
+        frontier = max(frontier, end)
+
+
 def kernel_families(session):
-    """Share of a decode step's kernel time by family, from the device's kernel records (CUPTI through the
-    tensor framework's profiler) of three replays.  Kernels of a step overlap at their edges, so the shares are of
-    the SUM of kernel durations, given beside that sum; None when the records cannot be had."""
+    """Share of a decode step's time by kernel family.  A kernel's share is its EXPOSED time (see _exposed), so the
+    shares add up to the step; the plain sum of kernel durations is given beside it (it counts overlaps twice).
+    None when the kernel records cannot be had."""
     try:
-        import torch
-        from torch.profiler import ProfilerActivity, profile
-        with profile(activities=[ProfilerActivity.CUDA]) as prof:
-            for _ in range(3):
-                session.step()
-            torch.cuda.synchronize()
-        totals, total = {}, 0.0
-        for event in prof.key_averages():
-            us = float(getattr(event, "device_time_total", 0.0) or getattr(event, "cuda_time_total", 0.0))
-            if us <= 0:
-                continue
-            name = event.key.lower()
-            family = next((f for f, marks in FAMILIES if any(m in name for m in marks)), "other")
-            totals[family] = totals.get(family, 0.0) + us
-            total += us
+        records = _kernel_records(session, 3)
+        totals, total, durations = {}, 0.0, 0.0
+        for name, duration, exposed in _exposed(records):
+            family = next((f for f, marks in FAMILIES if any(m in name.lower() for m in marks)), "other")
+            totals[family] = totals.get(family, 0.0) + exposed
+            total += exposed
+            durations += duration
         if total <= 0:
             return None
         out = {f: round(v / total, 4) for f, v in sorted(totals.items())}
-        out["kernel_ms_per_step"] = round(total / 3 / 1e3, 4)
+        out["step_ms_by_records"] = round(total / 3 / 1e3, 4)
+        out["kernel_ms_per_step"] = round(durations / 3 / 1e3, 4)
         return out
     except Exception:
         return None
+
+
+def step_timeline(session):
+    """Per kernel name of one decode step: launches, duration and exposed time in microseconds."""
+    records = _kernel_records(session, 3)
+    per_step = len(records) // 3
+    records = records[per_step:2 * per_step]
+    rows = {}
+    for name, duration, exposed in _exposed(records):
+        short = name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0].split("<")[0]
+        row = rows.setdefault(short, [0, 0.0, 0.0])
+        row[0] += 1
+        row[1] += duration
+        row[2] += exposed
+    span = records[-1][2] - records[0][1] if records else 0.0
+    return span, sorted(rows.items(), key=lambda kv: -kv[1][2])
 
 
 def run_mixed(args):
@@ -366,6 +406,19 @@ def run_ours(args):
         engine.cache.release("pf")
         return start.elapsed_time(end)
 
+    if args.only == "timeline":
+        # one captured decode step kernel by kernel: launches, summed durations, and what each adds to the step
+        session = DecodeSession(engine, prompts(args.batch), args.warmup + 8)
+        for _ in range(args.warmup):
+            session.step()
+        torch.cuda.synchronize()
+        span, rows = step_timeline(session)
+        session.close()
+        print(f"decode step, batch {args.batch}, {layers} layers of {args.model}, context {prompt_len}: {span:.1f} us by the kernel records")
+        print(f"{'kernel':40s} {'launches':>8s} {'duration us':>12s} {'exposed us':>11s} {'share':>6s}")
+        for name, (count, duration, exposed) in rows:
+            print(f"{name[:40]:40s} {count:8d} {duration:12.1f} {exposed:11.1f} {exposed / span:6.1%}")
+        return 0
     if args.only == "decode":
         prefill_ms = float("nan")
     else:
@@ -488,7 +541,7 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline"],
                     help="run just one timed part and print a short line (for profiler captures)")
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed"])
     ap.add_argument("--requests", type=int, default=64, help="mixed: how many requests")
