@@ -157,7 +157,11 @@ class LLM:
         self.engine.steps_run += 1
         self.engine.tokens_run += len(ids)
         t0 = time.perf_counter()
-        tokens = graph.read_tokens()
+        try:
+            tokens = graph.read_tokens()
+        except StepError:
+            self._graph = self._prepared = None          # nothing prepared on top of a failed step is to be trusted
+            raise
         self.wait_s += time.perf_counter() - t0
         finished = self.scheduler.update(plan, tokens)
         if finished:
