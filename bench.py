@@ -324,13 +324,23 @@ def run_mixed(args):
     llm = LLM(engine, max_tokens_per_step=args.chunk, max_seqs=args.requests)
     config = GenerationConfig(max_new_tokens=args.new_tokens, temperature=0.0)
 
+    kinds = {}
+
     def run_once():
         ids = [llm.submit(p, config) for p in prompts]
         launches0, steps, wait0 = LaunchCounter.own, 0, llm.wait_s
+        kinds.clear()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         while llm.has_work():
+            graph_steps, captures, t1 = llm.graph_steps, llm.graphs.captures if llm.graphs else 0, time.perf_counter()
             llm.step()
+            # a step ends with the read of its tokens, so its wall time is its own
+            kind = ("capturing" if llm.graphs and llm.graphs.captures > captures else
+                    "captured" if llm.graph_steps > graph_steps else "mixed")
+            entry = kinds.setdefault(kind, [0, 0.0])
+            entry[0] += 1
+            entry[1] += time.perf_counter() - t1
             steps += 1
         torch.cuda.synchronize()
         wall = time.perf_counter() - t0
@@ -364,7 +374,10 @@ def run_mixed(args):
         "wall_s": wall, "host_waits_for_gpu_frac": waited / wall, "gpu_utilization_sampled": sampler.utilization(),
         "gpu_launches": launches,
         "preemptions": metrics.get("preemptions", 0) - metrics0.get("preemptions", 0),
-        "graph_steps": llm.graph_steps, "clocks": sampler.summary(),
+        # steps that hold prompt portions (issued kernel by kernel), steps of decoded tokens only (a captured
+        # step replayed) and steps that had to capture one first: how many, and their wall time in ms
+        "step_kinds": {k: {"steps": n, "ms": round(t * 1e3, 1)} for k, (n, t) in sorted(kinds.items())},
+        "clocks": sampler.summary(),
     }
     print(json.dumps(out))
     return 0
