@@ -331,6 +331,52 @@ MLB_EXPORT int mlb_copy_async(void* dst, const void* src, long long bytes, int t
     return MLB_OK;
 }
 
+// ------------------------------------------------------------------ a second stream for independent work of a step
+// Two kernels of a step that do not depend on each other (the attention of the prompt portions and the attention
+// of the decoded tokens beside them) may run side by side: the first goes to a second stream that starts where
+// the main stream stands (fork) and the main stream waits for it before it goes on (join).  One stream and one
+// event of each kind per device, made at first use.
+namespace {
+struct SideStream { cudaStream_t stream; cudaEvent_t forked, joined; bool made; };
+SideStream side_streams[MAX_DEVICES] = {};
+
+SideStream* side_stream_of_device() {
+    SideStream& s = side_streams[device_index()];
+    if (!s.made) {
+        if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+        if (cudaEventCreateWithFlags(&s.forked, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        if (cudaEventCreateWithFlags(&s.joined, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        s.made = true;
+    }
+    return &s;
+}
+}  // namespace
+
+MLB_EXPORT void* mlb_side_stream() {
+    SideStream* s = side_stream_of_device();
+    return s ? (void*)s->stream : nullptr;
+}
+
+// the side stream continues from where `stream` stands now
+MLB_EXPORT int mlb_stream_fork(cudaStream_t side, cudaStream_t stream) {
+    SideStream* s = side_stream_of_device();
+    if (!s || side != s->stream) return fail(MLB_INVALID_ARGUMENT, "stream_fork: not this device's side stream");
+    cudaError_t e = cudaEventRecord(s->forked, stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(side, s->forked, 0);
+    if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "stream_fork: %s", cudaGetErrorString(e));
+    return MLB_OK;
+}
+
+// `stream` goes on only when everything queued on the side stream so far has run
+MLB_EXPORT int mlb_stream_join(cudaStream_t side, cudaStream_t stream) {
+    SideStream* s = side_stream_of_device();
+    if (!s || side != s->stream) return fail(MLB_INVALID_ARGUMENT, "stream_join: not this device's side stream");
+    cudaError_t e = cudaEventRecord(s->joined, side);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(stream, s->joined, 0);
+    if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "stream_join: %s", cudaGetErrorString(e));
+    return MLB_OK;
+}
+
 MLB_EXPORT int mlb_stream_synchronize(cudaStream_t stream) {
     cudaError_t e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return fail(MLB_CUDA_ERROR, "stream_synchronize: %s", cudaGetErrorString(e));

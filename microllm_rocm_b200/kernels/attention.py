@@ -37,6 +37,7 @@ RING_MIN_KEYS_PER_CTA = 1024        # measured: 16 stages of 64 keys per CTA and
 # whose CTAs take 160 KB of shared memory: beside two ring CTAs (113 KB each) they cannot start early.
 RING_MIN_TOKENS = 9
 
+CONCURRENT_ATTENTION = True         # the two attention launches of a mixed step side by side (tests may switch it off)
 TC_HEAD_DIMS = (64, 128)
 TC_KEYS_PER_TILE = 128
 TC_ROWS_PER_TILE = 128
@@ -178,13 +179,22 @@ def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx
     work, num_work, mode, splits, tc_work, num_tc, listed, num_listed, listed_splits, ring = _plan(
         ctx, num_heads // num_kv_heads, num_kv_heads, use_tc)
     ring_bits = 4 if (ring if DECODE_RING is None else DECODE_RING) else 8
+    side = None
     if num_tc:
+        # Prompt portions and the decoded tokens beside them are different sequences: their two launches write
+        # disjoint rows and read nothing of each other's.  The prompt portions' kernel goes to the device's second
+        # stream, so that both run at once (it leaves a quarter of the SMs idle at the benchmark's sizes).
+        stream = ops._stream()
+        if (num_work or num_listed) and CONCURRENT_ATTENTION:
+            side = ops.side_stream()
+            ops.fork(side)
+            stream = side
         T = ops.lib("attention_tc.cu", {"HEAD_DIM": head_dim})
         build.check(T, T.mlb_paged_attention_tc(
             q.data_ptr(), q.stride(0), pages.data_ptr(), out.data_ptr(), out.stride(0), q.shape[0], ctx.seq_starts.data_ptr(),
             ctx.seq_pos0.data_ptr(), block_table.data_ptr(), tc_work.data_ptr(), num_tc, block_table.shape[1],
             pages.shape[0], page_size, num_heads, num_kv_heads, int(window or 0), float(scale), ops._ptr(ctx.error_flag),
-            ops._stream()))
+            stream))
     if not num_work and not num_listed:
         return
     L = ops.lib("attention_mma.cu", {"HEAD_DIM": head_dim})
@@ -194,9 +204,10 @@ def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx
             q.data_ptr(), pages.data_ptr(), out.data_ptr(), ctx.seq_starts.data_ptr(), ctx.seq_pos0.data_ptr(), block_table.data_ptr(),
             listed.data_ptr(), num_listed, block_table.shape[1], pages.shape[0], page_size, num_heads, num_kv_heads,
             int(window or 0), float(scale), 2 + ring_bits, listed_splits, ops._ptr(ctx.error_flag), ops._stream()))
-    if not num_work:
-        return
-    build.check(L, L.mlb_paged_attention_mma(
-        q.data_ptr(), pages.data_ptr(), out.data_ptr(), ctx.seq_starts.data_ptr(), ctx.seq_pos0.data_ptr(), block_table.data_ptr(), work.data_ptr(), num_work,
-        block_table.shape[1], pages.shape[0], page_size, num_heads, num_kv_heads, int(window or 0), float(scale),
-        mode + (ring_bits if mode else 0), splits, ops._ptr(ctx.error_flag), ops._stream()))
+    if num_work:
+        build.check(L, L.mlb_paged_attention_mma(
+            q.data_ptr(), pages.data_ptr(), out.data_ptr(), ctx.seq_starts.data_ptr(), ctx.seq_pos0.data_ptr(), block_table.data_ptr(), work.data_ptr(), num_work,
+            block_table.shape[1], pages.shape[0], page_size, num_heads, num_kv_heads, int(window or 0), float(scale),
+            mode + (ring_bits if mode else 0), splits, ops._ptr(ctx.error_flag), ops._stream()))
+    if side is not None:
+        ops.join(side)

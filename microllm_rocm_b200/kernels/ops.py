@@ -58,6 +58,8 @@ _SIGNATURES = {
         "mlb_embed_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "mlb_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
         "mlb_add_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+        "mlb_stream_fork": [c_void_p, c_void_p],
+        "mlb_stream_join": [c_void_p, c_void_p],
         "mlb_add_inplace": [c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p],
         "mlb_silu_mul": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
         "mlb_cast_f32_bf16": [c_void_p, c_void_p, c_longlong, c_void_p],
@@ -268,6 +270,37 @@ def copy_raw(dst: int, src: int, nbytes: int, to_device: bool) -> None:
     status = L.mlb_copy_async(dst, src, nbytes, 1 if to_device else 0, _stream())
     if status != 0:
         build.check(L, status)
+
+
+_side_streams = {}
+
+
+def side_stream() -> int:
+    """This device's second stream, for work of a step that is independent of what the main stream does meanwhile
+    (see fork / join)."""
+    device = _current_device() if _current_device is not None else torch.cuda.current_device()
+    handle = _side_streams.get(device)
+    if handle is None:
+        L = lib("basic.cu")
+        L.mlb_side_stream.restype = c_void_p
+        L.mlb_side_stream.argtypes = []
+        handle = L.mlb_side_stream()
+        if not handle:
+            raise KernelError("the device's second stream could not be made")
+        _side_streams[device] = handle
+    return handle
+
+
+def fork(side: int) -> None:
+    """The side stream continues from where the current stream stands."""
+    L = lib("basic.cu")
+    build.check(L, L.mlb_stream_fork(side, _stream()))
+
+
+def join(side: int) -> None:
+    """The current stream waits for everything queued on the side stream."""
+    L = lib("basic.cu")
+    build.check(L, L.mlb_stream_join(side, _stream()))
 
 
 def stream_synchronize() -> None:
