@@ -331,6 +331,28 @@ MLB_EXPORT int mlb_copy_async(void* dst, const void* src, long long bytes, int t
     return MLB_OK;
 }
 
+// ------------------------------------------------------------------ tokens from one step's selection into the next step's input
+// dst[dst_index[i]] = src[src_index[i]]: the tokens a step selected go where the next step, whose metadata the
+// host packed before it knew them, reads its input tokens.  Indices outside either array are skipped.
+__global__ void scatter_int_kernel(int* __restrict__ dst, int dst_len, const int* __restrict__ dst_index,
+                                   const int* __restrict__ src, int src_len, const int* __restrict__ src_index, int n) {
+    pdl_prologue();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int to = dst_index[i], from = src_index[i];
+    if (to < 0 || to >= dst_len || from < 0 || from >= src_len) return;
+    dst[to] = src[from];
+}
+
+MLB_EXPORT int mlb_scatter_int(int* dst, int dst_len, const int* dst_index, const int* src, int src_len,
+                               const int* src_index, int n, cudaStream_t stream) {
+    if (n < 0 || dst_len < 0 || src_len < 0) return fail(MLB_INVALID_ARGUMENT, "scatter_int: negative size");
+    if (n == 0) return MLB_OK;
+    if (!dst || !dst_index || !src || !src_index) return fail(MLB_INVALID_ARGUMENT, "scatter_int: an array is missing");
+    launch_kernel(scatter_int_kernel, (n + 127) / 128, 128, 0, stream, dst, dst_len, dst_index, src, src_len, src_index, n);
+    return check_launch("scatter_int");
+}
+
 // ------------------------------------------------------------------ a second stream for independent work of a step
 // Two kernels of a step that do not depend on each other (the attention of the prompt portions and the attention
 // of the decoded tokens beside them) may run side by side: the first goes to a second stream that starts where

@@ -18,8 +18,17 @@ from ..sampling.config import GenerationConfig
 from ..sampling.sampler import Sampler
 from .decode_graph import DecodeGraph, DecodeGraphPool, graph_capable
 from .loading import DEFAULT_PAGE_SIZE, load_engine
-from .scheduler import Request, Scheduler, StepPlan
+from .scheduler import PENDING, Request, Scheduler, StepPlan
 from .step import Engine, StepEntry, StepError, device_error_text
+
+
+class _Issued:
+    """A step that was handed to the GPU and whose selected tokens have not been read yet: `packed` holds them on
+    the device (and the error flag behind them), `host` is the pinned copy that `copied` says has arrived."""
+    __slots__ = ("plan", "packed", "wanting", "host", "copied")
+
+    def __init__(self, plan: StepPlan, packed: torch.Tensor, wanting: List[Request], host: torch.Tensor, copied):
+        self.plan, self.packed, self.wanting, self.host, self.copied = plan, packed, wanting, host, copied
 
 
 class LLM:
@@ -49,6 +58,13 @@ class LLM:
         # happened in between that the scheduler would have decided differently.
         self._prepared: Optional[StepPlan] = None
         self.prepared_steps = 0
+        # Steps issued kernel by kernel: the one whose tokens are not read yet (see step())
+        self._inflight: Optional[_Issued] = None
+        self.lookahead = True
+        self.lookahead_steps = 0
+        # pinned landing places for the tokens of steps on their way (two are in use at most)
+        self._results = [torch.empty(self.scheduler.max_seqs + 1, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        self._results_next = 0
 
     # ------------------------------------------------------------------ request interface
     def submit(self, prompt: Sequence[int], config: Optional[GenerationConfig] = None) -> int:
@@ -62,42 +78,110 @@ class LLM:
         return self.scheduler.requests[request_id]
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
     def step(self) -> List[Request]:
         """One scheduler decision, one model step, one token selection.  Returns the requests
-        that finished in it."""
-        prepared, self._prepared = self._prepared, None
-        if (prepared is not None and not self.scheduler.waiting and len(prepared.entries) == len(self.scheduler.running)
-                and all(e.request.computed == e.begin and not e.request.finished for e in prepared.entries)):
-            return self._graph_step(prepared, prepared=True)
-        plan = self.scheduler.schedule()
-        if not plan.entries:
-            if self.scheduler.has_work() and not plan.preempted:
-                raise StepError("the scheduler has work but could plan nothing: the page pool is too small")
-            return []
-        if self.graphs is not None and not plan.preempted and all(
-                e.count == 1 and e.wants_logits and e.begin >= len(e.request.prompt) for e in plan.entries):
-            return self._graph_step(plan)
-        self._graph = None
-        entries = [StepEntry(e.request.id, e.request.tokens(e.begin, e.begin + e.count),
-                             [e.count - 1] if e.wants_logits else []) for e in plan.entries]
-        logits = self.engine.step(entries)
+        that finished in it.
+
+        Steps that hold prompt portions are issued kernel by kernel, and the host has work to do around them
+        (update, schedule, pack the metadata, issue the first layers).  So that the GPU does not idle meanwhile,
+        the NEXT such step is planned and issued while this one runs, before this one's tokens are read: the
+        requests that decode get a stand-in for their input token, and a small kernel behind this step's token
+        selection puts the selected tokens in their places (Engine.step's `patch`).  What this call returns is
+        still this step's outcome; a request that ends on a stop token has one void row in the step issued ahead."""
+        if self._inflight is None:
+            prepared, self._prepared = self._prepared, None
+            if (prepared is not None and not self.scheduler.waiting and len(prepared.entries) == len(self.scheduler.running)
+                    and all(e.request.computed == e.begin and not e.request.finished for e in prepared.entries)):
+                return self._graph_step(prepared, prepared=True)
+            plan = self.scheduler.schedule()
+            if not plan.entries:
+                if self.scheduler.has_work() and not plan.preempted:
+                    raise StepError("the scheduler has work but could plan nothing: the page pool is too small")
+                return []
+            if self._captured(plan):
+                return self._graph_step(plan)
+            self._graph = None
+            self._inflight = self._issue(plan, None)
+        current, self._inflight = self._inflight, None
+        ahead = self._issue_ahead(current)
+        try:
+            finished = self._collect(current)
+        except Exception:
+            self._inflight = None                 # nothing issued on top of a failed step is to be trusted
+            raise
+        self._inflight = ahead
+        return finished
+
+    def _captured(self, plan: StepPlan) -> bool:
+        """Every request brings its one last-selected token and steps are captured: the plan is a replay."""
+        return self.graphs is not None and not plan.preempted and all(
+            e.count == 1 and e.wants_logits and e.begin >= len(e.request.prompt) for e in plan.entries)
+
+    def _issue(self, plan: StepPlan, before) -> "_Issued":
+        """Hand `plan` to the step function and select its tokens, all asynchronously.  `before`: the step issued
+        just before it whose tokens are not read yet; input tokens that it selects are patched in on the device."""
+        entries, pairs = [], []
+        place = 0
+        rows_before = {id(r): i for i, r in enumerate(before.wanting)} if before is not None else {}
+        for e in plan.entries:
+            tokens = e.request.tokens(e.begin, e.begin + e.count)
+            for j, t in enumerate(tokens):
+                if t == PENDING:
+                    if id(e.request) not in rows_before:
+                        raise StepError("a plan feeds a token that no step on its way selects")
+                    tokens[j] = 0
+                    pairs.append((place + j, rows_before[id(e.request)]))
+            place += e.count
+            entries.append(StepEntry(e.request.id, tokens, [e.count - 1] if e.wants_logits else []))
+        logits = self.engine.step(entries, patch=(before.packed, pairs) if pairs else None)
         wanting = [e.request for e in plan.entries if e.wants_logits]
         R = len(wanting)
         packed = torch.empty(R + 1, dtype=torch.int32, device=self.engine.device)
         if R:
+            # draws are counted without the tokens still on their way
             self.sampler.sample_into(logits, [r.config for r in wanting], [len(r.generated) for r in wanting], packed[:R])
         packed[R:].copy_(self.engine.error_flag)
-        t0 = time.perf_counter()
-        host = packed.tolist()                                   # the step's one device -> host copy
-        self.wait_s += time.perf_counter() - t0
+        # the copy back is queued HERE, behind this step's selection: queued when the tokens are wanted it would
+        # stand behind whatever was issued in between (the next step)
+        host = self._results[self._results_next][:R + 1]
+        self._results_next = (self._results_next + 1) % len(self._results)
+        host.copy_(packed, non_blocking=True)
+        copied = torch.cuda.Event()
+        copied.record()
+        self.scheduler.begin(plan)
         self.h2d_bytes += 4 * plan.num_tokens
         self.d2h_bytes += 4 * (R + 1)
+        return _Issued(plan, packed, wanting, host, copied)
+
+    def _issue_ahead(self, current: "_Issued") -> Optional["_Issued"]:
+        """While `current` runs: plan and issue the step after it, if that is a step this path runs anyway (it holds
+        a prompt portion, or steps are not captured) and nobody has to give up pages for it."""
+        if not self.lookahead:
+            return None
+        sched = self.scheduler
+        if self.graphs is not None and not sched.waiting and all(r.known - r.computed <= 1 for r in sched.running):
+            return None                                   # what follows is steady decoding: captured steps take over
+        if sched.would_preempt():
+            return None
+        plan = sched.schedule()
+        if not plan.entries or plan.preempted or self._captured(plan):
+            return None                                   # (reservations and admissions it made stand: the next schedule() finds them)
+        self.lookahead_steps += 1
+        return self._issue(plan, current)
+
+    def _collect(self, issued: "_Issued") -> List[Request]:
+        """Read the step's tokens (the one device -> host copy, blocking) and let the scheduler conclude it."""
+        R = len(issued.wanting)
+        t0 = time.perf_counter()
+        issued.copied.synchronize()
+        host = issued.host.tolist()
+        self.wait_s += time.perf_counter() - t0
         if host[R]:
             self.engine.error_flag.zero_()
             raise StepError(device_error_text(host[R]))
-        return self.scheduler.update(plan, host[:R])
+        return self.scheduler.finish(issued.plan, host[:R])
 
     def _prepare_next(self, plan: StepPlan, graph: DecodeGraph) -> None:
         """While the GPU runs `plan` as a captured step: what the same requests' next step needs from the host.
@@ -179,7 +263,7 @@ class LLM:
         if len(configs) != len(prompts):
             raise ValueError("one GenerationConfig per prompt, or one for all")
         ids = [self.submit(p, c) for p, c in zip(prompts, configs)]
-        while self.scheduler.has_work():
+        while self.has_work():
             self.step()
         out = [list(self.scheduler.requests[i].generated) for i in ids]
         for i in ids:

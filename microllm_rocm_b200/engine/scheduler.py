@@ -20,6 +20,11 @@ Decisions:
     request always makes progress.
   * a request finishes on a stop token (appended first) or at max_new_tokens, and gives
     back its pages and slot in the same step.
+  * a plan may be made before the results of the plan before it are read: begin(plan) records what a plan that
+    was handed to the step function WILL have done (its tokens are in the cache; where logits are wanted one
+    more token is known, its value still PENDING), schedule() plans on from there, finish(plan, tokens) names
+    the pending tokens and ends requests.  A request that ends on a stop token may then already sit in the next
+    plan; that entry is void and finish() skips it.  update() is begin() and finish() in one.
 
 The reference's continuous scheduler (src/inference/scheduler.cpp:464-1069) has fixed slots
 with capacity reserved up front, admits only prompts of equal length together and prefills
@@ -36,6 +41,9 @@ from dataclasses import dataclass, field
 from typing import Deque, Dict, List, Optional, Sequence
 
 from ..sampling.config import GenerationConfig
+
+
+PENDING = -1        # stands in `generated` for a token that a step on its way will select
 
 
 class RequestState(enum.Enum):
@@ -96,6 +104,7 @@ class PlannedEntry:
 class StepPlan:
     entries: List[PlannedEntry]
     preempted: List[int] = field(default_factory=list)
+    begun: bool = False             # begin() has recorded it as on its way
 
     @property
     def num_tokens(self) -> int:
@@ -172,6 +181,7 @@ class Scheduler:
             self.waiting.remove(req)
         req.state, req.reason = RequestState.CANCELLED, FinishReason.CANCELLED
         req.completion_step, req.completed_at = self.step_index, time.perf_counter()
+        req.generated = [t for t in req.generated if t != PENDING]
         self.metrics.cancellations += 1
         return True
 
@@ -199,6 +209,9 @@ class Scheduler:
             req = self.running[i]
             if len(plan.entries) >= self.max_seqs or budget <= 0:
                 break
+            if req.computed >= req.known or self._ends_with_pending(req):
+                i += 1                                    # nothing to feed: its last token is on its way
+                continue
             count = min(req.known - req.computed, budget)
             while not self.cache.reserve(req.id, req.computed + count):
                 victim = self.running[-1]
@@ -229,10 +242,47 @@ class Scheduler:
             budget -= count
         return plan
 
-    # ------------------------------------------------------------------ after the step ran
-    def update(self, plan: StepPlan, drawn: Sequence[int]) -> List[Request]:
-        """Record that `plan` ran and that `drawn` are the tokens selected at its wanted rows
-        (in plan order).  Returns the requests that finished."""
+    # ------------------------------------------------------------------ around the step
+    @staticmethod
+    def _ends_with_pending(req: Request) -> bool:
+        """The request's last allowed token is being computed: nothing more may be planned for it."""
+        return bool(req.generated) and req.generated[-1] == PENDING and len(req.generated) >= req.config.max_new_tokens
+
+    def would_preempt(self) -> bool:
+        """Whether the next schedule() might have to take pages from a running request: the pools cannot give every
+        running request the pages of its next portion.  (A plan made ahead of its predecessor's results must not
+        preempt: the victim's latest token is not known yet.)"""
+        budget = self.max_tokens_per_step
+        need: Dict[str, int] = {}
+        seqs = 0
+        for req in self.running:
+            if seqs >= self.max_seqs or budget <= 0:
+                break
+            if req.computed >= req.known or self._ends_with_pending(req):
+                continue
+            count = min(req.known - req.computed, budget)
+            for group, pages in self.cache.pages_needed(req.id, req.computed + count).items():
+                need[group] = need.get(group, 0) + pages
+            budget -= count
+            seqs += 1
+        return any(pages > self.cache.groups[group].pool.free_count for group, pages in need.items())
+
+    def begin(self, plan: StepPlan) -> None:
+        """`plan` has been handed to the step function: record what it will have done, so that the next plan can be
+        made before its results are read."""
+        if plan.begun:
+            return
+        for e in plan.entries:
+            e.request.computed = e.begin + e.count
+            if e.wants_logits:
+                e.request.generated.append(PENDING)
+        plan.begun = True
+
+    def finish(self, plan: StepPlan, drawn: Sequence[int]) -> List[Request]:
+        """`drawn` are the tokens selected at the plan's wanted rows (in plan order): name the pending tokens, end
+        requests.  Returns the requests that finished."""
+        if not plan.begun:
+            self.begin(plan)
         finished: List[Request] = []
         now = time.perf_counter()
         it = iter(drawn)
@@ -242,28 +292,36 @@ class Scheduler:
         m.max_seqs_in_step = max(m.max_seqs_in_step, len(plan.entries))
         for e in plan.entries:
             req = e.request
-            req.computed = e.begin + e.count
+            token = int(next(it)) if e.wants_logits else None
+            if req.finished:
+                continue                  # ended (a stop token of the plan before, a cancel) while this plan was on its way
             if e.count == 1 and e.wants_logits and e.begin >= len(req.prompt):
                 m.decode_tokens += 1
             else:
                 m.prompt_tokens += e.count
-            if not e.wants_logits:
+            if token is None:
                 continue
-            token = int(next(it))
             if token < 0:
                 raise RuntimeError(f"request {req.id}: logits were not finite, no token could be selected")
-            req.generated.append(token)
+            req.generated[req.generated.index(PENDING)] = token
             m.tokens_generated += 1
             if req.first_token_step is None:
                 req.first_token_step, req.first_token_at = self.step_index, now
+            made = len(req.generated) - req.generated.count(PENDING)
             if token in req.config.stop_tokens:
                 self._finish(req, FinishReason.STOP_TOKEN)
-            elif len(req.generated) >= req.config.max_new_tokens:
+            elif made >= req.config.max_new_tokens:
                 self._finish(req, FinishReason.LENGTH)
             if req.finished:
                 finished.append(req)
         self.step_index += 1
         return finished
+
+    def update(self, plan: StepPlan, drawn: Sequence[int]) -> List[Request]:
+        """Record that `plan` ran and that `drawn` are the tokens selected at its wanted rows
+        (in plan order).  Returns the requests that finished."""
+        self.begin(plan)
+        return self.finish(plan, drawn)
 
     def _finish(self, req: Request, reason: FinishReason) -> None:
         if req in self.running:
@@ -271,4 +329,5 @@ class Scheduler:
             self.cache.release(req.id)
         req.state, req.reason = RequestState.COMPLETED, reason
         req.completion_step, req.completed_at = self.step_index, time.perf_counter()
+        req.generated = [t for t in req.generated if t != PENDING]       # what a plan on its way would have added
         self.metrics.completions += 1

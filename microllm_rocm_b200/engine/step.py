@@ -83,7 +83,11 @@ class Engine:
             self._pinned[i] = torch.empty(size, dtype=torch.int32, pin_memory=True)
         return i, self._pinned[i]
 
-    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+    def build_context(self, entries: Sequence[StepEntry], patch=None) -> StepContext:
+        """`patch` = (tokens of an earlier step on the device [int32], [(place among this step's flat tokens, index
+        into that tensor), ...]): input tokens the host does not know yet because the step that selects them has
+        not been read back.  The host packs a stand-in (token 0) and a small kernel, queued behind the metadata's
+        upload, puts the selected tokens in their places before the embedding reads them."""
         spec, cache = self.model.spec, self.cache
         if not entries:
             raise StepError("a step needs at least one entry")
@@ -121,7 +125,12 @@ class Engine:
         tables = {g: cache.block_table(g, requests) for g in groups}
         widths = {g: len(tables[g][0]) for g in groups}
 
-        total = 3 * T + (A + 1) + 3 * A + R + sum(A * w for w in widths.values())
+        pairs = list(patch[1]) if patch is not None else []
+        P = len(pairs)
+        for place, _ in pairs:
+            if not 0 <= place < T:
+                raise StepError(f"a token patch names place {place} of {T} tokens")
+        total = 3 * T + (A + 1) + 3 * A + R + sum(A * w for w in widths.values()) + 2 * P
         ring_index, host = self._pinned_buffer(total)
         arr = host.numpy()
         cursor = 0
@@ -135,6 +144,7 @@ class Engine:
         s_tok, s_pos, s_seq = take(T), take(T), take(T)
         s_starts, s_pos0, s_lens, s_slots, s_rows = take(A + 1), take(A), take(A), take(A), take(R)
         s_tables = {g: take(A * widths[g]) for g in groups}
+        s_patch_to, s_patch_from = take(P), take(P)
 
         tok = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
         if tok.min() < 0 or tok.max() >= spec.vocab_size:
@@ -154,8 +164,15 @@ class Engine:
         for g in groups:
             arr[s_tables[g][0]:s_tables[g][1]] = np.asarray(tables[g], dtype=np.int32).reshape(-1)
 
+        if P:
+            arr[s_patch_to[0]:s_patch_to[1]] = [place for place, _ in pairs]
+            arr[s_patch_from[0]:s_patch_from[1]] = [index for _, index in pairs]
+
         dev = torch.empty(total, dtype=torch.int32, device=self.device)
         dev.copy_(host[:total], non_blocking=True)               # the step's one metadata transfer
+        if P:
+            from ..kernels import ops
+            ops.scatter_int(dev[s_tok[0]:s_tok[1]], dev[s_patch_to[0]:s_patch_to[1]], patch[0], dev[s_patch_from[0]:s_patch_from[1]])
         event = self._pinned_events[ring_index] or torch.cuda.Event()
         event.record()
         self._pinned_events[ring_index] = event
@@ -172,13 +189,13 @@ class Engine:
             max_new_tokens=max(counts), max_seq_len=max(p + n for p, n in zip(pos0, counts)))
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry], tensor_sink=None) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], tensor_sink=None, patch=None) -> torch.Tensor:
         """Run the given tokens; returns fp32 logits [wanted, vocab] on the device, in the order
         of the entries and of each entry's `want`.  Lengths advance only if the step ran.
         `tensor_sink(name, tensor)`: receives the step's intermediate tensors (a tensor trace; see
-        StepContext.tensor_sink)."""
+        StepContext.tensor_sink).  `patch`: see build_context."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
-        ctx = self.build_context(entries)
+        ctx = self.build_context(entries, patch)
         ctx.tensor_sink = tensor_sink
         views = self.cache_views(ctx)
         logits = self.model.forward(ctx, views)

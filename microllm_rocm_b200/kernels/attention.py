@@ -150,13 +150,15 @@ def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
         tc_work.sort(key=lambda item: -item[0])
     device = ctx.positions.device
     sms = sm_count(device)
-    work_dev = torch.tensor(work, dtype=torch.int32).reshape(-1).to(device, non_blocking=True)
-    tc_dev = torch.tensor([(a, t) for _, a, t in tc_work], dtype=torch.int32).reshape(-1).to(device, non_blocking=True)
+    # (through pinned memory: a copy from pageable memory would first wait for the whole stream, and with it for the
+    # step before this one, which may still be running)
+    work_dev = ops.upload([x for item in work for x in item], "int32", device)
+    tc_dev = ops.upload([x for _, a, t in tc_work for x in (a, t)], "int32", device)
     splits = decode_splits(len(work) * num_kv_heads, ctx.max_seq_len, sms) if decode else 1
     ring = decode and decode_ring_pays(len(work) * num_kv_heads, splits, ctx.max_seq_len, sms, ctx.num_tokens)
     listed_dev, listed_splits = None, 1
     if listed:
-        listed_dev = torch.tensor(listed, dtype=torch.int32).to(device, non_blocking=True)
+        listed_dev = ops.upload(listed, "int32", device)
         longest = max(ctx.seq_pos0_host[a] for a in listed) + 1
         listed_splits = decode_splits(len(listed) * tiles_per_token * num_kv_heads, longest, sms)
         ring = decode_ring_pays(len(listed) * tiles_per_token * num_kv_heads, listed_splits, longest, sms, ctx.num_tokens)

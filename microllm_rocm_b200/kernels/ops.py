@@ -58,6 +58,7 @@ _SIGNATURES = {
         "mlb_embed_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "mlb_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
         "mlb_add_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+        "mlb_scatter_int": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p],
         "mlb_stream_fork": [c_void_p, c_void_p],
         "mlb_stream_join": [c_void_p, c_void_p],
         "mlb_add_inplace": [c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p],
@@ -270,6 +271,55 @@ def copy_raw(dst: int, src: int, nbytes: int, to_device: bool) -> None:
     status = L.mlb_copy_async(dst, src, nbytes, 1 if to_device else 0, _stream())
     if status != 0:
         build.check(L, status)
+
+
+# ------------------------------------------------------------------------------ small host -> device uploads
+# A copy from pageable host memory makes the runtime wait for everything queued on the stream before it stages the
+# data: a step that is issued while the step before it still runs would stall at its first small upload (a work
+# list, a row of sampling parameters).  These go through a ring of pinned slots instead and never wait for the GPU.
+_UPLOAD_SLOTS, _UPLOAD_SLOT_BYTES = 32, 64 << 10
+_staging = {}
+_NUMPY_TO_TORCH = {"int32": torch.int32, "int64": torch.int64, "float32": torch.float32}
+
+
+def upload(values, dtype: str, device: torch.device) -> torch.Tensor:
+    """A new device tensor holding `values` (a sequence or array; dtype 'int32', 'int64' or 'float32'), copied
+    asynchronously out of pinned memory on the current stream."""
+    import numpy as np
+    array = np.ascontiguousarray(np.asarray(values, dtype=dtype))
+    out = torch.empty(array.shape, dtype=_NUMPY_TO_TORCH[dtype], device=device)
+    if array.size == 0:
+        return out
+    if array.nbytes > _UPLOAD_SLOT_BYTES:
+        out.copy_(torch.from_numpy(array).pin_memory(), non_blocking=True)       # rare: too large for a slot
+        return out
+    key = str(device)
+    ring = _staging.get(key)
+    if ring is None:
+        ring = _staging[key] = {"pinned": torch.empty((_UPLOAD_SLOTS, _UPLOAD_SLOT_BYTES), dtype=torch.uint8, pin_memory=True),
+                                "events": [None] * _UPLOAD_SLOTS, "next": 0}
+    i = ring["next"]
+    ring["next"] = (i + 1) % _UPLOAD_SLOTS
+    if ring["events"][i] is not None:
+        ring["events"][i].synchronize()              # the copy that last read this slot (many uploads ago) has run
+    host = ring["pinned"][i, :array.nbytes].view(_NUMPY_TO_TORCH[dtype]).reshape(array.shape)
+    host.numpy()[...] = array
+    out.copy_(host, non_blocking=True)
+    event = ring["events"][i] or torch.cuda.Event()
+    event.record()
+    ring["events"][i] = event
+    return out
+
+
+def scatter_int(dst: torch.Tensor, dst_index: torch.Tensor, src: torch.Tensor, src_index: torch.Tensor) -> None:
+    """dst[dst_index[i]] = src[src_index[i]] for int32 arrays on the device (indices outside an array are skipped)."""
+    for name, t in (("dst", dst), ("dst_index", dst_index), ("src", src), ("src_index", src_index)):
+        _need(t, name, torch.int32, 1)
+    if dst_index.shape[0] != src_index.shape[0]:
+        raise KernelError("scatter_int: one source index per destination index")
+    L = lib("basic.cu")
+    build.check(L, L.mlb_scatter_int(dst.data_ptr(), dst.shape[0], dst_index.data_ptr(), src.data_ptr(), src.shape[0],
+                                     src_index.data_ptr(), dst_index.shape[0], _stream()))
 
 
 _side_streams = {}

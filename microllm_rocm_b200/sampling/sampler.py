@@ -39,9 +39,10 @@ class Sampler:
         if all(c.greedy for c in configs):
             ops.argmax_rows(logits, out)
             return out
-        temperature = torch.tensor([0.0 if c.greedy else c.temperature for c in configs], dtype=torch.float32).to(self.device, non_blocking=True)
-        top_k = torch.tensor([c.top_k for c in configs], dtype=torch.int32).to(self.device, non_blocking=True)
-        seed = torch.tensor([c.seed for c in configs], dtype=torch.int64).to(self.device, non_blocking=True)
-        draw = torch.tensor(list(draws), dtype=torch.int64).to(self.device, non_blocking=True)
+        # (uploads through pinned memory: they must not wait for what the GPU is still running)
+        temperature = ops.upload([0.0 if c.greedy else c.temperature for c in configs], "float32", self.device)
+        top_k = ops.upload([c.top_k for c in configs], "int32", self.device)
+        seed = ops.upload([c.seed for c in configs], "int64", self.device)
+        draw = ops.upload(list(draws), "int64", self.device)
         ops.sample_rows(logits, temperature, top_k, seed, draw, out)
         return out

@@ -370,6 +370,38 @@ def test_steps_prepared_ahead_give_way_to_cancels_arrivals_and_ends(folders):
     llm.engine.cache.check()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_issued_ahead_of_their_predecessors_tokens_change_nothing(folders, dtype):
+    """Steps that hold prompt portions are planned and issued while the step before them still runs; the tokens
+    that step selects reach their places through a kernel on the device.  Greedy and sampled requests, stop tokens
+    (a void row in the step issued ahead), a small token budget: with and without the look-ahead every request
+    gets the same tokens, in fp32 those it gets alone."""
+    import random
+    from microllm_rocm_b200 import GenerationConfig
+    key = "b"
+    cfg = tiny_config(key)
+    rng = random.Random(5)
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in [70, 3, 41, 120, 9, 64, 33, 17]]
+    alone = llm_for(folders[key], dtype, max_tokens=4096, cuda_graphs=False)
+    alone.lookahead = False
+    probe = alone.generate([prompts[0]], GenerationConfig(max_new_tokens=12, temperature=0.0))[0]
+    cfgs = [GenerationConfig(max_new_tokens=12 + 3 * i, temperature=0.0 if i % 2 == 0 else 0.8, seed=i,
+                             stop_tokens=(probe[5],) if i == 0 else ()) for i in range(len(prompts))]
+    results = []
+    for ahead in (False, True):
+        llm = llm_for(folders[key], dtype, max_tokens=4096, max_tokens_per_step=48, cuda_graphs=False)
+        llm.lookahead = ahead
+        results.append(llm.generate(prompts, cfgs))
+        assert (llm.lookahead_steps > 10) == ahead
+        assert llm.metrics()["cache"]["live_requests"] == 0
+        llm.engine.cache.check()
+    assert results[0] == results[1]
+    assert results[1][0] == probe[:probe.index(probe[5]) + 1]      # ended on its stop token
+    if dtype == "float32":
+        for p, c, got in zip(prompts, cfgs, results[1]):
+            assert alone.generate([p], c)[0] == got
+
+
 @pytest.mark.parametrize("key,pool,budget,seed,preempts", [("b", 320, 2048, 0, True), ("b", 400, 64, 7, False),
                                                           ("a", 0, 37, 1, False)])
 def test_many_requests_through_a_tight_pool_equal_one_by_one(folders, key, pool, budget, seed, preempts):
@@ -397,6 +429,8 @@ def test_many_requests_through_a_tight_pool_equal_one_by_one(folders, key, pool,
         if tight.has_work():
             tight.step()
     assert [list(tight.poll(i).generated) for i in ids] == want
+    if budget < 100:
+        assert tight.lookahead_steps > 0                  # prompts cut small: some steps were issued before their predecessors' tokens were read
     metrics = tight.metrics()
     assert metrics["cache"]["live_requests"] == 0
     if preempts:

@@ -241,3 +241,127 @@ def test_random_arrivals_cancellations_and_tight_pools_keep_the_books_and_the_to
     h.cache.check()
     stats = h.cache.stats()
     assert not h.cache.requests and all(stats[g]["used"] == 0 for g in h.cache.groups)
+
+
+class PipelinedHarness(Harness):
+    """The same fake step, but driven the way LLM.step drives it: a plan is begun when it is issued, the NEXT plan
+    is made and issued before the first one's tokens are read (unless pages would have to be taken from somebody),
+    and only then the first is finished.  A fed token that is still PENDING is looked up in the results of the
+    plan before, as the device-side patch does."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.inflight = None
+        self.issued_ahead = 0
+        self.void_rows = 0
+
+    def issue(self, plan, before):
+        from microllm_rocm_b200.engine.scheduler import PENDING
+        for rid in plan.preempted:
+            self.fed.pop(rid, None)
+        drawn = []
+        for e in plan.entries:
+            r = e.request
+            held = self.fed.setdefault(r.id, [])
+            assert len(held) == e.begin == self.cache.length(r.id), "a portion must continue where the cache ends"
+            tokens = r.tokens(e.begin, e.begin + e.count)
+            for j, t in enumerate(tokens):
+                if t == PENDING:
+                    assert before is not None and r.id in before[2], "a pending token must come from the plan on its way"
+                    tokens[j] = before[2][r.id]
+            held.extend(tokens)
+            self.cache.commit(r.id, e.begin + e.count)
+            if e.wants_logits:
+                drawn.append(next_token(held))
+        self.cache.check()
+        self.plans.append(plan)
+        by_request = {e.request.id: t for e, t in zip([e for e in plan.entries if e.wants_logits], drawn)}
+        self.s.begin(plan)
+        return plan, drawn, by_request
+
+    def step(self):
+        if self.inflight is None:
+            plan = self.s.schedule()
+            if not plan.entries:
+                return plan, []
+            self.inflight = self.issue(plan, None)
+        current, self.inflight = self.inflight, None
+        ahead = None
+        if not self.s.would_preempt():
+            plan2 = self.s.schedule()
+            if plan2.entries and not plan2.preempted:
+                ahead = self.issue(plan2, current)
+                self.issued_ahead += 1
+        live_before = {e.request.id for e in current[0].entries if not e.request.finished}
+        done = self.s.finish(current[0], current[1])
+        self.void_rows += sum(1 for e in current[0].entries if e.request.id not in live_before)
+        for r in done:
+            self.fed.pop(r.id, None)
+        self.inflight = ahead
+        return current[0], done
+
+    def run(self, limit=10000):
+        n = 0
+        while self.s.has_work() or self.inflight is not None:
+            self.step()
+            n += 1
+            assert n < limit, "the scheduler makes no progress"
+        return n
+
+
+@pytest.mark.parametrize("pages,budget", [(64, 16), (64, 5), (9, 16), (8, 7)])
+def test_plans_made_ahead_of_their_predecessors_results_give_the_same_tokens(pages, budget):
+    """With every plan issued before the plan before it is finished: the tokens of every request are still the
+    serial oracle's, also when requests end on stop tokens (their row in the plan issued ahead is void), when the
+    pool is so tight that running requests are preempted (no plan is made ahead then), and with cancels and
+    arrivals in between; nothing is left in the cache."""
+    import random
+    from microllm_rocm_b200.engine.scheduler import PENDING
+    rng = random.Random(pages * 100 + budget)
+    h = PipelinedHarness(num_pages=pages, page_size=4, max_requests=4, budget=budget, max_seqs=4)
+    specs = []
+    for i in range(14):
+        prompt = [rng.randrange(VOCAB) for _ in range(rng.choice([1, 2, 5, 9, 17]))]
+        cfg = GenerationConfig(max_new_tokens=rng.choice([1, 2, 6, 11]), temperature=0.0,
+                               stop_tokens=tuple(rng.sample(range(VOCAB), 6)) if i % 2 else ())
+        specs.append((prompt, cfg))
+    todo, ids, cancelled = list(specs), [], set()
+    n = 0
+    while todo or h.s.has_work() or h.inflight is not None:
+        for _ in range(rng.randrange(0, 3) if pages > 9 else len(todo)):      # a tight pool gets the whole burst at once
+            if todo:
+                ids.append(h.s.submit(*todo.pop(0)))
+        if ids and rng.random() < 0.08:
+            victim = rng.choice(ids)
+            if h.s.cancel(victim):
+                cancelled.add(victim)
+                h.fed.pop(victim, None)
+        h.step()
+        n += 1
+        assert n < 5000
+    for rid, (prompt, cfg) in zip(ids, specs):
+        r = h.s.requests[rid]
+        assert PENDING not in r.generated
+        want = oracle(prompt, cfg)
+        if rid in cancelled:
+            assert r.generated == want[:len(r.generated)] and r.state == RequestState.CANCELLED
+        else:
+            assert r.generated == want, rid
+            assert r.reason == (FinishReason.STOP_TOKEN if r.generated[-1] in cfg.stop_tokens else FinishReason.LENGTH)
+    assert not h.cache.requests and h.cache.stats()["full"]["used"] == 0
+    assert h.issued_ahead > 5
+    if pages <= 9:
+        assert h.s.metrics.preemptions > 0
+
+
+def test_a_request_that_ends_on_a_stop_token_leaves_a_void_row_in_the_plan_issued_ahead():
+    h = PipelinedHarness(budget=16)
+    prompt = [3, 1, 4]
+    full = oracle(prompt, GenerationConfig(max_new_tokens=8, temperature=0.0))
+    stop = full[2]
+    a = h.s.submit(prompt, GenerationConfig(max_new_tokens=8, temperature=0.0, stop_tokens=(stop,)))
+    b = h.s.submit([7] * 5, GenerationConfig(max_new_tokens=8, temperature=0.0))
+    h.run()
+    assert h.s.requests[a].generated == full[:full.index(stop) + 1] and h.s.requests[a].reason == FinishReason.STOP_TOKEN
+    assert h.s.requests[b].generated == oracle([7] * 5, GenerationConfig(max_new_tokens=8, temperature=0.0))
+    assert h.void_rows == 1 and h.s.metrics.tokens_generated == len(h.s.requests[a].generated) + 8
