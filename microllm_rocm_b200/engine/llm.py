@@ -19,7 +19,7 @@ from ..sampling.sampler import Sampler
 from .decode_graph import DecodeGraph, DecodeGraphPool, graph_capable
 from .loading import DEFAULT_PAGE_SIZE, load_engine
 from .scheduler import PENDING, Request, Scheduler, StepPlan
-from .step import Engine, StepEntry, StepError, device_error_text
+from .step import Engine, OutOfPages, StepEntry, StepError, device_error_text
 
 
 class _Issued:
@@ -168,8 +168,12 @@ class LLM:
         plan = sched.schedule()
         if not plan.entries or plan.preempted or self._captured(plan):
             return None                                   # (reservations and admissions it made stand: the next schedule() finds them)
+        try:
+            issued = self._issue(plan, current)
+        except OutOfPages:
+            return None                                   # nothing was launched; the next schedule() decides who gives way
         self.lookahead_steps += 1
-        return self._issue(plan, current)
+        return issued
 
     def _collect(self, issued: "_Issued") -> List[Request]:
         """Read the step's tokens (the one device -> host copy, blocking) and let the scheduler conclude it."""
