@@ -75,6 +75,7 @@ class LLM:
         return self.scheduler.cancel(request_id)
 
     def poll(self, request_id: int) -> Request:
+        """The request's record: `state`, `reason`, `output` (the tokens generated so far), timings."""
         return self.scheduler.requests[request_id]
 
     def has_work(self) -> bool:

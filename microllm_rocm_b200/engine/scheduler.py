@@ -81,6 +81,12 @@ class Request:
     def known(self) -> int:
         return len(self.prompt) + len(self.generated)
 
+    @property
+    def output(self) -> List[int]:
+        """The tokens generated so far.  (`generated` may end in PENDING entries while a step that will name them
+        is on its way; a reader between steps wants this list.)"""
+        return [t for t in self.generated if t != PENDING]
+
     def token(self, i: int) -> int:
         return self.prompt[i] if i < len(self.prompt) else self.generated[i - len(self.prompt)]
 
