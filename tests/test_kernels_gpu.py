@@ -430,6 +430,28 @@ def test_kernels_refuse_bad_sizes_with_a_clear_error():
         attention.check_head_dim(17)
 
 
+def test_scatter_int_and_pinned_uploads():
+    """The two small helpers of steps issued ahead: selected tokens go to their places in the next step's input
+    (indices outside either array are skipped, nothing else is touched), and small arrays reach the device through
+    pinned slots, many more of them than the ring has slots, with their values intact."""
+    o = ops()
+    dst = torch.full((10,), -7, dtype=torch.int32, device=DEV)
+    src = torch.arange(100, 106, dtype=torch.int32, device=DEV)
+    to = o.upload([0, 9, 4, 12, -1, 3], "int32", torch.device(DEV))
+    frm = o.upload([5, 0, 2, 1, 1, 77], "int32", torch.device(DEV))
+    o.scatter_int(dst, to, src, frm)
+    assert dst.tolist() == [105, -7, -7, -7, 102, -7, -7, -7, -7, 100]
+    kept = []
+    for i in range(100):                       # three times round the ring, while earlier copies may still be queued
+        values = [i * 1000 + j for j in range(1 + i % 7)]
+        kept.append((values, o.upload(values, "int64", torch.device(DEV))))
+    floats = o.upload([0.5, -1.25], "float32", torch.device(DEV))
+    big = o.upload(list(range(40000)), "int32", torch.device(DEV))        # larger than a slot
+    torch.cuda.synchronize()
+    assert all(t.tolist() == v for v, t in kept) and floats.tolist() == [0.5, -1.25] and big[-1].item() == 39999
+    assert o.upload([], "int32", torch.device(DEV)).numel() == 0
+
+
 # ------------------------------------------------------------------------------ tcgen05 products
 @pytest.mark.parametrize("M,N,K,splits,stages", [
     (9, 2048, 1536, None, 0), (16, 1536, 8960, None, 0), (33, 1000, 264, 2, 0), (64, 1536, 8960, None, 0),
