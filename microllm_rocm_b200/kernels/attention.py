@@ -152,13 +152,17 @@ def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
     sms = sm_count(device)
     # (through pinned memory: a copy from pageable memory would first wait for the whole stream, and with it for the
     # step before this one, which may still be running)
-    work_dev = ops.upload([x for item in work for x in item], "int32", device)
-    tc_dev = ops.upload([x for _, a, t in tc_work for x in (a, t)], "int32", device)
+    # the three lists travel as one array (the kernels read them int by int: no alignment beyond 4 bytes is needed)
+    flat_work = [x for item in work for x in item]
+    flat_tc = [x for _, a, t in tc_work for x in (a, t)]
+    lists = ops.upload(flat_work + flat_tc + listed, "int32", device)
+    work_dev = lists[:len(flat_work)]
+    tc_dev = lists[len(flat_work):len(flat_work) + len(flat_tc)]
     splits = decode_splits(len(work) * num_kv_heads, ctx.max_seq_len, sms) if decode else 1
     ring = decode and decode_ring_pays(len(work) * num_kv_heads, splits, ctx.max_seq_len, sms, ctx.num_tokens)
     listed_dev, listed_splits = None, 1
     if listed:
-        listed_dev = ops.upload(listed, "int32", device)
+        listed_dev = lists[len(flat_work) + len(flat_tc):]
         longest = max(ctx.seq_pos0_host[a] for a in listed) + 1
         listed_splits = decode_splits(len(listed) * tiles_per_token * num_kv_heads, longest, sms)
         ring = decode_ring_pays(len(listed) * tiles_per_token * num_kv_heads, listed_splits, longest, sms, ctx.num_tokens)

@@ -33,6 +33,12 @@ class CallRecord(ctypes.Structure):
                 ("pointer_mask", c_uint), ("num_slots", c_int), ("num_floats", c_int), ("library", c_int)]
 
 
+import struct
+
+# the layout of CallRecord (native alignment): function, slots, floats, pointer_mask, num_slots, num_floats, library
+_RECORD = struct.Struct(f"@P{MAX_SLOTS}Q{MAX_FLOATS}fIiii")
+assert _RECORD.size == ctypes.sizeof(CallRecord), "the packed record must have the layout of the ctypes structure"
+
 _active: Optional["Recorder"] = None
 
 
@@ -119,22 +125,20 @@ class Recording:
             raise KernelError(f"replay: {recorder.unrecordable}")
         self.libraries = []
         n = len(recorder.calls)
-        self.records = (CallRecord * max(1, n))()
         self.count = n
         self.pointers = set()
-        for i, (library, address, slots, floats, mask) in enumerate(recorder.calls):
+        # the records are packed in one go (one struct.pack per call): field-by-field assignment through ctypes
+        # costs more host time than the calls themselves
+        blob = bytearray()
+        for library, address, slots, floats, mask in recorder.calls:
             if library not in self.libraries:
                 self.libraries.append(library)
-            r = self.records[i]
-            r.function = address
             for j, v in enumerate(slots):
-                r.slots[j] = v
                 if (mask >> j) & 1 and v:
                     self.pointers.add(v)
-            for j, v in enumerate(floats):
-                r.floats[j] = v
-            r.pointer_mask, r.num_slots, r.num_floats = mask, len(slots), len(floats)
-            r.library = self.libraries.index(library)
+            blob += _RECORD.pack(address, *slots, *([0] * (MAX_SLOTS - len(slots))), *floats, *([0.0] * (MAX_FLOATS - len(floats))),
+                                 mask, len(slots), len(floats), self.libraries.index(library))
+        self.records = (CallRecord * max(1, n)).from_buffer_copy(bytes(blob) if n else bytes(ctypes.sizeof(CallRecord)))
         self._failed = c_int(-1)
         self._launched = c_int(0)
         self._swap_cache: Dict[Tuple[int, ...], Tuple[object, object, int]] = {}
