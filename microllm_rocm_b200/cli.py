@@ -392,6 +392,10 @@ def run(o) -> int:
             base = base + base
         prompts = [base[f:f + l] for l, f in zip(lengths, offsets)]
         llm = LLM(engine, max_tokens_per_step=o["max-tokens-per-step"], max_seqs=slots)
+        # arrival steps are meant exactly: a request that arrives at step k is planned in step k.  A step issued
+        # ahead of its predecessor's results would already be on its way when the request arrives, so that is
+        # switched off when arrivals are spread over steps.
+        llm.lookahead = not any(a > 0 for a in arrivals)
         pending = sorted(range(len(prompts)), key=lambda i: arrivals[i])
         submitted: Dict[int, int] = {}
 
