@@ -419,6 +419,33 @@ def run_ours(args):
         engine.cache.release("pf")
         return start.elapsed_time(end)
 
+    if args.only == "prefill-timeline":
+        # one prompt step kernel by kernel: launches, busy time, and the GPU's idle time in front of each kernel
+        class _Prompt:
+            def step(self_inner):
+                prefill_once()
+        for _ in range(max(3, args.warmup)):
+            prefill_once()
+        records = _kernel_records(_Prompt(), 3)
+        per_step = len(records) // 3
+        records = records[per_step:2 * per_step]
+        rows, frontier, idle_total = {}, records[0][1], 0.0
+        for name, begin, end in records:
+            short = name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0].split("<")[0]
+            idle, busy = max(0.0, begin - frontier), max(0.0, end - max(frontier, begin))
+            row = rows.setdefault(short, [0, 0.0, 0.0])
+            row[0] += 1
+            row[1] += busy
+            row[2] += idle
+            idle_total += idle
+            frontier = max(frontier, end)
+        span = records[-1][2] - records[0][1]
+        print(f"prompt step of {args.prefill_tokens} tokens, {layers} layers of {args.model}: {span:.0f} us from the first kernel's "
+              f"start to the last one's end, of which the GPU idles {idle_total:.0f} us")
+        print(f"{'kernel':44s} {'launches':>8s} {'busy us':>9s} {'idle before, us':>16s} {'each':>6s}")
+        for name, (count, busy, idle) in sorted(rows.items(), key=lambda kv: -kv[1][1]):
+            print(f"{name[:44]:44s} {count:8d} {busy:9.1f} {idle:16.1f} {idle / count:6.2f}")
+        return 0
     if args.only == "timeline":
         # one captured decode step kernel by kernel: launches, summed durations, and what each adds to the step
         session = DecodeSession(engine, prompts(args.batch), args.warmup + 8)
@@ -554,7 +581,7 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "prefill-timeline"],
                     help="run just one timed part and print a short line (for profiler captures)")
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed"])
     ap.add_argument("--requests", type=int, default=64, help="mixed: how many requests")
