@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, TcParams p) {
     pdl_launch_dependents();
     extern __shared__ unsigned char smem_dyn[];
-    __shared__ __align__(8) unsigned long long q_full, slot_full[SLOTS], slot_empty[SLOTS], s_full[2], s_empty[2], p_full, pv_done[2];
+    __shared__ __align__(8) unsigned long long q_full, slot_full[SLOTS], slot_empty[SLOTS], s_full[2], s_empty[2], p_full[2], pv_done[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int failed_s;
 
@@ -212,7 +212,11 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             mbar_init(smem_u32(&s_full[s]), 1);
             mbar_init(smem_u32(&s_empty[s]), 4);          // one arrival per softmax warp
         }
-        mbar_init(smem_u32(&p_full), 4);
+        // One barrier per P buffer.  A softmax warp may be a whole tile ahead of another (tile j + 1's scores exist
+        // before P V of tile j is issued): with a single barrier its arrival for tile j + 1 would complete tile j's
+        // phase in place of the slow warp's, and P V would read rows of P that were not written yet.
+        mbar_init(smem_u32(&p_full[0]), 4);
+        mbar_init(smem_u32(&p_full[1]), 4);
         mbar_init(smem_u32(&pv_done[0]), 1);        // P V of the even tiles, and of the odd ones: one per P buffer
         mbar_init(smem_u32(&pv_done[1]), 1);
         failed_s = 0;
@@ -332,7 +336,7 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             };
             for (int j = 0; j < 2 && j < n_tiles && ok; ++j) ok = issue_qk(j);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                ok = wait_warp(&p_full, j & 1, 25);
+                ok = wait_warp(&p_full[j & 1], (j >> 1) & 1, 25);
                 if (!ok) break;
                 const int slot = item % SLOTS;
                 ok = wait_warp(&slot_full[slot], (item / SLOTS) & 1, 26);
@@ -460,7 +464,7 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the cleared V rows, for the tensor core
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&p_full));
+            if (lane == 0) mbar_arrive(smem_u32(&p_full[buf]));
         }
         if (ok && n_tiles > 0) ok = wait_all(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, 31);
         if (ok && n_tiles > 0) {

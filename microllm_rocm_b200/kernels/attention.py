@@ -31,12 +31,13 @@ WIDE_CLUSTER_CTAS = 48              # measured: one sequence of two kv heads gai
 # never.  Tests set it to run both kernels on the same inputs.
 DECODE_RING = None
 RING_MIN_KEYS_PER_CTA = 1024        # measured: 16 stages of 64 keys per CTA and the ring wins by 7-8 %, 8 stages and it loses 12 %
-# Measured in whole decode steps at context 8,192 (8 layers of the 14B / 7B shapes): with 8 tokens the ring costs
-# 2.64 against 2.01 ms / 2.08 against 1.50 ms although the kernel alone is 8 % faster; with 16 tokens it wins, 2.03
-# against 2.42 / 1.35 against 1.52 ms.  Up to 8 tokens the kernels around the attention are the few-token products,
-# whose CTAs take 160 KB of shared memory: beside two ring CTAs (113 KB each) they cannot start early.
-RING_MIN_TOKENS = 9
-
+# Measured in whole decode steps at context 8,192 (8 layers of the 14B / 7B shapes), when the products around the
+# attention were still the few-token mma.sync kernels: with 8 tokens the ring cost 2.64 against 2.01 ms / 2.08
+# against 1.50 ms although the kernel alone is 8 % faster; with 16 tokens (tcgen05 streaming products around it)
+# it won, 2.03 against 2.42 / 1.35 against 1.52 ms.  The mma.sync products' CTAs take up to 160 KB of shared memory:
+# beside two ring CTAs (113 KB each) they cannot start early.  Since the wide models' few-token products went to
+# the streaming kernel too, the ring wins there at 8 tokens as well (14B: 1.85 -> 1.67 ms, 7B: 1.28 -> 1.19 ms).
+# So the caller says which products surround the attention (`beside_mma_products`).
 CONCURRENT_ATTENTION = True         # the two attention launches of a mixed step side by side (tests may switch it off)
 TC_HEAD_DIMS = (64, 128)
 TC_KEYS_PER_TILE = 128
@@ -94,14 +95,14 @@ def decode_splits(items: int, max_seq_len: int, sms: int = DEFAULT_SM_COUNT) -> 
 
 
 def decode_ring_pays(items: int, splits: int, max_seq_len: int, sms: int = DEFAULT_SM_COUNT,
-                     tokens: int = RING_MIN_TOKENS) -> bool:
+                     beside_mma_products: bool = False) -> bool:
     """Whether a decode step should bring its keys through the shared-memory ring (TMA, a copying warp) instead of
     straight into registers: when every multiprocessor has a CTA, each CTA streams a thousand keys or more, and
-    the step holds more tokens than the few-token products take.  Below that the ring's set-up and its extra
-    hand-offs cost more than the deeper prefetch brings, or its shared memory keeps the next kernel from
-    starting early."""
+    the products around the attention are not the few-token mma.sync kernels.  Below that the ring's set-up and
+    its extra hand-offs cost more than the deeper prefetch brings; beside those kernels its shared memory keeps
+    the next one from starting early."""
     return (items * splits >= sms and max_seq_len // max(1, splits) >= RING_MIN_KEYS_PER_CTA and splits <= 8
-            and tokens >= RING_MIN_TOKENS)
+            and not beside_mma_products)
 
 
 def decode_plan_stale(ctx, max_seq_len: int, sms: int = DEFAULT_SM_COUNT) -> bool:
@@ -111,7 +112,8 @@ def decode_plan_stale(ctx, max_seq_len: int, sms: int = DEFAULT_SM_COUNT) -> boo
     for key, plan in ctx.extras.items():
         if isinstance(key, tuple) and key and key[0] == "attention_mma" and plan[2] == 1:
             splits = decode_splits(plan[1] * key[2], max_seq_len, sms)
-            if splits != plan[3] or (len(plan) > 9 and decode_ring_pays(plan[1] * key[2], splits, max_seq_len, sms, ctx.num_tokens) != plan[9]):
+            beside = bool(key[4]) if len(key) > 4 else False
+            if splits != plan[3] or (len(plan) > 9 and decode_ring_pays(plan[1] * key[2], splits, max_seq_len, sms, beside) != plan[9]):
                 return True
     return False
 
@@ -121,9 +123,9 @@ def forget_plans(ctx) -> None:
         del ctx.extras[key]
 
 
-def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
+def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool, beside_mma_products: bool = False):
     """Work lists and split choice of a step, shared by every layer with the same group size."""
-    key = ("attention_mma", group, num_kv_heads, use_tc)
+    key = ("attention_mma", group, num_kv_heads, use_tc, bool(beside_mma_products))
     plan = ctx.extras.get(key)
     if plan is not None:
         return plan
@@ -159,13 +161,13 @@ def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
     work_dev = lists[:len(flat_work)]
     tc_dev = lists[len(flat_work):len(flat_work) + len(flat_tc)]
     splits = decode_splits(len(work) * num_kv_heads, ctx.max_seq_len, sms) if decode else 1
-    ring = decode and decode_ring_pays(len(work) * num_kv_heads, splits, ctx.max_seq_len, sms, ctx.num_tokens)
+    ring = decode and decode_ring_pays(len(work) * num_kv_heads, splits, ctx.max_seq_len, sms, beside_mma_products)
     listed_dev, listed_splits = None, 1
     if listed:
         listed_dev = lists[len(flat_work) + len(flat_tc):]
         longest = max(ctx.seq_pos0_host[a] for a in listed) + 1
         listed_splits = decode_splits(len(listed) * tiles_per_token * num_kv_heads, longest, sms)
-        ring = decode_ring_pays(len(listed) * tiles_per_token * num_kv_heads, listed_splits, longest, sms, ctx.num_tokens)
+        ring = decode_ring_pays(len(listed) * tiles_per_token * num_kv_heads, listed_splits, longest, sms, beside_mma_products)
     plan = (work_dev, len(work), 1 if decode else 0, splits, tc_dev, len(tc_work), listed_dev, len(listed) * tiles_per_token,
             listed_splits, ring)
     ctx.extras[key] = plan
@@ -173,7 +175,10 @@ def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool):
 
 
 def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx, block_table: torch.Tensor,
-                    num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int]) -> None:
+                    num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
+                    beside_mma_products: bool = False) -> None:
+    """`beside_mma_products`: the projections around this attention run on the few-token mma.sync kernels in this
+    step (a choice of the caller's products; it decides which decode kernel suits, see decode_ring_pays)."""
     page_size = pages.shape[3]
     if q.dtype != torch.bfloat16 or not mma_supported(head_dim, page_size):
         ops.paged_attention_plain(q, pages, out, ctx.positions, ctx.token_seq, block_table, num_heads, num_kv_heads,
@@ -183,7 +188,7 @@ def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx
         raise KernelError("paged_attention: the tensor-core kernel wants bf16 queries, pages and output")
     use_tc = tc_supported(head_dim, page_size, scale) and q.is_contiguous() and out.is_contiguous()
     work, num_work, mode, splits, tc_work, num_tc, listed, num_listed, listed_splits, ring = _plan(
-        ctx, num_heads // num_kv_heads, num_kv_heads, use_tc)
+        ctx, num_heads // num_kv_heads, num_kv_heads, use_tc, beside_mma_products)
     ring_bits = 4 if (ring if DECODE_RING is None else DECODE_RING) else 8
     side = None
     if num_tc:

@@ -143,6 +143,7 @@ class Attention(Mixer):
                               q, pages, self.nh, self.nkv, self.d, ctx.error_flag, cos_sin)
         o = ctx.buffer("attention.o", (T, self.nh * self.d), self.rt.dtype)
         attention_kernels.paged_attention(q, cache.pages, o, ctx, cache.block_table, self.nh, self.nkv, self.d,
-                                          self.scale, self.window)
+                                          self.scale, self.window,
+                                          beside_mma_products=x.dtype == torch.bfloat16 and gemm_bf16.gemv_preferred(x, self.w_o))
         return linear(o, self.w_o, self.b_o, torch.float32, partials_ok=True, error_flag=ctx.error_flag,      # [T, H] f32, or its partial sums
                       alloc=lambda shape, dtype: ctx.buffer("attention.out", shape, dtype))

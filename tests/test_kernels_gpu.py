@@ -135,9 +135,9 @@ def paged_from_dense(k, v, page_size, num_pages, dtype, seed=0):
     return pages.to(dtype), table
 
 
-def run_attention(q_list, k_list, v_list, pos0_list, nh, nkv, d, window, dtype, page_size=16, num_pages=64):
+def run_attention(q_list, k_list, v_list, pos0_list, nh, nkv, d, window, dtype, page_size=16, num_pages=64, repeats=None):
     """Queries q_list[s] ([n_s, NH, D]) sit at positions pos0_list[s].. of sequence s whose
-    keys are k_list[s]."""
+    keys are k_list[s].  `repeats`: run the same step that often and return every result, [repeats, T, NH * D]."""
     pages, table = paged_from_dense(k_list, v_list, page_size, num_pages, dtype)
     q = torch.cat([x.reshape(x.shape[0], nh * d) for x in q_list]).to(dtype)
     positions = torch.cat([torch.arange(p, p + x.shape[0], dtype=torch.int32) for p, x in zip(pos0_list, q_list)])
@@ -156,7 +156,14 @@ def run_attention(q_list, k_list, v_list, pos0_list, nh, nkv, d, window, dtype, 
                       seq_starts_host=[int(v) for v in np.cumsum([0] + [x.shape[0] for x in q_list])],
                       seq_pos0_host=list(pos0_list), max_new_tokens=max(x.shape[0] for x in q_list),
                       max_seq_len=max(p + x.shape[0] for p, x in zip(pos0_list, q_list)))
-    attention.paged_attention(q.to(DEV), pages.to(DEV), out, ctx, table.to(DEV), nh, nkv, d, 1.0 / math.sqrt(d), window)
+    q, pages, table = q.to(DEV), pages.to(DEV), table.to(DEV)
+    if repeats:
+        outs = torch.empty((repeats, *q.shape), dtype=dtype, device=DEV)
+        for i in range(repeats):
+            attention.paged_attention(q, pages, outs[i], ctx, table, nh, nkv, d, 1.0 / math.sqrt(d), window)
+        assert int(flag.item()) == 0
+        return outs.float().cpu()
+    attention.paged_attention(q, pages, out, ctx, table, nh, nkv, d, 1.0 / math.sqrt(d), window)
     assert int(flag.item()) == 0
     return out.float().cpu()
 
@@ -275,6 +282,60 @@ def test_tcgen05_prompt_attention_far_key_and_window_edge():
     assert torch.allclose(got_w, want_w, **tol(torch.bfloat16)), float((got_w - want_w).abs().max())
     assert torch.allclose(got_w[n - 2, 0], v[far, 0], atol=3e-2)
     assert not torch.allclose(got_w[n - 1, 0], v[far, 0], atol=0.2)
+
+
+def test_tcgen05_prompt_attention_when_one_softmax_warp_lags():
+    """The last 32 rows of every 128-row tile are aligned with keys that grow from key tile to key tile, so that
+    their maxima outgrow the rescale threshold at EVERY tile and their softmax warp has the accumulator to
+    rescale each time, while the three other warps never do and run ahead.  The result must not depend on which
+    warp is where: equal to the plain attention, and bit for bit the same every time."""
+    torch.manual_seed(17)
+    nh, nkv, d, n = 8, 2, 128, 4096
+    k, v = torch.randn(n, nkv, d) * 0.1, torch.randn(n, nkv, d)
+    q = torch.randn(n, nh, d) * 0.1
+    direction = torch.randn(d)
+    direction /= direction.norm()
+    tile = torch.arange(n) // 128
+    k += direction * 9.0 * tile[:, None, None]                 # + 81 * 0.088 * log2(e) = 10 > 8 doublings per key tile
+    lagging = (torch.arange(n) % 128) >= 96
+    q[lagging] = direction * 9.0
+    k, v, q = (x.bfloat16().float() for x in (k, v, q))
+    want = plain_attention_rows(q, k, v, 0, None).reshape(n, nh * d)
+    first = None
+    for _ in range(4):
+        got = run_attention([q], [k], [v], [0], nh, nkv, d, None, torch.bfloat16, page_size=64, num_pages=70)
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got, want, **tol(torch.bfloat16)), float((got - want).abs().max())
+        if first is None:
+            first = got
+        assert torch.equal(got, first)
+
+
+def test_prompt_portions_and_decoded_tokens_side_by_side_give_the_same_bits_every_time():
+    """Three decoded tokens at 8,200 keys, the last 22 tokens of a prompt at 8,170 and the first 2,023 of another, with
+    40 heads in 8 groups: the decoded tokens' kernel and the prompt portions' kernel run at the same time.  Thirty runs
+    of the same step must agree bit for bit, and with the run in which the two kernels follow one another.  (In the
+    22-row tile three of the four softmax warps work on rows of the NEXT sequence, so the warps of a CTA are out of
+    step with one another; what the kernels compute is checked against the plain attention by the tests above.)"""
+    from microllm_rocm_b200.kernels import attention
+    torch.manual_seed(23)
+    nh, nkv, d = 40, 8, 128
+    lens = [8207, 8202, 8198, 8192, 2023]
+    news = [1, 1, 1, 22, 2023]
+    ks = [(torch.randn(n, nkv, d) * 0.5).bfloat16().float() for n in lens]
+    vs = [torch.randn(n, nkv, d).bfloat16().float() for n in lens]
+    qs = [torch.randn(n, nh, d).bfloat16().float() for n in news]
+    pos0 = [l - n for l, n in zip(lens, news)]
+    pages = sum(-(-n // 64) for n in lens) + 2
+    attention.CONCURRENT_ATTENTION = False
+    try:
+        want = run_attention(qs, ks, vs, pos0, nh, nkv, d, None, torch.bfloat16, page_size=64, num_pages=pages)
+    finally:
+        attention.CONCURRENT_ATTENTION = True
+    got = run_attention(qs, ks, vs, pos0, nh, nkv, d, None, torch.bfloat16, page_size=64, num_pages=pages, repeats=30)
+    assert torch.isfinite(got).all()
+    for i in range(got.shape[0]):
+        assert torch.equal(got[i], want), (i, float((got[i] - want).abs().max()))
 
 
 @pytest.mark.parametrize("page_size", [4, 16, 64])

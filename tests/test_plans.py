@@ -63,8 +63,8 @@ def test_the_key_ring_is_for_long_streams_on_a_full_gpu():
     assert not attention.decode_ring_pays(64, 4, 2073)          # batch 32: 518 keys per CTA
     assert not attention.decode_ring_pays(16, 8, 2073)          # batch 8: fewer CTAs than multiprocessors
     assert attention.decode_ring_pays(64, 4, 8192) and not attention.decode_ring_pays(2, 16, 32768)
-    # eight tokens and fewer: the few-token products around the attention need the shared memory to start early
-    assert not attention.decode_ring_pays(64, 4, 8192, tokens=8) and attention.decode_ring_pays(128, 2, 8192, tokens=16)
+    # beside the few-token mma.sync products the next kernel needs the shared memory to start early
+    assert not attention.decode_ring_pays(64, 4, 8192, beside_mma_products=True) and attention.decode_ring_pays(128, 2, 8192)
 
 
 class _Ctx:
