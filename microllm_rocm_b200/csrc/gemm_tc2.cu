@@ -386,9 +386,9 @@ MLB_EXPORT int mlb_gemm_pair(const void* x, long long ldx, const void* w, long l
     config.blockDim = dim3(THREADS);
     config.dynamicSmemBytes = smem;
     config.stream = stream;
-    // No programmatic early start: a CTA of this kernel holds a whole SM and all of its tensor memory from its first
-    // instruction, and the prompt attention kernel, which does the same, stalled when it sat early in front of its
-    // dependency wait (see attention_tc.cu).  This kernel never did; an early start would hide ~2 us of ~100.
+    // No programmatic early start: a CTA of this kernel holds a whole SM and all of its tensor memory, so it becomes
+    // resident only where a CTA of the kernel in front has left; started early, 2,048-token steps of three model
+    // shapes take the same time within +-1 %.
     cudaLaunchAttribute attributes[1];
     attributes[0].id = cudaLaunchAttributeClusterDimension;
     attributes[0].val.clusterDim.x = 2;
