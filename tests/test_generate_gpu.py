@@ -402,6 +402,37 @@ def test_steps_issued_ahead_of_their_predecessors_tokens_change_nothing(folders,
             assert alone.generate([p], c)[0] == got
 
 
+def test_a_burst_at_a_serving_width_gives_the_same_tokens_issued_ahead_or_not():
+    """The tiny configurations never reach the kernels a served model runs on (the tcgen05 products and prompt
+    attention, the streaming products, the decode ring): a model of a served width (heads of 128 in groups of 5,
+    an odd vocabulary, six layers, random weights drawn on the device) takes 24 requests with prompts of 100 to
+    1,500 tokens in 512-token steps, so that prompt portions run beside decoded tokens and captured steps
+    follow.  Steps issued ahead or not, twice: the same tokens every time, all of them valid ids."""
+    import random
+    from microllm_rocm_b200 import GenerationConfig
+    from microllm_rocm_b200.config import Qwen2Config
+    from microllm_rocm_b200.engine.llm import LLM
+    from microllm_rocm_b200.engine.loading import random_engine
+    cfg = Qwen2Config.from_dict({
+        "architectures": ["Qwen2ForCausalLM"], "hidden_size": 2560, "num_attention_heads": 20, "num_key_value_heads": 4,
+        "head_dim": 128, "intermediate_size": 6912, "num_hidden_layers": 6, "vocab_size": 50021, "rms_norm_eps": 1e-6,
+        "rope_theta": 1000000.0, "max_position_embeddings": 4096, "tie_word_embeddings": False})
+    rng = random.Random(3)
+    lens = [rng.randint(100, 1500) for _ in range(24)]
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in lens]
+    engine = random_engine(cfg, seed=1, dtype="bfloat16", page_size=64, max_tokens=sum(lens) + 24 * 192, max_requests=24,
+                           draw_on_device=True)
+    results = []
+    for ahead in (True, False, True):
+        llm = LLM(engine, max_tokens_per_step=512, max_seqs=24)
+        llm.lookahead = ahead
+        results.append(llm.generate(prompts, GenerationConfig(max_new_tokens=48, temperature=0.0)))
+        assert (llm.lookahead_steps > 10) == ahead and llm.graph_steps > 10
+        assert llm.metrics()["cache"]["live_requests"] == 0
+    assert all(len(r) == 48 and all(0 <= t < cfg.vocab_size for t in r) for r in results[0])
+    assert results[0] == results[1] == results[2]
+
+
 @pytest.mark.parametrize("key,pool,budget,seed,preempts", [("b", 320, 2048, 0, True), ("b", 400, 64, 7, False),
                                                           ("a", 0, 37, 1, False)])
 def test_many_requests_through_a_tight_pool_equal_one_by_one(folders, key, pool, budget, seed, preempts):
