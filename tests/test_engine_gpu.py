@@ -219,8 +219,9 @@ def test_wider_layer_shapes_bf16_tracks_the_true_fp32_path(name):
 def test_prompt_steps_issued_back_to_back_leave_no_device_error():
     """Four layers of the 7B shape, three prompts of 2,048 tokens stepped one after the other WITHOUT a
     synchronisation in between, so that the host runs far ahead of the GPU and every kernel that may start
-    early does.  (The tensor-memory attention kernel, started early in this situation, had bounded waits run
-    out; it is launched after its predecessor now.)  The device error flag must stay clear and the logits finite."""
+    early does.  (In this situation bounded waits inside the tensor-memory attention kernel once ran out: its
+    softmax warps shared one barrier for two buffers of P.)  The device error flag must stay clear and the logits
+    finite."""
     from microllm_rocm_b200.config import preset
     from microllm_rocm_b200.engine.loading import random_engine
     from microllm_rocm_b200.engine.step import StepEntry
@@ -238,6 +239,58 @@ def test_prompt_steps_issued_back_to_back_leave_no_device_error():
     torch.cuda.synchronize()
     engine.check_device_errors()
     assert all(torch.isfinite(o).all() for o in outs)
+
+
+def test_a_mixed_step_at_a_wide_shape_and_long_context_gives_the_same_bits_every_time():
+    """Thirty-two layers of the 14B shape: three requests decode at 8,200 keys beside the last 22 tokens of a prompt and
+    the first 2,023 of the next one.  The decoded tokens' attention (the TMA ring kernel, which starts early) and the
+    prompt portions' (tensor memory) run side by side on two streams, both bound by memory; in that company a softmax
+    warp of the prompt kernel once got a tile ahead of another and completed its phase of the barrier they shared.
+    The step, rebuilt from scratch four times, must give the bits of the same step run with one kernel after the
+    other, and no device error."""
+    from microllm_rocm_b200.config import preset
+    from microllm_rocm_b200.engine.loading import random_engine
+    from microllm_rocm_b200.engine.step import StepEntry
+    from microllm_rocm_b200.kernels import attention
+    cfg = preset("qwen2.5-14b", num_hidden_layers=32)
+    engine = random_engine(cfg, seed=0, dtype="bfloat16", page_size=64, max_tokens=6 * 8448, max_requests=8, draw_on_device=True)
+    gen = torch.Generator().manual_seed(0)
+    toks = [torch.randint(0, cfg.vocab_size, (8300,), generator=gen).tolist() for _ in range(5)]
+    lens = [8206, 8201, 8197]
+
+    def feed(rid, seq, upto):
+        p = engine.cache.length(rid)
+        while p < upto:
+            n = min(2048, upto - p)
+            engine.step([StepEntry(rid, seq[p:p + n], [])])
+            p += n
+
+    def scenario(tag):
+        ids = [f"{tag}{i}" for i in range(5)]
+        for i in ids:
+            assert engine.cache.add(i)
+        for i in range(3):
+            feed(ids[i], toks[i], lens[i])
+        feed(ids[3], toks[3], 8170)
+        entries = [StepEntry(ids[i], [toks[i][lens[i]]], [0]) for i in range(3)]
+        entries.append(StepEntry(ids[3], toks[3][8170:8192], [0, 10, 21]))
+        entries.append(StepEntry(ids[4], toks[4][:2023], [0, 1000, 2022]))
+        out = engine.step(entries).clone()
+        torch.cuda.synchronize()
+        engine.check_device_errors()
+        for i in ids:
+            engine.cache.release(i)
+        return out
+
+    attention.CONCURRENT_ATTENTION = False
+    try:
+        want = scenario("one stream ")
+    finally:
+        attention.CONCURRENT_ATTENTION = True
+    assert torch.isfinite(want).all()
+    for trial in range(4):
+        got = scenario(f"trial {trial} ")
+        assert torch.equal(got, want), (trial, float((got - want).abs().max()))
 
 
 @pytest.mark.parametrize("key", ["a", "b"])

@@ -135,9 +135,25 @@ def paged_from_dense(k, v, page_size, num_pages, dtype, seed=0):
     return pages.to(dtype), table
 
 
-def run_attention(q_list, k_list, v_list, pos0_list, nh, nkv, d, window, dtype, page_size=16, num_pages=64, repeats=None):
+def memory_hog(milliseconds=30):
+    """Queues device-to-device copies of 1 GB on a second stream, about `milliseconds` of them: kernels launched on
+    the current stream right after this call run beside a kernel that saturates the memory system, which stretches
+    every wait inside them (a timing no quiet test sees).  Returns what must stay alive until the device is idle."""
+    side = torch.cuda.Stream()
+    a = torch.empty(1 << 30, dtype=torch.uint8, device=DEV)
+    b = torch.empty_like(a)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(max(1, int(milliseconds / 0.35))):          # ~0.35 ms a copy at 6 TB/s of reads + writes
+            b.copy_(a, non_blocking=True)
+    return side, a, b
+
+
+def run_attention(q_list, k_list, v_list, pos0_list, nh, nkv, d, window, dtype, page_size=16, num_pages=64, repeats=None,
+                  hog=False):
     """Queries q_list[s] ([n_s, NH, D]) sit at positions pos0_list[s].. of sequence s whose
-    keys are k_list[s].  `repeats`: run the same step that often and return every result, [repeats, T, NH * D]."""
+    keys are k_list[s].  `repeats`: run the same step that often and return every result, [repeats, T, NH * D];
+    `hog`: beside a kernel that saturates the memory system (see memory_hog)."""
     pages, table = paged_from_dense(k_list, v_list, page_size, num_pages, dtype)
     q = torch.cat([x.reshape(x.shape[0], nh * d) for x in q_list]).to(dtype)
     positions = torch.cat([torch.arange(p, p + x.shape[0], dtype=torch.int32) for p, x in zip(pos0_list, q_list)])
@@ -159,9 +175,13 @@ def run_attention(q_list, k_list, v_list, pos0_list, nh, nkv, d, window, dtype, 
     q, pages, table = q.to(DEV), pages.to(DEV), table.to(DEV)
     if repeats:
         outs = torch.empty((repeats, *q.shape), dtype=dtype, device=DEV)
+        torch.cuda.synchronize()
+        keep = memory_hog() if hog else None
         for i in range(repeats):
             attention.paged_attention(q, pages, outs[i], ctx, table, nh, nkv, d, 1.0 / math.sqrt(d), window)
         assert int(flag.item()) == 0
+        torch.cuda.synchronize()
+        del keep
         return outs.float().cpu()
     attention.paged_attention(q, pages, out, ctx, table, nh, nkv, d, 1.0 / math.sqrt(d), window)
     assert int(flag.item()) == 0
@@ -332,7 +352,7 @@ def test_prompt_portions_and_decoded_tokens_side_by_side_give_the_same_bits_ever
         want = run_attention(qs, ks, vs, pos0, nh, nkv, d, None, torch.bfloat16, page_size=64, num_pages=pages)
     finally:
         attention.CONCURRENT_ATTENTION = True
-    got = run_attention(qs, ks, vs, pos0, nh, nkv, d, None, torch.bfloat16, page_size=64, num_pages=pages, repeats=30)
+    got = run_attention(qs, ks, vs, pos0, nh, nkv, d, None, torch.bfloat16, page_size=64, num_pages=pages, repeats=30, hog=True)
     assert torch.isfinite(got).all()
     for i in range(got.shape[0]):
         assert torch.equal(got[i], want), (i, float((got[i] - want).abs().max()))
