@@ -371,6 +371,87 @@ def test_window_and_page_edges(page_size):
         assert torch.allclose(got.reshape(nh, d), want[pos], atol=2e-5), pos
 
 
+@pytest.mark.parametrize("kernel", ["stream_partials", "stream_silu", "stream_lm_head", "pair", "pair_dual", "gemv", "decode_ring",
+                                    "decode_t"])
+def test_kernels_with_barriers_or_rings_give_the_same_bits_beside_a_memory_hog(kernel):
+    """The kernels that hand data from warp to warp through mbarriers or rings, at served sizes, twenty times in a row
+    beside a kernel that saturates the memory system (every wait inside them is stretched, warps drift apart): each
+    run must give the bits of the quiet run and raise no flag."""
+    from microllm_rocm_b200.kernels import attention, gemm_bf16
+    torch.manual_seed(31)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+    def rand(*shape, scale=1.0):
+        return (torch.randn(*shape, device=DEV) * scale).bfloat16()
+
+    if kernel in ("stream_partials", "stream_silu", "stream_lm_head"):
+        m = 64
+        if kernel == "stream_partials":
+            x, w = rand(m, 8960), rand(1536, 8960, scale=0.02)
+            run = lambda: gemm_bf16.stream_partials(x, w, error_flag=flag).clone()
+        elif kernel == "stream_lm_head":
+            x, w = rand(m, 1536), rand(151936, 1536, scale=0.02)              # more tiles than SMs: persistent CTAs
+            run = lambda: gemm_bf16.stream_partials(x, w, error_flag=flag).clone()
+        else:
+            x, w = rand(m, 3584), rand(2 * 18944, 3584, scale=0.02)
+            def run():
+                out = torch.empty(m, 18944, dtype=torch.bfloat16, device=DEV)
+                gemm_bf16.stream_silu_mul(x, w, out, error_flag=flag)
+                return out
+    elif kernel in ("pair", "pair_dual"):
+        m = 2048
+        if kernel == "pair":
+            x, w = rand(m, 3584), rand(4608, 3584, scale=0.02)
+            def run():
+                out = torch.empty(m, 4608, dtype=torch.bfloat16, device=DEV)
+                gemm_bf16.gemm_pair(x, w, out, error_flag=flag)
+                return out
+        else:
+            x, w = rand(m, 1536), rand(2 * 8960, 1536, scale=0.02)
+            def run():
+                out = torch.empty(m, 8960, dtype=torch.bfloat16, device=DEV)
+                gemm_bf16.gemm_pair(x, w, out, dual_rows=8960, error_flag=flag)
+                return out
+    elif kernel == "gemv":
+        x, w = rand(8, 1536), rand(2 * 8960, 1536, scale=0.02)
+        def run():
+            out = torch.empty(8, 8960, dtype=torch.bfloat16, device=DEV)
+            gemm_bf16.gemv_silu_mul(x, w, out)
+            return out
+    else:
+        nh, nkv, d, batch, context = 28, 4, 128, 64, 2100
+        pages_per_seq = -(-context // 64)
+        pages = rand(batch * pages_per_seq + 1, 2, nkv, 64, d)
+        table = torch.randperm(batch * pages_per_seq, device=DEV).int().view(batch, pages_per_seq)
+        q = rand(batch, nh * d)
+        from microllm_rocm_b200.parts.base import StepContext
+        lens = [context - 7 * (i % 5) for i in range(batch)]
+        ints = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        ctx = StepContext(num_tokens=batch, num_seqs=batch, token_ids=ints([0] * batch), positions=ints([n - 1 for n in lens]),
+                          token_seq=ints(list(range(batch))), seq_starts=ints(list(range(batch + 1))),
+                          seq_pos0=ints([n - 1 for n in lens]), seq_lens=ints(lens), block_tables={}, state_slots=None,
+                          logit_rows=None, error_flag=flag, seq_starts_host=list(range(batch + 1)),
+                          seq_pos0_host=[n - 1 for n in lens], max_new_tokens=1, max_seq_len=max(lens))
+        attention.DECODE_RING = kernel == "decode_ring"
+        def run():
+            out = torch.empty_like(q)
+            attention.paged_attention(q, pages, out, ctx, table, nh, nkv, d, 1.0 / math.sqrt(d), None)
+            return out
+    try:
+        want = run()
+        torch.cuda.synchronize()
+        keep = memory_hog(40)
+        got = [run() for _ in range(20)]
+        torch.cuda.synchronize()
+        del keep
+    finally:
+        attention.DECODE_RING = None
+    assert int(flag.item()) == 0
+    assert torch.isfinite(want.float()).all()
+    for i, g in enumerate(got):
+        assert torch.equal(g, want), (kernel, i, float((g.float() - want.float()).abs().max()))
+
+
 # ------------------------------------------------------------------------------ rope + kv store
 @pytest.mark.parametrize("kv_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,d,rot,inter", [(4, 1, 16, 16, False), (6, 2, 32, 32, False), (3, 3, 128, 64, False),
