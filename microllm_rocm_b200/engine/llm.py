@@ -110,10 +110,21 @@ class LLM:
         try:
             finished = self._collect(current)
         except Exception:
-            self._inflight = None                 # nothing issued on top of a failed step is to be trusted
+            self._abandon(current.plan, ahead.plan if ahead is not None else None)
             raise
         self._inflight = ahead
         return finished
+
+    def _abandon(self, *plans: Optional[StepPlan]) -> None:
+        """A step failed (a device error, logits that were not finite).  What it computed, and what a step issued on
+        top of it computed, is not to be trusted, and their requests stand between two states (tokens counted as
+        computed, a token still pending).  They end as cancelled and give their pages back, so that the books stay
+        whole and the other requests, and new ones, go on."""
+        self._inflight = self._graph = self._prepared = None
+        for plan in plans:
+            for e in (plan.entries if plan is not None else ()):
+                if not e.request.finished:
+                    self.scheduler.cancel(e.request.id)
 
     def _captured(self, plan: StepPlan) -> bool:
         """Every request brings its one last-selected token and steps are captured: the plan is a replay."""
@@ -249,10 +260,14 @@ class LLM:
         try:
             tokens = graph.read_tokens()
         except StepError:
-            self._graph = self._prepared = None          # nothing prepared on top of a failed step is to be trusted
+            self._abandon(plan)
             raise
         self.wait_s += time.perf_counter() - t0
-        finished = self.scheduler.update(plan, tokens)
+        try:
+            finished = self.scheduler.update(plan, tokens)
+        except Exception:
+            self._abandon(plan)
+            raise
         if finished:
             self._graph = None
             self._prepared = None

@@ -322,15 +322,36 @@ def test_a_raised_device_flag_ends_the_step_with_an_error(folders, dtype):
     with pytest.raises(StepError, match="bounded wait"):
         llm.step()                                      # the prompt's step, launched kernel by kernel
     assert int(llm.engine.error_flag.item()) == 0
-    llm.cancel(rid)
+    # the failed step's request has ended and holds nothing; the engine goes on
+    assert llm.poll(rid).state.name == "CANCELLED" and not llm.has_work()
+    assert llm.metrics()["cache"]["live_requests"] == 0
     rid = llm.submit(random_tokens(9, tiny_config("a").vocab_size, 4), GenerationConfig(max_new_tokens=8, temperature=0.0))
-    llm.step()
-    llm.step()
-    assert llm.graph_steps >= 1
+    other = llm.submit(random_tokens(5, tiny_config("a").vocab_size, 5), GenerationConfig(max_new_tokens=8, temperature=0.0))
+    while llm.graph_steps < 1:
+        llm.step()
     llm.engine.error_flag.fill_(2)                      # as a kernel that met a token without a page would
     with pytest.raises(StepError, match="page"):
         llm.step()                                      # a replayed decode step
     assert int(llm.engine.error_flag.item()) == 0
+    assert llm.poll(rid).state.name == "CANCELLED" and llm.poll(other).state.name == "CANCELLED" and not llm.has_work()
+    llm.engine.cache.check()
+    # a failure while a step issued ahead is on its way: both steps' requests end, a later request is served whole
+    prompts = [random_tokens(n, tiny_config("a").vocab_size, n) for n in (40, 33, 21)]
+    fresh = llm_for(folders["a"], dtype, max_tokens=256)
+    want = fresh.generate([prompts[2]], GenerationConfig(max_new_tokens=6, temperature=0.0))[0]
+    small = llm_for(folders["a"], dtype, max_tokens=256, max_tokens_per_step=16, cuda_graphs=False)
+    ids = [small.submit(p, GenerationConfig(max_new_tokens=6, temperature=0.0)) for p in prompts[:2]]
+    small.step()
+    assert small._inflight is not None                  # a step is on its way on top of the one just collected
+    small.engine.error_flag.fill_(43)                   # (the step on its way has copied the flag already: the next one reports it)
+    with pytest.raises(StepError, match="bounded wait"):
+        small.step()
+        small.step()
+    assert small._inflight is None and not small.has_work()
+    assert all(small.poll(i).state.name == "CANCELLED" for i in ids)
+    small.engine.cache.check()
+    assert small.metrics()["cache"]["live_requests"] == 0
+    assert small.generate([prompts[2]], GenerationConfig(max_new_tokens=6, temperature=0.0))[0] == want
 
 
 def test_the_driver_entry_point_generates_and_compares():
