@@ -58,6 +58,10 @@ class LLM:
         # happened in between that the scheduler would have decided differently.
         self._prepared: Optional[StepPlan] = None
         self.prepared_steps = 0
+        # ... and when the tokens just read change nothing about the batch (no stop token among them, nobody new waiting),
+        # that step is launched before the scheduler's books are written: (plan, graph) of the replay on its way
+        self._launched: Optional[tuple] = None
+        self.launched_early = 0
         # Steps issued kernel by kernel: the one whose tokens are not read yet (see step())
         self._inflight: Optional[_Issued] = None
         self.lookahead = True
@@ -79,7 +83,7 @@ class LLM:
         return self.scheduler.requests[request_id]
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work() or self._inflight is not None
+        return self.scheduler.has_work() or self._inflight is not None or self._launched is not None
 
     def step(self) -> List[Request]:
         """One scheduler decision, one model step, one token selection.  Returns the requests
@@ -91,6 +95,9 @@ class LLM:
         requests that decode get a stand-in for their input token, and a small kernel behind this step's token
         selection puts the selected tokens in their places (Engine.step's `patch`).  What this call returns is
         still this step's outcome; a request that ends on a stop token has one void row in the step issued ahead."""
+        if self._launched is not None:
+            (plan, graph), self._launched = self._launched, None
+            return self._graph_step(plan, launched=graph)
         if self._inflight is None:
             prepared, self._prepared = self._prepared, None
             if (prepared is not None and not self.scheduler.waiting and len(prepared.entries) == len(self.scheduler.running)
@@ -120,7 +127,7 @@ class LLM:
         top of it computed, is not to be trusted, and their requests stand between two states (tokens counted as
         computed, a token still pending).  They end as cancelled and give their pages back, so that the books stay
         whole and the other requests, and new ones, go on."""
-        self._inflight = self._graph = self._prepared = None
+        self._inflight = self._graph = self._prepared = self._launched = None
         for plan in plans:
             for e in (plan.entries if plan is not None else ()):
                 if not e.request.finished:
@@ -216,13 +223,16 @@ class LLM:
         graph.refresh_tables()                           # queued behind the running step; the next replay finds them
         self._prepared = StepPlan([type(e)(e.request, e.begin + 1, 1, True) for e in plan.entries])
 
-    def _graph_step(self, plan: StepPlan, prepared: bool = False) -> List[Request]:
+    def _graph_step(self, plan: StepPlan, prepared: bool = False, launched: Optional[DecodeGraph] = None) -> List[Request]:
         """A step in which every request brings its one last-selected token: replay the captured
-        decode step instead of launching it kernel by kernel."""
+        decode step instead of launching it kernel by kernel.  `launched`: the replay is on its way already (it was
+        started at the end of the step before, see below); what remains is the bookkeeping and the read."""
         ids = [e.request.id for e in plan.entries]
         graph = self._graph
         longest = max(e.begin for e in plan.entries) + 1
-        if prepared and graph is not None and graph.requests == ids:
+        if launched is not None:
+            graph = launched
+        elif prepared and graph is not None and graph.requests == ids:
             # pages, tables and the captured plan were seen to while the last step ran
             graph.upload_tokens([e.request.token(e.begin) for e in plan.entries])
             self.h2d_bytes += 4 * graph.batch
@@ -247,10 +257,12 @@ class LLM:
                 graph.refresh_tables()
                 graph.upload_tokens([e.request.token(e.begin) for e in plan.entries])
                 self.h2d_bytes += 4 * graph.batch
-        graph.replay()
+        if launched is None:
+            graph.replay()
         # what does not need the step's tokens happens while the GPU runs
         for e in plan.entries:
-            self.engine.cache.commit(e.request.id, e.begin + 1)
+            if not e.request.finished:                   # (cancelled since a replay launched early took it along)
+                self.engine.cache.commit(e.request.id, e.begin + 1)
         self._prepare_next(plan, graph)
         self.d2h_bytes += 4 * (graph.batch + 1)
         self.graph_steps += 1
@@ -263,6 +275,18 @@ class LLM:
             self._abandon(plan)
             raise
         self.wait_s += time.perf_counter() - t0
+        # The next replay is prepared and these tokens change nothing about the batch (no stop token, nobody ended by
+        # length or it would not be prepared, nobody new waiting): it starts NOW, fed with the tokens just read, and
+        # the scheduler's books are written while it runs.  The next step() finds it on its way.
+        ahead = self._prepared
+        if (ahead is not None and self.lookahead and not self.scheduler.waiting and self._graph is graph and
+                all(t >= 0 and t not in e.request.config.stop_tokens for e, t in zip(plan.entries, tokens))):
+            graph.upload_tokens(tokens)
+            graph.replay()
+            self.h2d_bytes += 4 * graph.batch
+            self.prepared_steps += 1
+            self.launched_early += 1
+            self._prepared, self._launched = None, (ahead, graph)
         try:
             finished = self.scheduler.update(plan, tokens)
         except Exception:

@@ -279,6 +279,8 @@ class Scheduler:
         if plan.begun:
             return
         for e in plan.entries:
+            if e.request.finished:
+                continue                  # cancelled after the plan was made: its row runs for nothing
             e.request.computed = e.begin + e.count
             if e.wants_logits:
                 e.request.generated.append(PENDING)

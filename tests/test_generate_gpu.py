@@ -331,7 +331,8 @@ def test_a_raised_device_flag_ends_the_step_with_an_error(folders, dtype):
         llm.step()
     llm.engine.error_flag.fill_(2)                      # as a kernel that met a token without a page would
     with pytest.raises(StepError, match="page"):
-        llm.step()                                      # a replayed decode step
+        llm.step()                                      # a replayed decode step (if it was launched early it ran before the
+        llm.step()                                      # flag was raised: then the one after it reports)
     assert int(llm.engine.error_flag.item()) == 0
     assert llm.poll(rid).state.name == "CANCELLED" and llm.poll(other).state.name == "CANCELLED" and not llm.has_work()
     llm.engine.cache.check()
@@ -376,7 +377,8 @@ def test_steps_prepared_ahead_give_way_to_cancels_arrivals_and_ends(folders):
     ids = [llm.submit(p, c) for p, c in zip(prompts[:3], cfgs[:3])]
     for _ in range(12):
         llm.step()
-    assert llm.prepared_steps >= 8
+    assert llm.prepared_steps >= 8 and llm.launched_early >= 8
+    assert llm._launched is not None                       # the next replay is on its way already, with all three
     assert llm.cancel(ids[1])                              # one of the three leaves in the middle of steady decoding
     for _ in range(6):
         llm.step()
