@@ -94,7 +94,11 @@ class LLM:
         the NEXT such step is planned and issued while this one runs, before this one's tokens are read: the
         requests that decode get a stand-in for their input token, and a small kernel behind this step's token
         selection puts the selected tokens in their places (Engine.step's `patch`).  What this call returns is
-        still this step's outcome; a request that ends on a stop token has one void row in the step issued ahead."""
+        still this step's outcome; a request that ends on a stop token has one void row in the step issued ahead.
+
+        Captured decode steps: once a step's tokens are read and they change nothing about the batch, the next
+        replay (prepared while this one ran) is launched with them before this call returns; the next call finds it
+        on its way (`_launched`) and only has the bookkeeping and the read left."""
         if self._launched is not None:
             (plan, graph), self._launched = self._launched, None
             return self._graph_step(plan, launched=graph)
