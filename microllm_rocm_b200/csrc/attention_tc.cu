@@ -377,6 +377,11 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         };
         for (int j = 0; j < n_tiles; ++j) {
             const int buf = j & 1;
+#ifdef MLB_LAG_SOFTMAX_WARP
+            // Test builds only: one softmax warp is held back at every key tile, so that the others get as far ahead
+            // of it as the barriers allow.  The results must not depend on which warp reaches a barrier first.
+            if (warp == MLB_LAG_SOFTMAX_WARP) __nanosleep(4000);
+#endif
             ok = wait_all(&s_full[buf], (j >> 1) & 1, 28);
             if (!ok) break;
             tc_fence_after();
