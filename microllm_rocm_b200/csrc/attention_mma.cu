@@ -1245,6 +1245,7 @@ __global__ void __launch_bounds__(160, 2) fa_decode_ring_kernel(const __grid_con
             bool waited = false, ok = true;
             int issued = 0;
             for (int i = 0; i < num_stages && ok; ++i) {
+                lag_point();
                 const int s = i % RING_STAGES;
                 if (i >= RING_STAGES && !mbar_wait(smem_u32(&empty_bar[s]), ((i / RING_STAGES) - 1) & 1, p.error_flag, 61)) { ok = false; break; }
                 const int kt0 = tile_begin + 4 * i, n_tiles = min(4, tile_end - kt0);
@@ -1302,6 +1303,7 @@ __global__ void __launch_bounds__(160, 2) fa_decode_ring_kernel(const __grid_con
         asm volatile("bar.sync 1, 128;" ::: "memory");          // the queries are in shared memory (the four working warps only)
         bool ok = true;
         for (int i = 0; i < num_stages && ok; ++i) {
+            lag_point();
             const int s = i % RING_STAGES;
             const int kt = tile_begin + 4 * i + warp;
             ok = mbar_wait(smem_u32(&full_bar[s]), (i / RING_STAGES) & 1, p.error_flag, 62);

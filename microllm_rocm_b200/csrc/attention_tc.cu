@@ -276,6 +276,7 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         int issued = 0;
         int page_next = lookup(0);
         for (int i = 0; i < n_items; ++i) {
+            lag_point();
             int page = page_next;
             if (i + 1 < n_items) page_next = lookup(i + 1);          // in flight while this item waits and issues
             const int slot = i % SLOTS;
@@ -336,6 +337,7 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             };
             for (int j = 0; j < 2 && j < n_tiles && ok; ++j) ok = issue_qk(j);
             for (int j = 0; j < n_tiles && ok; ++j) {
+                lag_point();
                 ok = wait_warp(&p_full[j & 1], (j >> 1) & 1, 25);
                 if (!ok) break;
                 const int slot = item % SLOTS;
@@ -377,11 +379,7 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         };
         for (int j = 0; j < n_tiles; ++j) {
             const int buf = j & 1;
-#ifdef MLB_LAG_SOFTMAX_WARP
-            // Test builds only: one softmax warp is held back at every key tile, so that the others get as far ahead
-            // of it as the barriers allow.  The results must not depend on which warp reaches a barrier first.
-            if (warp == MLB_LAG_SOFTMAX_WARP) __nanosleep(4000);
-#endif
+            lag_point();
             ok = wait_all(&s_full[buf], (j >> 1) & 1, 28);
             if (!ok) break;
             tc_fence_after();

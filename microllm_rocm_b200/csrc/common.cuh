@@ -120,6 +120,24 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_prologue() { pdl_launch_dependents(); pdl_wait(); }
 
+// ---- a warp held back, for tests -------------------------------------------------------------
+// The warp-specialised kernels (copy warp, MMA warp, epilogue or softmax warps that meet at mbarriers) call
+// lag_point() once per turn of each role's loop.  It is empty unless the object is built with -DMLB_LAG_WARP=w
+// (and, for a kernel of CTA pairs or clusters, -DMLB_LAG_RANK=r): then warp w (of CTA r of its cluster) sleeps a few
+// microseconds there, so that the other warps get as far ahead of it as the barriers allow.  What a kernel computes
+// must not depend on which warp reaches a barrier first; the tests build such objects and compare.  Nothing else
+// changes in those builds, and the package never loads them.
+__device__ __forceinline__ void lag_point() {
+#ifdef MLB_LAG_WARP
+#ifdef MLB_LAG_RANK
+    unsigned rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    if (rank != (unsigned)(MLB_LAG_RANK)) return;
+#endif
+    if ((int)(threadIdx.x >> 5) == (MLB_LAG_WARP)) __nanosleep(3000);
+#endif
+}
+
 inline bool pdl_enabled() {
     static int enabled = -1;
     if (enabled < 0) {

@@ -222,6 +222,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             uint32_t it = (uint32_t)issued;
             bool ok = true;
             while (item < p.items) {
+                lag_point();
                 const int s = it % p.stages;
                 const uint32_t round = it / p.stages;
                 if (!mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, p.error_flag, 51)) { ok = false; break; }
@@ -255,6 +256,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem_base + buf * (uint32_t)p.tok_tile;
                 for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+                    lag_point();
                     const int s = it % p.stages;
                     if (!mbar_wait(smem_u32(&full_bar[s]), (it / p.stages) & 1, p.error_flag, 53)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -275,6 +277,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         bool ok = true;
         pdl_wait();                                       // nothing is stored while the kernel in front may still read it
         for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x, ++local) {
+            lag_point();
             const uint32_t buf = local & 1, use = local >> 1;
             const int tile = item % p.n_tiles, split = item / p.n_tiles;
             // ONE thread waits for the accumulator and tells the other 127: the four warps go on, or give up,

@@ -203,6 +203,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 const int n0 = (tile / p.m_tiles) * PAIR_W + (int)rank * BLOCK_W;
                 const int tok0 = (tile % p.m_tiles) * p.tok_tile + (int)rank * half_tok;
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    lag_point();
                     const int s = it % p.stages;
                     const uint32_t round = it / p.stages;
                     if (round > 0 && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, p.error_flag, 41)) { ok = false; break; }
@@ -231,6 +232,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem_base + buf * acc_cols;
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    lag_point();
                     const int s = it % p.stages;
                     // every lane polls (one broadcast read each time): no shuffle between the barrier and the issue.
                     // No tcgen05 fence here: the copies and the MMAs that read them are ordered by the mbarrier itself.
@@ -260,6 +262,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         uint32_t local = 0;
         bool ok = true;
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+            lag_point();
             const uint32_t buf = local & 1, use = local >> 1;
             const int n0 = (tile / p.m_tiles) * PAIR_W + (int)rank * BLOCK_W, tok0 = (tile % p.m_tiles) * p.tok_tile;
             const int f = n0 + quarter * 32 + lane;

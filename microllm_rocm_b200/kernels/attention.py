@@ -39,9 +39,6 @@ RING_MIN_KEYS_PER_CTA = 1024        # measured: 16 stages of 64 keys per CTA and
 # the streaming kernel too, the ring wins there at 8 tokens as well (14B: 1.85 -> 1.67 ms, 7B: 1.28 -> 1.19 ms).
 # So the caller says which products surround the attention (`beside_mma_products`).
 CONCURRENT_ATTENTION = True         # the two attention launches of a mixed step side by side (tests may switch it off)
-# further -D definitions for the prompt attention kernel's build; a test compiles the kernel with one softmax warp held
-# back (MLB_LAG_SOFTMAX_WARP, see attention_tc.cu) to show that the order in which warps reach its barriers does not matter
-TC_EXTRA_DEFINES: dict = {}
 TC_HEAD_DIMS = (64, 128)
 TC_KEYS_PER_TILE = 128
 TC_ROWS_PER_TILE = 128
@@ -203,7 +200,7 @@ def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx
             side = ops.side_stream()
             ops.fork(side)
             stream = side
-        T = ops.lib("attention_tc.cu", {"HEAD_DIM": head_dim, **TC_EXTRA_DEFINES})
+        T = ops.lib("attention_tc.cu", {"HEAD_DIM": head_dim})
         build.check(T, T.mlb_paged_attention_tc(
             q.data_ptr(), q.stride(0), pages.data_ptr(), out.data_ptr(), out.stride(0), q.shape[0], ctx.seq_starts.data_ptr(),
             ctx.seq_pos0.data_ptr(), block_table.data_ptr(), tc_work.data_ptr(), num_tc, block_table.shape[1],

@@ -93,7 +93,24 @@ _SIGNATURES = {
 _libs = {}
 
 
+# Further -D definitions per source, merged into what a caller asks for.  Empty in the product; tests load the
+# warp-specialised kernels with one warp held back (MLB_LAG_WARP, csrc/common.cuh) through it.
+TEST_DEFINES: dict = {}
+
+
+def lagged_sources():
+    """The held-back builds the tests ask for, so that the build check compiles them too and no test waits for nvcc:
+    every role of every kernel whose warps meet at mbarriers (copy, MMA issue, one epilogue or softmax warp)."""
+    out = [("attention_tc.cu", {"HEAD_DIM": 128, "MLB_LAG_WARP": w}) for w in (0, 1, 2, 5)]
+    out += [("gemm_stream.cu", {"MLB_LAG_WARP": w}) for w in (0, 1, 3)]
+    out += [("gemm_tc2.cu", {"MLB_LAG_WARP": w, "MLB_LAG_RANK": r}) for w, r in ((0, 1), (1, 0), (3, 0), (4, 1))]
+    out += [("attention_mma.cu", {"HEAD_DIM": 128, "MLB_LAG_WARP": w}) for w in (1, 4)]
+    return out
+
+
 def lib(source: str, defines=None) -> ctypes.CDLL:
+    if TEST_DEFINES.get(source):
+        defines = {**(defines or {}), **TEST_DEFINES[source]}
     key = (source, tuple(sorted((defines or {}).items())))
     got = _libs.get(key)
     if got is None:

@@ -304,15 +304,17 @@ def test_tcgen05_prompt_attention_far_key_and_window_edge():
     assert not torch.allclose(got_w[n - 1, 0], v[far, 0], atol=0.2)
 
 
-@pytest.mark.parametrize("lagging_warp", [None, 2, 5])
-def test_tcgen05_prompt_attention_when_one_softmax_warp_lags(lagging_warp):
-    """The four softmax warps of the prompt attention kernel meet at barriers that count arrivals; a warp that is a
-    whole key tile ahead of another must not be able to complete the slow warp's phase in its place.  Two ways to pull
-    the warps apart: the last 32 rows of every 128-row tile are aligned with keys that grow from key tile to key
-    tile, so that their warp has the accumulator to rescale at EVERY tile while the three others never do; and a
-    build of the kernel in which one warp sleeps 4 us at every tile (several tiles' worth of work).  Equal to the
-    plain attention and the same bits every time."""
-    from microllm_rocm_b200.kernels import attention
+def test_tcgen05_prompt_attention_when_one_softmax_warp_has_more_to_do():
+    """The last 32 rows of every 128-row tile are aligned with keys that grow from key tile to key tile, so that
+    their maxima outgrow the rescale threshold at EVERY tile and their softmax warp has the accumulator to rescale
+    each time, while the three other warps never do and run ahead.  Equal to the plain attention, the same bits
+    every time.  (test_a_held_back_warp_changes_nothing pulls the warps apart by force.)"""
+    got, want = lagging_rows_case()
+    assert torch.allclose(got[0], want, **tol(torch.bfloat16)), float((got[0] - want).abs().max())
+    assert torch.equal(got[0], got[1]) and torch.equal(got[0], got[2])
+
+
+def lagging_rows_case(repeats=3):
     torch.manual_seed(17)
     nh, nkv, d, n = 8, 2, 128, 2048
     k, v = torch.randn(n, nkv, d) * 0.1, torch.randn(n, nkv, d)
@@ -325,18 +327,131 @@ def test_tcgen05_prompt_attention_when_one_softmax_warp_lags(lagging_warp):
     q[lagging] = direction * 9.0
     k, v, q = (x.bfloat16().float() for x in (k, v, q))
     want = plain_attention_rows(q, k, v, 0, None).reshape(n, nh * d)
-    attention.TC_EXTRA_DEFINES = {} if lagging_warp is None else {"MLB_LAG_SOFTMAX_WARP": lagging_warp}
+    got = run_attention([q], [k], [v], [0], nh, nkv, d, None, torch.bfloat16, page_size=64, num_pages=40, repeats=repeats)
+    assert torch.isfinite(got).all()
+    return got, want
+
+
+def served_size_cases(flag):
+    """name -> a function that runs one of the warp-specialised kernels at a served size and returns its result."""
+    from microllm_rocm_b200.kernels import attention, gemm_bf16
+    from microllm_rocm_b200.parts.base import StepContext
+    torch.manual_seed(31)
+
+    def rand(*shape, scale=1.0):
+        return (torch.randn(*shape, device=DEV) * scale).bfloat16()
+
+    cases = {}
+    x1, w1 = rand(64, 8960), rand(1536, 8960, scale=0.02)
+    cases["stream_partials"] = lambda: gemm_bf16.stream_partials(x1, w1, error_flag=flag).clone()
+    x2, w2 = rand(16, 1536), rand(30000, 1536, scale=0.02)                # more tiles than SMs: persistent CTAs, two accumulators
+    cases["stream_many_tiles"] = lambda: gemm_bf16.stream_partials(x2, w2, error_flag=flag).clone()
+    x3, w3 = rand(64, 3584), rand(2 * 18944, 3584, scale=0.02)
+
+    def stream_silu():
+        out = torch.empty(64, 18944, dtype=torch.bfloat16, device=DEV)
+        gemm_bf16.stream_silu_mul(x3, w3, out, error_flag=flag)
+        return out
+    cases["stream_silu"] = stream_silu
+    x4, w4 = rand(2048, 3584), rand(4608, 3584, scale=0.02)
+
+    def pair():
+        out = torch.empty(2048, 4608, dtype=torch.bfloat16, device=DEV)
+        gemm_bf16.gemm_pair(x4, w4, out, error_flag=flag)
+        return out
+    cases["pair"] = pair
+    x5, w5 = rand(2048, 1536), rand(2 * 8960, 1536, scale=0.02)
+
+    def pair_dual():
+        out = torch.empty(2048, 8960, dtype=torch.bfloat16, device=DEV)
+        gemm_bf16.gemm_pair(x5, w5, out, dual_rows=8960, error_flag=flag)
+        return out
+    cases["pair_dual"] = pair_dual
+    x6 = rand(8, 1536)
+
+    def gemv():
+        out = torch.empty(8, 8960, dtype=torch.bfloat16, device=DEV)
+        gemm_bf16.gemv_silu_mul(x6, w5, out)
+        return out
+    cases["gemv"] = gemv
+
+    nh, nkv, d, batch, context = 28, 4, 128, 64, 2100
+    pages_per_seq = -(-context // 64)
+    pages = rand(batch * pages_per_seq + 1, 2, nkv, 64, d)
+    table = torch.randperm(batch * pages_per_seq, device=DEV).int().view(batch, pages_per_seq)
+    q = rand(batch, nh * d)
+    lens = [context - 7 * (i % 5) for i in range(batch)]
+    ints = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    ctx = StepContext(num_tokens=batch, num_seqs=batch, token_ids=ints([0] * batch), positions=ints([n - 1 for n in lens]),
+                      token_seq=ints(list(range(batch))), seq_starts=ints(list(range(batch + 1))),
+                      seq_pos0=ints([n - 1 for n in lens]), seq_lens=ints(lens), block_tables={}, state_slots=None,
+                      logit_rows=None, error_flag=flag, seq_starts_host=list(range(batch + 1)),
+                      seq_pos0_host=[n - 1 for n in lens], max_new_tokens=1, max_seq_len=max(lens))
+
+    def decode(ring):
+        def run():
+            attention.DECODE_RING = ring
+            try:
+                out = torch.empty_like(q)
+                attention.paged_attention(q, pages, out, ctx, table, nh, nkv, d, 1.0 / math.sqrt(d), None)
+                return out
+            finally:
+                attention.DECODE_RING = None
+        return run
+    cases["decode_ring"] = decode(True)
+    cases["decode_t"] = decode(False)
+    return cases
+
+
+@pytest.mark.parametrize("kernel", ["stream_partials", "stream_many_tiles", "stream_silu", "pair", "pair_dual", "gemv", "decode_ring",
+                                    "decode_t"])
+def test_kernels_with_barriers_or_rings_give_the_same_bits_beside_a_memory_hog(kernel):
+    """The kernels that hand data from warp to warp through mbarriers or rings, at served sizes, twenty times in a row
+    beside a kernel that saturates the memory system (every wait inside them is stretched, warps drift apart): each
+    run must give the bits of the quiet run and raise no flag."""
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    run = served_size_cases(flag)[kernel]
+    want = run()
+    torch.cuda.synchronize()
+    keep = memory_hog(40)
+    got = [run() for _ in range(20)]
+    torch.cuda.synchronize()
+    del keep
+    assert int(flag.item()) == 0
+    assert torch.isfinite(want.float()).all()
+    for i, g in enumerate(got):
+        assert torch.equal(g, want), (kernel, i, float((g.float() - want.float()).abs().max()))
+
+
+def held_back_builds():
+    from microllm_rocm_b200.kernels import ops as o
+    uses = {"attention_tc.cu": ["prompt"], "gemm_stream.cu": ["stream_partials", "stream_many_tiles", "stream_silu"],
+            "gemm_tc2.cu": ["pair", "pair_dual"], "attention_mma.cu": ["decode_ring"]}
+    return [(source, tuple(sorted(defines.items())), case) for source, defines in o.lagged_sources() for case in uses[source]]
+
+
+@pytest.mark.parametrize("source,defines,case", held_back_builds())
+def test_a_held_back_warp_changes_nothing(source, defines, case):
+    """Every kernel whose warps have roles of their own (copy, MMA issue, epilogue or softmax) and meet at mbarriers is
+    built once more per role with that role's warp sleeping 3 us at every turn of its loop (-DMLB_LAG_WARP, and
+    -DMLB_LAG_RANK for the kernel of CTA pairs): the others then run as far ahead as the barriers let them.  A
+    barrier that counts arrivals and can be completed by a fast warp's NEXT arrival in place of the slow warp's, a
+    parity wait that can miss a phase, a buffer handed back too early: each shows as other bits or as a wait that
+    runs out.  (The prompt attention kernel's single barrier for two P buffers did, with warp 2 or 5 held back.)"""
+    from microllm_rocm_b200.kernels import ops as o
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    run = (lambda: lagging_rows_case(repeats=1)[0][0]) if case == "prompt" else served_size_cases(flag)[case]
+    want = run()
+    torch.cuda.synchronize()
+    held = {k: v for k, v in defines if k.startswith("MLB_LAG")}
+    o.TEST_DEFINES[source] = held
     try:
-        first = None
-        for _ in range(3):
-            got = run_attention([q], [k], [v], [0], nh, nkv, d, None, torch.bfloat16, page_size=64, num_pages=40)
-            assert torch.isfinite(got).all()
-            assert torch.allclose(got, want, **tol(torch.bfloat16)), float((got - want).abs().max())
-            if first is None:
-                first = got
-            assert torch.equal(got, first)
+        got = run()
+        torch.cuda.synchronize()
     finally:
-        attention.TC_EXTRA_DEFINES = {}
+        del o.TEST_DEFINES[source]
+    assert int(flag.item()) == 0
+    assert torch.equal(got, want), float((got.float() - want.float()).abs().max())
 
 
 def test_prompt_portions_and_decoded_tokens_side_by_side_give_the_same_bits_every_time():
@@ -377,87 +492,6 @@ def test_window_and_page_edges(page_size):
         got = run_attention([q[pos:pos + 1]], [k[:pos + 1]], [v[:pos + 1]], [pos], nh, nkv, d, W, torch.float32,
                             page_size=page_size)
         assert torch.allclose(got.reshape(nh, d), want[pos], atol=2e-5), pos
-
-
-@pytest.mark.parametrize("kernel", ["stream_partials", "stream_silu", "stream_lm_head", "pair", "pair_dual", "gemv", "decode_ring",
-                                    "decode_t"])
-def test_kernels_with_barriers_or_rings_give_the_same_bits_beside_a_memory_hog(kernel):
-    """The kernels that hand data from warp to warp through mbarriers or rings, at served sizes, twenty times in a row
-    beside a kernel that saturates the memory system (every wait inside them is stretched, warps drift apart): each
-    run must give the bits of the quiet run and raise no flag."""
-    from microllm_rocm_b200.kernels import attention, gemm_bf16
-    torch.manual_seed(31)
-    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
-
-    def rand(*shape, scale=1.0):
-        return (torch.randn(*shape, device=DEV) * scale).bfloat16()
-
-    if kernel in ("stream_partials", "stream_silu", "stream_lm_head"):
-        m = 64
-        if kernel == "stream_partials":
-            x, w = rand(m, 8960), rand(1536, 8960, scale=0.02)
-            run = lambda: gemm_bf16.stream_partials(x, w, error_flag=flag).clone()
-        elif kernel == "stream_lm_head":
-            x, w = rand(m, 1536), rand(151936, 1536, scale=0.02)              # more tiles than SMs: persistent CTAs
-            run = lambda: gemm_bf16.stream_partials(x, w, error_flag=flag).clone()
-        else:
-            x, w = rand(m, 3584), rand(2 * 18944, 3584, scale=0.02)
-            def run():
-                out = torch.empty(m, 18944, dtype=torch.bfloat16, device=DEV)
-                gemm_bf16.stream_silu_mul(x, w, out, error_flag=flag)
-                return out
-    elif kernel in ("pair", "pair_dual"):
-        m = 2048
-        if kernel == "pair":
-            x, w = rand(m, 3584), rand(4608, 3584, scale=0.02)
-            def run():
-                out = torch.empty(m, 4608, dtype=torch.bfloat16, device=DEV)
-                gemm_bf16.gemm_pair(x, w, out, error_flag=flag)
-                return out
-        else:
-            x, w = rand(m, 1536), rand(2 * 8960, 1536, scale=0.02)
-            def run():
-                out = torch.empty(m, 8960, dtype=torch.bfloat16, device=DEV)
-                gemm_bf16.gemm_pair(x, w, out, dual_rows=8960, error_flag=flag)
-                return out
-    elif kernel == "gemv":
-        x, w = rand(8, 1536), rand(2 * 8960, 1536, scale=0.02)
-        def run():
-            out = torch.empty(8, 8960, dtype=torch.bfloat16, device=DEV)
-            gemm_bf16.gemv_silu_mul(x, w, out)
-            return out
-    else:
-        nh, nkv, d, batch, context = 28, 4, 128, 64, 2100
-        pages_per_seq = -(-context // 64)
-        pages = rand(batch * pages_per_seq + 1, 2, nkv, 64, d)
-        table = torch.randperm(batch * pages_per_seq, device=DEV).int().view(batch, pages_per_seq)
-        q = rand(batch, nh * d)
-        from microllm_rocm_b200.parts.base import StepContext
-        lens = [context - 7 * (i % 5) for i in range(batch)]
-        ints = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-        ctx = StepContext(num_tokens=batch, num_seqs=batch, token_ids=ints([0] * batch), positions=ints([n - 1 for n in lens]),
-                          token_seq=ints(list(range(batch))), seq_starts=ints(list(range(batch + 1))),
-                          seq_pos0=ints([n - 1 for n in lens]), seq_lens=ints(lens), block_tables={}, state_slots=None,
-                          logit_rows=None, error_flag=flag, seq_starts_host=list(range(batch + 1)),
-                          seq_pos0_host=[n - 1 for n in lens], max_new_tokens=1, max_seq_len=max(lens))
-        attention.DECODE_RING = kernel == "decode_ring"
-        def run():
-            out = torch.empty_like(q)
-            attention.paged_attention(q, pages, out, ctx, table, nh, nkv, d, 1.0 / math.sqrt(d), None)
-            return out
-    try:
-        want = run()
-        torch.cuda.synchronize()
-        keep = memory_hog(40)
-        got = [run() for _ in range(20)]
-        torch.cuda.synchronize()
-        del keep
-    finally:
-        attention.DECODE_RING = None
-    assert int(flag.item()) == 0
-    assert torch.isfinite(want.float()).all()
-    for i, g in enumerate(got):
-        assert torch.equal(g, want), (kernel, i, float((g.float() - want.float()).abs().max()))
 
 
 # ------------------------------------------------------------------------------ rope + kv store
