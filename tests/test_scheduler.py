@@ -4,7 +4,7 @@ pages run out."""
 import pytest
 
 from microllm_rocm_b200.cache import CacheManager
-from microllm_rocm_b200.engine.scheduler import FinishReason, RequestState, Scheduler
+from microllm_rocm_b200.engine.scheduler import PENDING, FinishReason, RequestState, Scheduler
 from microllm_rocm_b200.parts.base import PagedKVNeed
 from microllm_rocm_b200.sampling import GenerationConfig
 
@@ -365,3 +365,28 @@ def test_a_request_that_ends_on_a_stop_token_leaves_a_void_row_in_the_plan_issue
     assert h.s.requests[a].generated == full[:full.index(stop) + 1] and h.s.requests[a].reason == FinishReason.STOP_TOKEN
     assert h.s.requests[b].generated == oracle([7] * 5, GenerationConfig(max_new_tokens=8, temperature=0.0))
     assert h.void_rows == 1 and h.s.metrics.tokens_generated == len(h.s.requests[a].generated) + 8
+
+
+def test_a_plan_whose_request_was_cancelled_before_it_began_leaves_that_request_alone():
+    """A captured step may be launched for a plan before the books know of it; a request cancelled in between has a
+    void row: beginning and finishing the plan must not count tokens for it nor leave a pending token behind."""
+    h = Harness(budget=16)
+    a = h.s.submit([3, 1, 4], GenerationConfig(max_new_tokens=8, temperature=0.0))
+    b = h.s.submit([7] * 5, GenerationConfig(max_new_tokens=8, temperature=0.0))
+    h.step()                                   # both prompts, first tokens
+    plan = h.s.schedule()                      # both decode
+    assert [e.request.id for e in plan.entries] == [a, b] and all(e.count == 1 for e in plan.entries)
+    before = list(h.s.requests[a].generated)
+    assert h.s.cancel(a)
+    h.s.begin(plan)
+    assert h.s.requests[a].generated == before and PENDING not in h.s.requests[a].generated
+    held = h.fed[b] + h.s.requests[b].tokens(plan.entries[1].begin, plan.entries[1].begin + 1)
+    h.cache.commit(b, plan.entries[1].begin + 1)
+    done = h.s.finish(plan, [0, next_token(held)])           # row 0 is void: whatever it selected is dropped
+    assert done == [] and h.s.requests[a].generated == before
+    assert h.s.requests[b].generated[-1] == next_token(held) and PENDING not in h.s.requests[b].generated
+    h.fed[b] = held
+    h.fed.pop(a)
+    h.run()
+    assert h.s.requests[b].generated == oracle([7] * 5, GenerationConfig(max_new_tokens=8, temperature=0.0))
+    h.cache.check()
